@@ -1,0 +1,753 @@
+// Memory-bound kernels: RMSNorm (plain and Gemma 1+w, optional fused residual add) forward and
+// backward, fused QK-norm + RoPE forward and backward, GeGLU / SwiGLU forward and backward,
+// embedding gather and its scatter-add backward, row-wise softmax cross-entropy on a logits chunk
+// (loss + in-place gradient), and the flat multi-tensor AdamW update.
+//
+// All activations are bf16 with fp32 arithmetic; 128-bit vector accesses wherever alignment allows.
+#include "host_common.cuh"
+#include <cuda_bf16.h>
+#include <math.h>
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+__device__ __forceinline__ void unpack8(const bf16x8& a, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(a.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
+  bf16x8 a;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) a.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return a;
+}
+
+// ------------------------------------------------------------------ RMSNorm forward
+// One warp per row.  y = [residual +] x * rsqrt(mean(x^2)+eps) * (w or 1+w).  D % 8 == 0.
+constexpr int NORM_MAXV = 16;  // vectors of 8 kept in registers per lane (D <= 4096)
+
+template <bool CACHE>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ w,
+                                                         const __nv_bfloat16* __restrict__ res,
+                                                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
+                                                         int M, int D, float eps, int unit_offset) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= M) return;
+  const int nvec = D >> 3;
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + static_cast<size_t>(warp) * D);
+  const bf16x8* rr = res ? reinterpret_cast<const bf16x8*>(res + static_cast<size_t>(warp) * D) : nullptr;
+  bf16x8* yr = reinterpret_cast<bf16x8*>(y + static_cast<size_t>(warp) * D);
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  bf16x8 cache[CACHE ? NORM_MAXV : 1];
+  float ss = 0.f;
+  if (CACHE) {
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        cache[i] = xr[v];
+        float f[8];
+        unpack8(cache[i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+      }
+    }
+  } else {
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+    }
+  }
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
+  if (lane == 0 && rstd_out) rstd_out[warp] = rstd;
+  const float off = unit_offset ? 1.f : 0.f;
+  auto emit = [&](int v, const bf16x8& xv) {
+    float f[8], wf[8];
+    unpack8(xv, f);
+    if (w) {
+      unpack8(wr[v], wf);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) wf[e] = 1.f - off;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = f[e] * rstd * (wf[e] + off);
+    if (rr) {
+      // the normalised value is rounded to bf16 before the residual add, as separate ops would do
+      bf16x8 yn = pack8(f);
+      float g[8], r[8];
+      unpack8(yn, g);
+      unpack8(rr[v], r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = g[e] + r[e];
+    }
+    yr[v] = pack8(f);
+  };
+  if (CACHE) {
+#pragma unroll
+    for (int i = 0; i < NORM_MAXV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) emit(v, cache[i]);
+    }
+  } else {
+    for (int v = lane; v < nvec; v += 32) emit(v, xr[v]);
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward: dx
+// dx = rstd * (w' * dy - xhat * mean(xhat * w' * dy)),  xhat = x * rstd,  w' = w or 1+w.
+// If dres_add is non-null, dx is accumulated onto it (dx_out = dres_add + dx): used to merge the
+// gradient arriving through a residual branch.
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ w,
+                                                            const float* __restrict__ rstd_in,
+                                                            const __nv_bfloat16* __restrict__ dres_add,
+                                                            __nv_bfloat16* __restrict__ dx, int M, int D,
+                                                            int unit_offset) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= M) return;
+  const int nvec = D >> 3;
+  const size_t base = static_cast<size_t>(warp) * D;
+  const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + base);
+  const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + base);
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  const bf16x8* ar = dres_add ? reinterpret_cast<const bf16x8*>(dres_add + base) : nullptr;
+  bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + base);
+  const float rstd = rstd_in[warp];
+  const float off = unit_offset ? 1.f : 0.f;
+  float dot = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    float g[8], xf[8], wf[8];
+    unpack8(dyr[v], g);
+    unpack8(xr[v], xf);
+    if (w) unpack8(wr[v], wf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dot += g[e] * (w ? wf[e] + off : 1.f) * xf[e] * rstd;
+  }
+  dot = warp_sum(dot) / static_cast<float>(D);
+  for (int v = lane; v < nvec; v += 32) {
+    float g[8], xf[8], wf[8], o[8];
+    unpack8(dyr[v], g);
+    unpack8(xr[v], xf);
+    if (w) unpack8(wr[v], wf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = rstd * (g[e] * (w ? wf[e] + off : 1.f) - xf[e] * rstd * dot);
+    if (ar) {
+      float a[8];
+      unpack8(ar[v], a);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] += a[e];
+    }
+    dxr[v] = pack8(o);
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward: dw
+// dw[j] += sum_rows dy[r,j] * x[r,j] * rstd[r]  (fp32 atomics; dw is an accumulator).
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            const float* __restrict__ rstd, float* __restrict__ dw,
+                                                            int M, int D, int rows_per_block) {
+  __shared__ float red[8][64];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 64 + tx * 2;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(M, r0 + rows_per_block);
+  float a0 = 0.f, a1 = 0.f;
+  if (col < D) {
+    for (int r = r0 + ty; r < r1; r += 8) {
+      const size_t idx = static_cast<size_t>(r) * D + col;
+      float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dy + idx));
+      float2 xv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + idx));
+      const float s = rstd[r];
+      a0 += g.x * xv.x * s;
+      a1 += g.y * xv.y * s;
+    }
+  }
+  red[ty][tx * 2] = a0;
+  red[ty][tx * 2 + 1] = a1;
+  __syncthreads();
+  if (ty == 0) {
+#pragma unroll
+    for (int i = 1; i < 8; ++i) {
+      a0 += red[i][tx * 2];
+      a1 += red[i][tx * 2 + 1];
+    }
+    if (col < D) {
+      atomicAdd(dw + col, a0);
+      atomicAdd(dw + col + 1, a1);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ QK-norm + RoPE
+// Input  qkv  [T, (H+2KV)*hd]  (q heads, then k heads, then v heads)
+// Output qk   [T, (H+KV)*hd]   normalised (optional) and rotated q and k
+// One warp per (token, head); each lane owns E = hd/32 consecutive channels.
+// layout 0: half-split pairs (i, i + rot/2); layout 1: interleaved pairs (2i, 2i+1).
+// cs: [max_pos, rot/2, 2] fp32 (cos, sin); pos: [T] int32.
+template <int E>
+struct VecT;
+template <>
+struct VecT<8> { using type = uint4; };
+template <>
+struct VecT<4> { using type = uint2; };
+template <>
+struct VecT<2> { using type = uint32_t; };
+
+template <int E>
+__device__ __forceinline__ void load_e(const __nv_bfloat16* p, float (&f)[E]) {
+  typename VecT<E>::type raw = *reinterpret_cast<const typename VecT<E>::type*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < E / 2; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+template <int E>
+__device__ __forceinline__ void store_e(__nv_bfloat16* p, const float (&f)[E]) {
+  typename VecT<E>::type raw;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < E / 2; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<typename VecT<E>::type*>(p) = raw;
+}
+
+// rotate (forward: sign=+1, backward/transpose: sign=-1) the channels owned by this lane
+template <int E>
+__device__ __forceinline__ void rope_rotate(float (&f)[E], int lane, int rot, int layout, const float* cs_row,
+                                            float sign) {
+  if (layout == 1) {
+#pragma unroll
+    for (int j = 0; j < E / 2; ++j) {
+      const int ch = lane * E + 2 * j;
+      if (ch < rot) {
+        const float c = cs_row[ch], s = cs_row[ch + 1] * sign;  // pair index ch/2 -> offsets (ch, ch+1)
+        const float a = f[2 * j], b = f[2 * j + 1];
+        f[2 * j] = a * c - b * s;
+        f[2 * j + 1] = a * s + b * c;
+      }
+    }
+  } else {
+    const int half_lanes = (rot / 2) / E;  // lanes per half
+    float other[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) other[j] = __shfl_xor_sync(0xffffffffu, f[j], half_lanes);
+    if (lane < 2 * half_lanes) {
+      const bool first = lane < half_lanes;
+      const int i0 = (first ? lane : lane - half_lanes) * E;  // pair index of f[0]
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float c = cs_row[2 * (i0 + j)], s = cs_row[2 * (i0 + j) + 1] * sign;
+        // first half: a' = a c - b s ; second half: b' = a s + b c (a = first-half value)
+        f[j] = first ? (f[j] * c - other[j] * s) : (other[j] * s + f[j] * c);
+      }
+    }
+  }
+}
+
+template <int E>
+__global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv,
+                                                             const __nv_bfloat16* __restrict__ qw,
+                                                             const __nv_bfloat16* __restrict__ kw,
+                                                             const int* __restrict__ pos, const float* __restrict__ cs,
+                                                             __nv_bfloat16* __restrict__ out, long long items, int H,
+                                                             int KV, int rot, int layout, float eps, int unit_offset,
+                                                             long long in_stride, long long out_stride) {
+  constexpr int hd = E * 32;
+  const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const int heads = H + KV;
+  const long long t = item / heads;
+  const int h = static_cast<int>(item - t * heads);
+  float f[E];
+  load_e<E>(qkv + t * in_stride + static_cast<long long>(h) * hd + lane * E, f);
+  const __nv_bfloat16* w = (h < H) ? qw : kw;
+  if (w) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < E; ++j) ss += f[j] * f[j];
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / hd + eps);
+    float wf[E];
+    load_e<E>(w + lane * E, wf);
+    const float off = unit_offset ? 1.f : 0.f;
+#pragma unroll
+    for (int j = 0; j < E; ++j) f[j] = f[j] * rstd * (wf[j] + off);
+    // match separate norm -> rope ops: the normalised value is rounded to bf16 first
+#pragma unroll
+    for (int j = 0; j < E; ++j) f[j] = __bfloat162float(__float2bfloat16(f[j]));
+  }
+  if (cs) rope_rotate<E>(f, lane, rot, layout, cs + static_cast<long long>(pos[t]) * rot, 1.f);
+  store_e<E>(out + t * out_stride + static_cast<long long>(h) * hd + lane * E, f);
+}
+
+// Backward, in place on dqk (gradient w.r.t. rotated q,k) -> gradient w.r.t. the raw q,k.
+// dqw/dkw (fp32 [hd]) accumulate.  Grid-stride over items so weight grads reduce in registers.
+template <int E>
+__global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqk,
+                                                             const __nv_bfloat16* __restrict__ qkv,
+                                                             const __nv_bfloat16* __restrict__ qw,
+                                                             const __nv_bfloat16* __restrict__ kw,
+                                                             const int* __restrict__ pos, const float* __restrict__ cs,
+                                                             float* __restrict__ dqw, float* __restrict__ dkw,
+                                                             long long items, int H, int KV, int rot, int layout,
+                                                             float eps, int unit_offset, long long g_stride,
+                                                             long long in_stride) {
+  constexpr int hd = E * 32;
+  __shared__ float red[2][8][hd];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int heads = H + KV;
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  float accq[E], acck[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) accq[j] = acck[j] = 0.f;
+  const float off = unit_offset ? 1.f : 0.f;
+  for (long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wid; item < items; item += nwarps) {
+    const long long t = item / heads;
+    const int h = static_cast<int>(item - t * heads);
+    __nv_bfloat16* gp = dqk + t * g_stride + static_cast<long long>(h) * hd + lane * E;
+    float g[E];
+    load_e<E>(gp, g);
+    if (cs) rope_rotate<E>(g, lane, rot, layout, cs + static_cast<long long>(pos[t]) * rot, -1.f);
+    const __nv_bfloat16* w = (h < H) ? qw : kw;
+    if (w) {
+      float x[E], wf[E];
+      load_e<E>(qkv + t * in_stride + static_cast<long long>(h) * hd + lane * E, x);
+      load_e<E>(w + lane * E, wf);
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < E; ++j) ss += x[j] * x[j];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / hd + eps);
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < E; ++j) dot += g[j] * (wf[j] + off) * x[j] * rstd;
+      dot = warp_sum(dot) / hd;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float xh = x[j] * rstd;
+        if (h < H) accq[j] += g[j] * xh; else acck[j] += g[j] * xh;
+        g[j] = rstd * (g[j] * (wf[j] + off) - xh * dot);
+      }
+    }
+    store_e<E>(gp, g);
+  }
+  if (qw || kw) {
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      red[0][wid][lane * E + j] = accq[j];
+      red[1][wid][lane * E + j] = acck[j];
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < 2 * hd; c += blockDim.x) {
+      const int which = c / hd, ch = c - which * hd;
+      float s = 0.f;
+      for (int i = 0; i < (blockDim.x >> 5); ++i) s += red[which][i][ch];
+      float* dst = which == 0 ? dqw : dkw;
+      if (dst) atomicAdd(dst + ch, s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ gated linear units
+__device__ __forceinline__ float gelu_tanh(float x) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_tanh_grad(float x) {
+  const float k = 0.7978845608028654f;
+  const float u = k * (x + 0.044715f * x * x * x);
+  const float th = tanhf(u);
+  return 0.5f * (1.f + th) + 0.5f * x * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * x * x);
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu_grad(float x) {
+  const float s = 1.f / (1.f + __expf(-x));
+  return s * (1.f + x * (1.f - s));
+}
+
+// in: [M, 2F] = [gate | up]; out: [M, F].  act 0 = gelu_tanh, 1 = silu.
+__global__ void __launch_bounds__(256) glu_fwd_kernel(const __nv_bfloat16* __restrict__ in,
+                                                     __nv_bfloat16* __restrict__ out, long long M, int F, int act,
+                                                     long long ld_in) {
+  const int fv = F >> 3;
+  const long long total = M * fv;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i - r * fv) * 8;
+    float g[8], u[8], o[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(in + r * ld_in + c), g);
+    unpack8(*reinterpret_cast<const bf16x8*>(in + r * ld_in + F + c), u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = (act == 0 ? gelu_tanh(g[e]) : silu(g[e])) * u[e];
+    *reinterpret_cast<bf16x8*>(out + r * F + c) = pack8(o);
+  }
+}
+// din: [M, 2F] gradient of [gate | up]
+__global__ void __launch_bounds__(256) glu_bwd_kernel(const __nv_bfloat16* __restrict__ in,
+                                                     const __nv_bfloat16* __restrict__ dout,
+                                                     __nv_bfloat16* __restrict__ din, long long M, int F, int act,
+                                                     long long ld_in) {
+  const int fv = F >> 3;
+  const long long total = M * fv;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = i / fv;
+    const int c = static_cast<int>(i - r * fv) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(in + r * ld_in + c), g);
+    unpack8(*reinterpret_cast<const bf16x8*>(in + r * ld_in + F + c), u);
+    unpack8(*reinterpret_cast<const bf16x8*>(dout + r * F + c), d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float a = act == 0 ? gelu_tanh(g[e]) : silu(g[e]);
+      const float da = act == 0 ? gelu_tanh_grad(g[e]) : silu_grad(g[e]);
+      dg[e] = d[e] * u[e] * da;
+      du[e] = d[e] * a;
+    }
+    *reinterpret_cast<bf16x8*>(din + r * 2 * F + c) = pack8(dg);
+    *reinterpret_cast<bf16x8*>(din + r * 2 * F + F + c) = pack8(du);
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const long long* __restrict__ tok,
+                                                           const __nv_bfloat16* __restrict__ w,
+                                                           __nv_bfloat16* __restrict__ out, long long T, int D,
+                                                           float scale, int has_scale) {
+  const int dv = D >> 3;
+  const long long total = T * dv;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / dv;
+    const int c = static_cast<int>(i - t * dv) * 8;
+    bf16x8 v = *reinterpret_cast<const bf16x8*>(w + tok[t] * D + c);
+    if (has_scale) {
+      float f[8];
+      unpack8(v, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] *= scale;
+      v = pack8(f);
+    }
+    *reinterpret_cast<bf16x8*>(out + t * D + c) = v;
+  }
+}
+// dw[tok[t], :] += scale * dout[t, :]   (fp32 accumulator, vector atomics)
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const long long* __restrict__ tok,
+                                                           const __nv_bfloat16* __restrict__ dout,
+                                                           float* __restrict__ dw, long long T, int D, float scale) {
+  const int dv = D >> 2;
+  const long long total = T * dv;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = i / dv;
+    const int c = static_cast<int>(i - t * dv) * 4;
+    const uint2 raw = *reinterpret_cast<const uint2*>(dout + t * D + c);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    float4 v = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+    atomicAdd(reinterpret_cast<float4*>(dw + tok[t] * D + c), v);
+  }
+}
+
+// ------------------------------------------------------------------ softmax cross-entropy on a logits chunk
+// logits [R, V] bf16 (pitch ld).  For each row: loss_sum += (lse - logit[label]) and, in place,
+// logits <- (softmax - onehot) * (*grad_scale)   (zero row when label == ignore_index).
+// One CTA per row; two passes over the row (the second is served from L2).
+__global__ void __launch_bounds__(1024) ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits,
+                                                         const long long* __restrict__ labels,
+                                                         float* __restrict__ loss_sum,
+                                                         const float* __restrict__ grad_scale, float logit_scale,
+                                                         int V, long long ld, int ignore_index, int write_grad,
+                                                         float* __restrict__ lse_out) {
+  __shared__ float sm_m[32], sm_s[32];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const long long label = labels[row];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int nvec = V >> 3;
+  float m = -INFINITY, s = 0.f;
+  if (label != ignore_index || lse_out) {
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+      float f[8];
+      unpack8(reinterpret_cast<const bf16x8*>(lr)[v], f);
+      float mx = f[0] * logit_scale;
+#pragma unroll
+      for (int e = 1; e < 8; ++e) mx = fmaxf(mx, f[e] * logit_scale);
+      const float nm = fmaxf(m, mx);
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc += __expf(f[e] * logit_scale - nm);
+      s = s * __expf(m - nm) + acc;
+      m = nm;
+    }
+    for (int c = (nvec << 3) + threadIdx.x; c < V; c += blockDim.x) {
+      const float f = __bfloat162float(lr[c]) * logit_scale;
+      const float nm = fmaxf(m, f);
+      s = s * __expf(m - nm) + __expf(f - nm);
+      m = nm;
+    }
+    // combine (m, s) across the block
+    const float wm = warp_max(m);
+    s = warp_sum(s * (m == -INFINITY ? 0.f : __expf(m - wm)));
+    if (lane == 0) {
+      sm_m[wid] = wm;
+      sm_s[wid] = s;
+    }
+    __syncthreads();
+    float bm = -INFINITY;
+    for (int i = 0; i < nw; ++i) bm = fmaxf(bm, sm_m[i]);
+    float bs = 0.f;
+    for (int i = 0; i < nw; ++i) bs += sm_s[i] * (sm_m[i] == -INFINITY ? 0.f : __expf(sm_m[i] - bm));
+    m = bm;
+    s = bs;
+  }
+  const float lse = m + logf(s);
+  if (threadIdx.x == 0) {
+    if (lse_out) lse_out[row] = lse;
+    if (label != ignore_index) atomicAdd(loss_sum, lse - __bfloat162float(lr[label]) * logit_scale);
+  }
+  if (!write_grad) return;
+  const float gs = *grad_scale * logit_scale;
+  if (label == ignore_index) {
+    bf16x8 z;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) reinterpret_cast<bf16x8*>(lr)[v] = z;
+    for (int c = (nvec << 3) + threadIdx.x; c < V; c += blockDim.x) lr[c] = __float2bfloat16(0.f);
+    return;
+  }
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(lr)[v], f);
+    const int c0 = v << 3;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float p = __expf(f[e] * logit_scale - lse);
+      if (c0 + e == label) p -= 1.f;
+      f[e] = p * gs;
+    }
+    reinterpret_cast<bf16x8*>(lr)[v] = pack8(f);
+  }
+  for (int c = (nvec << 3) + threadIdx.x; c < V; c += blockDim.x) {
+    float p = __expf(__bfloat162float(lr[c]) * logit_scale - lse);
+    if (c == label) p -= 1.f;
+    lr[c] = __float2bfloat16(p * gs);
+  }
+}
+
+// ------------------------------------------------------------------ flat multi-tensor AdamW
+// Work is described by chunks {offset, length, tensor}; each tensor has {lr_mult, weight_decay}.
+// p/g/m/v are fp32 flat buffers, lp is the bf16 (or null) copy that the next forward reads.
+struct AdamChunk {
+  long long offset;
+  int len;
+  int tensor;
+};
+struct AdamTensor {
+  float lr_mult;
+  float wd;
+};
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                   float* __restrict__ m, float* __restrict__ v,
+                                                   __nv_bfloat16* __restrict__ lp, const AdamChunk* __restrict__ chunks,
+                                                   const AdamTensor* __restrict__ tensors, int nchunks,
+                                                   const float* __restrict__ lr_ptr, float beta1, float beta2,
+                                                   float eps, float bc1, float bc2_sqrt, float grad_scale,
+                                                   int zero_grad, float* __restrict__ g_mut) {
+  for (int ci = blockIdx.x; ci < nchunks; ci += gridDim.x) {
+    const AdamChunk ch = chunks[ci];
+    const AdamTensor tt = tensors[ch.tensor];
+    const float lr = (*lr_ptr) * tt.lr_mult;
+    const float decay = 1.f - lr * tt.wd;
+    const float step_size = lr / bc1;
+    for (int i = threadIdx.x; i < ch.len; i += blockDim.x) {
+      const long long idx = ch.offset + i;
+      const float gr = g[idx] * grad_scale;
+      const float mm = beta1 * m[idx] + (1.f - beta1) * gr;
+      const float vv = beta2 * v[idx] + (1.f - beta2) * gr * gr;
+      m[idx] = mm;
+      v[idx] = vv;
+      const float denom = sqrtf(vv) / bc2_sqrt + eps;
+      const float np = p[idx] * decay - step_size * mm / denom;
+      p[idx] = np;
+      if (lp) lp[idx] = __float2bfloat16(np);
+      if (zero_grad) g_mut[idx] = 0.f;
+    }
+  }
+}
+
+// fp32 -> bf16 cast, y = bf16(x * scale)
+__global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restrict__ x,
+                                                           __nv_bfloat16* __restrict__ y, long long n, float scale) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    y[i] = __float2bfloat16(x[i] * scale);
+}
+
+inline int grid_for(long long work_items, int threads) {
+  long long b = (work_items + threads - 1) / threads;
+  const long long cap = static_cast<long long>(mbh::sm_count()) * 16;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+}  // namespace
+
+extern "C" int mb_rmsnorm_fwd(const void* x, const void* w, const void* res, void* y, float* rstd, int M, int D,
+                              float eps, int unit_offset, cudaStream_t st) {
+  if (D & 7) return -3;
+  const int blocks = (M + 7) / 8;
+  if ((D >> 3) <= NORM_MAXV * 32)
+    rmsnorm_fwd_kernel<true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                     (const __nv_bfloat16*)res, (__nv_bfloat16*)y, rstd, M, D, eps,
+                                                     unit_offset);
+  else
+    rmsnorm_fwd_kernel<false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                                      (const __nv_bfloat16*)res, (__nv_bfloat16*)y, rstd, M, D, eps,
+                                                      unit_offset);
+  return mbh::check_launch("rmsnorm_fwd");
+}
+
+extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_add,
+                              void* dx, float* dw, int M, int D, int unit_offset, cudaStream_t st) {
+  if (D & 7) return -3;
+  rmsnorm_bwd_dx_kernel<<<(M + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                    (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres_add,
+                                                    (__nv_bfloat16*)dx, M, D, unit_offset);
+  if (dw) {
+    const int col_blocks = (D + 63) / 64;
+    int row_blocks = (mbh::sm_count() * 4 + col_blocks - 1) / col_blocks;
+    if (row_blocks < 1) row_blocks = 1;
+    int rpb = (M + row_blocks - 1) / row_blocks;
+    rpb = ((rpb + 7) / 8) * 8;
+    row_blocks = (M + rpb - 1) / rpb;
+    rmsnorm_bwd_dw_kernel<<<dim3(col_blocks, row_blocks), 256, 0, st>>>((const __nv_bfloat16*)dy,
+                                                                       (const __nv_bfloat16*)x, rstd, dw, M, D, rpb);
+  }
+  return mbh::check_launch("rmsnorm_bwd");
+}
+
+extern "C" int mb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos, const float* cs,
+                                  void* out, long long T, int H, int KV, int hd, int rot, int layout, float eps,
+                                  int unit_offset, long long in_stride, long long out_stride, cudaStream_t st) {
+  const long long items = T * (H + KV);
+  const int blocks = static_cast<int>((items + 7) / 8);
+#define MB_QK_FWD(E)                                                                                         \
+  qknorm_rope_fwd_kernel<E><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)qw,      \
+                                                    (const __nv_bfloat16*)kw, pos, cs, (__nv_bfloat16*)out,   \
+                                                    items, H, KV, rot, layout, eps, unit_offset, in_stride,   \
+                                                    out_stride)
+  if (hd == 256) MB_QK_FWD(8);
+  else if (hd == 128) MB_QK_FWD(4);
+  else if (hd == 64) MB_QK_FWD(2);
+  else return -3;
+#undef MB_QK_FWD
+  return mbh::check_launch("qknorm_rope_fwd");
+}
+
+extern "C" int mb_qknorm_rope_bwd(void* dqk, const void* qkv, const void* qw, const void* kw, const int* pos,
+                                  const float* cs, float* dqw, float* dkw, long long T, int H, int KV, int hd,
+                                  int rot, int layout, float eps, int unit_offset, long long g_stride,
+                                  long long in_stride, cudaStream_t st) {
+  const long long items = T * (H + KV);
+  long long want = (items + 7) / 8;
+  const long long cap = static_cast<long long>(mbh::sm_count()) * 8;
+  const int blocks = static_cast<int>(want < cap ? want : cap);
+#define MB_QK_BWD(E)                                                                                          \
+  qknorm_rope_bwd_kernel<E><<<blocks, 256, 0, st>>>((__nv_bfloat16*)dqk, (const __nv_bfloat16*)qkv,            \
+                                                    (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, pos,   \
+                                                    cs, dqw, dkw, items, H, KV, rot, layout, eps,              \
+                                                    unit_offset, g_stride, in_stride)
+  if (hd == 256) MB_QK_BWD(8);
+  else if (hd == 128) MB_QK_BWD(4);
+  else if (hd == 64) MB_QK_BWD(2);
+  else return -3;
+#undef MB_QK_BWD
+  return mbh::check_launch("qknorm_rope_bwd");
+}
+
+extern "C" int mb_glu_fwd(const void* in, void* out, long long M, int F, int act, long long ld_in, cudaStream_t st) {
+  if (F & 7) return -3;
+  glu_fwd_kernel<<<grid_for(M * (F >> 3), 256), 256, 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, M, F,
+                                                             act, ld_in);
+  return mbh::check_launch("glu_fwd");
+}
+extern "C" int mb_glu_bwd(const void* in, const void* dout, void* din, long long M, int F, int act, long long ld_in,
+                          cudaStream_t st) {
+  if (F & 7) return -3;
+  glu_bwd_kernel<<<grid_for(M * (F >> 3), 256), 256, 0, st>>>((const __nv_bfloat16*)in, (const __nv_bfloat16*)dout,
+                                                             (__nv_bfloat16*)din, M, F, act, ld_in);
+  return mbh::check_launch("glu_bwd");
+}
+
+extern "C" int mb_embedding_fwd(const long long* tok, const void* w, void* out, long long T, int D, float scale,
+                                int has_scale, cudaStream_t st) {
+  if (D & 7) return -3;
+  embedding_fwd_kernel<<<grid_for(T * (D >> 3), 256), 256, 0, st>>>(tok, (const __nv_bfloat16*)w,
+                                                                   (__nv_bfloat16*)out, T, D, scale, has_scale);
+  return mbh::check_launch("embedding_fwd");
+}
+extern "C" int mb_embedding_bwd(const long long* tok, const void* dout, float* dw, long long T, int D, float scale,
+                                cudaStream_t st) {
+  if (D & 3) return -3;
+  embedding_bwd_kernel<<<grid_for(T * (D >> 2), 256), 256, 0, st>>>(tok, (const __nv_bfloat16*)dout, dw, T, D,
+                                                                   scale);
+  return mbh::check_launch("embedding_bwd");
+}
+
+extern "C" int mb_ce_fwd_bwd(void* logits, const long long* labels, float* loss_sum, const float* grad_scale,
+                             float logit_scale, long long R, int V, long long ld, int ignore_index, int write_grad,
+                             float* lse_out, cudaStream_t st) {
+  if (R <= 0) return 0;
+  if (ld & 7) return -3;
+  ce_fwd_bwd_kernel<<<static_cast<unsigned>(R), 1024, 0, st>>>((__nv_bfloat16*)logits, labels, loss_sum, grad_scale,
+                                                              logit_scale, V, ld, ignore_index, write_grad, lse_out);
+  return mbh::check_launch("ce_fwd_bwd");
+}
+
+extern "C" int mb_adamw(float* p, float* g, float* m, float* v, void* lp, const void* chunks, const void* tensors,
+                        int nchunks, const float* lr_ptr, float beta1, float beta2, float eps, float bc1,
+                        float bc2_sqrt, float grad_scale, int zero_grad, cudaStream_t st) {
+  if (nchunks <= 0) return 0;
+  int blocks = nchunks < mbh::sm_count() * 8 ? nchunks : mbh::sm_count() * 8;
+  adamw_kernel<<<blocks, 256, 0, st>>>(p, g, m, v, (__nv_bfloat16*)lp, (const AdamChunk*)chunks,
+                                      (const AdamTensor*)tensors, nchunks, lr_ptr, beta1, beta2, eps, bc1, bc2_sqrt,
+                                      grad_scale, zero_grad, g);
+  return mbh::check_launch("adamw");
+}
+
+extern "C" int mb_cast_f32_bf16(const float* x, void* y, long long n, float scale, cudaStream_t st) {
+  cast_f32_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, (__nv_bfloat16*)y, n, scale);
+  return mbh::check_launch("cast_f32_bf16");
+}

@@ -1,0 +1,220 @@
+"""Thin tensor-level wrappers over the native launchers (no autograd here).
+
+Every wrapper checks layouts, passes raw pointers plus the current CUDA stream, and raises on a
+non-zero return code.  ``check_status()`` reads the host-mapped status word that kernels set when a
+bounded wait expires.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from maester_b200.ops import _lib
+
+EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_BF16_ADD = 0, 1, 2, 3
+
+_STATUS_NAMES = {
+    1: "consumer timed out waiting for a TMA stage",
+    2: "producer timed out waiting for a free stage",
+    3: "epilogue timed out waiting for the accumulator",
+    4: "MMA warp timed out waiting for a drained accumulator",
+    5: "timed out waiting on a peer GPU's flag",
+    6: "softmax warps timed out",
+    7: "pipeline wait timed out",
+    8: "bad argument detected on device",
+}
+
+launch_count = 0  # number of native kernel launches issued through this module
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _ck(rc: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise RuntimeError(f"maester_b200 native call {what} failed with code {rc}")
+
+
+def check_status(sync: bool = True) -> None:
+    """Raise if any kernel recorded a bounded-wait expiry since the last clear."""
+    if sync:
+        torch.cuda.synchronize()
+    l = _lib.lib()
+    s = l.mb_status()
+    if s != 0:
+        l.mb_status_clear()
+        raise RuntimeError(f"maester_b200 kernel reported status {s}: {_STATUS_NAMES.get(s, 'unknown')}")
+
+
+def _rows_pitch(t: torch.Tensor) -> int:
+    assert t.dim() == 2 and t.stride(1) == 1, f"expected a row-major 2-D tensor, got strides {t.stride()}"
+    return t.stride(0)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: torch.Tensor | None = None, epi: int = EPI_BF16, alpha: float = 1.0,
+         aux: torch.Tensor | None = None, alpha_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """``C = alpha * op(A) @ op(B).T`` on the tcgen05 GEMM.
+
+    a_mn=False: A is [M, K];  a_mn=True: A is stored [K, M].
+    b_mn=False: B is [N, K];  b_mn=True: B is stored [K, N].
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, device=a.device, dtype=torch.bfloat16 if epi in (EPI_BF16, EPI_BF16_ADD) else torch.float32)
+    assert out.shape == (M, N)
+    l = _lib.lib()
+    rc = l.mb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(aux), M, N, K,
+                        _rows_pitch(a), _rows_pitch(b), _rows_pitch(out),
+                        _rows_pitch(aux) if aux is not None else 0,
+                        int(a_mn), int(b_mn), epi, float(alpha), _ptr(alpha_dev), _stream())
+    _ck(rc, "gemm_bf16")
+    return out
+
+
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor | None, eps: float, unit_offset: bool,
+                residual: torch.Tensor | None = None):
+    D = x.shape[-1]
+    x2 = x.reshape(-1, D)
+    assert x2.is_contiguous()
+    M = x2.shape[0]
+    y = torch.empty_like(x2)
+    rstd = torch.empty(M, device=x.device, dtype=torch.float32)
+    r2 = residual.reshape(-1, D) if residual is not None else None
+    if r2 is not None:
+        assert r2.is_contiguous()
+    _ck(_lib.lib().mb_rmsnorm_fwd(x2.data_ptr(), _ptr(w), _ptr(r2), y.data_ptr(), rstd.data_ptr(), M, D,
+                                  float(eps), int(unit_offset), _stream()), "rmsnorm_fwd")
+    return y.view(x.shape), rstd
+
+
+def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor | None, rstd: torch.Tensor,
+                unit_offset: bool, dw_acc: torch.Tensor | None, dres_add: torch.Tensor | None = None):
+    D = x.shape[-1]
+    dy2, x2 = dy.reshape(-1, D), x.reshape(-1, D)
+    assert dy2.is_contiguous() and x2.is_contiguous()
+    dx = torch.empty_like(x2)
+    a2 = dres_add.reshape(-1, D) if dres_add is not None else None
+    _ck(_lib.lib().mb_rmsnorm_bwd(dy2.data_ptr(), x2.data_ptr(), _ptr(w), rstd.data_ptr(), _ptr(a2),
+                                  dx.data_ptr(), _ptr(dw_acc), x2.shape[0], D, int(unit_offset), _stream()),
+        "rmsnorm_bwd")
+    return dx.view(x.shape)
+
+
+def qknorm_rope_fwd(qkv: torch.Tensor, qw, kw, pos: torch.Tensor, cs: torch.Tensor | None, H: int, KV: int,
+                    hd: int, layout: int, eps: float, unit_offset: bool) -> torch.Tensor:
+    """qkv: [T, (H+2KV)*hd] -> rotated/normalised q,k packed as [T, (H+KV)*hd]."""
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1
+    out = torch.empty(T, (H + KV) * hd, device=qkv.device, dtype=qkv.dtype)
+    rot = cs.shape[1] * 2 if cs is not None else 0
+    _ck(_lib.lib().mb_qknorm_rope_fwd(qkv.data_ptr(), _ptr(qw), _ptr(kw), _ptr(pos), _ptr(cs), out.data_ptr(), T,
+                                      H, KV, hd, rot, layout, float(eps), int(unit_offset), qkv.stride(0),
+                                      out.stride(0), _stream()), "qknorm_rope_fwd")
+    return out
+
+
+def qknorm_rope_bwd(dqk: torch.Tensor, qkv: torch.Tensor, qw, kw, pos, cs, dqw, dkw, H: int, KV: int, hd: int,
+                    layout: int, eps: float, unit_offset: bool) -> None:
+    """In place on the q,k columns of ``dqk`` (row pitch arbitrary)."""
+    T = qkv.shape[0]
+    rot = cs.shape[1] * 2 if cs is not None else 0
+    _ck(_lib.lib().mb_qknorm_rope_bwd(dqk.data_ptr(), qkv.data_ptr(), _ptr(qw), _ptr(kw), _ptr(pos), _ptr(cs),
+                                      _ptr(dqw), _ptr(dkw), T, H, KV, hd, rot, layout, float(eps),
+                                      int(unit_offset), dqk.stride(0), qkv.stride(0), _stream()),
+        "qknorm_rope_bwd")
+
+
+def glu_fwd(gate_up: torch.Tensor, act: int) -> torch.Tensor:
+    F2 = gate_up.shape[-1]
+    g2 = gate_up.reshape(-1, F2)
+    assert g2.stride(1) == 1
+    out = torch.empty(g2.shape[0], F2 // 2, device=g2.device, dtype=g2.dtype)
+    _ck(_lib.lib().mb_glu_fwd(g2.data_ptr(), out.data_ptr(), g2.shape[0], F2 // 2, act, g2.stride(0), _stream()),
+        "glu_fwd")
+    return out.view(*gate_up.shape[:-1], F2 // 2)
+
+
+def glu_bwd(gate_up: torch.Tensor, dout: torch.Tensor, act: int) -> torch.Tensor:
+    F2 = gate_up.shape[-1]
+    g2 = gate_up.reshape(-1, F2)
+    d2 = dout.reshape(-1, F2 // 2)
+    assert d2.is_contiguous() and g2.stride(1) == 1
+    din = torch.empty(g2.shape[0], F2, device=g2.device, dtype=g2.dtype)
+    _ck(_lib.lib().mb_glu_bwd(g2.data_ptr(), d2.data_ptr(), din.data_ptr(), g2.shape[0], F2 // 2, act,
+                              g2.stride(0), _stream()), "glu_bwd")
+    return din.view(gate_up.shape)
+
+
+def embedding_fwd(tokens: torch.Tensor, w: torch.Tensor, scale: float | None) -> torch.Tensor:
+    tok = tokens.reshape(-1).to(torch.int64).contiguous()
+    D = w.shape[1]
+    out = torch.empty(tok.numel(), D, device=w.device, dtype=w.dtype)
+    s = 1.0 if scale is None else float(torch.tensor(scale, dtype=w.dtype).float())
+    _ck(_lib.lib().mb_embedding_fwd(tok.data_ptr(), w.data_ptr(), out.data_ptr(), tok.numel(), D, s,
+                                    int(scale is not None), _stream()), "embedding_fwd")
+    return out.view(*tokens.shape, D)
+
+
+def embedding_bwd(tokens: torch.Tensor, dout: torch.Tensor, dw_acc: torch.Tensor, scale: float | None) -> None:
+    tok = tokens.reshape(-1).to(torch.int64).contiguous()
+    D = dout.shape[-1]
+    d2 = dout.reshape(-1, D)
+    assert d2.is_contiguous() and dw_acc.dtype == torch.float32 and dw_acc.is_contiguous()
+    s = 1.0 if scale is None else float(torch.tensor(scale, dtype=dout.dtype).float())
+    _ck(_lib.lib().mb_embedding_bwd(tok.data_ptr(), d2.data_ptr(), dw_acc.data_ptr(), tok.numel(), D, s, _stream()),
+        "embedding_bwd")
+
+
+def ce_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, loss_sum: torch.Tensor, grad_scale: torch.Tensor,
+               logit_scale: float = 1.0, write_grad: bool = True, lse_out: torch.Tensor | None = None) -> None:
+    R, V = logits.shape
+    _ck(_lib.lib().mb_ce_fwd_bwd(logits.data_ptr(), labels.data_ptr(), loss_sum.data_ptr(), grad_scale.data_ptr(),
+                                 float(logit_scale), R, V, logits.stride(0), -100, int(write_grad), _ptr(lse_out),
+                                 _stream()), "ce_fwd_bwd")
+
+
+def adamw(p, g, m, v, lp, chunks, tensors, nchunks, lr_t, beta1, beta2, eps, step, grad_scale=1.0,
+          zero_grad=False) -> None:
+    bc1 = 1.0 - beta1 ** step
+    bc2s = math.sqrt(1.0 - beta2 ** step)
+    _ck(_lib.lib().mb_adamw(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), _ptr(lp), chunks.data_ptr(),
+                            tensors.data_ptr(), nchunks, lr_t.data_ptr(), beta1, beta2, eps, bc1, bc2s,
+                            float(grad_scale), int(zero_grad), _stream()), "adamw")
+
+
+def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:
+    _ck(_lib.lib().mb_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), _stream()), "cast")
+
+
+def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, causal: bool, window: int | None,
+             doc: torch.Tensor | None, kv_lo_blk: torch.Tensor | None):
+    """q: [B,S,H,hd] (last two dims dense, token stride arbitrary); k, v: [B,S,KV,hd]."""
+    B, S, H, hd = q.shape
+    KV = k.shape[2]
+    for t in (q, k, v):
+        assert t.stride(3) == 1 and t.stride(2) == hd and t.stride(0) == S * t.stride(1)
+    out = torch.empty(B, S, H, hd, device=q.device, dtype=q.dtype)
+    lse = torch.empty(B, H, S, device=q.device, dtype=torch.float32)
+    _ck(_lib.lib().mb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _ptr(doc),
+                               _ptr(kv_lo_blk), B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
+                               int(causal), -1 if window is None or window <= 0 else int(window), float(scale),
+                               _stream()), "attn_fwd")
+    return out, lse

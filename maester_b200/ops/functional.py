@@ -1,0 +1,339 @@
+"""Public op API used by the models: each op runs the native sm_100a kernel for bf16 CUDA tensors
+and the plain-PyTorch definition (``reference.py``) otherwise (CPU runs, fp32 oracles).
+
+Weight gradients: if a parameter carries a ``main_grad`` attribute (an fp32 accumulation buffer set
+up by the sharding runtime) the backward accumulates into it in place and returns no autograd
+gradient for that parameter; otherwise the gradient is returned normally.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from maester_b200.ops import reference as ref
+
+_ACT = {"gelu_tanh": 0, "silu": 1}
+
+
+def use_native(*tensors: torch.Tensor) -> bool:
+    t = tensors[0]
+    return t.is_cuda and t.dtype == torch.bfloat16
+
+
+def _C():
+    from maester_b200.ops import cuda
+    return cuda
+
+
+def _acc_or_return(param: torch.Tensor, make_grad_into):
+    """Accumulate into ``param.main_grad`` if present (returns None) else materialise a gradient."""
+    mg = getattr(param, "main_grad", None)
+    if mg is not None:
+        make_grad_into(mg, True)
+        return None
+    g = torch.zeros(param.shape, device=param.device, dtype=torch.float32)
+    make_grad_into(g, True)
+    return g.to(param.dtype)
+
+
+# --------------------------------------------------------------------------- linear
+class _Linear(Function):
+    @staticmethod
+    def forward(ctx, x, w, residual):
+        C = _C()
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.x_shape = x.shape
+        ctx.has_res = residual is not None
+        if residual is None:
+            y = C.gemm(x2, w)
+        else:
+            y = C.gemm(x2, w, epi=C.EPI_BF16_ADD, aux=residual.reshape(-1, w.shape[0]))
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _C()
+        x2, w = ctx.saved_tensors
+        N = w.shape[0]
+        dy2 = dy.reshape(-1, N)
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = C.gemm(dy2, w, b_mn=True).view(ctx.x_shape)  # [M,N] @ [N,K]
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dw = _acc_or_return(w, lambda buf, acc: C.gemm(dy2, x2, a_mn=True, b_mn=True, out=buf,
+                                                          epi=C.EPI_F32_ACC if acc else C.EPI_F32))
+        return dx, dw, (dy if ctx.has_res else None)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T (+ residual)``; w is [out, in]."""
+    if use_native(x, w):
+        return _Linear.apply(x, w, residual)
+    y = ref.linear(x, w)
+    return y if residual is None else y + residual
+
+
+# --------------------------------------------------------------------------- rmsnorm
+class _RMSNorm(Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, unit_offset, residual):
+        y, rstd = _C().rmsnorm_fwd(x, w, eps, unit_offset, residual)
+        ctx.save_for_backward(x, w, rstd)
+        ctx.unit_offset = unit_offset
+        ctx.has_res = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _C()
+        x, w, rstd = ctx.saved_tensors
+        dy = dy.contiguous()
+        dw = None
+        if w is not None and ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+            dx = C.rmsnorm_bwd(dy, x, w, rstd, ctx.unit_offset, buf)
+            dw = None if mg is not None else buf.to(w.dtype)
+        else:
+            dx = C.rmsnorm_bwd(dy, x, w, rstd, ctx.unit_offset, None)
+        return dx, dw, None, None, (dy if ctx.has_res else None)
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor | None, eps: float, unit_offset: bool = False,
+            residual: torch.Tensor | None = None) -> torch.Tensor:
+    """``[residual +] rmsnorm(x) * (w | 1+w)``."""
+    if use_native(x) and x.shape[-1] % 8 == 0:
+        return _RMSNorm.apply(x.contiguous(), w, eps, unit_offset,
+                              None if residual is None else residual.contiguous())
+    return ref.rmsnorm(x, w, eps, unit_offset, residual)
+
+
+# --------------------------------------------------------------------------- GLU
+class _GLU(Function):
+    @staticmethod
+    def forward(ctx, gate_up, act):
+        ctx.save_for_backward(gate_up)
+        ctx.act = act
+        return _C().glu_fwd(gate_up, act)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gate_up,) = ctx.saved_tensors
+        return _C().glu_bwd(gate_up, dout.contiguous(), ctx.act), None
+
+
+def glu(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
+    """``act(gate) * up`` for ``gate_up = [gate | up]`` on the last dim."""
+    if use_native(gate_up) and (gate_up.shape[-1] // 2) % 8 == 0:
+        return _GLU.apply(gate_up, _ACT[activation])
+    return ref.geglu(gate_up) if activation == "gelu_tanh" else ref.swiglu(gate_up)
+
+
+# --------------------------------------------------------------------------- embedding
+class _Embedding(Function):
+    @staticmethod
+    def forward(ctx, tokens, w, scale):
+        ctx.save_for_backward(tokens, w)
+        ctx.scale = scale
+        return _C().embedding_fwd(tokens, w, scale)
+
+    @staticmethod
+    def backward(ctx, dout):
+        tokens, w = ctx.saved_tensors
+        C = _C()
+        dout = dout.contiguous()
+        dw = _acc_or_return(w, lambda buf, acc: C.embedding_bwd(tokens, dout, buf, ctx.scale))
+        return None, dw, None
+
+
+def embedding(tokens: torch.Tensor, w: torch.Tensor, scale: float | None = None) -> torch.Tensor:
+    if use_native(w) and w.shape[1] % 8 == 0:
+        return _Embedding.apply(tokens, w, scale)
+    return ref.embedding(tokens, w, scale)
+
+
+# --------------------------------------------------------------------------- attention
+def kv_block_lower_bounds(S: int, block_q: int, window: int | None, doc: torch.Tensor | None, device,
+                          batch: int = 1) -> torch.Tensor | None:
+    """Per (batch, query block) lowest kv index any row of the block may attend to.
+
+    Document ids must form contiguous runs (packed sequences); the bound for a row is
+    ``max(start of its document, q - window)`` and the block takes the minimum over its rows.
+    No host synchronisation.
+    """
+    if doc is None and (window is None or window <= 0):
+        return None
+    idx = torch.arange(S, device=device, dtype=torch.int32)
+    if doc is not None:
+        d = doc.to(torch.int32)
+        change = torch.ones_like(d, dtype=torch.bool)
+        change[:, 1:] = d[:, 1:] != d[:, :-1]
+        start = torch.where(change, idx[None], torch.zeros_like(d)).cummax(dim=1).values
+    else:
+        start = torch.zeros(batch, S, device=device, dtype=torch.int32)
+    if window is not None and window > 0:
+        start = torch.maximum(start, (idx - window).clamp_min(0)[None].expand_as(start))
+    nqb = (S + block_q - 1) // block_q
+    pad = nqb * block_q - S
+    if pad:
+        start = torch.nn.functional.pad(start, (0, pad), value=S)
+    return start.view(start.shape[0], nqb, block_q).amin(dim=2).to(torch.int32).contiguous()
+
+
+def rope_table(inv_freq: torch.Tensor, max_pos: int, attn_factor: float = 1.0) -> torch.Tensor:
+    """[max_pos, rot/2, 2] fp32 (cos, sin) table gathered by position id inside the kernels."""
+    ang = torch.arange(max_pos, device=inv_freq.device, dtype=torch.float32)[:, None] * inv_freq.float()[None]
+    return torch.stack([ang.cos() * attn_factor, ang.sin() * attn_factor], dim=-1).contiguous()
+
+
+class _AttnBlock(Function):
+    """qkv (packed) -> [QK-norm] -> RoPE -> masked GQA attention, one autograd node."""
+
+    @staticmethod
+    def forward(ctx, qkv, qw, kw, pos, cs, doc, H, KV, hd, layout, eps, unit_offset, scale, causal, window):
+        C = _C()
+        B, S, _ = qkv.shape
+        qkv2 = qkv.reshape(B * S, -1)
+        pos32 = pos.reshape(-1).to(torch.int32).contiguous() if pos is not None else None
+        need_qk = (qw is not None) or (cs is not None)
+        if need_qk:
+            qk = C.qknorm_rope_fwd(qkv2, qw, kw, pos32, cs, H, KV, hd, layout, eps, unit_offset)
+        else:
+            qk = qkv2
+        q = qk[:, : H * hd].view(B, S, H, hd)
+        k = qk[:, H * hd:(H + KV) * hd].view(B, S, KV, hd)
+        v = qkv2[:, (H + KV) * hd:].view(B, S, KV, hd)
+        doc32 = doc.to(torch.int32).contiguous() if doc is not None else None
+        lo = kv_block_lower_bounds(S, 128, window, doc32, qkv.device, batch=B)
+        out, lse = C.attn_fwd(q, k, v, scale, causal, window, doc32, lo)
+        ctx.save_for_backward(qkv2, qk if need_qk else None, qw, kw, pos32, cs, doc32, lo, out, lse)
+        ctx.cfg = (B, S, H, KV, hd, layout, eps, unit_offset, scale, causal, window, need_qk)
+        return out.view(B, S, H * hd)
+
+    @staticmethod
+    def backward(ctx, dout):
+        C = _C()
+        qkv2, qk, qw, kw, pos32, cs, doc32, lo, out, lse = ctx.saved_tensors
+        B, S, H, KV, hd, layout, eps, unit_offset, scale, causal, window, need_qk = ctx.cfg
+        if qk is None:
+            qk = qkv2
+        q = qk[:, : H * hd].view(B, S, H, hd)
+        k = qk[:, H * hd:(H + KV) * hd].view(B, S, KV, hd)
+        v = qkv2[:, (H + KV) * hd:].view(B, S, KV, hd)
+        dqkv = torch.empty(B * S, (H + 2 * KV) * hd, device=dout.device, dtype=dout.dtype)
+        C.attn_bwd(q, k, v, out, dout.reshape(B, S, H, hd).contiguous(), lse, dqkv, scale, causal, window, doc32, lo)
+        dqw = dkw = None
+        if need_qk:
+            mq = getattr(qw, "main_grad", None) if qw is not None else None
+            mk = getattr(kw, "main_grad", None) if kw is not None else None
+            bq = mq if mq is not None else (torch.zeros(hd, device=dout.device) if qw is not None else None)
+            bk = mk if mk is not None else (torch.zeros(hd, device=dout.device) if kw is not None else None)
+            C.qknorm_rope_bwd(dqkv, qkv2, qw, kw, pos32, cs, bq, bk, H, KV, hd, layout, eps, unit_offset)
+            dqw = None if (mq is not None or qw is None) else bq.to(qw.dtype)
+            dkw = None if (mk is not None or kw is None) else bk.to(kw.dtype)
+        return (dqkv.view(B, S, -1), dqw, dkw) + (None,) * 12
+
+
+def attention_block(qkv: torch.Tensor, q_norm_w, k_norm_w, pos: torch.Tensor | None,
+                    inv_freq: torch.Tensor | None, rope_cs: torch.Tensor | None, doc_ids: torch.Tensor | None,
+                    n_heads: int, n_kv_heads: int, head_dim: int, *, layout: str = "half", eps: float = 1e-6,
+                    unit_offset: bool = False, scale: float | None = None, causal: bool = True,
+                    window: int | None = None) -> torch.Tensor:
+    """Packed ``qkv`` [B,S,(H+2KV)*hd] → attention output [B,S,H*hd].
+
+    Optional per-head RMSNorm on q and k, RoPE (``inv_freq`` for the reference path, ``rope_cs``
+    table for the native path), then softmax attention with causal / inclusive sliding-window /
+    same-document masking and GQA.
+    """
+    B, S, _ = qkv.shape
+    H, KV, hd = n_heads, n_kv_heads, head_dim
+    scale = hd ** -0.5 if scale is None else scale
+    if use_native(qkv) and hd in (64, 128, 256):
+        if pos is None and rope_cs is not None:
+            pos = torch.arange(S, device=qkv.device, dtype=torch.int32)[None].expand(B, S)
+        return _AttnBlock.apply(qkv, q_norm_w, k_norm_w, pos, rope_cs, doc_ids, H, KV, hd,
+                                0 if layout == "half" else 1, eps, unit_offset, scale, causal, window)
+    q, k, v = qkv.split([H * hd, KV * hd, KV * hd], dim=-1)
+    q = q.reshape(B, S, H, hd)
+    k = k.reshape(B, S, KV, hd)
+    v = v.reshape(B, S, KV, hd)
+    if pos is None:
+        pos = torch.arange(S, device=qkv.device)[None].expand(B, S)
+    q, k = ref.qk_norm_rope(q, k, q_norm_w, k_norm_w, pos, inv_freq, layout, eps, unit_offset)
+    out = ref.attention(q, k, v, scale, causal, window, doc_ids)
+    return out.reshape(B, S, H * hd)
+
+
+# --------------------------------------------------------------------------- linear + cross-entropy
+CE_CHUNK_ROWS = 4096
+CE_STORE_LIMIT_BYTES = 12 << 30
+
+
+class _LinearCE(Function):
+    """mean CE(h·Wᵀ, labels) over labels != -100 without holding all logits at once.
+
+    Forward walks row chunks: logits chunk = GEMM, then one kernel produces the chunk's loss and
+    overwrites the logits with d(loss)/d(logits).  Those gradient chunks are kept (or recomputed if
+    they would exceed ``CE_STORE_LIMIT_BYTES``) and backward turns them into dH and dW with two
+    GEMMs per chunk; dW accumulates in fp32 (directly into ``main_grad`` of a tied embedding).
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, labels, logit_scale):
+        C = _C()
+        M, D = h.shape
+        V = w.shape[0]
+        labels = labels.reshape(-1).to(torch.int64).contiguous()
+        nvalid = (labels != ref.IGNORE_INDEX).sum().clamp_min(1).to(torch.float32)
+        gs = (1.0 / nvalid).reshape(1)
+        loss_sum = torch.zeros(1, device=h.device, dtype=torch.float32)
+        store = ctx.needs_input_grad[0] and (M * V * 2 <= CE_STORE_LIMIT_BYTES)
+        chunks = []
+        for r0 in range(0, M, CE_CHUNK_ROWS):
+            r1 = min(M, r0 + CE_CHUNK_ROWS)
+            logits = C.gemm(h[r0:r1], w)
+            C.ce_fwd_bwd(logits, labels[r0:r1], loss_sum, gs, logit_scale, write_grad=store)
+            if store:
+                chunks.append(logits)
+        ctx.save_for_backward(h, w, labels, gs, *chunks)
+        ctx.store = store
+        ctx.logit_scale = logit_scale
+        return (loss_sum * gs).reshape(())
+
+    @staticmethod
+    def backward(ctx, gout):
+        C = _C()
+        h, w, labels, gs, *chunks = ctx.saved_tensors
+        M, D = h.shape
+        g = gout.reshape(1).to(torch.float32).contiguous()
+        dh = torch.empty_like(h)
+        mg = getattr(w, "main_grad", None)
+        dw_buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        scratch = torch.zeros(1, device=h.device, dtype=torch.float32)
+        for i, r0 in enumerate(range(0, M, CE_CHUNK_ROWS)):
+            r1 = min(M, r0 + CE_CHUNK_ROWS)
+            if ctx.store:
+                dl = chunks[i]
+            else:
+                dl = C.gemm(h[r0:r1], w)
+                C.ce_fwd_bwd(dl, labels[r0:r1], scratch, gs, ctx.logit_scale, write_grad=True)
+            C.gemm(dl, w, b_mn=True, out=dh[r0:r1], alpha_dev=g)                      # [R,V] @ [V,D]
+            C.gemm(dl, h[r0:r1], a_mn=True, b_mn=True, out=dw_buf, epi=C.EPI_F32_ACC, alpha_dev=g)
+        dw = None if mg is not None else dw_buf.to(w.dtype)
+        return dh, dw, None, None
+
+
+def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
+                         logit_scale: float = 1.0) -> torch.Tensor:
+    """Mean cross-entropy of ``h @ w.T * logit_scale`` against ``labels`` (ignore_index = -100)."""
+    h2 = h.reshape(-1, h.shape[-1])
+    if use_native(h2, w) and w.shape[0] % 8 == 0:
+        return _LinearCE.apply(h2.contiguous(), w, labels, logit_scale)
+    return ref.linear_cross_entropy(h2, w, labels.reshape(-1), logit_scale)

@@ -1,0 +1,117 @@
+"""Fused AdamW over flat fp32 buffers: one kernel launch updates every parameter of a shard.
+
+``FusedAdamW`` is a regular ``torch.optim.Optimizer`` (so LR schedulers, state_dict and the
+optimizer container work unchanged).  When its parameters are views into one flat fp32 buffer whose
+gradients are views into a matching flat buffer (the layout the sharding runtime creates), the whole
+update is a single native launch that also emits the bf16 copy consumed by the next forward.
+Otherwise it falls back to a per-tensor update with the same arithmetic.
+Reference behaviour: torch.optim.AdamW(fused=True) as configured in maester/config.py:147-154.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch.optim import Optimizer
+
+from maester_b200.ops import reference as ref
+
+CHUNK = 32768
+
+
+def build_chunk_table(segments, device):
+    """segments: iterable of (offset, numel, lr_mult, weight_decay) → (chunks, tensors, nchunks).
+
+    ``chunks`` is an int8 view of packed {int64 offset, int32 len, int32 tensor} records and
+    ``tensors`` an fp32 [n, 2] table of (lr_mult, weight_decay).
+    """
+    import numpy as np
+
+    recs = []
+    tens = []
+    for ti, (off, n, lrm, wd) in enumerate(segments):
+        tens.append((lrm, wd))
+        for c0 in range(0, n, CHUNK):
+            recs.append((off + c0, min(CHUNK, n - c0), ti))
+    arr = np.zeros(len(recs), dtype=np.dtype([("offset", "<i8"), ("len", "<i4"), ("tensor", "<i4")]))
+    for i, r in enumerate(recs):
+        arr[i] = r
+    chunks = torch.from_numpy(arr.view(np.uint8).copy()).to(device)
+    tensors = torch.tensor(tens, dtype=torch.float32, device=device).reshape(-1, 2).contiguous()
+    return chunks, tensors, len(recs)
+
+
+class FusedAdamW(Optimizer):
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, fused=None, **_):
+        defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+        self._flat = None  # set by attach_flat()
+
+    def attach_flat(self, master: torch.Tensor, grad: torch.Tensor, lowp: torch.Tensor | None, segments_by_param):
+        """Register the flat layout: ``segments_by_param`` maps each parameter to (offset, numel).
+
+        master / grad are fp32 flat buffers of equal length, lowp the bf16 buffer that receives the
+        updated values (may be None).  State tensors exp_avg / exp_avg_sq become views of two more
+        flat buffers so that checkpoints keep the per-parameter layout.
+        """
+        self._flat = dict(master=master, grad=grad, lowp=lowp, seg=segments_by_param,
+                          m=torch.zeros_like(master), v=torch.zeros_like(master), table=None)
+        for group in self.param_groups:
+            for p in group["params"]:
+                off, n = segments_by_param[p]
+                st = self.state[p]
+                st["step"] = torch.tensor(0.0)
+                st["exp_avg"] = self._flat["m"][off:off + n].view(p.shape)
+                st["exp_avg_sq"] = self._flat["v"][off:off + n].view(p.shape)
+
+    def _table(self):
+        f = self._flat
+        key = tuple((g["lr"], g["weight_decay"]) for g in self.param_groups)
+        if f["table"] is None or f["table"][0] != key:
+            base_lr = self.param_groups[0]["lr"] or 1.0
+            segs = []
+            for g in self.param_groups:
+                for p in g["params"]:
+                    off, n = f["seg"][p]
+                    segs.append((off, n, g["lr"] / base_lr if base_lr else 1.0, g["weight_decay"]))
+            dev = f["master"].device
+            f["table"] = (key, build_chunk_table(segs, dev), torch.tensor([base_lr], device=dev, dtype=torch.float32))
+        return f["table"][1], f["table"][2]
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        f = self._flat
+        if f is not None and f["master"].is_cuda:
+            from maester_b200.ops import cuda as C
+            g0 = self.param_groups[0]
+            any_p = g0["params"][0]
+            st = self.state[any_p]
+            st_step = int(st["step"].item()) + 1 if torch.is_tensor(st["step"]) else int(st["step"]) + 1
+            (chunks, tensors, nch), lr_t = self._table()
+            b1, b2 = g0["betas"]
+            C.adamw(f["master"], f["grad"], f["m"], f["v"], f["lowp"], chunks, tensors, nch, lr_t, b1, b2,
+                    g0["eps"], st_step)
+            for g in self.param_groups:
+                for p in g["params"]:
+                    self.state[p]["step"] = torch.tensor(float(st_step))
+            return loss
+        for group in self.param_groups:
+            b1, b2 = group["betas"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if "exp_avg" not in st:
+                    st["step"] = torch.tensor(0.0)
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                st["step"] = st["step"] + 1
+                p32 = p.data if p.dtype == torch.float32 else p.data.float()
+                ref.adamw_step(p32, p.grad.float(), st["exp_avg"], st["exp_avg_sq"], int(st["step"].item()),
+                               group["lr"], b1, b2, group["eps"], group["weight_decay"])
+                if p32 is not p.data:
+                    p.data.copy_(p32)
+        if f is not None and f["lowp"] is not None:
+            f["lowp"].copy_(f["master"])
+        return loss

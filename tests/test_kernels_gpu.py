@@ -1,0 +1,211 @@
+"""CUDA kernels against the plain-PyTorch fp32 oracle (maester_b200/ops/reference.py)."""
+import math
+
+import pytest
+import torch
+
+from maester_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status():
+    from maester_b200.ops import cuda as C
+    yield
+    C.check_status()
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 520, 136), (1024, 2560, 4096), (77, 40, 72)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    from maester_b200.ops import cuda as C
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a pitch that is a multiple of 8")
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    want = A.float() @ B.float().T
+    a = A.T.contiguous() if a_mn else A
+    b = B.T.contiguous() if b_mn else B
+    got = C.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    C.check_status()
+    assert _rel(got, want) < 5e-3
+    got32 = C.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=C.EPI_F32)
+    assert _rel(got32, want) < 1e-5 * math.sqrt(K) + 1e-4
+    acc = torch.ones(M, N, device="cuda")
+    C.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=C.EPI_F32_ACC, out=acc, alpha=0.5)
+    assert _rel(acc, 1 + 0.5 * want) < 1e-4
+
+
+def test_gemm_residual_epilogue():
+    from maester_b200.ops import cuda as C
+    A = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(768, 512, device="cuda", dtype=torch.bfloat16)
+    R = torch.randn(256, 768, device="cuda", dtype=torch.bfloat16)
+    got = C.gemm(A, B, epi=C.EPI_BF16_ADD, aux=R)
+    assert _rel(got, A.float() @ B.float().T + R.float()) < 5e-3
+
+
+@pytest.mark.parametrize("M,D", [(64, 256), (1000, 2560), (33, 4096), (16, 5376)])
+@pytest.mark.parametrize("unit", [False, True])
+def test_rmsnorm(M, D, unit):
+    from maester_b200.ops import cuda as C
+    x = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(D, device="cuda") * 0.1).to(torch.bfloat16)
+    res = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    y, rstd = C.rmsnorm_fwd(x, w, 1e-6, unit)
+    assert _rel(y, ref.rmsnorm(x.float(), w.float(), 1e-6, unit)) < 4e-3
+    y2, _ = C.rmsnorm_fwd(x, w, 1e-6, unit, residual=res)
+    assert _rel(y2, ref.rmsnorm(x, w, 1e-6, unit, residual=res)) < 4e-3
+    # backward
+    dy = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    xf = x.float().requires_grad_()
+    wf = w.float().requires_grad_()
+    ref.rmsnorm(xf, wf, 1e-6, unit).backward(dy.float())
+    dw = torch.zeros(D, device="cuda")
+    dx = C.rmsnorm_bwd(dy, x, w, rstd, unit, dw)
+    assert _rel(dx, xf.grad) < 5e-3
+    assert _rel(dw, wf.grad) < 5e-3
+
+
+@pytest.mark.parametrize("hd,rot,layout", [(256, 256, "half"), (128, 128, "interleaved"), (128, 64, "half"), (64, 64, "interleaved")])
+@pytest.mark.parametrize("norm", [True, False])
+def test_qknorm_rope(hd, rot, layout, norm):
+    from maester_b200.ops import cuda as C
+    torch.manual_seed(1)
+    B, S, H, KV = 2, 96, 4, 2
+    T = B * S
+    qkv = torch.randn(T, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
+    qw = (torch.randn(hd, device="cuda") * 0.1).to(torch.bfloat16) if norm else None
+    kw = (torch.randn(hd, device="cuda") * 0.1).to(torch.bfloat16) if norm else None
+    pos = torch.randint(0, 500, (B, S), device="cuda")
+    inv = ref.rope_inv_freq(rot, 10000.0, device="cuda")
+    ang = torch.arange(512, device="cuda").float()[:, None] * inv[None]
+    cs = torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous()
+    lay = 0 if layout == "half" else 1
+    out = C.qknorm_rope_fwd(qkv, qw, kw, pos.reshape(-1).int(), cs, H, KV, hd, lay, 1e-6, True)
+    q = qkv[:, : H * hd].view(B, S, H, hd)
+    k = qkv[:, H * hd:(H + KV) * hd].view(B, S, KV, hd)
+    qf, kf = q.float().requires_grad_(), k.float().requires_grad_()
+    qwf = qw.float().requires_grad_() if norm else None
+    kwf = kw.float().requires_grad_() if norm else None
+    rq, rk = ref.qk_norm_rope(qf, kf, qwf, kwf, pos, inv, layout, 1e-6, True)
+    want = torch.cat([rq.reshape(T, -1), rk.reshape(T, -1)], dim=1)
+    assert _rel(out, want) < 6e-3
+    g = torch.randn_like(out)
+    want.backward(g.float())
+    dqk = g.clone()
+    dqw = torch.zeros(hd, device="cuda") if norm else None
+    dkw = torch.zeros(hd, device="cuda") if norm else None
+    C.qknorm_rope_bwd(dqk, qkv, qw, kw, pos.reshape(-1).int(), cs, dqw, dkw, H, KV, hd, lay, 1e-6, True)
+    wantg = torch.cat([qf.grad.reshape(T, -1), kf.grad.reshape(T, -1)], dim=1)
+    assert _rel(dqk, wantg) < 8e-3
+    if norm:
+        assert _rel(dqw, qwf.grad) < 8e-3
+        assert _rel(dkw, kwf.grad) < 8e-3
+
+
+@pytest.mark.parametrize("act", [0, 1])
+def test_glu(act):
+    from maester_b200.ops import cuda as C
+    x = torch.randn(300, 2 * 640, device="cuda", dtype=torch.bfloat16)
+    f = ref.geglu if act == 0 else ref.swiglu
+    assert _rel(C.glu_fwd(x, act), f(x.float())) < 4e-3
+    xf = x.float().requires_grad_()
+    d = torch.randn(300, 640, device="cuda", dtype=torch.bfloat16)
+    f(xf).backward(d.float())
+    assert _rel(C.glu_bwd(x, d, act), xf.grad) < 5e-3
+
+
+def test_embedding():
+    from maester_b200.ops import cuda as C
+    w = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16)
+    tok = torch.randint(0, 1000, (4, 50), device="cuda")
+    out = C.embedding_fwd(tok, w, 16.0)
+    assert torch.equal(out, ref.embedding(tok, w, 16.0))
+    d = torch.randn(4, 50, 256, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(1000, 256, device="cuda")
+    C.embedding_bwd(tok, d, dw, 16.0)
+    want = torch.zeros(1000, 256, device="cuda").index_add_(0, tok.reshape(-1), d.reshape(-1, 256).float() * 16.0)
+    assert _rel(dw, want) < 1e-5
+
+
+@pytest.mark.parametrize("V", [1000, 32003, 262208])
+def test_cross_entropy(V):
+    from maester_b200.ops import cuda as C
+    R = 64
+    logits = (torch.randn(R, V, device="cuda") * 3).to(torch.bfloat16)
+    labels = torch.randint(0, V, (R,), device="cuda")
+    labels[::7] = -100
+    lf = logits.float().requires_grad_()
+    want = torch.nn.functional.cross_entropy(lf, labels, ignore_index=-100, reduction="sum")
+    nvalid = (labels != -100).sum()
+    (want / nvalid).backward()
+    loss = torch.zeros(1, device="cuda")
+    gs = (1.0 / nvalid.float()).reshape(1)
+    lg = logits.clone()
+    C.ce_fwd_bwd(lg, labels, loss, gs)
+    assert abs(loss.item() - want.item()) / want.item() < 1e-4
+    assert _rel(lg, lf.grad) < 8e-3
+
+
+def test_adamw_flat():
+    from maester_b200.ops import cuda as C
+    from maester_b200.optimizers.adamw import build_chunk_table
+    n = 100_000
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    lp = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    segs = [(0, 60_000, 1.0, 0.1), (60_000, 40_000, 0.5, 0.0)]
+    chunks, tensors, nch = build_chunk_table(segs, "cuda")
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    lr = torch.tensor([1e-2], device="cuda")
+    for step in (1, 2):
+        C.adamw(p, g, m, v, lp, chunks, tensors, nch, lr, 0.9, 0.95, 1e-8, step)
+        for off, ln, lrm, wd in segs:
+            sl = slice(off, off + ln)
+            ref.adamw_step(pr[sl], g[sl], mr[sl], vr[sl], step, 1e-2 * lrm, 0.9, 0.95, 1e-8, wd)
+    assert _rel(p, pr) < 1e-5
+    assert _rel(lp, pr) < 4e-3
+
+
+def _attn_case(B, S, H, KV, hd, causal, window, docs):
+    from maester_b200.ops import cuda as C
+    from maester_b200.ops.functional import kv_block_lower_bounds
+    torch.manual_seed(2)
+    qkv = torch.randn(B, S, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
+    q = qkv[..., : H * hd].view(B, S, H, hd)
+    k = qkv[..., H * hd:(H + KV) * hd].view(B, S, KV, hd)
+    v = qkv[..., (H + KV) * hd:].view(B, S, KV, hd)
+    doc = None
+    if docs:
+        doc = torch.zeros(B, S, dtype=torch.int32, device="cuda")
+        for b in range(B):
+            cuts = sorted(torch.randint(1, S, (3,)).tolist())
+            for c in cuts:
+                doc[b, c:] += 1
+    scale = hd ** -0.5
+    lo = kv_block_lower_bounds(S, 128, window, doc, device="cuda", batch=B)
+    out, lse = C.attn_fwd(q, k, v, scale, causal, window, doc, lo)
+    C.check_status()
+    want, wlse = ref.attention(q, k, v, scale, causal, window, doc, return_lse=True)
+    assert _rel(out, want) < 1e-2, _rel(out, want)
+    assert (lse - wlse).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("hd", [64, 128, 256])
+@pytest.mark.parametrize("causal,window,docs", [(True, None, False), (True, 100, False), (True, None, True), (True, 64, True), (False, None, False)])
+def test_attention_fwd(hd, causal, window, docs):
+    _attn_case(2, 384, 4, 2, hd, causal, window, docs)
+
+
+def test_attention_fwd_ragged_len():
+    _attn_case(1, 200, 2, 1, 128, True, None, False)
+    _attn_case(1, 333, 2, 2, 256, True, 50, True)
