@@ -1,0 +1,678 @@
+// Attention backward on tcgen05, as three kernels:
+//   1. delta[b,h,q] = sum_d O[q,d] * dO[q,d]
+//   2. dQ kernel   : one CTA per 128 query rows of one (batch, q-head); loops over kv blocks of 64:
+//                    S = Q K^T and dP = dO V^T into TMEM, the softmax warps form
+//                    dS = P * (dP - delta) * scale (bf16, shared memory), then dQ += dS K.
+//   3. dK/dV kernel: one CTA per 128 kv rows of one (batch, kv-head[, half of the head dim when
+//                    head_dim = 256]); loops over the q-heads of the GQA group and over query tiles
+//                    of 64: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T to shared memory, then
+//                    dV += P^T dO and dK += dS^T Q.  The 256-wide head is split in two CTAs because
+//                    dK, dV, S^T and dP^T must share the 512 TMEM columns.
+// P is recomputed from the saved log-sum-exp.  Masks as in the forward kernel.
+// Gradients are written into one packed buffer [T, (H + 2 KV) * hd] (q heads, k heads, v heads).
+#include "host_common.cuh"
+#include "sm100.cuh"
+#include <math.h>
+
+namespace {
+using namespace mb;
+
+constexpr int BWD_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct BwdParams {
+  const float* lse;      // [B,H,S] natural log
+  const float* delta;    // [B,H,S]
+  __nv_bfloat16* dqkv;   // packed gradients
+  long long g_stride;    // row pitch of dqkv (elements)
+  const int* doc;        // [B,S] or null
+  const int* kv_lo_blk;  // [B, ceil(S/128)] or null   (dQ kernel)
+  const int* q_hi_blk;   // [B, ceil(S/128)] or null   (dK/dV kernel): exclusive upper bound on q
+  int B, S, H, KV;
+  int causal, window;
+  float scale, scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ bool is_masked(const BwdParams& p, const int* docb, int q, int kv, int dq, int dk) {
+  bool bad = (kv >= p.S) | (q >= p.S);
+  if (p.causal) bad |= kv > q;
+  if (p.window >= 0) bad |= (q - kv) > p.window;
+  if (docb) bad |= dq != dk;
+  return bad;
+}
+
+// ---------------------------------------------------------------------------------- delta
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                                        const __nv_bfloat16* __restrict__ dout,
+                                                        float* __restrict__ delta, int B, int S, int H, int hd) {
+  const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;  // (b, s, h)
+  const int lane = threadIdx.x & 31;
+  const long long items = static_cast<long long>(B) * S * H;
+  if (item >= items) return;
+  const __nv_bfloat16* op = o + item * hd;
+  const __nv_bfloat16* dp = dout + item * hd;
+  float acc = 0.f;
+  for (int c = lane * 2; c < hd; c += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + c));
+    float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + c));
+    acc += a.x * d.x + a.y * d.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) {
+    const int h = static_cast<int>(item % H);
+    const long long bs = item / H;
+    const int s = static_cast<int>(bs % S);
+    const int b = static_cast<int>(bs / S);
+    delta[(static_cast<long long>(b) * H + h) * S + s] = acc;
+  }
+}
+
+// write 32 consecutive bf16 values of row `row` starting at column col0 (multiple of 32) into a
+// K-major swizzled tile made of 64-column blocks of [rows_per_block x 128 B]
+__device__ __forceinline__ void store_row32(uint8_t* tile, int rows_per_block, int row, int col0, const float (&v)[32]) {
+  const int blk = col0 >> 6;
+  const int chunk0 = (col0 & 63) >> 3;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 o;
+    o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+    o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+    o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+    o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+    *reinterpret_cast<uint4*>(tile + blk * (rows_per_block * 128) + swz128(row, chunk0 + j)) = o;
+  }
+}
+
+// ---------------------------------------------------------------------------------- dQ kernel
+constexpr int BKV = 64;
+
+template <int HD, int NST>
+struct SmemDQ {
+  static constexpr int Q_BYTES = 128 * HD * 2;
+  static constexpr int KV_BYTES = BKV * HD * 2;
+  static constexpr int DS_BYTES = 128 * BKV * 2;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_DO = Q_BYTES;
+  static constexpr int OFF_K = 2 * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + NST * KV_BYTES;
+  static constexpr int OFF_DS = OFF_V + NST * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_DS + 2 * DS_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+template <int HD, int NST>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                   const BwdParams p) {
+  using L = SmemDQ<HD, NST>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* qdo_full = bars;       // 1
+  uint64_t* kv_full = bars + 1;    // [2]
+  uint64_t* kv_empty = bars + 3;   // [2]
+  uint64_t* sdp_full = bars + 5;   // [2]
+  uint64_t* sdp_empty = bars + 7;  // [2]
+  uint64_t* ds_full = bars + 9;    // [2]
+  uint64_t* ds_empty = bars + 11;  // [2]
+  uint64_t* dq_done = bars + 13;   // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.S + 127) / 128;
+  const int qb = nqb - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int kvh = h / (p.H / p.KV);
+  const int q0 = qb * 128;
+  const int kv_end = p.causal ? min(p.S, q0 + 128) : p.S;
+  int kv_begin = 0;
+  if (p.kv_lo_blk) kv_begin = p.kv_lo_blk[b * nqb + qb];
+  else if (p.window >= 0) kv_begin = max(0, q0 - p.window);
+  const int jb = kv_begin / BKV, je = (kv_end + BKV - 1) / BKV;
+  const int nblk = je - jb;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
+    mbar_init(qdo_full, 1);
+    mbar_init(dq_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&sdp_empty[i], 128);
+      mbar_init(&ds_full[i], 128);
+      mbar_init(&ds_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_dq = tmem_base;
+  const uint32_t tmem_s = tmem_base + 256;            // 2 x 64
+  const uint32_t tmem_dp = tmem_base + 256 + 2 * BKV; // 2 x 64
+
+  if (warp == 4) {
+    if (lane == 0 && nblk > 0) {
+      mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_4d(smem + L::OFF_Q + c * (128 * 128), &tmap_q, qdo_full, c * 64, h, q0, b);
+        tma_load_4d(smem + L::OFF_DO + c * (128 * 128), &tmap_do, qdo_full, c * 64, h, q0, b);
+      }
+      for (int n = 0; n < nblk; ++n) {
+        const int s = n % NST, use = n / NST;
+        if (!mbar_wait(&kv_empty[s], (use & 1) ^ 1)) {
+          atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
+          break;
+        }
+        mbar_expect_tx(&kv_full[s], 2 * L::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_4d(smem + L::OFF_K + s * L::KV_BYTES + c * (BKV * 128), &tmap_k, &kv_full[s], c * 64, kvh, (jb + n) * BKV, b);
+          tma_load_4d(smem + L::OFF_V + s * L::KV_BYTES + c * (BKV * 128), &tmap_v, &kv_full[s], c * 64, kvh, (jb + n) * BKV, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
+      const uint32_t sq = smem_u32(smem + L::OFF_Q), sdo = smem_u32(smem + L::OFF_DO);
+      bool ok = mbar_wait(qdo_full, 0);
+      auto issue_sdp = [&](int n) -> bool {
+        const int s = n % NST, use = n / NST, buf = n & 1;
+        if (!mbar_wait(&kv_full[s], use & 1)) return false;
+        if (!mbar_wait(&sdp_empty[buf], ((n >> 1) & 1) ^ 1)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::OFF_K + s * L::KV_BYTES);
+        const uint32_t sv = smem_u32(smem + L::OFF_V + s * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t blk = k >> 2, kk = k & 3;
+          umma_bf16_ss(tmem_s + buf * BKV, make_smem_desc(sq + blk * (128 * 128) + kk * 32, 16, 1024),
+                       make_smem_desc(sk + blk * (BKV * 128) + kk * 32, 16, 1024), idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t blk = k >> 2, kk = k & 3;
+          umma_bf16_ss(tmem_dp + buf * BKV, make_smem_desc(sdo + blk * (128 * 128) + kk * 32, 16, 1024),
+                       make_smem_desc(sv + blk * (BKV * 128) + kk * 32, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(&sdp_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int n = 0; n < nblk && ok; ++n) {
+        if (NST > 1 && n + 1 < nblk) ok = issue_sdp(n + 1);
+        if (!ok) break;
+        const int s = n % NST, buf = n & 1;
+        if (!mbar_wait(&ds_full[buf], (n >> 1) & 1)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sds = smem_u32(smem + L::OFF_DS + buf * L::DS_BYTES);
+        const uint32_t sk = smem_u32(smem + L::OFF_K + s * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKV / 16; ++k)
+          umma_bf16_ss(tmem_dq, make_smem_desc(sds + k * 32, 16, 1024),
+                       make_smem_desc(sk + k * 2048, BKV * 128, 1024), idesc_dq, (n | k) != 0);
+        umma_commit(&kv_empty[s]);
+        umma_commit(&ds_empty[buf]);
+        if (n == nblk - 1) umma_commit(dq_done);
+        if (NST == 1 && n + 1 < nblk) ok = issue_sdp(n + 1);
+      }
+      if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
+    }
+  } else {
+    const int row = warp * 32 + lane;
+    const int q = q0 + row;
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int* docb = p.doc ? p.doc + static_cast<long long>(b) * p.S : nullptr;
+    const int dq_doc = (docb && q < p.S) ? docb[q] : 0;
+    const long long stat_idx = (static_cast<long long>(b) * p.H + h) * p.S + q;
+    const float lse2 = (q < p.S) ? p.lse[stat_idx] * LOG2E : INFINITY;
+    const float delta = (q < p.S) ? p.delta[stat_idx] : 0.f;
+    bool ok = true;
+    for (int n = 0; n < nblk && ok; ++n) {
+      const int buf = n & 1;
+      const int kv0 = (jb + n) * BKV;
+      if (!mbar_wait(&sdp_full[buf], (n >> 1) & 1) || !mbar_wait(&ds_empty[buf], ((n >> 1) & 1) ^ 1)) {
+        atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint8_t* dsb = smem + L::OFF_DS + buf * L::DS_BYTES;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_s + buf * BKV + c * 32 + lane_sel, rs);
+        tmem_ld_32x32(tmem_dp + buf * BKV + c * 32 + lane_sel, rp);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int kv = kv0 + c * 32 + i;
+          const int dk = (docb && kv < p.S) ? docb[kv] : 0;
+          float pr = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2);
+          if (is_masked(p, docb, q, kv, dq_doc, dk)) pr = 0.f;
+          ds[i] = pr * (__uint_as_float(rp[i]) - delta) * p.scale;
+        }
+        store_row32(dsb, 128, row, c * 32, ds);
+      }
+      tc_fence_before();
+      mbar_arrive(&sdp_empty[buf]);
+      fence_proxy_async_smem();
+      mbar_arrive(&ds_full[buf]);
+    }
+    if (ok && nblk > 0 && !mbar_wait(dq_done, 0)) {
+      atomicCAS(p.status, 0, ERR_WAIT_ACC_FULL);
+      ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* grow = p.dqkv + (static_cast<long long>(b) * p.S + q) * p.g_stride + static_cast<long long>(h) * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        if (nblk > 0) {
+          tmem_ld_32x32(tmem_dq + c * 32 + lane_sel, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0;
+        }
+        if (q < p.S) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+            o.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+            o.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+            o.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+            reinterpret_cast<uint4*>(grow + c * 32)[j] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------- dK/dV kernel
+constexpr int BQ2 = 64;
+
+template <int HD, int NSTQ>
+struct SmemKV {
+  static constexpr int KV_BYTES = 128 * HD * 2;
+  static constexpr int Q_BYTES = BQ2 * HD * 2;
+  static constexpr int PT_BYTES = 128 * BQ2 * 2;
+  static constexpr int OFF_K = 0;
+  static constexpr int OFF_V = KV_BYTES;
+  static constexpr int OFF_Q = 2 * KV_BYTES;
+  static constexpr int OFF_DO = OFF_Q + NSTQ * Q_BYTES;
+  static constexpr int OFF_PT = OFF_DO + NSTQ * Q_BYTES;
+  static constexpr int OFF_DST = OFF_PT + NSTQ * PT_BYTES;
+  static constexpr int OFF_STAT = OFF_DST + NSTQ * PT_BYTES;  // [2][2][BQ2] floats
+  static constexpr int OFF_BAR = OFF_STAT + 2 * 2 * BQ2 * 4;
+  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+};
+
+template <int HD, int DV, int NSTQ>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                     const BwdParams p) {
+  using L = SmemKV<HD, NSTQ>;
+  constexpr int NSPLIT = HD / DV;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* kv_full = bars;         // 1
+  uint64_t* q_full = bars + 1;      // [2]
+  uint64_t* q_empty = bars + 3;     // [2]
+  uint64_t* sdp_full = bars + 5;    // [2]
+  uint64_t* sdp_empty = bars + 7;   // [2]
+  uint64_t* pt_full = bars + 9;     // [2]
+  uint64_t* pt_empty = bars + 11;   // [2]
+  uint64_t* acc_done = bars + 13;   // 1
+  uint64_t* stat_bar = bars + 14;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  float* stat = reinterpret_cast<float*>(smem + L::OFF_STAT);  // [buf][0: lse2, 1: delta][BQ2]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (p.S + 127) / 128;
+  const int kb = blockIdx.x;
+  const int kvh = blockIdx.y / NSPLIT, split = blockIdx.y % NSPLIT;
+  const int b = blockIdx.z;
+  const int G = p.H / p.KV;
+  const int kv0 = kb * 128;
+  const int dv0 = split * DV;
+  const int q_lo = p.causal ? kv0 : 0;
+  int q_hi = p.S;
+  if (p.q_hi_blk) q_hi = min(p.S, p.q_hi_blk[b * nkb + kb]);
+  else if (p.window >= 0) q_hi = min(p.S, kv0 + 128 + p.window);
+  const int ib = q_lo / BQ2, ie = (q_hi + BQ2 - 1) / BQ2;
+  const int ntile = max(0, ie - ib);
+  const int ntot = ntile * G;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_k);
+    prefetch_tmap(&tmap_v);
+    prefetch_tmap(&tmap_do);
+    mbar_init(kv_full, 1);
+    mbar_init(acc_done, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&sdp_full[i], 1);
+      mbar_init(&sdp_empty[i], 128);
+      mbar_init(&pt_full[i], 128);
+      mbar_init(&pt_empty[i], 1);
+      mbar_init(&stat_bar[i], 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_dk = tmem_base;          // DV <= 128 columns
+  const uint32_t tmem_dv = tmem_base + 128;
+  const uint32_t tmem_st = tmem_base + 256;    // 2 x 64
+  const uint32_t tmem_dpt = tmem_base + 384;   // 2 x 64
+
+  if (warp == 4) {
+    if (lane == 0 && ntot > 0) {
+      mbar_expect_tx(kv_full, 2 * L::KV_BYTES);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_4d(smem + L::OFF_K + c * (128 * 128), &tmap_k, kv_full, c * 64, kvh, kv0, b);
+        tma_load_4d(smem + L::OFF_V + c * (128 * 128), &tmap_v, kv_full, c * 64, kvh, kv0, b);
+      }
+      for (int n = 0; n < ntot; ++n) {
+        const int g = n / ntile, i = ib + n % ntile;
+        const int h = kvh * G + g;
+        const int s = n % NSTQ, use = n / NSTQ;
+        if (!mbar_wait(&q_empty[s], (use & 1) ^ 1)) {
+          atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
+          break;
+        }
+        mbar_expect_tx(&q_full[s], 2 * L::Q_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_4d(smem + L::OFF_Q + s * L::Q_BYTES + c * (BQ2 * 128), &tmap_q, &q_full[s], c * 64, h, i * BQ2, b);
+          tma_load_4d(smem + L::OFF_DO + s * L::Q_BYTES + c * (BQ2 * 128), &tmap_do, &q_full[s], c * 64, h, i * BQ2, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && ntot > 0) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, BQ2, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, DV, false, true);
+      const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V);
+      bool ok = mbar_wait(kv_full, 0);
+      auto issue_sdp = [&](int n) -> bool {
+        const int s = n % NSTQ, use = n / NSTQ, buf = n & 1;
+        if (!mbar_wait(&q_full[s], use & 1)) return false;
+        if (!mbar_wait(&sdp_empty[buf], ((n >> 1) & 1) ^ 1)) return false;
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::Q_BYTES);
+        const uint32_t sdo = smem_u32(smem + L::OFF_DO + s * L::Q_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t blk = k >> 2, kk = k & 3;
+          umma_bf16_ss(tmem_st + buf * BQ2, make_smem_desc(sk + blk * (128 * 128) + kk * 32, 16, 1024),
+                       make_smem_desc(sq + blk * (BQ2 * 128) + kk * 32, 16, 1024), idesc_st, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t blk = k >> 2, kk = k & 3;
+          umma_bf16_ss(tmem_dpt + buf * BQ2, make_smem_desc(sv + blk * (128 * 128) + kk * 32, 16, 1024),
+                       make_smem_desc(sdo + blk * (BQ2 * 128) + kk * 32, 16, 1024), idesc_st, k != 0);
+        }
+        umma_commit(&sdp_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int n = 0; n < ntot && ok; ++n) {
+        if (NSTQ > 1 && n + 1 < ntot) ok = issue_sdp(n + 1);
+        if (!ok) break;
+        const int s = n % NSTQ, pb = n % NSTQ;
+        if (!mbar_wait(&pt_full[pb], (n / NSTQ) & 1)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t spt = smem_u32(smem + L::OFF_PT + pb * L::PT_BYTES);
+        const uint32_t sdst = smem_u32(smem + L::OFF_DST + pb * L::PT_BYTES);
+        // B operands: the [BQ2 x DV] slice of dO / Q starting at channel dv0, MN-major
+        const uint32_t sdo = smem_u32(smem + L::OFF_DO + s * L::Q_BYTES) + (dv0 / 64) * (BQ2 * 128);
+        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::Q_BYTES) + (dv0 / 64) * (BQ2 * 128);
+#pragma unroll
+        for (int k = 0; k < BQ2 / 16; ++k)
+          umma_bf16_ss(tmem_dv, make_smem_desc(spt + k * 32, 16, 1024),
+                       make_smem_desc(sdo + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
+#pragma unroll
+        for (int k = 0; k < BQ2 / 16; ++k)
+          umma_bf16_ss(tmem_dk, make_smem_desc(sdst + k * 32, 16, 1024),
+                       make_smem_desc(sq + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
+        umma_commit(&q_empty[s]);
+        umma_commit(&pt_empty[pb]);
+        if (n == ntot - 1) umma_commit(acc_done);
+        if (NSTQ == 1 && n + 1 < ntot) ok = issue_sdp(n + 1);
+      }
+      if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
+    }
+  } else {
+    // one thread per kv row
+    const int row = warp * 32 + lane;
+    const int kv = kv0 + row;
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const int* docb = p.doc ? p.doc + static_cast<long long>(b) * p.S : nullptr;
+    const int dk_doc = (docb && kv < p.S) ? docb[kv] : 0;
+    bool ok = true;
+    for (int n = 0; n < ntot && ok; ++n) {
+      const int g = n / ntile, i = ib + n % ntile;
+      const int h = kvh * G + g;
+      const int buf = n & 1, pb = n % NSTQ;
+      const int q0 = i * BQ2;
+      // stage lse (log2 domain) and delta of this query tile in shared memory
+      {
+        const int t = threadIdx.x;  // 0..127
+        const int qq = q0 + (t & 63);
+        const long long idx = (static_cast<long long>(b) * p.H + h) * p.S + qq;
+        float val;
+        if (t < 64) val = (qq < p.S) ? p.lse[idx] * LOG2E : INFINITY;
+        else val = (qq < p.S) ? p.delta[idx] : 0.f;
+        stat[buf * 2 * BQ2 + (t >> 6) * BQ2 + (t & 63)] = val;
+      }
+      mbar_arrive(&stat_bar[buf]);
+      if (!mbar_wait(&stat_bar[buf], (n >> 1) & 1) || !mbar_wait(&sdp_full[buf], (n >> 1) & 1) || !mbar_wait(&pt_empty[pb], ((n / NSTQ) & 1) ^ 1)) {
+        atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint8_t* ptb = smem + L::OFF_PT + pb * L::PT_BYTES;
+      uint8_t* dstb = smem + L::OFF_DST + pb * L::PT_BYTES;
+      const float* lse_s = stat + buf * 2 * BQ2;
+      const float* del_s = lse_s + BQ2;
+#pragma unroll 1
+      for (int c = 0; c < BQ2 / 32; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tmem_st + buf * BQ2 + c * 32 + lane_sel, rs);
+        tmem_ld_32x32(tmem_dpt + buf * BQ2 + c * 32 + lane_sel, rp);
+        tmem_ld_wait();
+        float pv[32], ds[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int qq = q0 + c * 32 + j;
+          const int dq_doc = (docb && qq < p.S) ? docb[qq] : 0;
+          float pr = exp2f(__uint_as_float(rs[j]) * p.scale_log2 - lse_s[c * 32 + j]);
+          if (is_masked(p, docb, qq, kv, dq_doc, dk_doc)) pr = 0.f;
+          pv[j] = pr;
+          ds[j] = pr * (__uint_as_float(rp[j]) - del_s[c * 32 + j]) * p.scale;
+        }
+        store_row32(ptb, 128, row, c * 32, pv);
+        store_row32(dstb, 128, row, c * 32, ds);
+      }
+      tc_fence_before();
+      mbar_arrive(&sdp_empty[buf]);
+      fence_proxy_async_smem();
+      mbar_arrive(&pt_full[pb]);
+    }
+    if (ok && ntot > 0 && !mbar_wait(acc_done, 0)) {
+      atomicCAS(p.status, 0, ERR_WAIT_ACC_FULL);
+      ok = false;
+    }
+    if (ok) {
+      tc_fence_after();
+      __nv_bfloat16* base = p.dqkv + (static_cast<long long>(b) * p.S + kv) * p.g_stride;
+      __nv_bfloat16* dkrow = base + static_cast<long long>(p.H + kvh) * HD + dv0;
+      __nv_bfloat16* dvrow = base + static_cast<long long>(p.H + p.KV + kvh) * HD + dv0;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t src = which == 0 ? tmem_dk : tmem_dv;
+        __nv_bfloat16* dst = which == 0 ? dkrow : dvrow;
+#pragma unroll 1
+        for (int c = 0; c < DV / 32; ++c) {
+          uint32_t r[32];
+          if (ntot > 0) {
+            tmem_ld_32x32(src + c * 32 + lane_sel, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
+          if (kv < p.S) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(r[j * 8 + 0]), __uint_as_float(r[j * 8 + 1]));
+              o.y = pack_bf16(__uint_as_float(r[j * 8 + 2]), __uint_as_float(r[j * 8 + 3]));
+              o.z = pack_bf16(__uint_as_float(r[j * 8 + 4]), __uint_as_float(r[j * 8 + 5]));
+              o.w = pack_bf16(__uint_as_float(r[j * 8 + 6]), __uint_as_float(r[j * 8 + 7]));
+              reinterpret_cast<uint4*>(dst + c * 32)[j] = o;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+int make_maps(CUtensorMap* tq, CUtensorMap* tk, CUtensorMap* tv, CUtensorMap* tdo, const void* q, const void* k,
+              const void* v, const void* dout, int B, int S, int H, int KV, int HD, long long qs, long long ks,
+              long long vs, uint32_t q_rows, uint32_t kv_rows) {
+  const uint64_t dq[4] = {(uint64_t)HD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  const uint64_t sq[3] = {(uint64_t)HD, (uint64_t)qs, (uint64_t)qs * S};
+  const uint64_t sdo[3] = {(uint64_t)HD, (uint64_t)H * HD, (uint64_t)H * HD * S};
+  const uint32_t bq[4] = {64, 1, q_rows, 1};
+  const uint64_t dk[4] = {(uint64_t)HD, (uint64_t)KV, (uint64_t)S, (uint64_t)B};
+  const uint64_t sk[3] = {(uint64_t)HD, (uint64_t)ks, (uint64_t)ks * S};
+  const uint64_t sv[3] = {(uint64_t)HD, (uint64_t)vs, (uint64_t)vs * S};
+  const uint32_t bk[4] = {64, 1, kv_rows, 1};
+  if (mbh::make_tmap_bf16_nd(tq, q, 4, dq, sq, bq)) return -2;
+  if (mbh::make_tmap_bf16_nd(tdo, dout, 4, dq, sdo, bq)) return -2;
+  if (mbh::make_tmap_bf16_nd(tk, k, 4, dk, sk, bk)) return -2;
+  if (mbh::make_tmap_bf16_nd(tv, v, 4, dk, sv, bk)) return -2;
+  return 0;
+}
+
+template <int HD, int NST, int DV, int NSTQ>
+int launch_bwd(const void* q, const void* k, const void* v, const void* dout, const BwdParams& p, long long qs,
+               long long ks, long long vs, cudaStream_t st) {
+  CUtensorMap tq, tk, tv, tdo;
+  // ---- dQ
+  if (make_maps(&tq, &tk, &tv, &tdo, q, k, v, dout, p.B, p.S, p.H, p.KV, HD, qs, ks, vs, 128, BKV)) return -2;
+  using LQ = SmemDQ<HD, NST>;
+  static bool attr1 = false;
+  if (!attr1) {
+    cudaFuncSetAttribute(attn_bwd_dq_kernel<HD, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, LQ::TOTAL);
+    attr1 = true;
+  }
+  dim3 g1((p.S + 127) / 128, p.H, p.B);
+  attn_bwd_dq_kernel<HD, NST><<<g1, BWD_THREADS, LQ::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  int e = mbh::check_launch("attn_bwd_dq");
+  if (e) return e;
+  // ---- dK/dV
+  if (make_maps(&tq, &tk, &tv, &tdo, q, k, v, dout, p.B, p.S, p.H, p.KV, HD, qs, ks, vs, BQ2, 128)) return -2;
+  using LK = SmemKV<HD, NSTQ>;
+  static bool attr2 = false;
+  if (!attr2) {
+    cudaFuncSetAttribute(attn_bwd_dkdv_kernel<HD, DV, NSTQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, LK::TOTAL);
+    attr2 = true;
+  }
+  dim3 g2((p.S + 127) / 128, p.KV * (HD / DV), p.B);
+  attn_bwd_dkdv_kernel<HD, DV, NSTQ><<<g2, BWD_THREADS, LK::TOTAL, st>>>(tq, tk, tv, tdo, p);
+  return mbh::check_launch("attn_bwd_dkdv");
+}
+
+}  // namespace
+
+// q,k (after norm/rope) and v as in mb_attn_fwd; out/dout: [B,S,H,hd] contiguous; lse: [B,H,S];
+// delta_ws: fp32 [B,H,S] scratch; dqkv: packed gradient buffer with row pitch g_stride.
+extern "C" int mb_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                           const float* lse, float* delta_ws, void* dqkv, const int* doc, const int* kv_lo_blk,
+                           const int* q_hi_blk, int B, int S, int H, int KV, int hd, long long q_tok_stride,
+                           long long k_tok_stride, long long v_tok_stride, long long g_stride, int causal,
+                           int window, float scale, cudaStream_t st) {
+  BwdParams p;
+  p.lse = lse;
+  p.delta = delta_ws;
+  p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  p.g_stride = g_stride;
+  p.doc = doc;
+  p.kv_lo_blk = kv_lo_blk;
+  p.q_hi_blk = q_hi_blk;
+  p.B = B;
+  p.S = S;
+  p.H = H;
+  p.KV = KV;
+  p.causal = causal;
+  p.window = window;
+  p.scale = scale;
+  p.scale_log2 = scale * LOG2E;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  if ((q_tok_stride & 7) || (k_tok_stride & 7) || (v_tok_stride & 7) || (g_stride & 7)) return -3;
+  const long long items = static_cast<long long>(B) * S * H;
+  attn_delta_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta_ws, B, S, H, hd);
+  int e = mbh::check_launch("attn_delta");
+  if (e) return e;
+  if (hd == 256) return launch_bwd<256, 1, 128, 1>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
+  if (hd == 128) return launch_bwd<128, 2, 128, 2>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
+  if (hd == 64) return launch_bwd<64, 2, 64, 2>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
+  return -3;
+}

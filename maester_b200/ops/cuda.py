@@ -218,3 +218,16 @@ def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, ca
                                int(causal), -1 if window is None or window <= 0 else int(window), float(scale),
                                _stream()), "attn_fwd")
     return out, lse
+
+
+def attn_bwd(q, k, v, out, dout, lse, dqkv, scale, causal, window, doc, kv_lo_blk, q_hi_blk=None) -> None:
+    """Fills ``dqkv`` [B*S, (H+2KV)*hd] with the gradients of q, k (post norm/rope) and v."""
+    B, S, H, hd = q.shape
+    KV = k.shape[2]
+    assert out.is_contiguous() and dout.is_contiguous() and dqkv.stride(1) == 1
+    delta = torch.empty(B, H, S, device=q.device, dtype=torch.float32)
+    _ck(_lib.lib().mb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
+                               lse.data_ptr(), delta.data_ptr(), dqkv.data_ptr(), _ptr(doc), _ptr(kv_lo_blk),
+                               _ptr(q_hi_blk), B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
+                               dqkv.stride(0), int(causal), -1 if window is None or window <= 0 else int(window),
+                               float(scale), _stream()), "attn_bwd")

@@ -187,6 +187,32 @@ def kv_block_lower_bounds(S: int, block_q: int, window: int | None, doc: torch.T
     return start.view(start.shape[0], nqb, block_q).amin(dim=2).to(torch.int32).contiguous()
 
 
+def q_block_upper_bounds(S: int, block_kv: int, window: int | None, doc: torch.Tensor | None, device,
+                         batch: int = 1) -> torch.Tensor | None:
+    """Per (batch, kv block) exclusive upper bound on the query index that may attend to the block:
+    ``min(end of the kv row's document, kv + window + 1)`` maximised over the block's rows."""
+    if doc is None and (window is None or window <= 0):
+        return None
+    idx = torch.arange(S, device=device, dtype=torch.int32)
+    if doc is not None:
+        d = doc.to(torch.int32)
+        change = torch.zeros_like(d, dtype=torch.bool)
+        change[:, 1:] = d[:, 1:] != d[:, :-1]
+        nxt = torch.where(change, idx[None], torch.full_like(d, S))
+        # end[kv] = smallest run start strictly after kv
+        suffix = nxt.flip(1).cummin(dim=1).values.flip(1)
+        end = torch.cat([suffix[:, 1:], torch.full_like(suffix[:, :1], S)], dim=1)
+    else:
+        end = torch.full((batch, S), S, device=device, dtype=torch.int32)
+    if window is not None and window > 0:
+        end = torch.minimum(end, (idx + window + 1).clamp_max(S)[None].expand_as(end))
+    nkb = (S + block_kv - 1) // block_kv
+    pad = nkb * block_kv - S
+    if pad:
+        end = torch.nn.functional.pad(end, (0, pad), value=0)
+    return end.view(end.shape[0], nkb, block_kv).amax(dim=2).to(torch.int32).contiguous()
+
+
 def rope_table(inv_freq: torch.Tensor, max_pos: int, attn_factor: float = 1.0) -> torch.Tensor:
     """[max_pos, rot/2, 2] fp32 (cos, sin) table gathered by position id inside the kernels."""
     ang = torch.arange(max_pos, device=inv_freq.device, dtype=torch.float32)[:, None] * inv_freq.float()[None]
@@ -228,7 +254,9 @@ class _AttnBlock(Function):
         k = qk[:, H * hd:(H + KV) * hd].view(B, S, KV, hd)
         v = qkv2[:, (H + KV) * hd:].view(B, S, KV, hd)
         dqkv = torch.empty(B * S, (H + 2 * KV) * hd, device=dout.device, dtype=dout.dtype)
-        C.attn_bwd(q, k, v, out, dout.reshape(B, S, H, hd).contiguous(), lse, dqkv, scale, causal, window, doc32, lo)
+        hi = q_block_upper_bounds(S, 128, window, doc32, dout.device, batch=B)
+        C.attn_bwd(q, k, v, out, dout.reshape(B, S, H, hd).contiguous(), lse, dqkv, scale, causal, window, doc32,
+                   lo, hi)
         dqw = dkw = None
         if need_qk:
             mq = getattr(qw, "main_grad", None) if qw is not None else None

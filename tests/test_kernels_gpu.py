@@ -139,7 +139,8 @@ def test_embedding():
 def test_cross_entropy(V):
     from maester_b200.ops import cuda as C
     R = 64
-    logits = (torch.randn(R, V, device="cuda") * 3).to(torch.bfloat16)
+    pitch = (V + 7) // 8 * 8  # the kernel needs a row pitch that is a multiple of 8 elements
+    logits = (torch.randn(R, pitch, device="cuda") * 3).to(torch.bfloat16)[:, :V]
     labels = torch.randint(0, V, (R,), device="cuda")
     labels[::7] = -100
     lf = logits.float().requires_grad_()
@@ -148,7 +149,8 @@ def test_cross_entropy(V):
     (want / nvalid).backward()
     loss = torch.zeros(1, device="cuda")
     gs = (1.0 / nvalid.float()).reshape(1)
-    lg = logits.clone()
+    lg = torch.empty(R, pitch, device="cuda", dtype=torch.bfloat16)[:, :V]
+    lg.copy_(logits)
     C.ce_fwd_bwd(lg, labels, loss, gs)
     assert abs(loss.item() - want.item()) / want.item() < 1e-4
     assert _rel(lg, lf.grad) < 8e-3
@@ -209,3 +211,103 @@ def test_attention_fwd(hd, causal, window, docs):
 def test_attention_fwd_ragged_len():
     _attn_case(1, 200, 2, 1, 128, True, None, False)
     _attn_case(1, 333, 2, 2, 256, True, 50, True)
+
+
+def _attn_bwd_case(B, S, H, KV, hd, causal, window, docs):
+    from maester_b200.ops.functional import attention_block
+    torch.manual_seed(3)
+    qkv = (torch.randn(B, S, (H + 2 * KV) * hd, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    doc = None
+    if docs:
+        doc = torch.zeros(B, S, dtype=torch.int32, device="cuda")
+        for b in range(B):
+            for c in sorted(torch.randint(1, S, (3,)).tolist()):
+                doc[b, c:] += 1
+    scale = hd ** -0.5
+    out = attention_block(qkv, None, None, None, None, None, doc, H, KV, hd, scale=scale, causal=causal, window=window)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qf = qkv.detach().float().requires_grad_()
+    want = attention_block(qf, None, None, None, None, None, doc, H, KV, hd, scale=scale, causal=causal, window=window)
+    want.backward(g.float())
+    assert _rel(out, want) < 1e-2
+    for name, sl in (("dq", slice(0, H * hd)), ("dk", slice(H * hd, (H + KV) * hd)), ("dv", slice((H + KV) * hd, None))):
+        r = _rel(qkv.grad[..., sl], qf.grad[..., sl])
+        assert r < 2e-2, (name, r)
+
+
+@pytest.mark.parametrize("hd", [64, 128, 256])
+@pytest.mark.parametrize("causal,window,docs", [(True, None, False), (True, 100, False), (True, 64, True), (False, None, False)])
+def test_attention_bwd(hd, causal, window, docs):
+    _attn_bwd_case(2, 384, 4, 2, hd, causal, window, docs)
+
+
+def test_attention_bwd_ragged():
+    _attn_bwd_case(1, 200, 4, 1, 128, True, None, True)
+    _attn_bwd_case(1, 333, 2, 2, 256, True, 50, True)
+
+
+def test_attention_block_norm_rope_grads():
+    from maester_b200.ops.functional import attention_block, rope_table
+    torch.manual_seed(4)
+    B, S, H, KV, hd = 2, 256, 4, 2, 256
+    qkv = (torch.randn(B, S, (H + 2 * KV) * hd, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    qw = (torch.randn(hd, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_()
+    kw = (torch.randn(hd, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_()
+    inv = ref.rope_inv_freq(hd, 10000.0, device="cuda")
+    cs = rope_table(inv, 1024)
+    pos = torch.arange(S, device="cuda")[None].expand(B, S).contiguous()
+    out = attention_block(qkv, qw, kw, pos, inv, cs, None, H, KV, hd, unit_offset=True, window=64)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qf, qwf, kwf = (t.detach().float().requires_grad_() for t in (qkv, qw, kw))
+    want = attention_block(qf, qwf, kwf, pos, inv, None, None, H, KV, hd, unit_offset=True, window=64)
+    want.backward(g.float())
+    assert _rel(out, want) < 1.5e-2
+    assert _rel(qkv.grad, qf.grad) < 3e-2
+    assert _rel(qw.grad, qwf.grad) < 3e-2
+    assert _rel(kw.grad, kwf.grad) < 3e-2
+
+
+def test_linear_autograd_and_main_grad():
+    from maester_b200.ops.functional import linear
+    x = torch.randn(4, 100, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(384, 256, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    y = linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    (xf @ wf.T).backward(g.float())
+    assert _rel(y, xf @ wf.T) < 5e-3
+    assert _rel(x.grad, xf.grad) < 5e-3
+    assert _rel(w.grad, wf.grad) < 5e-3
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.zeros(384, 256, device="cuda")
+    for _ in range(2):
+        linear(x.detach(), w2).backward(g)
+    assert w2.grad is None
+    assert _rel(w2.main_grad, 2 * wf.grad) < 5e-3
+
+
+def test_linear_cross_entropy_fused():
+    from maester_b200.ops.functional import linear_cross_entropy
+    import maester_b200.ops.functional as Fm
+    torch.manual_seed(5)
+    M, D, V = 700, 256, 5000
+    h = torch.randn(M, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(V, D, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, V, (M,), device="cuda")
+    labels[::5] = -100
+    old = Fm.CE_CHUNK_ROWS
+    Fm.CE_CHUNK_ROWS = 256
+    try:
+        loss = linear_cross_entropy(h, w, labels)
+        (loss * 0.5).backward()
+    finally:
+        Fm.CE_CHUNK_ROWS = old
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    want = ref.linear_cross_entropy(hf, wf, labels)
+    (want * 0.5).backward()
+    assert abs(loss.item() - want.item()) < 2e-2
+    assert _rel(h.grad, hf.grad) < 2e-2
+    assert _rel(w.grad, wf.grad) < 2e-2
