@@ -57,13 +57,14 @@ class FusedWeight:
     place.  Otherwise it is ``torch.cat`` of the parameters (ordinary autograd).
     """
 
-    def __init__(self, params: list[nn.Parameter]):
-        self.params = params
+    def __init__(self, owners: list[nn.Module], attr: str = "weight"):
+        # modules, not Parameters: the sharding runtime replaces Parameter objects after construction
+        self.owners, self.attr = owners, attr
         self._view = None
         self._key = None
 
     def get(self) -> torch.Tensor:
-        ps = self.params
+        ps = [getattr(m, self.attr) for m in self.owners]
         grads = [getattr(p, "main_grad", None) for p in ps]
         flat_ok = all(g is not None for g in grads) and all(
             _adjacent(ps[i].data, ps[i + 1].data) and _adjacent(grads[i], grads[i + 1]) for i in range(len(ps) - 1)

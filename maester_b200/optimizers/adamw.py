@@ -47,7 +47,8 @@ class FusedAdamW(Optimizer):
         super().__init__(params, defaults)
         self._flat = None  # set by attach_flat()
 
-    def attach_flat(self, master: torch.Tensor, grad: torch.Tensor, lowp: torch.Tensor | None, segments_by_param):
+    def attach_flat(self, master: torch.Tensor, grad: torch.Tensor, lowp: torch.Tensor | None, segments_by_param,
+                    m: torch.Tensor | None = None, v: torch.Tensor | None = None):
         """Register the flat layout: ``segments_by_param`` maps each parameter to (offset, numel).
 
         master / grad are fp32 flat buffers of equal length, lowp the bf16 buffer that receives the
@@ -55,7 +56,8 @@ class FusedAdamW(Optimizer):
         flat buffers so that checkpoints keep the per-parameter layout.
         """
         self._flat = dict(master=master, grad=grad, lowp=lowp, seg=segments_by_param,
-                          m=torch.zeros_like(master), v=torch.zeros_like(master), table=None)
+                          m=m if m is not None else torch.zeros_like(master),
+                          v=v if v is not None else torch.zeros_like(master), table=None)
         for group in self.param_groups:
             for p in group["params"]:
                 off, n = segments_by_param[p]

@@ -1,0 +1,347 @@
+"""Sharded data parallelism over flat buffers ("FSDP" of this framework).
+
+The reference wraps every transformer block and the root with PyTorch FSDP2 ``fully_shard``
+(maester/parallelisms/parallelize_llama.py:265-286, parallelize_gemma.py:268-289): bf16 parameters
+are all-gathered per block, gradients reduce-scattered in fp32 and divided by the data-parallel
+size, fp32 master shards feed the optimizer.  This runtime keeps those semantics (dim-0 sharding
+per parameter, bf16 compute / fp32 reduce / fp32 master and optimizer state, per-block units,
+gradient-sync toggle for accumulation) with a layout chosen for 180 GB GPUs:
+
+* every parameter of the model is a view into one flat ``full`` buffer in the compute dtype; fused
+  projections (qkv, gate/up) are single GEMMs over adjacent views;
+* weight gradients accumulate in fp32 straight from the GEMM epilogues into ``main_grad`` views of a
+  flat gradient buffer, so there is no per-parameter ``.grad`` allocation, cast or copy;
+* each rank owns rows ``[r*c, (r+1)*c)`` of every parameter (``c = ceil(dim0 / world)``) in flat fp32
+  ``master`` / ``grad`` shards, which is the shard geometry DCP expects for ``Shard(0)`` DTensors;
+* the full bf16 model stays resident between steps (it is 2 bytes/param), so a step needs ONE
+  all-gather of the updated shards (issued per unit on a side stream right after the optimizer
+  step, consumed by forward pre-hooks) and ONE reduce-scatter per unit, launched from backward hooks
+  so it overlaps the backward of the preceding unit.
+
+With one rank the shard and full buffers coincide and no communication code runs.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from maester_b200.log_utils import logger
+
+
+@dataclass
+class ParamSlot:
+    fqn: str
+    param: nn.Parameter          # compute-dtype view into `full`
+    shape: torch.Size
+    rows: int                    # dim 0 (1 for scalars)
+    row_numel: int
+    chunk_rows: int              # rows owned per rank (ceil)
+    full_off: int = 0            # offset into the flat full buffer (padded rows included)
+    shard_off: int = 0           # offset into the flat shard buffers
+    master: nn.Parameter | None = None  # fp32 shard view given to the optimizer
+
+    @property
+    def padded_numel(self) -> int:
+        return self.chunk_rows * self.row_numel
+
+
+@dataclass
+class Unit:
+    name: str
+    module: nn.Module
+    slots: list[ParamSlot] = field(default_factory=list)
+    full_lo: int = 0
+    full_hi: int = 0
+    shard_lo: int = 0
+    shard_hi: int = 0
+    gather_event: torch.cuda.Event | None = None
+    gathered: bool = True
+    grads_pending: bool = False
+
+
+def _ordered_params(module: nn.Module, prefix: str, seen: set, skip_modules: set):
+    """(fqn, param) in registration order, except that a module may pin the order of its direct
+    children with ``fused_param_order`` so that fused projections are adjacent in memory."""
+    out = []
+    for n, p in module.named_parameters(recurse=False):
+        if p is not None and id(p) not in seen:
+            seen.add(id(p))
+            out.append((f"{prefix}{n}", p))
+    children = dict(module.named_children())
+    order = list(getattr(module, "fused_param_order", ())) + [c for c in children if c not in getattr(module, "fused_param_order", ())]
+    for cname in order:
+        child = children[cname]
+        if child in skip_modules:
+            continue
+        out.extend(_ordered_params(child, f"{prefix}{cname}.", seen, skip_modules))
+    return out
+
+
+class ShardedModel:
+    """Owns the flat buffers of ``model`` and the collectives that keep them consistent."""
+
+    def __init__(self, model: nn.Module, unit_modules: list[tuple[str, nn.Module]], *, device: torch.device,
+                 param_dtype: torch.dtype = torch.bfloat16, reduce_dtype: torch.dtype = torch.float32,
+                 shard_group=None, replicate_group=None, gradient_divide_factor: float | None = None):
+        self.model = model
+        self.device = device
+        self.param_dtype, self.reduce_dtype = param_dtype, reduce_dtype
+        self.group = shard_group
+        self.replicate_group = replicate_group
+        self.world = dist.get_world_size(shard_group) if (shard_group is not None and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(shard_group) if self.world > 1 else 0
+        self.rep_world = dist.get_world_size(replicate_group) if replicate_group is not None else 1
+        self.divide = gradient_divide_factor or float(self.world * self.rep_world)
+        self.require_sync = True
+        self.lowp_fresh = False
+        self._use_cuda = device.type == "cuda"
+        self.comm_stream = torch.cuda.Stream(device) if (self._use_cuda and self.world * self.rep_world > 1) else None
+
+        # ---- units: listed blocks first, everything left over forms the root unit
+        seen: set = set()
+        block_mods = {m for _, m in unit_modules}
+        self.units: list[Unit] = []
+        prefix_of = {m: n for n, m in model.named_modules()}
+        for name, mod in unit_modules:
+            u = Unit(name, mod)
+            for fqn, p in _ordered_params(mod, prefix_of[mod] + ".", seen, set()):
+                u.slots.append(self._slot(fqn, p))
+            self.units.append(u)
+        root = Unit("root", model)
+        for fqn, p in _ordered_params(model, "", seen, block_mods):
+            root.slots.append(self._slot(fqn, p))
+        self.units.append(root)
+        self.root = root
+
+        # ---- offsets (each parameter start is aligned to 256 elements: 16-byte TMA alignment for
+        #      any dtype and whole 1 KiB lines for the optimizer kernel)
+        def align(x: int) -> int:
+            return (x + 255) // 256 * 256
+
+        f = s = 0
+        for u in self.units:
+            u.full_lo, u.shard_lo = f, s
+            for sl in u.slots:
+                sl.full_off, sl.shard_off = f, s
+                f = align(f + sl.padded_numel * self.world)
+                s = align(s + sl.padded_numel)
+            u.full_hi, u.shard_hi = f, s
+        self.full_numel, self.shard_numel = f, s
+
+        # ---- buffers
+        self.full = torch.zeros(f, dtype=param_dtype, device=device)
+        self.master = torch.zeros(s, dtype=torch.float32, device=device)
+        self.shard_grad = torch.zeros(s, dtype=torch.float32, device=device)
+        if self.world > 1:
+            self.full_grad = torch.zeros(f, dtype=torch.float32, device=device)
+            self.shard_lp = torch.zeros(s, dtype=param_dtype, device=device)
+        else:
+            self.full_grad = self.shard_grad  # identical geometry with one rank
+            self.shard_lp = self.full
+        self._rebind_parameters()
+        self._install_hooks()
+        logger.info(
+            f"ShardedModel: {sum(len(u.slots) for u in self.units)} params in {len(self.units)} units, "
+            f"full={f * self.full.element_size() / 2**30:.2f} GiB {param_dtype}, "
+            f"shard={s * 4 / 2**30:.2f} GiB fp32 x3 (master, grad + optimizer state), world={self.world}"
+        )
+
+    # ------------------------------------------------------------------ construction helpers
+    def _slot(self, fqn: str, p: nn.Parameter) -> ParamSlot:
+        shape = p.shape
+        rows = shape[0] if p.dim() > 0 else 1
+        row_numel = int(math.prod(shape[1:])) if p.dim() > 1 else 1
+        chunk = (rows + self.world - 1) // self.world
+        return ParamSlot(fqn, p, shape, rows, row_numel, chunk)
+
+    def _rebind_parameters(self) -> None:
+        """Point every model parameter at its view of ``full`` and create the fp32 master shards."""
+        for u in self.units:
+            for sl in u.slots:
+                n = sl.rows * sl.row_numel
+                view = self.full[sl.full_off: sl.full_off + n].view(sl.shape)
+                gview = self.full_grad[sl.full_off: sl.full_off + n].view(sl.shape)
+                new = nn.Parameter(view, requires_grad=sl.param.requires_grad)
+                new.main_grad = gview
+                self._replace_param(sl.param, new)
+                sl.param = new
+                lo, hi = self._own_rows(sl)
+                m = self.master[sl.shard_off: sl.shard_off + (hi - lo) * sl.row_numel]
+                g = self.shard_grad[sl.shard_off: sl.shard_off + (hi - lo) * sl.row_numel]
+                shard_shape = (hi - lo, *sl.shape[1:]) if len(sl.shape) > 0 else ()
+                mp = nn.Parameter(m.view(shard_shape), requires_grad=True)
+                mp.grad = g.view(shard_shape)
+                mp.fqn = sl.fqn
+                sl.master = mp
+
+    def _replace_param(self, old: nn.Parameter, new: nn.Parameter) -> None:
+        """Swap a Parameter object everywhere it is registered (tied weights appear more than once)."""
+        for mod in self.model.modules():
+            for k, v in list(mod._parameters.items()):
+                if v is old:
+                    mod._parameters[k] = new
+
+    def _own_rows(self, sl: ParamSlot) -> tuple[int, int]:
+        lo = min(sl.rows, self.rank * sl.chunk_rows)
+        hi = min(sl.rows, lo + sl.chunk_rows)
+        return lo, hi
+
+    # ------------------------------------------------------------------ views for the optimizer / checkpoint
+    def named_master_parameters(self):
+        for u in self.units:
+            for sl in u.slots:
+                yield sl.fqn, sl.master
+
+    def slot_of(self, master: nn.Parameter) -> ParamSlot:
+        if not hasattr(self, "_by_master"):
+            self._by_master = {id(sl.master): sl for u in self.units for sl in u.slots}
+        return self._by_master[id(master)]
+
+    def flat_segments(self):
+        """{master parameter: (offset, numel)} into the flat shard buffers (for the fused optimizer)."""
+        return {sl.master: (sl.shard_off, sl.master.numel()) for u in self.units for sl in u.slots}
+
+    # ------------------------------------------------------------------ initialisation
+    @torch.no_grad()
+    def init_master_from_full(self) -> None:
+        """After ``model.init_weights()`` filled the compute-dtype parameters: broadcast rank 0's
+        values (so all ranks agree) and load this rank's rows into the fp32 master shards."""
+        if self.world * self.rep_world > 1:
+            dist.broadcast(self.full, src=0)  # default group spans shard x replicate
+        for u in self.units:
+            for sl in u.slots:
+                lo, hi = self._own_rows(sl)
+                if hi > lo:
+                    src = sl.param.data.reshape(sl.rows, -1)[lo:hi]
+                    sl.master.data.view(hi - lo, -1).copy_(src)
+        self.lowp_fresh = True
+
+    # ------------------------------------------------------------------ hooks
+    def _install_hooks(self) -> None:
+        if self.world * self.rep_world == 1:
+            return
+        for i, u in enumerate(self.units[:-1]):
+            u.module.register_forward_pre_hook(lambda m, a, u=u: self._wait_gather(u))
+            u.module.register_full_backward_pre_hook(lambda m, g, i=i: self._on_backward_reach(i))
+        self.model.register_forward_pre_hook(lambda m, a: (self._wait_gather(self.root), self.mark_backward_start()))
+
+    def _wait_gather(self, u: Unit) -> None:
+        if u.gather_event is not None:
+            torch.cuda.current_stream().wait_event(u.gather_event) if self._use_cuda else None
+            u.gather_event = None
+
+    def _on_backward_reach(self, i: int) -> None:
+        # backward has reached unit i, so unit i+1 (the one after it in forward order) is complete
+        if i + 1 < len(self.units) - 1:
+            self._reduce_unit(self.units[i + 1])
+
+    # ------------------------------------------------------------------ collectives
+    def set_requires_gradient_sync(self, flag: bool) -> None:
+        self.require_sync = flag
+
+    def mark_backward_start(self) -> None:
+        for u in self.units:
+            u.grads_pending = True
+
+    @torch.no_grad()
+    def _reduce_unit(self, u: Unit) -> None:
+        """Reduce-scatter (and replicate all-reduce) of one unit's accumulated fp32 gradients."""
+        if not u.grads_pending or not self.require_sync:
+            return
+        u.grads_pending = False
+        if self.world * self.rep_world == 1:
+            return
+        stream = self.comm_stream
+        if stream is not None:
+            stream.wait_stream(torch.cuda.current_stream())
+        ctx = torch.cuda.stream(stream) if stream is not None else _null()
+        with ctx:
+            shard = self.shard_grad[u.shard_lo:u.shard_hi]
+            if self.world > 1:
+                # pack rank-major: [rank][slot] so that the scatter leaves each rank its own rows
+                n_shard = u.shard_hi - u.shard_lo
+                send = torch.empty(self.world * n_shard, dtype=self.reduce_dtype, device=self.device)
+                sv = send.view(self.world, n_shard)
+                for sl in u.slots:
+                    src = self.full_grad[sl.full_off: sl.full_off + sl.padded_numel * self.world]
+                    sv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel].copy_(
+                        src.view(self.world, sl.padded_numel))
+                    src.zero_()
+                out = shard if self.reduce_dtype == torch.float32 else torch.empty(n_shard, dtype=self.reduce_dtype, device=self.device)
+                dist.reduce_scatter_tensor(out, send, op=dist.ReduceOp.SUM, group=self.group)
+                if out is not shard:
+                    shard.copy_(out)
+            if self.rep_world > 1:
+                dist.all_reduce(shard, op=dist.ReduceOp.SUM, group=self.replicate_group)
+            shard.mul_(1.0 / self.divide)
+
+    @torch.no_grad()
+    def collect_autograd_grads(self) -> None:
+        """Fold gradients that ordinary autograd left in ``param.grad`` (ops running on their
+        plain-PyTorch path) into the flat fp32 accumulation buffer, then drop them."""
+        for u in self.units:
+            for sl in u.slots:
+                g = sl.param.grad
+                if g is not None:
+                    sl.param.main_grad.add_(g.to(torch.float32))
+                    sl.param.grad = None
+
+    def finish_backward(self) -> None:
+        """Call after ``loss.backward()``: reduces the units whose hooks cannot fire (first block, root)
+        and makes the compute stream wait for all reductions."""
+        self.collect_autograd_grads()
+        for u in self.units:
+            self._reduce_unit(u)
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    @torch.no_grad()
+    def gather_params(self) -> None:
+        """After the optimizer step: cast the updated master shards and all-gather them into ``full``,
+        one unit at a time on the side stream; forward pre-hooks wait per unit."""
+        if not self.lowp_fresh:
+            self.shard_lp.copy_(self.master) if self.world > 1 else self.full.copy_(self.master)
+        self.lowp_fresh = False
+        if self.world == 1:
+            return
+        stream = self.comm_stream
+        if stream is not None:
+            stream.wait_stream(torch.cuda.current_stream())
+        # the root unit is needed first (embedding), then blocks in forward order
+        order = [self.root] + self.units[:-1]
+        ctx = torch.cuda.stream(stream) if stream is not None else _null()
+        with ctx:
+            for u in order:
+                n_shard = u.shard_hi - u.shard_lo
+                recv = torch.empty(self.world * n_shard, dtype=self.param_dtype, device=self.device)
+                dist.all_gather_into_tensor(recv, self.shard_lp[u.shard_lo:u.shard_hi], group=self.group)
+                rv = recv.view(self.world, n_shard)
+                for sl in u.slots:
+                    dst = self.full[sl.full_off: sl.full_off + sl.padded_numel * self.world]
+                    dst.view(self.world, sl.padded_numel).copy_(
+                        rv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel])
+                if stream is not None:
+                    u.gather_event = torch.cuda.Event()
+                    u.gather_event.record(stream)
+
+    @torch.no_grad()
+    def zero_grad(self) -> None:
+        self.shard_grad.zero_()
+        if self.full_grad is not self.shard_grad:
+            self.full_grad.zero_()
+
+    # ------------------------------------------------------------------ state for checkpoints
+    def master_state_dict(self) -> dict[str, torch.Tensor]:
+        return {fqn: p.data for fqn, p in self.named_master_parameters()}
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False

@@ -1,0 +1,143 @@
+"""Apply the parallel plan to a model: activation checkpointing, then flat-buffer sharding.
+
+Reference entry points: ``parallelize_llama`` / ``parallelize_gemma`` / ``parallelize_deepseek``
+(maester/parallelisms/parallelize_*.py), called as ``parallelize(model, world_mesh, parallel_dims,
+cfg)`` before the weights exist.  The order there is TP -> AC -> compile -> FSDP; here there is no
+compile step, and sharding also materialises the parameters (the model may arrive on the meta
+device).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from maester_b200.config import TORCH_DTYPE_MAP
+from maester_b200.log_utils import logger
+from maester_b200.parallel.fsdp import ShardedModel
+from maester_b200.utils import device_for_training
+
+
+def transformer_blocks(model: nn.Module) -> list[tuple[str, nn.Module]]:
+    """The per-layer units of a model: ``model.layers`` (Gemma) or ``layers`` (Llama, DeepSeek, GLM4)."""
+    inner = getattr(model, "language_model", model)
+    holder = inner.model if hasattr(inner, "model") and hasattr(inner.model, "layers") else inner
+    layers = holder.layers
+    items = layers.items() if isinstance(layers, nn.ModuleDict) else enumerate(layers)
+    return [(f"layer{i}", m) for i, m in items]
+
+
+class CheckpointWrapper(nn.Module):
+    """Full activation checkpointing of one block: keep only its inputs, recompute in backward.
+    The wrapped module keeps its attribute name, so parameter FQNs do not change."""
+
+    def __init__(self, mod: nn.Module):
+        super().__init__()
+        self._checkpoint_wrapped_module = mod
+
+    def forward(self, *args, **kwargs):
+        if not torch.is_grad_enabled():
+            return self._checkpoint_wrapped_module(*args, **kwargs)
+        return checkpoint(self._checkpoint_wrapped_module, *args, use_reentrant=False, preserve_rng_state=False,
+                          **kwargs)
+
+
+def apply_ac(model: nn.Module, cfg) -> None:
+    """ac_mode: none | full | selective; selective_ac_option: "op" or an integer N (every N-th block).
+
+    "op" is the per-op policy of the reference (save GEMM and attention outputs, recompute the rest,
+    parallelize_llama.py:183-250): with hand-written kernels it becomes an explicit plan in the
+    blocks — norms and the gated activation are recomputed, GEMM and attention outputs are kept.
+    """
+    mode = cfg.ac_mode
+    if mode == "none":
+        return
+    blocks = transformer_blocks(model)
+    if mode == "selective" and str(cfg.selective_ac_option) == "op":
+        for _, b in blocks:
+            b.selective_recompute = True
+        logger.info("Applied selective (per-op) activation recomputation to %d blocks", len(blocks))
+        return
+    every = 1
+    if mode == "selective":
+        every = int(cfg.selective_ac_option)
+        assert every >= 1
+    elif mode != "full":
+        raise ValueError(f"Invalid ac_mode {mode}")
+    inner = getattr(model, "language_model", model)
+    holder = inner.model if hasattr(inner, "model") and hasattr(inner.model, "layers") else inner
+    count = 0
+    for idx, (name, b) in enumerate(blocks):
+        if (idx + 1) % every == 0 or mode == "full":
+            key = name[len("layer"):]
+            w = _Checkpointed(b)
+            if isinstance(holder.layers, nn.ModuleDict):
+                holder.layers[key] = w
+            else:
+                holder.layers[int(key)] = w
+            count += 1
+    logger.info("Applied %s activation checkpointing to %d of %d blocks", mode, count, len(blocks))
+
+
+class _Checkpointed(nn.Module):
+    """Same as CheckpointWrapper but transparent for FQNs: parameters are reached through the inner
+    module registered under the reserved name ``_orig_mod``-free path by overriding ``named_*``."""
+
+    def __init__(self, mod: nn.Module):
+        super().__init__()
+        object.__setattr__(self, "inner", mod)
+        # register children/params of the inner module as our own so FQNs are unchanged
+        self._modules = mod._modules
+        self._parameters = mod._parameters
+        self._buffers = mod._buffers
+
+    def __getattr__(self, name):
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(object.__getattribute__(self, "inner"), name)
+
+    def forward(self, *args, **kwargs):
+        inner = object.__getattribute__(self, "inner")
+        if not torch.is_grad_enabled():
+            return inner(*args, **kwargs)
+        return checkpoint(inner, *args, use_reentrant=False, preserve_rng_state=False, **kwargs)
+
+
+def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
+    """Checkpointing plan + sharded flat buffers.  Stores the runtime as ``model._sharded`` and adds
+    ``model.set_requires_gradient_sync`` (the hook the training loop uses during accumulation)."""
+    if parallel_dims.tp_enabled:
+        from maester_b200.parallel.tensor_parallel import apply_tp
+        apply_tp(model, parallel_dims, cfg)
+    apply_ac(model, cfg)
+    device = device_for_training()
+    param_dtype = TORCH_DTYPE_MAP[cfg.mixed_precision_param]
+    reduce_dtype = TORCH_DTYPE_MAP[cfg.mixed_precision_reduce]
+    if device.type == "cpu":
+        param_dtype = torch.float32 if param_dtype == torch.bfloat16 and not getattr(cfg, "cpu_bf16", False) else param_dtype
+    shard_group = parallel_dims.mesh_group("dp_shard_cp") if parallel_dims.fsdp_enabled else None
+    rep_group = parallel_dims.mesh_group("dp_replicate") if parallel_dims.dp_replicate_enabled else None
+    sharded = ShardedModel(
+        model, transformer_blocks(model), device=device, param_dtype=param_dtype, reduce_dtype=reduce_dtype,
+        shard_group=shard_group, replicate_group=rep_group,
+        gradient_divide_factor=float(parallel_dims.fsdp_gradient_divide_factor),
+    )
+    object.__setattr__(model, "_sharded", sharded)
+    model.set_requires_gradient_sync = sharded.set_requires_gradient_sync
+    # buffers that are still on the meta device (RoPE tables) are rebuilt by init_weights()
+    return model
+
+
+def materialize(model: nn.Module) -> None:
+    """``to_empty`` + ``init_weights`` of the reference start-up (train.py:189-190) for a sharded
+    model: parameters already live in the flat buffers, so only initialise and load the shards."""
+    model.init_weights()
+    sharded = getattr(model, "_sharded", None)
+    if sharded is not None:
+        sharded.init_master_from_full()
+
+
+parallelize_llama = parallelize
+parallelize_gemma = parallelize
+parallelize_deepseek = parallelize
