@@ -1,0 +1,203 @@
+"""Checkpoint manager on top of ``torch.distributed.checkpoint`` (DCP).
+
+Same contract as the reference (maester/checkpoint.py:95-255): states ``train_state``, ``model``,
+``optimizer``, ``lr_scheduler`` saved under ``<dump_dir>/<job_name>/<checkpoint_folder>/step-<N>``
+every ``checkpoint_interval`` steps; the forced save at the last step keeps only
+``{"model": {fqn: tensor.to(export_dtype)}}`` when ``model_weights_only``; ``load`` prefers
+``forced_load_path`` (model only), else the highest ``step-*`` folder, and loads only the model for
+step 0 (seed checkpoint) or ``model_only=True``.
+
+Sharded tensors are published as ``DTensor`` with ``Shard(0)`` placement built over this rank's rows
+of the flat fp32 master / optimizer-state buffers, so DCP writes the same per-rank shard files as for
+an FSDP2 model and can reshard on load.  Keys are the model's parameter FQNs.
+"""
+from __future__ import annotations
+
+import enum
+import os
+import re
+import time
+from typing import Any
+
+import torch
+import torch.distributed as dist
+import torch.distributed.checkpoint as dcp
+import torch.nn as nn
+from torch.distributed.checkpoint.stateful import Stateful
+
+from maester_b200.config import TORCH_DTYPE_MAP
+from maester_b200.log_utils import logger
+
+
+class IntervalType(enum.Enum):
+    SECONDS = enum.auto()
+    STEPS = enum.auto()
+
+
+def _as_dtensor(local: torch.Tensor, full_shape, sharded) -> torch.Tensor:
+    """Present this rank's dim-0 rows as a DTensor (plain tensor when the model is not distributed)."""
+    mesh = getattr(sharded, "device_mesh", None)
+    if sharded is None or sharded.world == 1 or mesh is None:
+        return local
+    from torch.distributed.tensor import DTensor, Shard
+
+    shape = torch.Size(full_shape)
+    stride = torch.empty(shape, device="meta").stride()
+    return DTensor.from_local(local, mesh, [Shard(0)], run_check=False, shape=shape, stride=stride)
+
+
+class ModelWrapper(Stateful):
+    """fp32 master weights (sharded) plus persistent buffers, keyed by FQN."""
+
+    def __init__(self, model: nn.Module):
+        self.model = model
+
+    def state_dict(self) -> dict[str, Any]:
+        sharded = getattr(self.model, "_sharded", None)
+        out: dict[str, Any] = {}
+        if sharded is None:
+            out.update({k: v for k, v in self.model.state_dict().items()})
+            return out
+        for u in sharded.units:
+            for sl in u.slots:
+                out[sl.fqn] = _as_dtensor(sl.master.data, sl.shape, sharded)
+        for name, buf in self.model.named_buffers():
+            mod_name, _, leaf = name.rpartition(".")
+            owner = self.model.get_submodule(mod_name) if mod_name else self.model
+            if leaf not in owner._non_persistent_buffers_set:
+                out[name] = buf
+        return out
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        sharded = getattr(self.model, "_sharded", None)
+        if sharded is None:
+            self.model.load_state_dict(state_dict, strict=False)
+            return
+        # DCP loaded in place into the master shards; refresh the compute-dtype copy
+        sharded.lowp_fresh = False
+        sharded.gather_params()
+
+
+class OptimizerWrapper(Stateful):
+    def __init__(self, model: nn.Module, optimizer):
+        self.model, self.optimizer = model, optimizer
+
+    def state_dict(self) -> dict[str, Any]:
+        sharded = getattr(self.model, "_sharded", None)
+        flat = self.optimizer.state_dict()
+        if sharded is None:
+            return flat
+        shapes = {sl.fqn: sl.shape for u in sharded.units for sl in u.slots}
+        out: dict[str, Any] = {}
+        for k, v in flat.items():
+            if torch.is_tensor(v) and v.dim() > 0 and ".state." in f".{k}":
+                fqn = k.split("state.", 1)[1].rsplit(".", 1)[0]
+                if fqn in shapes and v.shape[1:] == shapes[fqn][1:]:
+                    v = _as_dtensor(v, shapes[fqn], sharded)
+            out[k] = v
+        return out
+
+    def load_state_dict(self, state_dict: dict[str, Any]) -> None:
+        plain = {}
+        for k, v in state_dict.items():
+            if hasattr(v, "to_local"):
+                v = v.to_local()
+            plain[k] = v
+        self.optimizer.load_state_dict(plain)
+
+
+class CheckpointManager:
+    def __init__(self, model: nn.Module, optimizer, lr_scheduler, dataloader, states: dict[str, Any], cfg) -> None:
+        self.enable_checkpoint: bool = cfg.enable_checkpoint
+        self.forced_load_path: str | None = cfg.forced_load_path
+        if not self.enable_checkpoint:
+            return
+        self.states = states
+        self.states.update({
+            "model": ModelWrapper(model),
+            "optimizer": OptimizerWrapper(model, optimizer),
+            "lr_scheduler": lr_scheduler,
+        })
+        self.dataloader = dataloader
+        self.folder = os.path.join(cfg.dump_dir, cfg.job_name, cfg.checkpoint_folder)
+        self.interval_type = IntervalType.STEPS
+        self.interval = cfg.checkpoint_interval
+        self.model_weights_only = cfg.model_weights_only
+        self.export_dtype = TORCH_DTYPE_MAP[cfg.export_dtype]
+        self.begin = 0.0
+        # CPU-side coordination group, as in the reference (time-based interval agreement)
+        self.pg = dist.new_group(backend="gloo") if dist.is_initialized() else None
+        logger.info(f"Checkpointing active. Checkpoints will be loaded from and saved to {self.folder}")
+
+    def reset(self) -> None:
+        self.begin = time.monotonic()
+
+    def _checkpoint_id(self, step: int) -> str:
+        return os.path.join(self.folder, f"step-{step}")
+
+    def _no_dist(self) -> bool:
+        return not dist.is_initialized()
+
+    def save(self, curr_step: int, force: bool = False) -> None:
+        if not self.enable_checkpoint:
+            return
+        if not force and curr_step % self.interval != 0:
+            return
+        states: dict[str, Any] = self.states
+        if force and self.model_weights_only:
+            sd = self.states["model"].state_dict()
+            if self.export_dtype != torch.float32:
+                sd = {k: v.to(self.export_dtype) for k, v in sd.items()}
+            states = {"model": sd}
+            logger.info(f"Saving a model weights only checkpoint in {self.export_dtype} at step {curr_step}")
+        else:
+            logger.info(f"Saving a full checkpoint at step {curr_step}")
+        begin = time.monotonic()
+        dcp.save(states, checkpoint_id=self._checkpoint_id(curr_step), no_dist=self._no_dist())
+        if self.dataloader is not None and hasattr(self.dataloader, "state_dict"):
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            d = os.path.join(self.folder, "dataloader", f"step-{curr_step}")
+            os.makedirs(d, exist_ok=True)
+            torch.save(self.dataloader.state_dict(), os.path.join(d, f"loader_state_{rank}.pth"))
+        self.reset()
+        logger.info(f"Finished saving the checkpoint in {time.monotonic() - begin:.2f} seconds")
+
+    def latest_step(self) -> int | None:
+        if not os.path.isdir(self.folder):
+            return None
+        steps = [int(m.group(1)) for f in os.listdir(self.folder) if (m := re.fullmatch(r"step-(\d+)", f))]
+        return max(steps) if steps else None
+
+    def load(self, step: int = -1, model_only: bool = False) -> bool:
+        if not self.enable_checkpoint:
+            return False
+        if self.forced_load_path:
+            if not os.path.isdir(self.forced_load_path):
+                raise ValueError(f"Checkpoint folder {self.forced_load_path} does not exist")
+            logger.info(f"Forcing load from {self.forced_load_path}")
+            self._load({"model": self.states["model"]}, self.forced_load_path)
+            return True
+        if step == -1:
+            found = self.latest_step()
+            if found is None:
+                return False
+            step = found
+        elif not os.path.isdir(self._checkpoint_id(step)):
+            return False
+        states = self.states
+        if step == 0 or model_only:
+            states = {"model": self.states["model"]}
+        logger.info(f"Loading the checkpoint at step {step}, containing keys {list(states.keys())}")
+        begin = time.monotonic()
+        self._load(states, self._checkpoint_id(step))
+        if states is self.states and self.dataloader is not None and hasattr(self.dataloader, "load_state_dict"):
+            rank = dist.get_rank() if dist.is_initialized() else 0
+            f = os.path.join(self.folder, "dataloader", f"step-{step}", f"loader_state_{rank}.pth")
+            if os.path.exists(f):
+                self.dataloader.load_state_dict(torch.load(f, weights_only=False))
+        logger.info(f"Finished loading the checkpoint in {time.monotonic() - begin:.2f} seconds")
+        return True
+
+    def _load(self, states: dict[str, Any], path: str) -> None:
+        # tolerate keys written through a torch.compile wrapper ("._orig_mod")
+        dcp.load(states, checkpoint_id=path, no_dist=self._no_dist())

@@ -227,7 +227,11 @@ class ShardedModel:
         for i, u in enumerate(self.units[:-1]):
             u.module.register_forward_pre_hook(lambda m, a, u=u: self._wait_gather(u))
             u.module.register_full_backward_pre_hook(lambda m, g, i=i: self._on_backward_reach(i))
-        self.model.register_forward_pre_hook(lambda m, a: (self._wait_gather(self.root), self.mark_backward_start()))
+        def root_pre_forward(m, a):  # must return None: a returned value would replace the inputs
+            self._wait_gather(self.root)
+            self.mark_backward_start()
+
+        self.model.register_forward_pre_hook(root_pre_forward)
 
     def _wait_gather(self, u: Unit) -> None:
         if u.gather_event is not None:

@@ -123,6 +123,7 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
         shard_group=shard_group, replicate_group=rep_group,
         gradient_divide_factor=float(parallel_dims.fsdp_gradient_divide_factor),
     )
+    sharded.device_mesh = world_mesh["dp_shard_cp"] if (shard_group is not None and world_mesh is not None) else None
     object.__setattr__(model, "_sharded", sharded)
     model.set_requires_gradient_sync = sharded.set_requires_gradient_sync
     # buffers that are still on the meta device (RoPE tables) are rebuilt by init_weights()

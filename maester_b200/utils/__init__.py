@@ -88,7 +88,10 @@ def set_pg_timeouts(timeout: timedelta, world_mesh=None) -> None:
         torch.cuda.synchronize()
     groups = [None]
     if world_mesh is not None:
-        groups += list(world_mesh.all_groups())
+        try:
+            groups += list(world_mesh.get_all_groups())
+        except Exception:  # older meshes: one group per dimension
+            groups += [world_mesh.get_group(d) for d in range(world_mesh.ndim)]
     for g in groups:
         try:
             dist.distributed_c10d._set_pg_timeout(timeout, g)
