@@ -676,3 +676,94 @@ extern "C" int mb_attn_bwd(const void* q, const void* k, const void* v, const vo
   if (hd == 64) return launch_bwd<64, 2, 64, 2>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
   return -3;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in maester_b200_noalloc.h; no counterpart in the reference).
+// The delta work buffer lives in the library's device image instead of caller-allocated memory.
+#include "maester_b200_noalloc.h"
+
+namespace {
+
+static __device__ __align__(256) float g_noalloc_delta[MB_NOALLOC_MAX_ROWS];
+static __device__ int g_noalloc_status;
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoallocDevice {
+  bool ready = false;
+  float* delta = nullptr;  // device address of g_noalloc_delta on that GPU
+  int* status = nullptr;   // device address of g_noalloc_status
+};
+NoallocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];
+
+// Once per device, with that device current.  In host code the array's name is only a handle for
+// the runtime; the address a kernel can use has to be asked for.
+int noalloc_setup(int dev) {
+  NoallocDevice& d = g_noalloc_dev[dev];
+  if (d.ready) return 0;
+  void* p = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_delta);
+  if (e != cudaSuccess || !p) {
+    fprintf(stderr, "maester_b200: cudaGetSymbolAddress(work array) failed on device %d: %s\n", dev,
+            cudaGetErrorString(e));
+    return MB_NOALLOC_SETUP_FAILED;
+  }
+  d.delta = static_cast<float*>(p);
+  e = cudaGetSymbolAddress(&p, g_noalloc_status);
+  if (e != cudaSuccess || !p) {
+    fprintf(stderr, "maester_b200: cudaGetSymbolAddress(status word) failed on device %d: %s\n", dev,
+            cudaGetErrorString(e));
+    return MB_NOALLOC_SETUP_FAILED;
+  }
+  d.status = static_cast<int*>(p);
+  d.ready = true;
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int mb_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                   const float* lse, void* dqkv, const int* doc, const int* kv_lo_blk,
+                                   const int* q_hi_blk, int B, int S, int H, int KV, int hd, long long q_tok_stride,
+                                   long long k_tok_stride, long long v_tok_stride, long long g_stride, int causal,
+                                   int window, float scale, int* status_out, cudaStream_t st) {
+  if (B <= 0 || S <= 0 || H <= 0 || KV <= 0) return -3;
+  const long long rows = static_cast<long long>(B) * S * H;
+  if (rows > MB_NOALLOC_MAX_ROWS) {
+    fprintf(stderr,
+            "maester_b200: mb_attn_bwd_noalloc needs B*H*S = %lld work entries but the built-in array holds %d; "
+            "use mb_attn_bwd with a caller-provided buffer\n",
+            rows, MB_NOALLOC_MAX_ROWS);
+    return MB_NOALLOC_TOO_LARGE;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return MB_NOALLOC_SETUP_FAILED;
+  if (int e = noalloc_setup(dev)) return e;
+  const NoallocDevice& d = g_noalloc_dev[dev];
+
+  BwdParams p;
+  p.lse = lse;
+  p.delta = d.delta;
+  p.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  p.g_stride = g_stride;
+  p.doc = doc;
+  p.kv_lo_blk = kv_lo_blk;
+  p.q_hi_blk = q_hi_blk;
+  p.B = B;
+  p.S = S;
+  p.H = H;
+  p.KV = KV;
+  p.causal = causal;
+  p.window = window;
+  p.scale = scale;
+  p.scale_log2 = scale * LOG2E;
+  p.status = status_out ? status_out : d.status;
+  if ((q_tok_stride & 7) || (k_tok_stride & 7) || (v_tok_stride & 7) || (g_stride & 7)) return -3;
+  // the kernels read delta[0 .. B*H*S): this launch rewrites exactly that range first
+  attn_delta_kernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), d.delta, B, S, H, hd);
+  if (int e = mbh::check_launch("attn_delta(noalloc)")) return e;
+  if (hd == 256) return launch_bwd<256, 1, 128, 1>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
+  if (hd == 128) return launch_bwd<128, 2, 128, 2>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
+  if (hd == 64) return launch_bwd<64, 2, 64, 2>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
+  return -3;
+}
