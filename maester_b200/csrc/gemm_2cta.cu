@@ -1,0 +1,307 @@
+// bf16 GEMM with CTA pairs: C[M,N] = alpha * op(A) * op(B)^T, 256x256 output tile per pair of SMs.
+//
+// The two CTAs of a cluster share one tcgen05.mma.cta_group::2 (M256 N256 K16) issued by the even
+// CTA: each CTA stages its own 128 rows of A and its own 128-row half of B, so per SM only
+// 32 KiB of operands enter shared memory per 64-deep k-block (48 KiB for the single-CTA kernel) and
+// the tensor core reads half of B from the partner.  That relieves the shared-memory port, which
+// the single-CTA 128x256 tile saturates (MMA operand reads + TMA writes).
+//
+// Per CTA: warp 0 = TMA producer (6-stage ring; loads use .cta_group::2 and complete on the even
+// CTA's barrier, no multicast), warp 1 = MMA issuer (even CTA only) + TMEM allocation, warps 2-5 =
+// epilogue over this CTA's 128 accumulator rows (two 256-column TMEM buffers, so the epilogue of
+// one tile overlaps the main loop of the next).  Operand layouts as in gemm.cu.
+// All mbarrier waits are bounded; both CTAs always reach the cluster barriers.
+#include "gemm_common.cuh"
+#include "host_common.cuh"
+
+namespace {
+using namespace mb;
+using namespace mbg;
+
+constexpr int BM = 128;        // rows per CTA (256 per pair)
+constexpr int BN = 256;        // tile columns (each CTA stages BN/2 rows of B)
+constexpr int BNH = BN / 2;
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BNH * BK * 2;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 32 KiB
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 4;     // in units of 256-row tiles
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // shared::cluster address of the same offset in the even CTA
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive (+ expected bytes) on the barrier at the same offset in the even CTA of the pair
+__device__ __forceinline__ void mbar_expect_tx_leader(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(smem_u32(bar) & PEER_MASK), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & PEER_MASK) : "memory");
+}
+// TMA load whose completion bytes are counted on the even CTA's barrier (no multicast)
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar) & PEER_MASK), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(z), "r"(z), "r"(z), "r"(z), "r"(z),
+        "r"(z), "r"(z), "r"(z)
+      : "memory");
+}
+// arrive on the barrier at this offset in both CTAs once all MMAs issued so far have completed
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                         // [STAGES]  used in the even CTA only
+  uint64_t* empty = bars + STAGES;               // [STAGES]  one per CTA
+  uint64_t* acc_full = bars + 2 * STAGES;        // [2]       one per CTA
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;   // [2]       used in the even CTA only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();        // 0 = even CTA (issues the MMAs), 1 = partner
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int tm = (p.M + 2 * BM - 1) / (2 * BM), tn = (p.N + BN - 1) / BN;
+  const int num_tiles = tm * tn;
+  const int kblocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 2);    // one arrive.expect_tx from each CTA's producer
+      mbar_init(&empty[s], 1);   // multicast commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);     // multicast commit
+      mbar_init(&acc_empty[a], 256);  // epilogue threads of both CTAs
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // partner's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs) {
+        int mt, nt;
+        tile_coords(t, tm, tn, GROUP_M, mt, nt);
+        const int m0 = mt * 2 * BM + static_cast<int>(cta) * BM;
+        const int n0 = nt * BN + static_cast<int>(cta) * BNH;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1)) {
+            atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx_leader(&full[s], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d_pair(sa, &tmap_a, &full[s], k0, m0);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BM / 64; ++b) tma_load_2d_pair(sa + b * (BK * 128), &tmap_a, &full[s], m0 + b * 64, k0);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sb, &tmap_b, &full[s], k0, n0);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BNH / 64; ++b) tma_load_2d_pair(sb + b * (BK * 128), &tmap_b, &full[s], n0 + b * 64, k0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += npairs, ++tcount) {
+        const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1)) {
+          atomicCAS(p.status, 0, ERR_WAIT_ACC_EMPTY);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph)) {
+            atomicCAS(p.status, 0, ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc(sb + k * 32, 16, 1024);
+            umma2_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma2_commit_both(&empty[s]);
+        }
+        if (ok) umma2_commit_both(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const float alpha = p.alpha * (p.alpha_dev ? __ldg(p.alpha_dev) : 1.f);
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += npairs, ++tcount) {
+      int mt, nt;
+      tile_coords(t, tm, tn, GROUP_M, mt, nt);
+      const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_ph)) {
+        atomicCAS(p.status, 0, ERR_WAIT_ACC_FULL);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = mt * 2 * BM + static_cast<int>(cta) * BM + q * 32 + lane;
+      const int n0 = nt * BN;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        store_acc_chunk(p, r, alpha, row, n0 + c * 32);
+      }
+      tc_fence_before();
+      mbar_arrive_leader(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the partner may still touch its memory or barriers
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc2(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch2(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int e;
+  if (!A_MN) e = mbh::make_tmap_bf16_2d(&ta, A, p.K, p.M, lda, 64, BM);
+  else e = mbh::make_tmap_bf16_2d(&ta, A, p.M, p.K, lda, 64, BK);
+  if (e) return e;
+  if (!B_MN) e = mbh::make_tmap_bf16_2d(&tb, B, p.K, p.N, ldb, 64, BNH);
+  else e = mbh::make_tmap_bf16_2d(&tb, B, p.N, p.K, ldb, 64, BK);
+  if (e) return e;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    attr_set = true;
+  }
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+  const int max_pairs = mbh::sm_count() / 2;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t err = cudaLaunchKernelEx(&cfg, gemm_bf16_2cta_kernel<A_MN, B_MN>, ta, tb, p);
+  if (err != cudaSuccess) {
+    fprintf(stderr, "maester_b200: cluster launch of gemm_bf16_2cta failed: %s\n", cudaGetErrorString(err));
+    return -100 - static_cast<int>(err);
+  }
+  return mbh::check_launch("gemm_bf16_2cta");
+}
+
+}  // namespace
+
+// Same contract as mb_gemm_bf16 (gemm.cu); uses CTA pairs.
+extern "C" int mb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* aux, int M, int N, int K,
+                                 long long lda, long long ldb, long long ldc, long long ldaux, int a_mn, int b_mn,
+                                 int epi, float alpha, const float* alpha_dev, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -3;
+  GemmParams p;
+  p.C = C;
+  p.aux = aux;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.ldaux = ldaux;
+  p.epi = epi;
+  p.alpha = alpha;
+  p.alpha_dev = alpha_dev;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  if (!a_mn && !b_mn) return launch2<false, false>(A, B, p, lda, ldb, stream);
+  if (!a_mn && b_mn) return launch2<false, true>(A, B, p, lda, ldb, stream);
+  if (a_mn && !b_mn) return launch2<true, false>(A, B, p, lda, ldb, stream);
+  return launch2<true, true>(A, B, p, lda, ldb, stream);
+}

@@ -1,0 +1,98 @@
+// Pieces shared by the GEMM kernels: parameters, epilogue modes, tile rasterisation, and the
+// accumulator-row epilogue (32 fp32 values of one output row -> global memory).
+#pragma once
+#include "sm100.cuh"
+
+namespace mbg {
+
+enum EpiMode : int {
+  EPI_BF16 = 0,      // C(bf16) = alpha*acc
+  EPI_F32 = 1,       // C(fp32) = alpha*acc
+  EPI_F32_ACC = 2,   // C(fp32) += alpha*acc
+  EPI_BF16_ADD = 3,  // C(bf16) = alpha*acc + aux(bf16)
+};
+
+struct GemmParams {
+  void* C;
+  const void* aux;
+  int M, N, K;
+  long long ldc, ldaux;
+  int epi;
+  float alpha;
+  const float* alpha_dev;  // optional device scalar multiplied into alpha
+  int* status;
+};
+
+// group GROUP_M row-tiles together so that concurrently running CTAs share operand tiles in L2
+__device__ __forceinline__ void tile_coords(int t, int tm, int tn, int group_m, int& mt, int& nt) {
+  const int group_size = group_m * tn;
+  const int g = t / group_size;
+  const int first_m = g * group_m;
+  const int gm = min(tm - first_m, group_m);
+  const int r = t - g * group_size;
+  mt = first_m + r % gm;
+  nt = r / gm;
+}
+
+// Store 32 consecutive accumulator columns [col0, col0+32) of output row `row`.
+__device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint32_t (&r)[32], float alpha, int row,
+                                                int col0) {
+  using namespace mb;
+  if (row >= p.M || col0 >= p.N) return;
+  const bool full_chunk = (col0 + 32 <= p.N);
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+  if (p.epi == EPI_BF16 || p.epi == EPI_BF16_ADD) {
+    __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.epi == EPI_BF16_ADD) {
+      const __nv_bfloat16* arow =
+          reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;
+      if (full_chunk && (p.ldaux & 7) == 0) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 a4 = reinterpret_cast<const uint4*>(arow)[j];
+          const __nv_bfloat162* ab = reinterpret_cast<const __nv_bfloat162*>(&a4);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 f = __bfloat1622float2(ab[e]);
+            v[j * 8 + e * 2] += f.x;
+            v[j * 8 + e * 2 + 1] += f.y;
+          }
+        }
+      } else {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) v[i] += __bfloat162float(arow[i]);
+      }
+    }
+    if (full_chunk && (p.ldc & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 o;
+        o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+        o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+        o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+        o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+        reinterpret_cast<uint4*>(crow)[j] = o;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) crow[i] = __float2bfloat16(v[i]);
+    }
+  } else {
+    float* crow = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (full_chunk && (p.ldc & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        if (p.epi == EPI_F32_ACC) {
+          float4 old = reinterpret_cast<float4*>(crow)[j];
+          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+        }
+        reinterpret_cast<float4*>(crow)[j] = o;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) crow[i] = (p.epi == EPI_F32_ACC ? crow[i] : 0.f) + v[i];
+    }
+  }
+}
+
+}  // namespace mbg

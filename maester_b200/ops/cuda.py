@@ -7,6 +7,7 @@ bounded wait expires.
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -26,6 +27,7 @@ _STATUS_NAMES = {
 }
 
 launch_count = 0  # number of native kernel launches issued through this module
+GEMM_TWO_CTA = os.environ.get("MB_GEMM_2CTA", "1") != "0"
 
 
 def _stream() -> int:
@@ -61,8 +63,12 @@ def _rows_pitch(t: torch.Tensor) -> int:
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, epi: int = EPI_BF16, alpha: float = 1.0,
-         aux: torch.Tensor | None = None, alpha_dev: torch.Tensor | None = None) -> torch.Tensor:
+         aux: torch.Tensor | None = None, alpha_dev: torch.Tensor | None = None,
+         two_cta: bool | None = None) -> torch.Tensor:
     """``C = alpha * op(A) @ op(B).T`` on the tcgen05 GEMM.
+
+    ``two_cta`` selects the CTA-pair kernel (256x256 tiles, ``cta_group::2``); by default it is used
+    whenever the problem has more than one 128-row tile.
 
     a_mn=False: A is [M, K];  a_mn=True: A is stored [K, M].
     b_mn=False: B is [N, K];  b_mn=True: B is stored [K, N].
@@ -81,10 +87,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out = torch.empty(M, N, device=a.device, dtype=torch.bfloat16 if epi in (EPI_BF16, EPI_BF16_ADD) else torch.float32)
     assert out.shape == (M, N)
     l = _lib.lib()
-    rc = l.mb_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(aux), M, N, K,
-                        _rows_pitch(a), _rows_pitch(b), _rows_pitch(out),
-                        _rows_pitch(aux) if aux is not None else 0,
-                        int(a_mn), int(b_mn), epi, float(alpha), _ptr(alpha_dev), _stream())
+    if two_cta is None:
+        two_cta = GEMM_TWO_CTA and M > 128
+    fn = l.mb_gemm_bf16_2cta if two_cta else l.mb_gemm_bf16
+    rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(aux), M, N, K,
+            _rows_pitch(a), _rows_pitch(b), _rows_pitch(out), _rows_pitch(aux) if aux is not None else 0,
+            int(a_mn), int(b_mn), epi, float(alpha), _ptr(alpha_dev), _stream())
     _ck(rc, "gemm_bf16")
     return out
 

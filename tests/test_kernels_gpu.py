@@ -42,6 +42,28 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     assert _rel(acc, 1 + 0.5 * want) < 1e-4
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (1000, 520, 136), (2048, 2560, 4096), (300, 40, 72)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_two_cta(M, N, K, a_mn, b_mn):
+    from maester_b200.ops import cuda as C
+    if (a_mn and M % 8) or (b_mn and N % 8):
+        pytest.skip("MN-major operands need a pitch that is a multiple of 8")
+    torch.manual_seed(0)
+    A = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    B = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    want = A.float() @ B.float().T
+    a = A.T.contiguous() if a_mn else A
+    b = B.T.contiguous() if b_mn else B
+    got = C.gemm(a, b, a_mn=a_mn, b_mn=b_mn, two_cta=True)
+    C.check_status()
+    assert _rel(got, want) < 5e-3
+    acc = torch.ones(M, N, device="cuda")
+    C.gemm(a, b, a_mn=a_mn, b_mn=b_mn, epi=C.EPI_F32_ACC, out=acc, alpha=0.5, two_cta=True)
+    assert _rel(acc, 1 + 0.5 * want) < 1e-4
+    one = C.gemm(a, b, a_mn=a_mn, b_mn=b_mn, two_cta=False)
+    assert torch.equal(one, got)
+
+
 def test_gemm_residual_epilogue():
     from maester_b200.ops import cuda as C
     A = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16)
