@@ -239,3 +239,35 @@ def attn_bwd(q, k, v, out, dout, lse, dqkv, scale, causal, window, doc, kv_lo_bl
                                _ptr(q_hi_blk), B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
                                dqkv.stride(0), int(causal), -1 if window is None or window <= 0 else int(window),
                                float(scale), _stream()), "attn_bwd")
+
+
+def gemm_grouped_rows(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, *, b_mn: bool,
+                      out: torch.Tensor | None = None, epi: int = EPI_BF16, alpha: float = 1.0) -> torch.Tensor:
+    """Per-group GEMM over row groups of ``a`` ([rows_cap, K]); ``offs`` are padded (x128) int32 device offsets.
+
+    b_mn=True : b is [E, K, N] and out_e = a_e @ b_e;  b_mn=False: b is [E, N, K] and out_e = a_e @ b_e.T
+    """
+    rows_cap, K = a.shape
+    E = b.shape[0]
+    N = b.shape[2] if b_mn else b.shape[1]
+    assert (b.shape[1] if b_mn else b.shape[2]) == K and b.is_contiguous() and offs.dtype == torch.int32
+    if out is None:
+        out = torch.empty(rows_cap, N, device=a.device, dtype=torch.bfloat16 if epi == EPI_BF16 else torch.float32)
+    b2 = b.view(E * b.shape[1], b.shape[2])
+    _ck(_lib.lib().mb_gemm_bf16_grouped_rows(a.data_ptr(), b2.data_ptr(), out.data_ptr(), offs.data_ptr(), E,
+                                             rows_cap, N, K, _rows_pitch(a), _rows_pitch(b2), _rows_pitch(out),
+                                             int(b_mn), epi, float(alpha), _stream()), "gemm_grouped_rows")
+    return out
+
+
+def gemm_grouped_contr(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, out: torch.Tensor,
+                       epi: int = EPI_F32_ACC, alpha: float = 1.0) -> torch.Tensor:
+    """out[e] (+)= a_e.T @ b_e for row groups of a ([rows_cap, M]) and b ([rows_cap, N]); out is [E, M, N]."""
+    rows_cap, M = a.shape
+    N = b.shape[1]
+    E = out.shape[0]
+    assert out.shape == (E, M, N) and out.is_contiguous() and offs.dtype == torch.int32
+    _ck(_lib.lib().mb_gemm_bf16_grouped_contr(a.data_ptr(), b.data_ptr(), out.data_ptr(), offs.data_ptr(), E,
+                                              rows_cap, M, N, _rows_pitch(a), _rows_pitch(b), N, epi, float(alpha),
+                                              _stream()), "gemm_grouped_contr")
+    return out

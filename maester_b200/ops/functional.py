@@ -365,3 +365,54 @@ def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
     if use_native(h2, w) and w.shape[0] % 8 == 0:
         return _LinearCE.apply(h2.contiguous(), w, labels, logit_scale)
     return ref.linear_cross_entropy(h2, w, labels.reshape(-1), logit_scale)
+
+
+# --------------------------------------------------------------------------- grouped (expert) linear
+GROUP_ALIGN = 128  # row groups are padded to the GEMM tile height
+
+
+def padded_group_offsets(counts: torch.Tensor, align: int = GROUP_ALIGN) -> torch.Tensor:
+    """int32 [E+1] start offsets of groups whose sizes are rounded up to ``align`` (no host sync)."""
+    padded = (counts.to(torch.int64) + align - 1) // align * align
+    offs = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=counts.device)
+    offs[1:] = padded.cumsum(0)
+    return offs.to(torch.int32)
+
+
+class _GroupedLinear(Function):
+    @staticmethod
+    def forward(ctx, x, w, offs):
+        C = _C()
+        ctx.save_for_backward(x, w, offs)
+        return C.gemm_grouped_rows(x, w, offs, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _C()
+        x, w, offs = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = C.gemm_grouped_rows(dy, w, offs, b_mn=False) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+            C.gemm_grouped_contr(x, dy, offs, buf)
+            dw = None if mg is not None else buf.to(w.dtype)
+        return dx, dw, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, counts: torch.Tensor | None = None):
+    """``y[rows of group e] = x[rows of group e] @ w[e]`` with w: [E, in, out].
+
+    ``offs`` are the padded int32 offsets of the groups inside ``x`` (see ``padded_group_offsets``); rows
+    between a group's real size and its padded size must be zero.
+    """
+    if use_native(x, w) and x.shape[0] % GROUP_ALIGN == 0 and w.shape[1] % 64 == 0 and w.shape[2] % 8 == 0:
+        return _GroupedLinear.apply(x, w, offs)
+    out = x.new_zeros(x.shape[0], w.shape[2])
+    bounds = offs.tolist()
+    for e in range(w.shape[0]):
+        lo, hi = bounds[e], bounds[e + 1]
+        if hi > lo:
+            out[lo:hi] = x[lo:hi] @ w[e]
+    return out
