@@ -319,11 +319,12 @@ int dispatch(const void* A, const void* B, const GemmParams& p, const GroupParam
 // Requirements: bf16 operands, 16-byte aligned bases, pitches multiples of 8 elements.
 extern "C" int mb_gemm_bf16(const void* A, const void* B, void* C, const void* aux, int M, int N, int K,
                             long long lda, long long ldb, long long ldc, long long ldaux, int a_mn, int b_mn,
-                            int epi, float alpha, const float* alpha_dev, cudaStream_t stream) {
+                            int epi, float alpha, float beta, const float* alpha_dev, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -3;
   GemmParams p;
+  p.beta = beta;
   p.C = C;
   p.aux = aux;
   p.M = M;
@@ -361,6 +362,7 @@ extern "C" int mb_gemm_bf16_grouped_rows(const void* A, const void* B, void* C, 
   p.epi = epi;
   p.alpha = alpha;
   p.alpha_dev = nullptr;
+  p.beta = 1.f;
   p.status = mbh::status().dev;
   if (!p.status) return -4;
   GroupParams g = {GROUP_ROWS, num_groups, offs, b_mn ? K : N, 0};
@@ -388,6 +390,7 @@ extern "C" int mb_gemm_bf16_grouped_contr(const void* A, const void* B, void* C,
   p.epi = epi;
   p.alpha = alpha;
   p.alpha_dev = nullptr;
+  p.beta = 1.f;
   p.status = mbh::status().dev;
   if (!p.status) return -4;
   GroupParams g = {GROUP_CONTR, num_groups, offs, 0, static_cast<long long>(M) * ldc};

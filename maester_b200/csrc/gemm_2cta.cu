@@ -283,7 +283,7 @@ int launch2(const void* A, const void* B, const GemmParams& p, long long lda, lo
 // Same contract as mb_gemm_bf16 (gemm.cu); uses CTA pairs.
 extern "C" int mb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* aux, int M, int N, int K,
                                  long long lda, long long ldb, long long ldc, long long ldaux, int a_mn, int b_mn,
-                                 int epi, float alpha, const float* alpha_dev, cudaStream_t stream) {
+                                 int epi, float alpha, float beta, const float* alpha_dev, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
     return -3;
@@ -298,6 +298,7 @@ extern "C" int mb_gemm_bf16_2cta(const void* A, const void* B, void* C, const vo
   p.epi = epi;
   p.alpha = alpha;
   p.alpha_dev = alpha_dev;
+  p.beta = beta;
   p.status = mbh::status().dev;
   if (!p.status) return -4;
   if (!a_mn && !b_mn) return launch2<false, false>(A, B, p, lda, ldb, stream);

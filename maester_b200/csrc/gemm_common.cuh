@@ -9,7 +9,7 @@ enum EpiMode : int {
   EPI_BF16 = 0,      // C(bf16) = alpha*acc
   EPI_F32 = 1,       // C(fp32) = alpha*acc
   EPI_F32_ACC = 2,   // C(fp32) += alpha*acc
-  EPI_BF16_ADD = 3,  // C(bf16) = alpha*acc + aux(bf16)
+  EPI_BF16_ADD = 3,  // C(bf16) = alpha*acc + beta*aux(bf16)
 };
 
 struct GemmParams {
@@ -19,6 +19,7 @@ struct GemmParams {
   long long ldc, ldaux;
   int epi;
   float alpha;
+  float beta;              // scale of aux in EPI_BF16_ADD
   const float* alpha_dev;  // optional device scalar multiplied into alpha
   int* status;
 };
@@ -56,12 +57,12 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint3
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float2 f = __bfloat1622float2(ab[e]);
-            v[j * 8 + e * 2] += f.x;
-            v[j * 8 + e * 2 + 1] += f.y;
+            v[j * 8 + e * 2] += p.beta * f.x;
+            v[j * 8 + e * 2 + 1] += p.beta * f.y;
           }
         }
       } else {
-        for (int i = 0; i < 32 && col0 + i < p.N; ++i) v[i] += __bfloat162float(arow[i]);
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) v[i] += p.beta * __bfloat162float(arow[i]);
       }
     }
     if (full_chunk && (p.ldc & 7) == 0) {

@@ -132,8 +132,16 @@ class TransformerBlock(nn.Module):
         self.weight_init_std = args.init_std / math.sqrt(args.mup_width_mul) if args.enable_mup else args.init_std
         self.selective_recompute = args.selective_recompute
 
+    tp = None  # set by apply_tp: the residual stream is then sharded along the sequence
+
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids):
         rc = self.selective_recompute
+        if self.tp is not None:
+            from maester_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
+            a_in = gather_seq(maybe_checkpoint(self.attention_norm, rc, x), self.tp)
+            h = x + reduce_scatter_seq(self.attention(a_in, position_ids, inv_freq, rope_cs, document_ids), self.tp)
+            f_in = gather_seq(maybe_checkpoint(self.ffn_norm, rc, h), self.tp)
+            return h + reduce_scatter_seq(self.feed_forward(f_in, recompute_act=rc), self.tp)
         h = self.attention(maybe_checkpoint(self.attention_norm, rc, x), position_ids, inv_freq, rope_cs,
                            document_ids, residual=x)
         return self.feed_forward(maybe_checkpoint(self.ffn_norm, rc, h), residual=h, recompute_act=rc)
@@ -202,12 +210,28 @@ class Transformer(nn.Module):
             position_ids = position_ids.unsqueeze(0)
         if position_ids is None:
             position_ids = torch.arange(S, device=tokens.device, dtype=torch.int32)[None].expand(B, S)
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            from maester_b200.parallel.tensor_parallel import gather_seq, scatter_seq, vocab_parallel_cross_entropy
+            h = scatter_seq(h, tp)  # every rank embeds all tokens, keeps its sequence slice
         for layer in self.layers.values():
             h = layer(h, position_ids, self.inv_freq, self.rope_cs, document_ids)
         h = self.norm(h)
         if self.model_args.enable_mup:
             h = h * (self.model_args.mup_output_alpha / self.model_args.mup_width_mul)
         w = self.tok_embeddings.weight if self.model_args.tied_embeddings else self.output.weight
+        if tp is not None:
+            h = gather_seq(h, tp)
+            if self.model_args.tied_embeddings:  # replicated head: ordinary loss on the gathered sequence
+                return ops.linear_cross_entropy(h, w, labels) if labels is not None else ops.linear(h, w)
+            if labels is not None:
+                return vocab_parallel_cross_entropy(h, w, labels, tp)
+            logits = ops.linear(h, w)  # vocabulary-sharded logits [B, S, V/tp]
+            if tp.loss_parallel:
+                return logits
+            full = torch.empty(tp.size, *logits.shape, device=logits.device, dtype=logits.dtype)
+            torch.distributed.all_gather_into_tensor(full.view(-1), logits.contiguous().view(-1), group=tp.group)
+            return full.permute(1, 2, 0, 3).reshape(*logits.shape[:2], -1)
         if labels is not None:
             return ops.linear_cross_entropy(h, w, labels)
         return ops.linear(h, w)

@@ -110,12 +110,12 @@ _F = ctypes.c_float
 
 def _declare(l: ctypes.CDLL) -> None:
     sig = {
-        "mb_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _I, _I, _F, _P, _P],
+        "mb_gemm_bf16": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _I, _I, _F, _F, _P, _P],
         "mb_rmsnorm_fwd": [_P, _P, _P, _P, _P, _I, _I, _F, _I, _P],
         "mb_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
         "mb_qknorm_rope_fwd": [_P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _I, _L, _L, _P],
         "mb_qknorm_rope_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _F, _I, _L, _L, _P],
-        "mb_gemm_bf16_2cta": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _I, _I, _F, _P, _P],
+        "mb_gemm_bf16_2cta": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _I, _I, _F, _F, _P, _P],
         "mb_gemm_bf16_grouped_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _I, _F, _P],
         "mb_gemm_bf16_grouped_contr": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _F, _P],
         "mb_glu_fwd": [_P, _P, _L, _I, _I, _L, _P],

@@ -64,7 +64,7 @@ def _rows_pitch(t: torch.Tensor) -> int:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: torch.Tensor | None = None, epi: int = EPI_BF16, alpha: float = 1.0,
          aux: torch.Tensor | None = None, alpha_dev: torch.Tensor | None = None,
-         two_cta: bool | None = None) -> torch.Tensor:
+         two_cta: bool | None = None, beta: float = 1.0) -> torch.Tensor:
     """``C = alpha * op(A) @ op(B).T`` on the tcgen05 GEMM.
 
     ``two_cta`` selects the CTA-pair kernel (256x256 tiles, ``cta_group::2``); by default it is used
@@ -92,7 +92,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     fn = l.mb_gemm_bf16_2cta if two_cta else l.mb_gemm_bf16
     rc = fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), _ptr(aux), M, N, K,
             _rows_pitch(a), _rows_pitch(b), _rows_pitch(out), _rows_pitch(aux) if aux is not None else 0,
-            int(a_mn), int(b_mn), epi, float(alpha), _ptr(alpha_dev), _stream())
+            int(a_mn), int(b_mn), epi, float(alpha), float(beta), _ptr(alpha_dev), _stream())
     _ck(rc, "gemm_bf16")
     return out
 

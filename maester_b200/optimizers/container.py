@@ -138,6 +138,8 @@ def _make_optimizer(opt_class, params_or_groups, opt_cfg: dict, model) -> Optimi
     if "betas" in cfg:
         cfg["betas"] = tuple(cfg["betas"])
     opt = opt_class(params_or_groups, **cfg)
+    if sharded is not None and hasattr(opt, "attach_sharding"):
+        opt.attach_sharding(sharded)
     if isinstance(opt, FusedAdamW) and sharded is not None:
         seg = sharded.flat_segments()
         mine = {p: seg[p] for g in opt.param_groups for p in g["params"]}

@@ -1,0 +1,222 @@
+"""Muon: momentum + Newton–Schulz orthogonalised updates for matrices, Adam for the rest.
+
+Reference: maester/optimizers/muon.py.  Semantics kept: momentum buffer ``m`` per matrix, EMA
+``m ← lerp(m, g, 1-μ)`` followed by the Nesterov blend ``u ← lerp(g, m, μ)`` (:153-179); five
+quintic Newton–Schulz iterations in bf16 with coefficients (3.4445, −4.7750, 2.0315) after Frobenius
+normalisation, on the wide orientation of the matrix (:22-49); update
+``p ← p·(1 − lr·wd) − lr·sqrt(max(1, rows/cols))·NS(u)`` (:228-232); parameters whose group has
+``use_muon=False`` get a built-in Adam (:184-208).
+
+Distribution: parameters are dim-0 shards of the flat-buffer sharding runtime.  Matrix ``i`` is owned
+by rank ``i % world``: the shards of ``u`` are gathered there, orthogonalised once and scattered
+back, with up to ``prefetch_factor`` matrices in flight (reference :210-264).  ``MuonDDP`` is the
+replicated-parameter variant: every rank holds full matrices, work is split round-robin and the
+results are exchanged with one all-gather per bucket (reference :297-460).
+
+The Newton–Schulz iteration runs on the tcgen05 GEMM: ``A = X Xᵀ``, ``B = c·A·A + b·A`` and
+``X ← B·X + a·X`` are three launches per iteration, the axpby terms live in the GEMM epilogue.
+"""
+from __future__ import annotations
+
+import math
+from collections import deque
+
+import torch
+import torch.distributed as dist
+from torch.optim import Optimizer
+
+from maester_b200.ops import reference as ref
+
+NS_COEFFS = (3.4445, -4.7750, 2.0315)
+
+
+def syrk(a: torch.Tensor, c: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """``alpha·A·Aᵀ + beta·C`` (reference kernel: maester/optimizers/muon_/syrk.py:143-169).
+
+    Runs on the native GEMM for bf16 CUDA inputs; the product is computed in full (a triangular
+    tile schedule with mirrored stores is a possible refinement, the result is symmetric either way).
+    """
+    if a.is_cuda and a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0:
+        from maester_b200.ops import cuda as C
+        if c is not None and beta != 0.0:
+            return C.gemm(a, a, epi=C.EPI_BF16_ADD, aux=c, alpha=alpha, beta=beta)
+        return C.gemm(a, a, alpha=alpha)
+    out = alpha * (a @ a.mT)
+    return out + beta * c if (c is not None and beta != 0.0) else out
+
+
+def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.Tensor:
+    """Approximate ``U Vᵀ`` of ``g = U S Vᵀ`` (bf16)."""
+    if not (g.is_cuda and g.dim() == 2 and g.shape[0] % 8 == 0 and g.shape[1] % 8 == 0):
+        return ref.newton_schulz(g, steps, eps)
+    from maester_b200.ops import cuda as C
+    a, b, c = NS_COEFFS
+    x = g.to(torch.bfloat16)
+    transposed = x.shape[0] > x.shape[1]
+    if transposed:
+        x = x.t().contiguous()
+    x = (x / (x.norm() + eps)).contiguous()
+    for _ in range(steps):
+        A = C.gemm(x, x)                                                   # X Xᵀ            [m, m]
+        Bm = C.gemm(A, A, epi=C.EPI_BF16_ADD, aux=A, alpha=c, beta=b)      # c·A·A + b·A     (A symmetric)
+        x = C.gemm(Bm, x, b_mn=True, epi=C.EPI_BF16_ADD, aux=x, alpha=1.0, beta=a)  # B·X + a·X
+    return x.t().contiguous() if transposed else x
+
+
+def _adam_update(p, g, state, group) -> None:
+    if "exp_avg" not in state:
+        state["step"] = 0
+        state["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+        state["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+    state["step"] += 1
+    b1, b2 = group.get("adam_betas", group.get("betas", (0.9, 0.95)))
+    ref.adamw_step(p.data, g.float(), state["exp_avg"], state["exp_avg_sq"], state["step"], group["lr"], b1, b2,
+                   group.get("adam_eps", group.get("eps", 1e-8)), group.get("wd", group.get("weight_decay", 0.0)))
+
+
+class Muon(Optimizer):
+    """Muon over (possibly dim-0 sharded) 2-D parameters.
+
+    ``shard_group`` / ``full_shape_of`` describe the sharding: ``full_shape_of(p)`` returns the
+    unsharded shape of ``p``.  When they are omitted the parameters are treated as full matrices.
+    """
+
+    def __init__(self, params, lr: float = 0.02, momentum: float = 0.95, ns_steps: int = 5, wd: float = 0.01,
+                 nesterov: bool = True, use_muon: bool = True, prefetch_factor: int = 8, shard_group=None,
+                 full_shape_of=None, **adam_kw):
+        defaults = dict(lr=lr, momentum=momentum, ns_steps=ns_steps, wd=wd, nesterov=nesterov, use_muon=use_muon,
+                        **adam_kw)
+        super().__init__(params, defaults)
+        self.prefetch_factor = prefetch_factor
+        self.shard_group = shard_group
+        self.full_shape_of = full_shape_of
+
+    def attach_sharding(self, sharded) -> None:
+        """Use the sharding runtime's group and shapes (called by the optimizer builder)."""
+        self.shard_group = sharded.group if sharded.world > 1 else None
+        self.full_shape_of = lambda p: sharded.slot_of(p).shape
+
+    def _world(self) -> tuple[int, int]:
+        if self.shard_group is None or not dist.is_initialized():
+            return 1, 0
+        return dist.get_world_size(self.shard_group), dist.get_rank(self.shard_group)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        world, rank = self._world()
+        work = []  # (param, group, update-direction shard u)
+        for group in self.param_groups:
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not group["use_muon"] or p.dim() < 2:
+                    _adam_update(p, p.grad, st, group)
+                    continue
+                g = p.grad.reshape(p.shape[0], -1).float()
+                if "m" not in st:
+                    st["m"] = torch.zeros_like(g)
+                m = st["m"]
+                m.lerp_(g, 1 - group["momentum"])
+                u = g.lerp(m, group["momentum"]) if group["nesterov"] else m
+                work.append((p, group, u.to(torch.bfloat16)))
+
+        inflight: deque = deque()
+
+        def launch(i: int):
+            p, group, u = work[i]
+            owner = i % world
+            if world == 1:
+                return (i, None, None, u)
+            full_rows = self.full_shape_of(p)[0] if self.full_shape_of else u.shape[0] * world
+            chunk = (full_rows + world - 1) // world
+            padded = u if u.shape[0] == chunk else torch.cat([u, u.new_zeros(chunk - u.shape[0], u.shape[1])])
+            gather_list = [torch.empty_like(padded) for _ in range(world)] if rank == owner else None
+            h = dist.gather(padded, gather_list, group_dst=owner, group=self.shard_group, async_op=True)
+            return (i, h, gather_list, padded)
+
+        def finish(item):
+            i, h, gather_list, padded = item
+            p, group, u = work[i]
+            owner = i % world
+            if world == 1:
+                o = newton_schulz(u, group["ns_steps"])
+            else:
+                h.wait()
+                full_rows = self.full_shape_of(p)[0] if self.full_shape_of else u.shape[0] * world
+                scatter_list = None
+                if rank == owner:
+                    full = torch.cat(gather_list)[:full_rows]
+                    of = newton_schulz(full, group["ns_steps"])
+                    chunk = padded.shape[0]
+                    if of.shape[0] < chunk * world:
+                        of = torch.cat([of, of.new_zeros(chunk * world - of.shape[0], of.shape[1])])
+                    scatter_list = list(of.split(chunk))
+                o = torch.empty_like(padded)
+                dist.scatter(o, scatter_list, group_src=owner, group=self.shard_group)
+                o = o[: u.shape[0]]
+            shape = self.full_shape_of(p) if self.full_shape_of else p.shape
+            rows, cols = shape[0], math.prod(shape[1:])
+            scale = max(1.0, rows / cols) ** 0.5
+            p.data.mul_(1 - group["lr"] * group["wd"])
+            p.data.add_(o.reshape(p.shape).to(p.dtype), alpha=-group["lr"] * scale)
+
+        for i in range(len(work)):
+            inflight.append(launch(i))
+            if len(inflight) >= self.prefetch_factor:
+                finish(inflight.popleft())
+        while inflight:
+            finish(inflight.popleft())
+        return loss
+
+
+class MuonDDP(Optimizer):
+    """Muon for replicated parameters: matrices are split round-robin over ranks, each rank
+    orthogonalises its share and one all-gather per size bucket returns everybody's results."""
+
+    def __init__(self, params, lr: float = 0.02, momentum: float = 0.95, ns_steps: int = 5, wd: float = 0.01,
+                 nesterov: bool = True, group=None):
+        super().__init__(params, dict(lr=lr, momentum=momentum, ns_steps=ns_steps, wd=wd, nesterov=nesterov))
+        self.group = group
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        distributed = dist.is_initialized() and dist.get_world_size(self.group) > 1
+        world = dist.get_world_size(self.group) if distributed else 1
+        rank = dist.get_rank(self.group) if distributed else 0
+        for group in self.param_groups:
+            buckets: dict[tuple, list] = {}
+            for p in group["params"]:
+                if p.grad is not None:
+                    buckets.setdefault(tuple(p.shape), []).append(p)
+            for shape, plist in buckets.items():
+                # pad the bucket so every rank handles the same number of matrices
+                n = (len(plist) + world - 1) // world * world
+                mine = []
+                for j in range(rank, n, world):
+                    if j < len(plist):
+                        p = plist[j]
+                        g = p.grad.reshape(p.shape[0], -1).float()
+                        st = self.state[p]
+                        if "m" not in st:
+                            st["m"] = torch.zeros_like(g)
+                        st["m"].lerp_(g, 1 - group["momentum"])
+                        u = g.lerp(st["m"], group["momentum"]) if group["nesterov"] else st["m"]
+                        mine.append(newton_schulz(u.to(torch.bfloat16), group["ns_steps"]).reshape(-1))
+                    else:
+                        mine.append(torch.zeros(math.prod(shape), device=plist[0].device, dtype=torch.bfloat16))
+                local = torch.stack(mine)  # [n/world, numel]
+                if distributed:
+                    out = torch.empty(world, *local.shape, device=local.device, dtype=local.dtype)
+                    dist.all_gather_into_tensor(out.view(-1, local.shape[1]), local, group=self.group)
+                else:
+                    out = local[None]
+                rows, cols = shape[0], math.prod(shape[1:])
+                scale = max(1.0, rows / cols) ** 0.5
+                for j, p in enumerate(plist):
+                    o = out[j % world, j // world].reshape(p.shape)
+                    p.data.mul_(1 - group["lr"] * group["wd"])
+                    p.data.add_(o.to(p.dtype), alpha=-group["lr"] * scale)
+        return loss

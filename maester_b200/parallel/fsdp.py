@@ -86,12 +86,14 @@ class ShardedModel:
 
     def __init__(self, model: nn.Module, unit_modules: list[tuple[str, nn.Module]], *, device: torch.device,
                  param_dtype: torch.dtype = torch.bfloat16, reduce_dtype: torch.dtype = torch.float32,
-                 shard_group=None, replicate_group=None, gradient_divide_factor: float | None = None):
+                 shard_group=None, replicate_group=None, gradient_divide_factor: float | None = None,
+                 tp_group=None):
         self.model = model
         self.device = device
         self.param_dtype, self.reduce_dtype = param_dtype, reduce_dtype
         self.group = shard_group
         self.replicate_group = replicate_group
+        self.tp_group = tp_group
         self.world = dist.get_world_size(shard_group) if (shard_group is not None and dist.is_initialized()) else 1
         self.rank = dist.get_rank(shard_group) if self.world > 1 else 0
         self.rep_world = dist.get_world_size(replicate_group) if replicate_group is not None else 1
@@ -167,6 +169,8 @@ class ShardedModel:
                 gview = self.full_grad[sl.full_off: sl.full_off + n].view(sl.shape)
                 new = nn.Parameter(view, requires_grad=sl.param.requires_grad)
                 new.main_grad = gview
+                if getattr(sl.param, "tp_replicated", False):
+                    new.tp_replicated = True
                 self._replace_param(sl.param, new)
                 sl.param = new
                 lo, hi = self._own_rows(sl)
@@ -210,8 +214,15 @@ class ShardedModel:
     def init_master_from_full(self) -> None:
         """After ``model.init_weights()`` filled the compute-dtype parameters: broadcast rank 0's
         values (so all ranks agree) and load this rank's rows into the fp32 master shards."""
-        if self.world * self.rep_world > 1:
-            dist.broadcast(self.full, src=0)  # default group spans shard x replicate
+        # ranks that hold the same (tensor-parallel) slice of the model must start identical
+        for g in (self.group, self.replicate_group):
+            if g is not None and dist.get_world_size(g) > 1:
+                dist.broadcast(self.full, group=g, group_src=0)
+        if self.tp_group is not None and dist.get_world_size(self.tp_group) > 1:
+            for u in self.units:
+                for sl in u.slots:
+                    if getattr(sl.param, "tp_replicated", False):
+                        dist.broadcast(sl.param.data, group=self.tp_group, group_src=0)
         for u in self.units:
             for sl in u.slots:
                 lo, hi = self._own_rows(sl)
@@ -257,6 +268,14 @@ class ShardedModel:
         if not u.grads_pending or not self.require_sync:
             return
         u.grads_pending = False
+        tp_sync = self.tp_group is not None and dist.get_world_size(self.tp_group) > 1
+        for sl in u.slots:  # gradients that ordinary autograd left in .grad (plain-PyTorch op path)
+            g = sl.param.grad
+            if g is not None:
+                sl.param.main_grad.add_(g.to(torch.float32))
+                sl.param.grad = None
+            if tp_sync and getattr(sl.param, "tp_replicated", False):
+                dist.all_reduce(sl.param.main_grad, group=self.tp_group)
         if self.world * self.rep_world == 1:
             return
         stream = self.comm_stream
@@ -296,8 +315,12 @@ class ShardedModel:
 
     def finish_backward(self) -> None:
         """Call after ``loss.backward()``: reduces the units whose hooks cannot fire (first block, root)
-        and makes the compute stream wait for all reductions."""
-        self.collect_autograd_grads()
+        and makes the compute stream wait for all reductions.  Without gradient sync (accumulation
+        micro-steps) the gradients are only folded into the accumulation buffer."""
+        if not self.require_sync:
+            self.collect_autograd_grads()
+        if self.world * self.rep_world == 1:
+            self.mark_backward_start()  # no forward hooks are installed without data parallelism
         for u in self.units:
             self._reduce_unit(u)
         if self.comm_stream is not None:

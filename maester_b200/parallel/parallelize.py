@@ -122,6 +122,7 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
         model, transformer_blocks(model), device=device, param_dtype=param_dtype, reduce_dtype=reduce_dtype,
         shard_group=shard_group, replicate_group=rep_group,
         gradient_divide_factor=float(parallel_dims.fsdp_gradient_divide_factor),
+        tp_group=parallel_dims.mesh_group("tp") if parallel_dims.tp_enabled else None,
     )
     sharded.device_mesh = world_mesh["dp_shard_cp"] if (shard_group is not None and world_mesh is not None) else None
     object.__setattr__(model, "_sharded", sharded)

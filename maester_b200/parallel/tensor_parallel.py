@@ -1,0 +1,239 @@
+"""Tensor parallelism with sequence parallelism and loss parallelism.
+
+Reference plan (maester/parallelisms/parallelize_llama.py:107-181): ``wq/wk/wv/w1/w3`` column-parallel,
+``wo/w2`` row-parallel with sequence-sharded outputs (reduce-scatter along the sequence), norms and
+residual stream on sequence shards, all-gather along the sequence in front of attention and FFN,
+``output`` column-parallel with vocabulary-sharded logits feeding a loss that exchanges per-row
+(max, sum-exp, target logit).  The reference expresses this with DTensor styles; here the model code
+calls the four communication primitives below explicitly, each an autograd function whose backward
+is the mirrored collective, and ``apply_tp`` re-shapes the parameters of a model that still lives on
+the meta device.
+
+Embedding and norm weights are replicated across the TP group and see only this rank's sequence
+slice, so their gradients are summed over the group after backward (``tp_replicated`` flag, handled
+by the sharding runtime).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from maester_b200.log_utils import logger
+
+
+@dataclass
+class TPInfo:
+    group: object
+    size: int
+    rank: int
+    loss_parallel: bool = True
+
+
+# ------------------------------------------------------------------------------ primitives
+def _all_gather_seq(x: torch.Tensor, tp: TPInfo) -> torch.Tensor:
+    """[B, S/tp, D] → [B, S, D]."""
+    B, s, D = x.shape
+    out = torch.empty(tp.size, B, s, D, device=x.device, dtype=x.dtype)
+    dist.all_gather_into_tensor(out.view(-1), x.contiguous().view(-1), group=tp.group)
+    return out.permute(1, 0, 2, 3).reshape(B, tp.size * s, D)
+
+
+def _reduce_scatter_seq(x: torch.Tensor, tp: TPInfo) -> torch.Tensor:
+    """Sum over the group of [B, S, D], keep this rank's sequence slice [B, S/tp, D]."""
+    B, S, D = x.shape
+    s = S // tp.size
+    inp = x.reshape(B, tp.size, s, D).permute(1, 0, 2, 3).contiguous()
+    out = torch.empty(B, s, D, device=x.device, dtype=x.dtype)
+    dist.reduce_scatter_tensor(out.view(-1), inp.view(-1), op=dist.ReduceOp.SUM, group=tp.group)
+    return out
+
+
+class _GatherSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _all_gather_seq(x, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _reduce_scatter_seq(g, ctx.tp), None
+
+
+class _ReduceScatterSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _reduce_scatter_seq(x, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_seq(g, ctx.tp), None
+
+
+class _ScatterSeq(torch.autograd.Function):
+    """Keep this rank's sequence slice of a replicated tensor; backward all-gathers the slices."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        s = x.shape[1] // tp.size
+        return x[:, tp.rank * s:(tp.rank + 1) * s].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return _all_gather_seq(g, ctx.tp), None
+
+
+def gather_seq(x: torch.Tensor, tp: TPInfo | None) -> torch.Tensor:
+    return x if tp is None or tp.size == 1 else _GatherSeq.apply(x, tp)
+
+
+def reduce_scatter_seq(x: torch.Tensor, tp: TPInfo | None) -> torch.Tensor:
+    return x if tp is None or tp.size == 1 else _ReduceScatterSeq.apply(x, tp)
+
+
+def scatter_seq(x: torch.Tensor, tp: TPInfo | None) -> torch.Tensor:
+    return x if tp is None or tp.size == 1 else _ScatterSeq.apply(x, tp)
+
+
+# ------------------------------------------------------------------------------ loss parallel
+class _VocabParallelCE(torch.autograd.Function):
+    """Mean CE over vocabulary-sharded logits ``h @ W_localᵀ`` (W_local = rows [v0, v0+Vl) of W).
+
+    Per chunk of rows: local logits, local log-sum-exp and target logit, two small all-reduces over
+    the TP group to form the global log-sum-exp and target logit, then the local gradient
+    ``softmax_global − onehot``.  Backward turns the kept gradient chunks into dH and dW_local.
+    """
+
+    CHUNK = 4096
+
+    @staticmethod
+    def forward(ctx, h, w, labels, tp: TPInfo):
+        M, D = h.shape
+        Vl = w.shape[0]
+        v0 = tp.rank * Vl
+        labels = labels.reshape(-1)
+        valid = labels != -100
+        nvalid = valid.sum().clamp_min(1).float()
+        local = (labels >= v0) & (labels < v0 + Vl) & valid
+        loss_sum = h.new_zeros((), dtype=torch.float32)
+        grads = []
+        for r0 in range(0, M, _VocabParallelCE.CHUNK):
+            r1 = min(M, r0 + _VocabParallelCE.CHUNK)
+            logits = torch.nn.functional.linear(h[r0:r1], w).float() if not h.is_cuda else _native_logits(h[r0:r1], w)
+            m_loc = logits.max(dim=1).values
+            m_glob = m_loc.clone()
+            dist.all_reduce(m_glob, op=dist.ReduceOp.MAX, group=tp.group)
+            e = torch.exp(logits - m_glob[:, None])
+            stats = torch.stack([e.sum(dim=1), torch.zeros_like(m_loc)])
+            lab = (labels[r0:r1] - v0).clamp(0, Vl - 1)
+            tgt = logits.gather(1, lab[:, None]).squeeze(1)
+            stats[1] = torch.where(local[r0:r1], tgt, torch.zeros_like(tgt))
+            dist.all_reduce(stats, op=dist.ReduceOp.SUM, group=tp.group)
+            lse = m_glob + stats[0].log()
+            v = valid[r0:r1]
+            loss_sum = loss_sum + torch.where(v, lse - stats[1], torch.zeros_like(lse)).sum()
+            g = e / stats[0][:, None]
+            g.scatter_add_(1, lab[:, None], -local[r0:r1].to(g.dtype)[:, None])
+            g = g * (v.to(g.dtype) / nvalid)[:, None]
+            grads.append(g.to(h.dtype))
+        ctx.save_for_backward(h, w, *grads)
+        ctx.tp = tp
+        return loss_sum / nvalid
+
+    @staticmethod
+    def backward(ctx, gout):
+        h, w, *grads = ctx.saved_tensors
+        dh = torch.empty_like(h)
+        mg = getattr(w, "main_grad", None)
+        dw = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        for i, r0 in enumerate(range(0, h.shape[0], _VocabParallelCE.CHUNK)):
+            g = grads[i]
+            r1 = r0 + g.shape[0]
+            dh[r0:r1] = ((g.float() @ w.float()) * gout).to(h.dtype)
+            dw.add_((g.float().t() @ h[r0:r1].float()) * gout)
+        # dH is a partial sum over the vocabulary shards
+        dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=ctx.tp.group)
+        return dh, (None if mg is not None else dw.to(w.dtype)), None, None
+
+
+def _native_logits(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    from maester_b200 import ops
+    if ops.use_native(h, w):
+        from maester_b200.ops import cuda as C
+        return C.gemm(h.contiguous(), w, epi=C.EPI_F32)
+    return torch.nn.functional.linear(h, w).float()
+
+
+def vocab_parallel_cross_entropy(h: torch.Tensor, w_local: torch.Tensor, labels: torch.Tensor, tp: TPInfo):
+    return _VocabParallelCE.apply(h.reshape(-1, h.shape[-1]), w_local, labels, tp)
+
+
+# ------------------------------------------------------------------------------ applying the plan
+def _reshape_linear(lin: nn.Module, out_features: int, in_features: int) -> None:
+    lin.weight = nn.Parameter(torch.empty(out_features, in_features, device=lin.weight.device,
+                                          dtype=lin.weight.dtype))
+    lin.in_features, lin.out_features = in_features, out_features
+
+
+def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
+    """Shard a Llama-family ``Transformer`` over the ``tp`` mesh dimension (model still on meta)."""
+    from maester_b200.models.llama.model import Transformer
+
+    if not isinstance(model, Transformer):
+        raise NotImplementedError(
+            f"tensor parallelism is implemented for the Llama family; got {type(model).__name__}")
+    group = parallel_dims.mesh_group("tp")
+    tp = TPInfo(group, dist.get_world_size(group), dist.get_rank(group), parallel_dims.loss_parallel_enabled)
+    a = model.model_args
+    n_kv = a.n_kv_heads or a.n_heads
+    assert a.n_heads % tp.size == 0 and n_kv % tp.size == 0, "heads must divide by the TP degree"
+    assert a.vocab_size % tp.size == 0, "vocabulary must divide by the TP degree"
+    for layer in model.layers.values():
+        att, ff = layer.attention, layer.feed_forward
+        hd = att.head_dim
+        att.n_heads //= tp.size
+        att.n_kv_heads //= tp.size
+        _reshape_linear(att.wq, att.n_heads * hd, a.dim)
+        _reshape_linear(att.wk, att.n_kv_heads * hd, a.dim)
+        _reshape_linear(att.wv, att.n_kv_heads * hd, a.dim)
+        _reshape_linear(att.wo, a.dim, att.n_heads * hd)
+        hidden = ff.w1.out_features
+        assert hidden % tp.size == 0
+        _reshape_linear(ff.w1, hidden // tp.size, a.dim)
+        _reshape_linear(ff.w3, hidden // tp.size, a.dim)
+        _reshape_linear(ff.w2, a.dim, hidden // tp.size)
+        layer.tp = tp
+        for norm in (layer.attention_norm, layer.ffn_norm):
+            for p in norm.parameters():
+                p.tp_replicated = True
+    if not a.tied_embeddings:
+        _reshape_linear(model.output, a.vocab_size // tp.size, a.dim)
+    model.tok_embeddings.weight.tp_replicated = True
+    for p in model.norm.parameters():
+        p.tp_replicated = True
+    model.tp = tp
+    logger.info(f"Applied tensor parallelism (degree {tp.size}, sequence parallel, "
+                f"loss parallel={tp.loss_parallel})")
+
+
+# ------------------------------------------------------------------------------ checkpoints / tests
+_COLWISE = ("attention.wq.", "attention.wk.", "attention.wv.", "feed_forward.w1.", "feed_forward.w3.", "output.")
+_ROWWISE = ("attention.wo.", "feed_forward.w2.")
+
+
+def tp_slice_state_dict(full_state: dict[str, torch.Tensor], tp_size: int, tp_rank: int) -> dict[str, torch.Tensor]:
+    """This rank's tensor-parallel slices of an unsharded Llama state dict (column-parallel weights
+    split on dim 0, row-parallel on dim 1, everything else replicated)."""
+    out = {}
+    for k, v in full_state.items():
+        if any(t in k for t in _COLWISE) and v.dim() == 2:
+            out[k] = v.chunk(tp_size, dim=0)[tp_rank].contiguous()
+        elif any(t in k for t in _ROWWISE) and v.dim() == 2:
+            out[k] = v.chunk(tp_size, dim=1)[tp_rank].contiguous()
+        else:
+            out[k] = v
+    return out

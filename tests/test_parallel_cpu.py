@@ -1,0 +1,173 @@
+"""Multi-process (gloo, CPU) checks of the sharding runtime, tensor parallelism and the trainer."""
+import copy
+import os
+import socket
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from maester_b200.config import Config
+
+ADAMW = [{"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3, "betas": (0.9, 0.95), "weight_decay": 0.1, "eps": 1e-6},
+          "min_dim": 0}]
+
+
+def _close(a, b, tol=5e-3):
+    """Adam turns rounding-level gradient differences into +-lr steps on near-zero-gradient entries,
+    so compare in the Frobenius norm rather than element-wise."""
+    return ((a - b).norm() / (b.norm() + 1e-12)).item() < tol
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn, args, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        res = fn(rank, world, *args)
+        torch.save(res, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def run_ranks(world, fn, *args):
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker, args=(world, _free_port(), fn, args, d), nprocs=world, join=True)
+        return [torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False) for r in range(world)]
+
+
+def _cfg(**kw):
+    base = dict(model_name="llama3", flavor="tiny", seq_len=64, train_batch_size=2, enable_checkpoint=False,
+                synthetic_vocab_size=512, optimizer_groups=ADAMW, scheduler="constant", ac_mode="none",
+                data_parallel_shard_degree=1)
+    base.update(kw)
+    return Config(**base)
+
+
+def _full_weights(cfg):
+    """Deterministic unsharded fp32 weights for the tiny model."""
+    from maester_b200.trainer import build_model_args
+    from maester_b200.models import model_name_to_cls
+    torch.manual_seed(1234)
+    args = build_model_args(cfg, cfg.synthetic_vocab_size)
+    model = model_name_to_cls[cfg.model_name].from_model_args(args)
+    if hasattr(model, "init_weights"):
+        model.init_weights()
+    return {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
+def _load_full(trainer, full, tp=None):
+    from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
+    sd = tp_slice_state_dict(full, tp[0], tp[1]) if tp else full
+    sh = trainer.sharded
+    with torch.no_grad():
+        for u in sh.units:
+            for sl in u.slots:
+                sl.param.data.copy_(sd[sl.fqn])
+    sh.init_master_from_full()
+
+
+def _batches(n, bs, seq, vocab, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        t = torch.randint(2, vocab, (bs, seq + 1), generator=g)
+        out.append({"input_ids": t[:, :-1].contiguous(), "labels": t[:, 1:].contiguous()})
+    return out
+
+
+def _single(cfg, full, batches):
+    from maester_b200.trainer import Trainer
+    tr = Trainer(cfg)
+    _load_full(tr, full)
+    losses = [tr.train_step(b).item() for b in batches]
+    return losses, {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+def _fsdp_rank(rank, world, cfg_kw, full, batches):
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_cfg(**cfg_kw))
+    _load_full(tr, full)
+    losses = []
+    for b in batches:
+        mine = {k: v[rank * 2:(rank + 1) * 2] for k, v in b.items()}  # this rank's half of the global batch
+        losses.append(tr.train_step(mine).item())
+    return losses, {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+@pytest.mark.parametrize("mode", ["shard", "replicate"])
+def test_two_rank_data_parallel_matches_single_process(mode):
+    cfg1 = _cfg(train_batch_size=4)
+    full = _full_weights(cfg1)
+    batches = _batches(3, 4, 64, 512)
+    want_losses, want_params = _single(cfg1, full, batches)
+    kw = dict(data_parallel_shard_degree=2) if mode == "shard" else \
+        dict(data_parallel_shard_degree=1, data_parallel_replicate_degree=2)
+    res = run_ranks(2, _fsdp_rank, kw, full, batches)
+    for r in range(2):
+        losses, params = res[r]
+        for k in want_params:
+            assert _close(params[k], want_params[k]), (mode, k)
+    mean_losses = [(a + b) / 2 for a, b in zip(res[0][0], res[1][0])]
+    assert mean_losses == pytest.approx(want_losses, abs=1e-4)
+
+
+def _tp_rank(rank, world, full, batches):
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_cfg(tensor_parallel_degree=2, data_parallel_shard_degree=1))
+    _load_full(tr, full, tp=(2, rank))
+    losses = [tr.train_step(b).item() for b in batches]
+    return losses, {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+def test_tensor_parallel_matches_single_process():
+    from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
+    cfg1 = _cfg(tied_override=None) if False else _cfg()
+    # the tiny flavor ties embeddings; use an untied variant so the loss-parallel path is exercised
+    full = _full_weights(_cfg(flavor="debugmodel", seq_len=64))
+    batches = _batches(2, 2, 64, 512)
+    want_losses, want_params = _single(_cfg(flavor="debugmodel"), full, batches)
+    res = run_ranks(2, _tp_rank_debug, full, batches)
+    for r in range(2):
+        losses, params = res[r]
+        assert losses == pytest.approx(want_losses, abs=1e-4)
+        want = tp_slice_state_dict(want_params, 2, r)
+        for k in want:
+            assert _close(params[k], want[k]), k
+
+
+def _tp_rank_debug(rank, world, full, batches):
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_cfg(flavor="debugmodel", tensor_parallel_degree=2, data_parallel_shard_degree=1))
+    _load_full(tr, full, tp=(2, rank))
+    losses = [tr.train_step(b).item() for b in batches]
+    return losses, {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+def _accum_rank(rank, world, full, batches):
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_cfg(data_parallel_shard_degree=2, gradient_accumulation_steps=2))
+    _load_full(tr, full)
+    micro = [{k: v[rank * 2:(rank + 1) * 2] for k, v in b.items()} for b in batches]
+    loss = tr.train_step(micro).item()
+    return loss, {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+def test_gradient_accumulation_equals_one_big_batch():
+    cfg1 = _cfg(train_batch_size=8)
+    full = _full_weights(cfg1)
+    b = _batches(2, 4, 64, 512)
+    big = {k: torch.cat([b[0][k], b[1][k]]) for k in b[0]}
+    _, want = _single(cfg1, full, [big])
+    res = run_ranks(2, _accum_rank, full, b)
+    for k in want:
+        assert _close(res[0][1][k], want[k]), k
