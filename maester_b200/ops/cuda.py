@@ -208,6 +208,26 @@ def adamw(p, g, m, v, lp, chunks, tensors, nchunks, lr_t, beta1, beta2, eps, ste
                             float(grad_scale), int(zero_grad), _stream()), "adamw")
 
 
+def fused_rs_adamw_ag(symm_grad, symm_full, master, m, v, shard_grad_out, chunks, tensors, nchunks, lr_t, beta1,
+                      beta2, eps, step, divide: float) -> None:
+    """Reduce-scatter + AdamW + all-gather in one kernel over peer memory (``symm_*``: SymmBuffer)."""
+    bc1 = 1.0 - beta1 ** step
+    bc2s = math.sqrt(1.0 - beta2 ** step)
+    use_mc = bool(symm_grad.multicast_ptr and symm_full.multicast_ptr)
+    _ck(_lib.lib().mb_fused_rs_adamw_ag(
+        symm_grad.multicast_ptr if use_mc else None, symm_full.multicast_ptr if use_mc else None,
+        symm_grad.ptr_array, symm_full.ptr_array, symm_grad.world, master.data_ptr(), m.data_ptr(), v.data_ptr(),
+        _ptr(shard_grad_out), chunks.data_ptr(), tensors.data_ptr(), nchunks, lr_t.data_ptr(), beta1, beta2, eps,
+        bc1, bc2s, 1.0 / divide, _stream()), "fused_rs_adamw_ag")
+
+
+def push_shards(master: torch.Tensor, symm_full, chunks: torch.Tensor, nchunks: int) -> None:
+    """bf16 copy of this rank's fp32 shard into every rank's param-major parameter buffer."""
+    mc = symm_full.multicast_ptr or None
+    _ck(_lib.lib().mb_push_shards(master.data_ptr(), mc, symm_full.ptr_array, symm_full.world, chunks.data_ptr(),
+                                  nchunks, _stream()), "push_shards")
+
+
 def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:
     _ck(_lib.lib().mb_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), _stream()), "cast")
 

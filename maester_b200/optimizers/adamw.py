@@ -92,8 +92,19 @@ class FusedAdamW(Optimizer):
             st_step = int(st["step"].item()) + 1 if torch.is_tensor(st["step"]) else int(st["step"]) + 1
             (chunks, tensors, nch), lr_t = self._table()
             b1, b2 = g0["betas"]
-            C.adamw(f["master"], f["grad"], f["m"], f["v"], f["lowp"], chunks, tensors, nch, lr_t, b1, b2,
-                    g0["eps"], st_step)
+            sharded = f.get("sharded")
+            if sharded is not None and sharded.fused:
+                # reduce-scatter + update + all-gather in one kernel over the peers' buffers
+                if f.get("fused_table") is None or f["fused_table"][0] is not chunks:
+                    order = [p for g in self.param_groups for p in g["params"]]
+                    tensor_of = {id(p): i for i, p in enumerate(order)}
+                    f["fused_table"] = (chunks, sharded.fused_chunk_table(order, tensor_of))
+                fchunks, fn = f["fused_table"][1]
+                C.fused_rs_adamw_ag(sharded.symm_grad, sharded.symm_full, f["master"], f["m"], f["v"], f["grad"],
+                                    fchunks, tensors, fn, lr_t, b1, b2, g0["eps"], st_step, sharded.divide)
+            else:
+                C.adamw(f["master"], f["grad"], f["m"], f["v"], f["lowp"], chunks, tensors, nch, lr_t, b1, b2,
+                        g0["eps"], st_step)
             for g in self.param_groups:
                 for p in g["params"]:
                     self.state[p]["step"] = torch.tensor(float(st_step))

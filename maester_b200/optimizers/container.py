@@ -49,10 +49,15 @@ class OptimizersContainer(Optimizer, Stateful):
     # -- stepping
     def step(self, closure=None):  # hooks registered on the container wrap this method
         loss = None
+        sharded = getattr(self.model, "_sharded", None)
+        if sharded is not None and sharded.fused:
+            if not all(isinstance(o, FusedAdamW) and o._flat is not None for o in self.optimizers):
+                raise RuntimeError("fused_collectives=True needs every optimizer group to be AdamW; "
+                                   "set fused_collectives=False to use other optimizers")
+            sharded.pre_optimizer_step()
         for opt in self.optimizers:
             out = opt.step(closure) if closure is not None else opt.step()
             loss = out if out is not None else loss
-        sharded = getattr(self.model, "_sharded", None)
         if sharded is not None:
             sharded.lowp_fresh = sharded.device.type == "cuda" and all(
                 isinstance(o, FusedAdamW) and o._flat is not None for o in self.optimizers)
@@ -147,6 +152,7 @@ def _make_optimizer(opt_class, params_or_groups, opt_cfg: dict, model) -> Optimi
             sharded.adam_m = torch.zeros_like(sharded.master)
             sharded.adam_v = torch.zeros_like(sharded.master)
         opt.attach_flat(sharded.master, sharded.shard_grad, sharded.shard_lp, mine, sharded.adam_m, sharded.adam_v)
+        opt._flat["sharded"] = sharded
     return opt
 
 

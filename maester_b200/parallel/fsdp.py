@@ -87,7 +87,7 @@ class ShardedModel:
     def __init__(self, model: nn.Module, unit_modules: list[tuple[str, nn.Module]], *, device: torch.device,
                  param_dtype: torch.dtype = torch.bfloat16, reduce_dtype: torch.dtype = torch.float32,
                  shard_group=None, replicate_group=None, gradient_divide_factor: float | None = None,
-                 tp_group=None):
+                 tp_group=None, fused_comm: bool = False):
         self.model = model
         self.device = device
         self.param_dtype, self.reduce_dtype = param_dtype, reduce_dtype
@@ -135,12 +135,26 @@ class ShardedModel:
         self.full_numel, self.shard_numel = f, s
 
         # ---- buffers
-        self.full = torch.zeros(f, dtype=param_dtype, device=device)
+        self.fused = False
+        self.symm_full = self.symm_grad = None
+        if fused_comm and self.world > 1 and self.rep_world == 1 and param_dtype == torch.bfloat16 and all(
+                sl.padded_numel % 4 == 0 for u in self.units for sl in u.slots):
+            from maester_b200.parallel.symm import SymmBuffer, symmetric_memory_available
+            if symmetric_memory_available(shard_group):
+                try:
+                    self.symm_full = SymmBuffer(f, param_dtype, device, shard_group)
+                    self.symm_grad = SymmBuffer(f, torch.float32, device, shard_group)
+                    self.fused = True
+                except Exception as e:  # noqa: BLE001  (no peer access, unsupported driver, ...)
+                    logger.warning(f"symmetric memory unavailable, using NCCL collectives: {e}")
+                    self.symm_full = self.symm_grad = None
+        self.full = self.symm_full.tensor.zero_() if self.fused else torch.zeros(f, dtype=param_dtype, device=device)
         self.master = torch.zeros(s, dtype=torch.float32, device=device)
         self.shard_grad = torch.zeros(s, dtype=torch.float32, device=device)
         if self.world > 1:
-            self.full_grad = torch.zeros(f, dtype=torch.float32, device=device)
-            self.shard_lp = torch.zeros(s, dtype=param_dtype, device=device)
+            self.full_grad = self.symm_grad.tensor.zero_() if self.fused else \
+                torch.zeros(f, dtype=torch.float32, device=device)
+            self.shard_lp = torch.zeros(s if not self.fused else 1, dtype=param_dtype, device=device)
         else:
             self.full_grad = self.shard_grad  # identical geometry with one rank
             self.shard_lp = self.full
@@ -276,8 +290,8 @@ class ShardedModel:
                 sl.param.grad = None
             if tp_sync and getattr(sl.param, "tp_replicated", False):
                 dist.all_reduce(sl.param.main_grad, group=self.tp_group)
-        if self.world * self.rep_world == 1:
-            return
+        if self.world * self.rep_world == 1 or self.fused:
+            return  # fused mode: the optimizer kernel reduces straight from the peers' gradient buffers
         stream = self.comm_stream
         if stream is not None:
             stream.wait_stream(torch.cuda.current_stream())
@@ -330,6 +344,15 @@ class ShardedModel:
     def gather_params(self) -> None:
         """After the optimizer step: cast the updated master shards and all-gather them into ``full``,
         one unit at a time on the side stream; forward pre-hooks wait per unit."""
+        if self.fused:
+            if not self.lowp_fresh:  # no fused optimizer step wrote the parameters: push the shards
+                from maester_b200.ops import cuda as C
+                chunks, n = self.fused_chunk_table()
+                self.symm_full.barrier()
+                C.push_shards(self.master, self.symm_full, chunks, n)
+            self.lowp_fresh = False
+            self.symm_full.barrier()  # every rank's stores have landed before anyone's next forward
+            return
         if not self.lowp_fresh:
             self.shard_lp.copy_(self.master) if self.world > 1 else self.full.copy_(self.master)
         self.lowp_fresh = False
@@ -354,6 +377,32 @@ class ShardedModel:
                 if stream is not None:
                     u.gather_event = torch.cuda.Event()
                     u.gather_event.record(stream)
+
+    # ------------------------------------------------------------------ fused (peer-memory) mode
+    def fused_chunk_table(self, params=None, tensor_of=None):
+        """Chunk records {shard offset, full offset of this rank's rows, length, tensor index} for the
+        fused kernels, for all parameters or for the given master parameters."""
+        import numpy as np
+
+        recs = []
+        wanted = None if params is None else {id(p) for p in params}
+        for u in self.units:
+            for sl in u.slots:
+                if wanted is not None and id(sl.master) not in wanted:
+                    continue
+                ti = 0 if tensor_of is None else tensor_of[id(sl.master)]
+                full0 = sl.full_off + self.rank * sl.padded_numel
+                for c0 in range(0, sl.padded_numel, 32768):
+                    recs.append((sl.shard_off + c0, full0 + c0, min(32768, sl.padded_numel - c0), ti))
+        arr = np.zeros(len(recs), dtype=np.dtype([("s", "<i8"), ("f", "<i8"), ("len", "<i4"), ("t", "<i4")]))
+        for i, r in enumerate(recs):
+            arr[i] = r
+        return torch.from_numpy(arr.view(np.uint8).copy()).to(self.device), len(recs)
+
+    def pre_optimizer_step(self) -> None:
+        """Fused mode: all ranks' gradient buffers must be complete before any rank reduces them."""
+        if self.fused:
+            self.symm_grad.barrier()
 
     @torch.no_grad()
     def zero_grad(self) -> None:

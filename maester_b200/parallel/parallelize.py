@@ -123,6 +123,9 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
         shard_group=shard_group, replicate_group=rep_group,
         gradient_divide_factor=float(parallel_dims.fsdp_gradient_divide_factor),
         tp_group=parallel_dims.mesh_group("tp") if parallel_dims.tp_enabled else None,
+        # the fused reduce-scatter + AdamW + all-gather kernel only exists for AdamW groups
+        fused_comm=bool(cfg.fused_collectives) and device.type == "cuda" and all(
+            str(g.get("opt_class", "")).endswith("AdamW") for g in cfg.optimizer_groups),
     )
     sharded.device_mesh = world_mesh["dp_shard_cp"] if (shard_group is not None and world_mesh is not None) else None
     object.__setattr__(model, "_sharded", sharded)

@@ -1,0 +1,70 @@
+"""Two-GPU check: the fused reduce-scatter + AdamW + all-gather kernel (peer memory / NVLS multimem)
+must train like the NCCL reduce-scatter / all-gather path."""
+import os
+import socket
+import tempfile
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+ADAMW = [{"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3, "betas": (0.9, 0.95), "weight_decay": 0.1},
+          "min_dim": 2, "exclude_names": ["tok_embeddings"]},
+         {"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3, "betas": (0.9, 0.95), "weight_decay": 0.0},
+          "min_dim": 0}]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from maester_b200.config import Config
+    from maester_b200.datasets.synthetic import SyntheticLoader
+    from maester_b200.ops import cuda as C
+    from maester_b200.trainer import Trainer
+    results = {}
+    for fused in (False, True):
+        torch.manual_seed(0)
+        cfg = Config(model_name="gemma3", flavor="debug", seq_len=512, train_batch_size=2,
+                     data_parallel_shard_degree=world, ac_mode="selective", enable_checkpoint=False,
+                     optimizer_groups=ADAMW, scheduler="constant", fused_collectives=fused)
+        tr = Trainer(cfg)
+        assert tr.sharded.fused == fused, "fused mode was not enabled" if fused else "unexpected fused mode"
+        loader = SyntheticLoader(2, 512, tr.model_args.vocab_size, "uniform:16:256", seed=3, rank=rank)
+        losses = [tr.train_step(next(loader)).item() for _ in range(4)]
+        C.check_status()
+        results[fused] = (losses, tr.sharded.full.float().clone(), tr.sharded.master.clone(),
+                          bool(tr.sharded.symm_grad.multicast_ptr) if fused else False)
+        del tr
+    torch.save({k: (v[0], v[3]) for k, v in results.items()}, os.path.join(out_dir, f"r{rank}.pt"))
+    a, b = results[False], results[True]
+    rel_full = ((a[1] - b[1]).norm() / a[1].norm()).item()
+    rel_master = ((a[2] - b[2]).norm() / a[2].norm()).item()
+    torch.save((rel_full, rel_master), os.path.join(out_dir, f"rel{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_optimizer_collective_matches_nccl_path():
+    world = 2
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker, args=(world, _free_port(), d), nprocs=world, join=True)
+        for r in range(world):
+            res = torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False)
+            rel_full, rel_master = torch.load(os.path.join(d, f"rel{r}.pt"), weights_only=False)
+            nccl_losses, fused_losses = res[False][0], res[True][0]
+            print(f"rank {r}: nccl {nccl_losses} fused {fused_losses} multicast={res[True][1]} "
+                  f"rel_full={rel_full:.2e} rel_master={rel_master:.2e}")
+            assert fused_losses == pytest.approx(nccl_losses, abs=2e-2)
+            assert rel_master < 2e-3 and rel_full < 5e-3
