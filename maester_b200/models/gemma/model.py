@@ -100,6 +100,9 @@ class GemmaMLP(nn.Module):
 
 
 class GemmaAttention(nn.Module):
+    cp_capable = True  # context parallelism may set .cp on instances
+    cp = None
+
     def __init__(self, config: ModelArgs, attn_type: str):
         super().__init__()
         self.num_heads = config.n_heads
@@ -121,8 +124,9 @@ class GemmaAttention(nn.Module):
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids):
         qkv = self.qkv_proj(x)
         window = self.sliding_window_size if (self.attn_type == "local_sliding" and self.sliding_window_size) else None
-        out = ops.attention_block(
-            qkv,
+        from maester_b200.parallel.context_parallel import attention as cp_aware_attention
+        out = cp_aware_attention(
+            self, qkv,
             self.query_norm.weight if self.query_norm is not None else None,
             self.key_norm.weight if self.key_norm is not None else None,
             position_ids, inv_freq, rope_cs, document_ids,

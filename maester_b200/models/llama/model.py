@@ -82,11 +82,15 @@ class Attention(nn.Module):
             nn.init.normal_(lin.weight, mean=0.0, std=init_std)
 
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids, residual=None):
+        from maester_b200.parallel.context_parallel import attention as cp_aware_attention
         qkv = ops.linear(x, self._wqkv.get())
-        out = ops.attention_block(qkv, None, None, position_ids, inv_freq, rope_cs, document_ids,
-                                  self.n_heads, self.n_kv_heads, self.head_dim, layout="interleaved",
-                                  scale=self.attn_scale, causal=True, window=None)
+        out = cp_aware_attention(self, qkv, None, None, position_ids, inv_freq, rope_cs, document_ids,
+                                 self.n_heads, self.n_kv_heads, self.head_dim, layout="interleaved",
+                                 scale=self.attn_scale, causal=True, window=None)
         return self.wo(out, residual=residual)
+
+    cp_capable = True  # context parallelism may set .cp on instances
+    cp = None
 
 
 class FeedForward(nn.Module):

@@ -83,6 +83,10 @@ class Trainer:
         logger.info(f"Model {cfg.model_name} {cfg.flavor} size: {self.nparams:,} total parameters")
         self.peak_flops = get_peak_flops(torch.cuda.get_device_name(self.device)) if self.device.type == "cuda" else 312e12
         model_name_to_parallelize[cfg.model_name](self.model, self.world_mesh, pd, cfg)
+        self.cp = None
+        if pd.cp_enabled:
+            from maester_b200.parallel.context_parallel import apply_cp
+            self.cp = apply_cp(self.model, pd)
         materialize(self.model)
         self.sharded = getattr(self.model, "_sharded", None)
         self.optimizers = model_name_to_optimizers_builder[cfg.model_name](self.model, cfg, pd)
@@ -106,6 +110,9 @@ class Trainer:
         if self.sharded is not None and self.grad_accum > 1:
             self.sharded.set_requires_gradient_sync(sync)
         b = self.to_device(batch)
+        if self.cp is not None:
+            from maester_b200.parallel.context_parallel import shard_batch_for_cp
+            b = shard_batch_for_cp(b, self.cp)
         if cfg.enable_cut_cross_entropy:
             loss = self.model(b["input_ids"], b["labels"], position_ids=b.get("position_ids"),
                               document_ids=b.get("document_ids"))
