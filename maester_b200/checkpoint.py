@@ -34,16 +34,26 @@ class IntervalType(enum.Enum):
     STEPS = enum.auto()
 
 
-def _as_dtensor(local: torch.Tensor, full_shape, sharded) -> torch.Tensor:
-    """Present this rank's dim-0 rows as a DTensor (plain tensor when the model is not distributed)."""
-    mesh = getattr(sharded, "device_mesh", None)
-    if sharded is None or sharded.world == 1 or mesh is None:
-        return local
+def _as_dtensor(local: torch.Tensor, slot, sharded) -> torch.Tensor:
+    """Present this rank's dim-0 rows as a DTensor (plain tensor when the model is not distributed).
+    Expert-parallel tensors are sharded twice along dim 0: over ``ep``, then over the ranks that hold
+    the same experts."""
     from torch.distributed.tensor import DTensor, Shard
 
-    shape = torch.Size(full_shape)
+    if sharded is not None and slot.dom == 1:
+        mesh = getattr(sharded, "expert_mesh", None)
+        if mesh is None:
+            return local
+        from torch.distributed.tensor.placement_types import _StridedShard
+        placements = [_StridedShard(0, split_factor=mesh.size(1)), Shard(0)]
+    else:
+        mesh = getattr(sharded, "device_mesh", None)
+        if sharded is None or sharded.world == 1 or mesh is None:
+            return local
+        placements = [Shard(0)]
+    shape = slot.global_shape
     stride = torch.empty(shape, device="meta").stride()
-    return DTensor.from_local(local, mesh, [Shard(0)], run_check=False, shape=shape, stride=stride)
+    return DTensor.from_local(local, mesh, placements, run_check=False, shape=shape, stride=stride)
 
 
 class ModelWrapper(Stateful):
@@ -60,7 +70,7 @@ class ModelWrapper(Stateful):
             return out
         for u in sharded.units:
             for sl in u.slots:
-                out[sl.fqn] = _as_dtensor(sl.master.data, sl.shape, sharded)
+                out[sl.fqn] = _as_dtensor(sl.master.data, sl, sharded)
         for name, buf in self.model.named_buffers():
             mod_name, _, leaf = name.rpartition(".")
             owner = self.model.get_submodule(mod_name) if mod_name else self.model
@@ -87,13 +97,13 @@ class OptimizerWrapper(Stateful):
         flat = self.optimizer.state_dict()
         if sharded is None:
             return flat
-        shapes = {sl.fqn: sl.shape for u in sharded.units for sl in u.slots}
+        slots = {sl.fqn: sl for u in sharded.units for sl in u.slots}
         out: dict[str, Any] = {}
         for k, v in flat.items():
             if torch.is_tensor(v) and v.dim() > 0 and ".state." in f".{k}":
                 fqn = k.split("state.", 1)[1].rsplit(".", 1)[0]
-                if fqn in shapes and v.shape[1:] == shapes[fqn][1:]:
-                    v = _as_dtensor(v, shapes[fqn], sharded)
+                if fqn in slots and v.shape[1:] == slots[fqn].shape[1:]:
+                    v = _as_dtensor(v, slots[fqn], sharded)
             out[k] = v
         return out
 

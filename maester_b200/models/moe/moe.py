@@ -68,6 +68,8 @@ class GroupedExperts(nn.Module):
     def __init__(self, dim: int, hidden_dim: int, num_experts: int, use_grouped_mm: bool = True):
         super().__init__()
         self.num_experts, self.use_grouped_mm = num_experts, use_grouped_mm
+        # expert parallelism replaces the parameters by this rank's E/ep experts and sets these
+        self.num_local_experts, self.ep_rank, self.ep_size = num_experts, 0, 1
         self.w1 = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
         self.w2 = nn.Parameter(torch.empty(num_experts, hidden_dim, dim))
         self.w3 = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
@@ -80,9 +82,14 @@ class GroupedExperts(nn.Module):
         return grouped_linear(act, self.w2, offs)
 
     def init_weights(self, init_std: float) -> None:
-        nn.init.trunc_normal_(self.w1, mean=0.0, std=0.02)
-        nn.init.trunc_normal_(self.w2, mean=0.0, std=init_std)
-        nn.init.trunc_normal_(self.w3, mean=0.0, std=init_std)
+        gen = None
+        if self.ep_size > 1:  # every expert-parallel rank draws different experts
+            gen = torch.Generator(device=self.w1.device)
+            base = int(torch.randint(0, 2**31 - 1, (1,)).item())  # global RNG: same on all ranks, new per layer
+            gen.manual_seed(base + 7919 * (self.ep_rank + 1))
+        nn.init.trunc_normal_(self.w1, mean=0.0, std=0.02, generator=gen)
+        nn.init.trunc_normal_(self.w2, mean=0.0, std=init_std, generator=gen)
+        nn.init.trunc_normal_(self.w3, mean=0.0, std=init_std, generator=gen)
 
 
 class TokenChoiceTopKRouter(nn.Module):
@@ -191,12 +198,16 @@ class MoE(nn.Module):
             self.expert_bias = None
         self.register_buffer("tokens_per_expert", torch.zeros(E, dtype=torch.float32), persistent=False)
         self.aux_loss: torch.Tensor | None = None
-        self.dispatcher = None  # set by expert parallelism: object with dispatch()/combine()
+        self.dispatcher = None  # set by expert parallelism: callable doing dispatch + experts + combine
+        self.tp_group = None    # set by expert tensor parallelism
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         bs, slen, dim = x.shape
         x = x.reshape(-1, dim)
         T = x.shape[0]
+        if self.tp_group is not None:  # hidden dimension sharded over tp: partial outputs, summed below
+            from maester_b200.parallel.expert_parallel import _CopyToTP
+            x = _CopyToTP.apply(x, self.tp_group)
         top, idx, counts_f, scores = self.router(x, self.expert_bias)
         with torch.no_grad():
             self.tokens_per_expert.add_(counts_f)
@@ -226,6 +237,9 @@ class MoE(nn.Module):
 
         out = self.shared_experts(x) if self.shared_experts is not None else torch.zeros_like(x)
         out = out.index_add(0, token_idx, routed_out)
+        if self.tp_group is not None:
+            from maester_b200.parallel.expert_parallel import _ReduceFromTP
+            out = _ReduceFromTP.apply(out, self.tp_group)
         return out.reshape(bs, slen, dim)
 
     def init_weights(self, init_std: float, buffer_device: torch.device | None = None) -> None:

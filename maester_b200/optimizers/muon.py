@@ -95,16 +95,20 @@ class Muon(Optimizer):
         """Use the sharding runtime's group and shapes (called by the optimizer builder)."""
         self.shard_group = sharded.group if sharded.world > 1 else None
         self.full_shape_of = lambda p: sharded.slot_of(p).shape
+        # expert-parallel parameters are sharded over their own (smaller) group
+        self.group_of = lambda p: (lambda d: d.group if d.world > 1 else None)(sharded.domains[sharded.slot_of(p).dom])
 
-    def _world(self) -> tuple[int, int]:
-        if self.shard_group is None or not dist.is_initialized():
-            return 1, 0
-        return dist.get_world_size(self.shard_group), dist.get_rank(self.shard_group)
+    group_of = None
+
+    def _world(self, p=None) -> tuple[object, int, int]:
+        g = self.group_of(p) if (self.group_of is not None and p is not None) else self.shard_group
+        if g is None or not dist.is_initialized():
+            return None, 1, 0
+        return g, dist.get_world_size(g), dist.get_rank(g)
 
     @torch.no_grad()
     def step(self, closure=None):
         loss = closure() if closure is not None else None
-        world, rank = self._world()
         work = []  # (param, group, update-direction shard u)
         for group in self.param_groups:
             for p in group["params"]:
@@ -126,6 +130,7 @@ class Muon(Optimizer):
 
         def launch(i: int):
             p, group, u = work[i]
+            pg, world, rank = self._world(p)
             owner = i % world
             if world == 1:
                 return (i, None, None, u)
@@ -133,12 +138,13 @@ class Muon(Optimizer):
             chunk = (full_rows + world - 1) // world
             padded = u if u.shape[0] == chunk else torch.cat([u, u.new_zeros(chunk - u.shape[0], u.shape[1])])
             gather_list = [torch.empty_like(padded) for _ in range(world)] if rank == owner else None
-            h = dist.gather(padded, gather_list, group_dst=owner, group=self.shard_group, async_op=True)
+            h = dist.gather(padded, gather_list, group_dst=owner, group=pg, async_op=True)
             return (i, h, gather_list, padded)
 
         def finish(item):
             i, h, gather_list, padded = item
             p, group, u = work[i]
+            pg, world, rank = self._world(p)
             owner = i % world
             if world == 1:
                 o = newton_schulz(u, group["ns_steps"])
@@ -154,7 +160,7 @@ class Muon(Optimizer):
                         of = torch.cat([of, of.new_zeros(chunk * world - of.shape[0], of.shape[1])])
                     scatter_list = list(of.split(chunk))
                 o = torch.empty_like(padded)
-                dist.scatter(o, scatter_list, group_src=owner, group=self.shard_group)
+                dist.scatter(o, scatter_list, group_src=owner, group=pg)
                 o = o[: u.shape[0]]
             shape = self.full_shape_of(p) if self.full_shape_of else p.shape
             rows, cols = shape[0], math.prod(shape[1:])

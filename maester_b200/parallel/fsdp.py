@@ -43,10 +43,26 @@ class ParamSlot:
     full_off: int = 0            # offset into the flat full buffer (padded rows included)
     shard_off: int = 0           # offset into the flat shard buffers
     master: nn.Parameter | None = None  # fp32 shard view given to the optimizer
+    dom: int = 0                 # 0: sharded over the data-parallel shard group; 1: expert-parallel local
+                                 # slice, sharded over the ranks that hold the same experts
+    global_rows: int = 0         # dim 0 of the whole (all experts) tensor
+    row_base: int = 0            # first global row of this rank's local slice (expert-parallel offset)
 
     @property
     def padded_numel(self) -> int:
         return self.chunk_rows * self.row_numel
+
+    @property
+    def global_shape(self) -> torch.Size:
+        return torch.Size((self.global_rows, *self.shape[1:])) if len(self.shape) else self.shape
+
+
+@dataclass
+class Domain:
+    """A set of ranks that parameters are sharded over (process group, its size, this rank's index)."""
+    group: object
+    world: int
+    rank: int
 
 
 @dataclass
@@ -57,6 +73,7 @@ class Unit:
     full_lo: int = 0
     full_hi: int = 0
     shard_lo: int = 0
+    shard_mid: int = 0           # dense slots occupy [shard_lo, shard_mid), expert slots [shard_mid, shard_hi)
     shard_hi: int = 0
     gather_event: torch.cuda.Event | None = None
     gathered: bool = True
@@ -87,7 +104,7 @@ class ShardedModel:
     def __init__(self, model: nn.Module, unit_modules: list[tuple[str, nn.Module]], *, device: torch.device,
                  param_dtype: torch.dtype = torch.bfloat16, reduce_dtype: torch.dtype = torch.float32,
                  shard_group=None, replicate_group=None, gradient_divide_factor: float | None = None,
-                 tp_group=None, fused_comm: bool = False):
+                 tp_group=None, fused_comm: bool = False, expert_group=None, ep_size: int = 1, ep_rank: int = 0):
         self.model = model
         self.device = device
         self.param_dtype, self.reduce_dtype = param_dtype, reduce_dtype
@@ -97,6 +114,12 @@ class ShardedModel:
         self.world = dist.get_world_size(shard_group) if (shard_group is not None and dist.is_initialized()) else 1
         self.rank = dist.get_rank(shard_group) if self.world > 1 else 0
         self.rep_world = dist.get_world_size(replicate_group) if replicate_group is not None else 1
+        # expert-parallel parameters (marked ``ep_local`` by apply_ep) hold E/ep experts per rank and are
+        # sharded over the ranks with the same experts (reference: parallelize_deepseek.py:315-355)
+        e_world = dist.get_world_size(expert_group) if (expert_group is not None and dist.is_initialized()) else 1
+        e_rank = dist.get_rank(expert_group) if e_world > 1 else 0
+        self.domains = [Domain(shard_group, self.world, self.rank), Domain(expert_group, e_world, e_rank)]
+        self.ep_size, self.ep_rank = ep_size, ep_rank
         self.divide = gradient_divide_factor or float(self.world * self.rep_world)
         self.require_sync = True
         self.lowp_fresh = False
@@ -112,11 +135,14 @@ class ShardedModel:
             u = Unit(name, mod)
             for fqn, p in _ordered_params(mod, prefix_of[mod] + ".", seen, set()):
                 u.slots.append(self._slot(fqn, p))
+            u.slots.sort(key=lambda sl: sl.dom)  # stable: dense first, fused-projection adjacency kept
             self.units.append(u)
         root = Unit("root", model)
         for fqn, p in _ordered_params(model, "", seen, block_mods):
             root.slots.append(self._slot(fqn, p))
+        root.slots.sort(key=lambda sl: sl.dom)
         self.units.append(root)
+        self.has_experts = any(sl.dom == 1 for u in self.units for sl in u.slots)
         self.root = root
 
         # ---- offsets (each parameter start is aligned to 256 elements: 16-byte TMA alignment for
@@ -127,17 +153,22 @@ class ShardedModel:
         f = s = 0
         for u in self.units:
             u.full_lo, u.shard_lo = f, s
+            u.shard_mid = -1
             for sl in u.slots:
+                if sl.dom == 1 and u.shard_mid < 0:
+                    u.shard_mid = s
                 sl.full_off, sl.shard_off = f, s
-                f = align(f + sl.padded_numel * self.world)
+                f = align(f + sl.padded_numel * self.domains[sl.dom].world)
                 s = align(s + sl.padded_numel)
             u.full_hi, u.shard_hi = f, s
+            if u.shard_mid < 0:
+                u.shard_mid = s
         self.full_numel, self.shard_numel = f, s
 
         # ---- buffers
         self.fused = False
         self.symm_full = self.symm_grad = None
-        if fused_comm and self.world > 1 and self.rep_world == 1 and param_dtype == torch.bfloat16 and all(
+        if fused_comm and not self.has_experts and self.world > 1 and self.rep_world == 1 and param_dtype == torch.bfloat16 and all(
                 sl.padded_numel % 4 == 0 for u in self.units for sl in u.slots):
             from maester_b200.parallel.symm import SymmBuffer, symmetric_memory_available
             if symmetric_memory_available(shard_group):
@@ -171,8 +202,10 @@ class ShardedModel:
         shape = p.shape
         rows = shape[0] if p.dim() > 0 else 1
         row_numel = int(math.prod(shape[1:])) if p.dim() > 1 else 1
-        chunk = (rows + self.world - 1) // self.world
-        return ParamSlot(fqn, p, shape, rows, row_numel, chunk)
+        dom = 1 if getattr(p, "ep_local", False) else 0
+        chunk = (rows + self.domains[dom].world - 1) // self.domains[dom].world
+        ep, er = (self.ep_size, self.ep_rank) if dom == 1 else (1, 0)
+        return ParamSlot(fqn, p, shape, rows, row_numel, chunk, dom=dom, global_rows=rows * ep, row_base=rows * er)
 
     def _rebind_parameters(self) -> None:
         """Point every model parameter at its view of ``full`` and create the fp32 master shards."""
@@ -183,8 +216,9 @@ class ShardedModel:
                 gview = self.full_grad[sl.full_off: sl.full_off + n].view(sl.shape)
                 new = nn.Parameter(view, requires_grad=sl.param.requires_grad)
                 new.main_grad = gview
-                if getattr(sl.param, "tp_replicated", False):
-                    new.tp_replicated = True
+                for attr in ("tp_replicated", "ep_local"):
+                    if getattr(sl.param, attr, False):
+                        setattr(new, attr, True)
                 self._replace_param(sl.param, new)
                 sl.param = new
                 lo, hi = self._own_rows(sl)
@@ -204,7 +238,7 @@ class ShardedModel:
                     mod._parameters[k] = new
 
     def _own_rows(self, sl: ParamSlot) -> tuple[int, int]:
-        lo = min(sl.rows, self.rank * sl.chunk_rows)
+        lo = min(sl.rows, self.domains[sl.dom].rank * sl.chunk_rows)
         hi = min(sl.rows, lo + sl.chunk_rows)
         return lo, hi
 
@@ -229,9 +263,16 @@ class ShardedModel:
         """After ``model.init_weights()`` filled the compute-dtype parameters: broadcast rank 0's
         values (so all ranks agree) and load this rank's rows into the fp32 master shards."""
         # ranks that hold the same (tensor-parallel) slice of the model must start identical
-        for g in (self.group, self.replicate_group):
-            if g is not None and dist.get_world_size(g) > 1:
-                dist.broadcast(self.full, group=g, group_src=0)
+        if not self.has_experts:
+            for g in (self.group, self.replicate_group):
+                if g is not None and dist.get_world_size(g) > 1:
+                    dist.broadcast(self.full, group=g, group_src=0)
+        else:  # expert slices differ between expert-parallel ranks: broadcast inside each slot's own domain
+            for u in self.units:
+                for sl in u.slots:
+                    for g in (self.domains[sl.dom].group, self.replicate_group):
+                        if g is not None and dist.get_world_size(g) > 1:
+                            dist.broadcast(sl.param.data, group=g, group_src=0)
         if self.tp_group is not None and dist.get_world_size(self.tp_group) > 1:
             for u in self.units:
                 for sl in u.slots:
@@ -298,23 +339,38 @@ class ShardedModel:
         ctx = torch.cuda.stream(stream) if stream is not None else _null()
         with ctx:
             shard = self.shard_grad[u.shard_lo:u.shard_hi]
-            if self.world > 1:
+            for dom, lo, hi, slots in self._segments(u):
+                seg = self.shard_grad[lo:hi]
+                if dom.world == 1:
+                    if self.full_grad is not self.shard_grad:  # same geometry: move and clear
+                        for sl in slots:
+                            src = self.full_grad[sl.full_off: sl.full_off + sl.padded_numel]
+                            self.shard_grad[sl.shard_off: sl.shard_off + sl.padded_numel].copy_(src)
+                            src.zero_()
+                    continue
                 # pack rank-major: [rank][slot] so that the scatter leaves each rank its own rows
-                n_shard = u.shard_hi - u.shard_lo
-                send = torch.empty(self.world * n_shard, dtype=self.reduce_dtype, device=self.device)
-                sv = send.view(self.world, n_shard)
-                for sl in u.slots:
-                    src = self.full_grad[sl.full_off: sl.full_off + sl.padded_numel * self.world]
-                    sv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel].copy_(
-                        src.view(self.world, sl.padded_numel))
+                n_shard = hi - lo
+                send = torch.empty(dom.world * n_shard, dtype=self.reduce_dtype, device=self.device)
+                sv = send.view(dom.world, n_shard)
+                for sl in slots:
+                    src = self.full_grad[sl.full_off: sl.full_off + sl.padded_numel * dom.world]
+                    sv[:, sl.shard_off - lo: sl.shard_off - lo + sl.padded_numel].copy_(
+                        src.view(dom.world, sl.padded_numel))
                     src.zero_()
-                out = shard if self.reduce_dtype == torch.float32 else torch.empty(n_shard, dtype=self.reduce_dtype, device=self.device)
-                dist.reduce_scatter_tensor(out, send, op=dist.ReduceOp.SUM, group=self.group)
-                if out is not shard:
-                    shard.copy_(out)
+                out = seg if self.reduce_dtype == torch.float32 else torch.empty(n_shard, dtype=self.reduce_dtype, device=self.device)
+                dist.reduce_scatter_tensor(out, send, op=dist.ReduceOp.SUM, group=dom.group)
+                if out is not seg:
+                    seg.copy_(out)
             if self.rep_world > 1:
                 dist.all_reduce(shard, op=dist.ReduceOp.SUM, group=self.replicate_group)
             shard.mul_(1.0 / self.divide)
+
+    def _segments(self, u: Unit):
+        """(domain, shard range, slots) of a unit: dense parameters first, then expert-parallel ones."""
+        if u.shard_mid > u.shard_lo:
+            yield self.domains[0], u.shard_lo, u.shard_mid, [sl for sl in u.slots if sl.dom == 0]
+        if u.shard_hi > u.shard_mid:
+            yield self.domains[1], u.shard_mid, u.shard_hi, [sl for sl in u.slots if sl.dom == 1]
 
     @torch.no_grad()
     def collect_autograd_grads(self) -> None:
@@ -366,14 +422,20 @@ class ShardedModel:
         ctx = torch.cuda.stream(stream) if stream is not None else _null()
         with ctx:
             for u in order:
-                n_shard = u.shard_hi - u.shard_lo
-                recv = torch.empty(self.world * n_shard, dtype=self.param_dtype, device=self.device)
-                dist.all_gather_into_tensor(recv, self.shard_lp[u.shard_lo:u.shard_hi], group=self.group)
-                rv = recv.view(self.world, n_shard)
-                for sl in u.slots:
-                    dst = self.full[sl.full_off: sl.full_off + sl.padded_numel * self.world]
-                    dst.view(self.world, sl.padded_numel).copy_(
-                        rv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel])
+                for dom, lo, hi, slots in self._segments(u):
+                    if dom.world == 1:
+                        for sl in slots:
+                            self.full[sl.full_off: sl.full_off + sl.padded_numel].copy_(
+                                self.shard_lp[sl.shard_off: sl.shard_off + sl.padded_numel])
+                        continue
+                    n_shard = hi - lo
+                    recv = torch.empty(dom.world * n_shard, dtype=self.param_dtype, device=self.device)
+                    dist.all_gather_into_tensor(recv, self.shard_lp[lo:hi], group=dom.group)
+                    rv = recv.view(dom.world, n_shard)
+                    for sl in slots:
+                        dst = self.full[sl.full_off: sl.full_off + sl.padded_numel * dom.world]
+                        dst.view(dom.world, sl.padded_numel).copy_(
+                            rv[:, sl.shard_off - lo: sl.shard_off - lo + sl.padded_numel])
                 if stream is not None:
                     u.gather_event = torch.cuda.Event()
                     u.gather_event.record(stream)

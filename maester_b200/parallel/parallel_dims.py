@@ -79,7 +79,7 @@ class ParallelDims:
             flat(["dp_replicate"] + shard, "dp")
             flat(shard, "dp_shard_cp")
             flat(["dp_replicate"] + shard, "dp_cp")
-            flat(["dp_shard_in_ep", "tp"], "ep")
+            flat(["dp_shard_in_ep"], "ep")  # experts are split over ep/tp ranks and, inside, by tp
         else:
             flat(["dp_replicate", "dp_shard"], "dp")
             flat(["dp_shard", "cp"], "dp_shard_cp")

@@ -107,9 +107,20 @@ class _Checkpointed(nn.Module):
 def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
     """Checkpointing plan + sharded flat buffers.  Stores the runtime as ``model._sharded`` and adds
     ``model.set_requires_gradient_sync`` (the hook the training loop uses during accumulation)."""
+    from maester_b200.models.moe.moe import MoE
+    has_moe = any(isinstance(m, MoE) for m in model.modules())
+    ep = None
+    if parallel_dims.ep_enabled:
+        from maester_b200.parallel.expert_parallel import apply_ep
+        assert has_moe, "expert_parallel_degree > 1 needs a mixture-of-experts model"
+        ep = apply_ep(model, parallel_dims, use_peer_memory=bool(getattr(cfg, "ep_peer_dispatch", False)))
     if parallel_dims.tp_enabled:
-        from maester_b200.parallel.tensor_parallel import apply_tp
-        apply_tp(model, parallel_dims, cfg)
+        if has_moe:  # as in the reference, only the MoE parts of DeepSeek / GLM-4.5 have a TP plan
+            from maester_b200.parallel.expert_parallel import apply_expert_tp
+            apply_expert_tp(model, parallel_dims)
+        else:
+            from maester_b200.parallel.tensor_parallel import apply_tp
+            apply_tp(model, parallel_dims, cfg)
     apply_ac(model, cfg)
     device = device_for_training()
     param_dtype = TORCH_DTYPE_MAP[cfg.mixed_precision_param]
@@ -126,12 +137,26 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
         # the fused reduce-scatter + AdamW + all-gather kernel only exists for AdamW groups
         fused_comm=bool(cfg.fused_collectives) and device.type == "cuda" and all(
             str(g.get("opt_class", "")).endswith("AdamW") for g in cfg.optimizer_groups),
+        expert_group=parallel_dims.mesh_group("dp_shard_mod_ep") if ep is not None else None,
+        ep_size=ep.size if ep is not None else 1, ep_rank=ep.rank if ep is not None else 0,
     )
     sharded.device_mesh = world_mesh["dp_shard_cp"] if (shard_group is not None and world_mesh is not None) else None
+    sharded.expert_mesh = _expert_checkpoint_mesh(world_mesh, parallel_dims) if ep is not None else None
     object.__setattr__(model, "_sharded", sharded)
     model.set_requires_gradient_sync = sharded.set_requires_gradient_sync
     # buffers that are still on the meta device (RoPE tables) are rebuilt by init_weights()
     return model
+
+
+def _expert_checkpoint_mesh(world_mesh, parallel_dims):
+    """2-D sub-mesh ``(dp_shard_mod_ep, dp_shard_in_ep)`` for checkpointing expert tensors ``[E, ...]``:
+    experts are split over ``ep`` first and each rank's slice over the ranks holding the same experts,
+    which is a strided shard on the first mesh dimension and a plain shard on the second (the layout
+    FSDP2 on top of expert parallelism produces).  ``None`` with tensor-parallel experts (their
+    checkpoints are per-rank)."""
+    if world_mesh is None or parallel_dims.tp_enabled:
+        return None
+    return world_mesh["dp_shard_mod_ep", "dp_shard_in_ep"]
 
 
 def materialize(model: nn.Module) -> None:
