@@ -17,8 +17,16 @@
 namespace {
 using namespace mb;
 
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;     // warps 0-7: element-wise stage (two threads per row), 8: TMA, 9: MMA
+constexpr int EW_THREADS = 256;
+constexpr int WARP_TMA = 8, WARP_MMA = 9;
 constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 struct BwdParams {
   const float* lse;      // [B,H,S] natural log
@@ -145,13 +153,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 128);
-      mbar_init(&ds_full[i], 128);
+      mbar_init(&sdp_empty[i], EW_THREADS);
+      mbar_init(&ds_full[i], EW_THREADS);
       mbar_init(&ds_empty[i], 1);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -163,7 +171,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const uint32_t tmem_s = tmem_base + 256;            // 2 x 64
   const uint32_t tmem_dp = tmem_base + 256 + 2 * BKV; // 2 x 64
 
-  if (warp == 4) {
+  if (warp == WARP_TMA) {
     if (lane == 0 && nblk > 0) {
       mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
 #pragma unroll
@@ -185,7 +193,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == WARP_MMA) {
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
@@ -237,44 +245,53 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
     }
   } else {
-    const int row = warp * 32 + lane;
+    const int half = warp >> 2;  // which 32 of the 64 score columns / which half of the dQ columns
+    const int row = (warp & 3) * 32 + lane;
     const int q = q0 + row;
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int* docb = p.doc ? p.doc + static_cast<long long>(b) * p.S : nullptr;
     const int dq_doc = (docb && q < p.S) ? docb[q] : 0;
     const long long stat_idx = (static_cast<long long>(b) * p.H + h) * p.S + q;
-    const float lse2 = (q < p.S) ? p.lse[stat_idx] * LOG2E : INFINITY;
+    const float lse2 = (q < p.S) ? p.lse[stat_idx] * LOG2E : INFINITY;  // rows past the end give P = 0
     const float delta = (q < p.S) ? p.delta[stat_idx] : 0.f;
     bool ok = true;
     for (int n = 0; n < nblk && ok; ++n) {
       const int buf = n & 1;
       const int kv0 = (jb + n) * BKV;
-      if (!mbar_wait(&sdp_full[buf], (n >> 1) & 1) || !mbar_wait(&ds_empty[buf], ((n >> 1) & 1) ^ 1)) {
+      if (!mbar_wait(&sdp_full[buf], (n >> 1) & 1)) {
         atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
         ok = false;
         break;
       }
       tc_fence_after();
-      uint8_t* dsb = smem + L::OFF_DS + buf * L::DS_BYTES;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_s + buf * BKV + c * 32 + lane_sel, rs);
-        tmem_ld_32x32(tmem_dp + buf * BKV + c * 32 + lane_sel, rp);
-        tmem_ld_wait();
-        float ds[32];
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(tmem_s + buf * BKV + half * 32 + lane_sel, rs);
+      tmem_ld_32x32(tmem_dp + buf * BKV + half * 32 + lane_sel, rp);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&sdp_empty[buf]);  // scores are in registers: the MMA warp may refill this buffer
+      const bool need_mask = (docb != nullptr) || (kv0 + BKV > p.S) || (p.causal && kv0 + BKV - 1 > q0) ||
+                             (p.window >= 0 && (q0 + 127) - kv0 > p.window);
+      float ds[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float pr = ex2(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+        ds[i] = pr * (__uint_as_float(rp[i]) - delta) * p.scale;
+      }
+      if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int kv = kv0 + c * 32 + i;
+          const int kv = kv0 + half * 32 + i;
           const int dk = (docb && kv < p.S) ? docb[kv] : 0;
-          float pr = exp2f(__uint_as_float(rs[i]) * p.scale_log2 - lse2);
-          if (is_masked(p, docb, q, kv, dq_doc, dk)) pr = 0.f;
-          ds[i] = pr * (__uint_as_float(rp[i]) - delta) * p.scale;
+          if (is_masked(p, docb, q, kv, dq_doc, dk)) ds[i] = 0.f;
         }
-        store_row32(dsb, 128, row, c * 32, ds);
       }
-      tc_fence_before();
-      mbar_arrive(&sdp_empty[buf]);
+      if (!mbar_wait(&ds_empty[buf], ((n >> 1) & 1) ^ 1)) {
+        atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
+        ok = false;
+        break;
+      }
+      store_row32(smem + L::OFF_DS + buf * L::DS_BYTES, 128, row, half * 32, ds);
       fence_proxy_async_smem();
       mbar_arrive(&ds_full[buf]);
     }
@@ -284,12 +301,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     }
     if (ok) {
       tc_fence_after();
-      __nv_bfloat16* grow = p.dqkv + (static_cast<long long>(b) * p.S + q) * p.g_stride + static_cast<long long>(h) * HD;
+      __nv_bfloat16* grow = p.dqkv + (static_cast<long long>(b) * p.S + q) * p.g_stride + static_cast<long long>(h) * HD +
+                            half * (HD / 2);
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = 0; c < HD / 64; ++c) {
         uint32_t r[32];
         if (nblk > 0) {
-          tmem_ld_32x32(tmem_dq + c * 32 + lane_sel, r);
+          tmem_ld_32x32(tmem_dq + half * (HD / 2) + c * 32 + lane_sel, r);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -311,7 +329,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }
@@ -385,14 +403,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 128);
-      mbar_init(&pt_full[i], 128);
+      mbar_init(&sdp_empty[i], EW_THREADS);
+      mbar_init(&pt_full[i], EW_THREADS);
       mbar_init(&pt_empty[i], 1);
-      mbar_init(&stat_bar[i], 128);
+      mbar_init(&stat_bar[i], EW_THREADS);
     }
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -405,7 +423,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem_st = tmem_base + 256;    // 2 x 64
   const uint32_t tmem_dpt = tmem_base + 384;   // 2 x 64
 
-  if (warp == 4) {
+  if (warp == WARP_TMA) {
     if (lane == 0 && ntot > 0) {
       mbar_expect_tx(kv_full, 2 * L::KV_BYTES);
 #pragma unroll
@@ -429,7 +447,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == WARP_MMA) {
     if (lane == 0 && ntot > 0) {
       constexpr uint32_t idesc_st = make_idesc_bf16(128, BQ2, false, false);
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, DV, false, true);
@@ -488,10 +506,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
     }
   } else {
-    // one thread per kv row
-    const int row = warp * 32 + lane;
+    // two threads per kv row: each takes 32 of the 64 query columns of a tile
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
     const int kv = kv0 + row;
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int* docb = p.doc ? p.doc + static_cast<long long>(b) * p.S : nullptr;
     const int dk_doc = (docb && kv < p.S) ? docb[kv] : 0;
     bool ok = true;
@@ -500,9 +519,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const int h = kvh * G + g;
       const int buf = n & 1, pb = n % NSTQ;
       const int q0 = i * BQ2;
-      // stage lse (log2 domain) and delta of this query tile in shared memory
-      {
-        const int t = threadIdx.x;  // 0..127
+      // stage lse (log2 domain; +inf past the end, which makes P = 0) and delta of this query tile
+      if (threadIdx.x < 2 * BQ2) {
+        const int t = threadIdx.x;
         const int qq = q0 + (t & 63);
         const long long idx = (static_cast<long long>(b) * p.H + h) * p.S + qq;
         float val;
@@ -511,37 +530,53 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         stat[buf * 2 * BQ2 + (t >> 6) * BQ2 + (t & 63)] = val;
       }
       mbar_arrive(&stat_bar[buf]);
-      if (!mbar_wait(&stat_bar[buf], (n >> 1) & 1) || !mbar_wait(&sdp_full[buf], (n >> 1) & 1) || !mbar_wait(&pt_empty[pb], ((n / NSTQ) & 1) ^ 1)) {
+      if (!mbar_wait(&stat_bar[buf], (n >> 1) & 1) || !mbar_wait(&sdp_full[buf], (n >> 1) & 1)) {
         atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
         ok = false;
         break;
       }
       tc_fence_after();
-      uint8_t* ptb = smem + L::OFF_PT + pb * L::PT_BYTES;
-      uint8_t* dstb = smem + L::OFF_DST + pb * L::PT_BYTES;
-      const float* lse_s = stat + buf * 2 * BQ2;
-      const float* del_s = lse_s + BQ2;
-#pragma unroll 1
-      for (int c = 0; c < BQ2 / 32; ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld_32x32(tmem_st + buf * BQ2 + c * 32 + lane_sel, rs);
-        tmem_ld_32x32(tmem_dpt + buf * BQ2 + c * 32 + lane_sel, rp);
-        tmem_ld_wait();
-        float pv[32], ds[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int qq = q0 + c * 32 + j;
-          const int dq_doc = (docb && qq < p.S) ? docb[qq] : 0;
-          float pr = exp2f(__uint_as_float(rs[j]) * p.scale_log2 - lse_s[c * 32 + j]);
-          if (is_masked(p, docb, qq, kv, dq_doc, dk_doc)) pr = 0.f;
-          pv[j] = pr;
-          ds[j] = pr * (__uint_as_float(rp[j]) - del_s[c * 32 + j]) * p.scale;
-        }
-        store_row32(ptb, 128, row, c * 32, pv);
-        store_row32(dstb, 128, row, c * 32, ds);
-      }
+      uint32_t rs[32], rp[32];
+      tmem_ld_32x32(tmem_st + buf * BQ2 + half * 32 + lane_sel, rs);
+      tmem_ld_32x32(tmem_dpt + buf * BQ2 + half * 32 + lane_sel, rp);
+      tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&sdp_empty[buf]);
+      const float4* lse4 = reinterpret_cast<const float4*>(stat + buf * 2 * BQ2 + half * 32);
+      const float4* del4 = reinterpret_cast<const float4*>(stat + buf * 2 * BQ2 + BQ2 + half * 32);
+      const bool need_mask = (docb != nullptr) || (kv0 + 128 > p.S) || (p.causal && kv0 + 127 > q0) ||
+                             (p.window >= 0 && (q0 + BQ2 - 1) - kv0 > p.window);
+      float pv[32], ds[32];
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const float4 ls = lse4[j4], dl = del4[j4];
+        const float lsv[4] = {ls.x, ls.y, ls.z, ls.w}, dlv[4] = {dl.x, dl.y, dl.z, dl.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j4 * 4 + e;
+          const float pr = ex2(fmaf(__uint_as_float(rs[j]), p.scale_log2, -lsv[e]));
+          pv[j] = pr;
+          ds[j] = pr * (__uint_as_float(rp[j]) - dlv[e]) * p.scale;
+        }
+      }
+      if (need_mask) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int qq = q0 + half * 32 + j;
+          const int dq_doc = (docb && qq < p.S) ? docb[qq] : 0;
+          if (is_masked(p, docb, qq, kv, dq_doc, dk_doc)) {
+            pv[j] = 0.f;
+            ds[j] = 0.f;
+          }
+        }
+      }
+      if (!mbar_wait(&pt_empty[pb], ((n / NSTQ) & 1) ^ 1)) {
+        atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
+        ok = false;
+        break;
+      }
+      store_row32(smem + L::OFF_PT + pb * L::PT_BYTES, 128, row, half * 32, pv);
+      store_row32(smem + L::OFF_DST + pb * L::PT_BYTES, 128, row, half * 32, ds);
       fence_proxy_async_smem();
       mbar_arrive(&pt_full[pb]);
     }
@@ -552,17 +587,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (ok) {
       tc_fence_after();
       __nv_bfloat16* base = p.dqkv + (static_cast<long long>(b) * p.S + kv) * p.g_stride;
-      __nv_bfloat16* dkrow = base + static_cast<long long>(p.H + kvh) * HD + dv0;
-      __nv_bfloat16* dvrow = base + static_cast<long long>(p.H + p.KV + kvh) * HD + dv0;
+      __nv_bfloat16* dkrow = base + static_cast<long long>(p.H + kvh) * HD + dv0 + half * (DV / 2);
+      __nv_bfloat16* dvrow = base + static_cast<long long>(p.H + p.KV + kvh) * HD + dv0 + half * (DV / 2);
 #pragma unroll 1
       for (int which = 0; which < 2; ++which) {
         const uint32_t src = which == 0 ? tmem_dk : tmem_dv;
         __nv_bfloat16* dst = which == 0 ? dkrow : dvrow;
 #pragma unroll 1
-        for (int c = 0; c < DV / 32; ++c) {
+        for (int c = 0; c < DV / 64; ++c) {
           uint32_t r[32];
           if (ntot > 0) {
-            tmem_ld_32x32(src + c * 32 + lane_sel, r);
+            tmem_ld_32x32(src + half * (DV / 2) + c * 32 + lane_sel, r);
             tmem_ld_wait();
           } else {
 #pragma unroll
@@ -585,7 +620,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }

@@ -1,10 +1,14 @@
 // Flash-style attention forward on tcgen05: causal / sliding-window / same-document masks, GQA.
 //
-// One CTA handles 128 query rows of one (batch, q-head).  Warp 4 streams Q once and K/V blocks
-// through a 2-stage TMA ring; warp 5 issues S = Q K^T into one of two TMEM score buffers and
-// O += P V into a TMEM output accumulator; warps 0-3 (one thread per query row) run the online
-// softmax: read S from TMEM, apply the mask, write P (bf16) into swizzled shared memory for the
-// second MMA and lazily rescale O in TMEM only when the running maximum grew by more than 2^8.
+// One CTA handles 128 query rows of one (batch, q-head).  Warp 8 streams Q once and K/V blocks
+// through a 2-stage TMA ring; warp 9 issues S = Q K^T into one of two TMEM score buffers and
+// O += P V into a TMEM output accumulator.  Warps 0-7 run the online softmax with TWO threads per
+// query row (warps w and w+4 share the TMEM lanes of rows 32*(w&3).. and each takes half of the
+// score columns): one TMEM read per block kept in registers (the score buffer is released right
+// after it), the row maximum exchanged through shared memory (rounded up to bf16 on both sides, so
+// both threads use the same reference; any upper bound of the true maximum is a valid reference),
+// P (bf16) written into swizzled shared memory for the second MMA, O rescaled in TMEM only when the
+// running maximum grew by more than 2^8.  Two warps per scheduler hide each other's latencies.
 //
 // The mask is   kv <= q  (causal)  AND  q - kv <= window  (inclusive window, if window >= 0)
 //           AND doc[q] == doc[kv] (if document ids are given);
@@ -20,7 +24,15 @@ namespace {
 using namespace mb;
 
 constexpr int BQ = 128;
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;
+constexpr int SOFTMAX_THREADS = 256;
+constexpr int WARP_TMA = 8, WARP_MMA = 9;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 constexpr int KV_STAGES = 2;
 
 struct AttnParams {
@@ -44,7 +56,8 @@ struct Smem {
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
   static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
   static constexpr int OFF_BAR = OFF_P + 2 * P_BYTES;
-  static constexpr int TOTAL = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_XCH = OFF_BAR + 256;   // 1 KiB: row-maximum / row-sum exchange between the column halves
+  static constexpr int TOTAL = OFF_XCH + 1024 + 1024;
 };
 
 template <int HD, int BKV>
@@ -92,14 +105,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&v_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&s_empty[i], SOFTMAX_THREADS);
+      mbar_init(&p_full[i], SOFTMAX_THREADS);
       mbar_init(&p_empty[i], 1);
     }
     mbar_init(o_done, 1);
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -110,7 +123,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t tmem_o = tmem_base;             // HD columns
   const uint32_t tmem_s = tmem_base + 256;       // 2 x BKV columns (BKV <= 128)
 
-  if (warp == 4) {
+  if (warp == WARP_TMA) {
     // ---------------------------------------------------------------- producer
     if (lane == 0 && nblk > 0) {
       mbar_expect_tx(q_full, L::Q_BYTES);
@@ -133,7 +146,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           tma_load_4d(smem + L::OFF_V + s * L::KV_BYTES + c * (BKV * 128), &tmap_v, &v_full[s], c * 64, kvh, j * BKV, b);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == WARP_MMA) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(BQ, BKV, false, false);
@@ -184,69 +197,79 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
     }
   } else {
-    // ---------------------------------------------------------------- softmax + epilogue (warps 0..3)
-    const int row = warp * 32 + lane;
+    // ---------------------------------------------------------------- softmax + epilogue (warps 0..7)
+    constexpr int NC = BKV / 2;  // score columns per thread
+    constexpr int OC = HD / 2;   // output columns per thread
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
     const int q = q0 + row;
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int col_base = half * NC;
+    __nv_bfloat16* xch = reinterpret_cast<__nv_bfloat16*>(smem + L::OFF_XCH);  // [parity][half][128 rows]
     const int* docb = p.doc ? p.doc + static_cast<long long>(b) * p.S : nullptr;
     const int dq = (docb && q < p.S) ? docb[q] : 0;
     float m_used = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int n = 0; n < nblk && ok; ++n) {
+    bool ok = true;  // after a failed wait the thread keeps going (every barrier below is CTA-uniform)
+    for (int n = 0; n < nblk; ++n) {
       const int s = n & 1;
       const int kv0 = (jb + n) * BKV;
-      if (!mbar_wait(&s_full[s], (n >> 1) & 1)) {
+      if (ok && !mbar_wait(&s_full[s], (n >> 1) & 1)) {
         atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
         ok = false;
-        break;
       }
       tc_fence_after();
+      uint32_t r[NC];
+#pragma unroll
+      for (int c = 0; c < NC / 32; ++c)
+        tmem_ld_32x32(tmem_s + s * BKV + col_base + c * 32 + lane_sel, reinterpret_cast<uint32_t(&)[32]>(r[c * 32]));
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[s]);  // the scores now live in registers
       const bool need_mask = (docb != nullptr) || (kv0 + BKV > p.S) || (p.causal && kv0 + BKV - 1 > q0) ||
                              (p.window >= 0 && (q0 + BQ - 1) - kv0 > p.window);
-      auto masked = [&](int col) -> bool {  // true = excluded
-        const int kv = kv0 + col;
-        bool bad = kv >= p.S;
-        if (p.causal) bad |= kv > q;
-        if (p.window >= 0) bad |= (q - kv) > p.window;
-        if (docb && kv < p.S) bad |= docb[kv] != dq;
-        return bad;
-      };
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + s * BKV + c * 32 + lane_sel, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (!masked(c * 32 + i)) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < NC; ++i) {
+          const int kv = kv0 + col_base + i;
+          bool bad = kv >= p.S;
+          if (p.causal) bad |= kv > q;
+          if (p.window >= 0) bad |= (q - kv) > p.window;
+          if (docb && kv < p.S) bad |= docb[kv] != dq;
+          if (bad) r[i] = 0xFF800000u;  // -inf: exp2 gives exactly 0
         }
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < NC; i += 4) {
+        mx4[0] = fmaxf(mx4[0], __uint_as_float(r[i]));
+        mx4[1] = fmaxf(mx4[1], __uint_as_float(r[i + 1]));
+        mx4[2] = fmaxf(mx4[2], __uint_as_float(r[i + 2]));
+        mx4[3] = fmaxf(mx4[3], __uint_as_float(r[i + 3]));
+      }
+      // both halves round their maximum up to bf16 before use, so the two threads of a row agree
+      const __nv_bfloat16 mine = __float2bfloat16_ru(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+      xch[(n & 1) * 256 + half * 128 + row] = mine;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const float mx = fmaxf(__bfloat162float(mine), __bfloat162float(xch[(n & 1) * 256 + (half ^ 1) * 128 + row]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // lazy rescale of the accumulator: only when the maximum moved by more than 2^8
       const bool grow = m_new > m_used + 8.f;
       if (__any_sync(0xffffffffu, grow)) {
         if (n > 0) {
-          if (!mbar_wait(o_done, (n - 1) & 1)) {
+          if (ok && !mbar_wait(o_done, (n - 1) & 1)) {
             atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
             ok = false;
-            break;
           }
           tc_fence_after();
-          const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+          const float alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - m_new);
 #pragma unroll 1
-          for (int c = 0; c < HD / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(tmem_o + c * 32 + lane_sel, r);
+          for (int c = 0; c < OC / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_o + half * OC + c * 32 + lane_sel, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tmem_o + c * 32 + lane_sel, r);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tmem_o + half * OC + c * 32 + lane_sel, o);
           }
           tmem_st_wait();
           l *= alpha;
@@ -255,43 +278,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
       // wait until the MMA that read the previous contents of this P buffer has finished
-      if (!mbar_wait(&p_empty[s], ((n >> 1) & 1) ^ 1)) {
+      if (ok && !mbar_wait(&p_empty[s], ((n >> 1) & 1) ^ 1)) {
         atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
         ok = false;
-        break;
       }
       uint8_t* pbuf = smem + L::OFF_P + s * L::P_BYTES;
-      // pass 2: probabilities -> bf16 -> swizzled K-major tile [128 rows][BKV]
-#pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + s * BKV + c * 32 + lane_sel, r);
-        tmem_ld_wait();
-        float pv[32];
+      float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(r[i]) * p.scale_log2 - m_safe);
-          if (need_mask && masked(c * 32 + i)) e = 0.f;
-          pv[i] = e;
-          l += e;
-        }
-        const int blk = (c * 32) / 64;           // 64-column block of the P tile
-        const int chunk0 = ((c * 32) % 64) / 8;  // first 16-byte chunk inside the 128-byte row
+      for (int c = 0; c < NC / 8; ++c) {  // 8 columns = one 16-byte chunk of the swizzled bf16 tile
+        float e[8];
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 o;
-          o.x = pack_bf16(pv[v * 8 + 0], pv[v * 8 + 1]);
-          o.y = pack_bf16(pv[v * 8 + 2], pv[v * 8 + 3]);
-          o.z = pack_bf16(pv[v * 8 + 4], pv[v * 8 + 5]);
-          o.w = pack_bf16(pv[v * 8 + 6], pv[v * 8 + 7]);
-          *reinterpret_cast<uint4*>(pbuf + blk * (BQ * 128) + swz128(row, chunk0 + v)) = o;
+        for (int i = 0; i < 8; ++i) {
+          e[i] = ex2(fmaf(__uint_as_float(r[c * 8 + i]), p.scale_log2, -m_safe));
+          l4[i & 3] += e[i];
         }
+        uint4 o;
+        o.x = pack_bf16(e[0], e[1]);
+        o.y = pack_bf16(e[2], e[3]);
+        o.z = pack_bf16(e[4], e[5]);
+        o.w = pack_bf16(e[6], e[7]);
+        const int col = col_base + c * 8;
+        *reinterpret_cast<uint4*>(pbuf + (col / 64) * (BQ * 128) + swz128(row, (col % 64) / 8)) = o;
       }
-      tc_fence_before();
-      mbar_arrive(&s_empty[s]);
+      l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       fence_proxy_async_smem();
       mbar_arrive(&p_full[s]);
     }
+    // ---- row sums of the two column halves
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // nobody still reads the maximum exchange area
+    float* xl = reinterpret_cast<float*>(smem + L::OFF_XCH);  // [half][128 rows]
+    xl[half * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += xl[(half ^ 1) * 128 + row];
     // ---- epilogue: O / l -> global, log-sum-exp
     if (nblk > 0 && ok) {
       if (!mbar_wait(o_done, (nblk - 1) & 1)) {
@@ -302,30 +320,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (ok) {
       tc_fence_after();
       const float inv_l = (nblk > 0 && l > 0.f) ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.O + ((static_cast<long long>(b) * p.S + q) * p.H + h) * HD;
+      __nv_bfloat16* orow = p.O + ((static_cast<long long>(b) * p.S + q) * p.H + h) * HD + half * OC;
 #pragma unroll 1
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t r[32];
+      for (int c = 0; c < OC / 32; ++c) {
+        uint32_t o32[32];
         if (nblk > 0) {
-          tmem_ld_32x32(tmem_o + c * 32 + lane_sel, r);
+          tmem_ld_32x32(tmem_o + half * OC + c * 32 + lane_sel, o32);
           tmem_ld_wait();
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0;
+          for (int i = 0; i < 32; ++i) o32[i] = 0;
         }
         if (q < p.S) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 o;
-            o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]) * inv_l, __uint_as_float(r[v * 8 + 1]) * inv_l);
-            o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]) * inv_l, __uint_as_float(r[v * 8 + 3]) * inv_l);
-            o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]) * inv_l, __uint_as_float(r[v * 8 + 5]) * inv_l);
-            o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]) * inv_l, __uint_as_float(r[v * 8 + 7]) * inv_l);
+            o.x = pack_bf16(__uint_as_float(o32[v * 8 + 0]) * inv_l, __uint_as_float(o32[v * 8 + 1]) * inv_l);
+            o.y = pack_bf16(__uint_as_float(o32[v * 8 + 2]) * inv_l, __uint_as_float(o32[v * 8 + 3]) * inv_l);
+            o.z = pack_bf16(__uint_as_float(o32[v * 8 + 4]) * inv_l, __uint_as_float(o32[v * 8 + 5]) * inv_l);
+            o.w = pack_bf16(__uint_as_float(o32[v * 8 + 6]) * inv_l, __uint_as_float(o32[v * 8 + 7]) * inv_l);
             reinterpret_cast<uint4*>(orow + c * 32)[v] = o;
           }
         }
       }
-      if (q < p.S && p.lse)
+      if (half == 0 && q < p.S && p.lse)
         p.lse[(static_cast<long long>(b) * p.H + h) * p.S + q] =
             (nblk > 0 && l > 0.f) ? (m_used * 0.6931471805599453f + logf(l)) : -INFINITY;
     }
@@ -333,7 +351,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == WARP_MMA) {
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }
