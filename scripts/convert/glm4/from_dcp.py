@@ -1,0 +1,10 @@
+"""glm4: DCP checkpoint -> Hugging Face safetensors (see maester_b200/convert/cli.py for the options)."""
+import os
+import sys
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", ".."))
+
+from maester_b200.convert.cli import from_dcp_main  # noqa: E402
+
+if __name__ == "__main__":
+    from_dcp_main("glm4")
