@@ -237,6 +237,16 @@ class Glm4MoeTextModel(nn.Module):
             return loss + sum(aux) if aux else loss
         return ops.linear(h, w)
 
+    # the two ends of forward(), for runners that stream the blocks through the GPU one group at a time
+    def forward_embed(self, tokens: torch.Tensor) -> dict:
+        B, S = tokens.shape
+        pos = torch.arange(S, device=tokens.device, dtype=torch.int32)[None].expand(B, S)
+        return {"h": ops.embedding(tokens, self.tok_embeddings.weight), "args": (pos, self.inv_freq, self.rope_cs, None)}
+
+    def forward_head(self, h: torch.Tensor) -> torch.Tensor:
+        w = self.tok_embeddings.weight if self.config.tie_word_embeddings else self.output.weight
+        return ops.linear(self.norm(h), w)
+
     @classmethod
     def from_model_args(cls, model_args: ModelArgs) -> "Glm4MoeTextModel":
         return cls(model_args)
