@@ -36,6 +36,8 @@ class ParquetDataset(_Stateful_Dataset):
     names and sizes; other ranks wait at a barrier.
     """
 
+    file_suffix = ".parquet"  # subclasses reading another container format override this
+
     def __init__(self, data_dir: str, rank: int, worldsize: int, tokenizer, delimiter_token: Any,
                  bos_token: Optional[Any] = None, strip_tokens: Optional[Set[Any]] = None, seed: int = 42,
                  min_length: int = 1, max_chunksize: int = 1024, verbose: bool = False, shuffle: bool = True,
@@ -55,8 +57,8 @@ class ParquetDataset(_Stateful_Dataset):
         rng = random.Random(seed + rank)  # deliberately different shuffles on different ranks
 
         self.parquet_files = sorted(os.path.join(r, f) for r, _, fs in os.walk(data_dir) for f in fs
-                                    if f.endswith(".parquet"))
-        assert self.parquet_files, f"No parquet files found in {data_dir}"
+                                    if f.endswith(self.file_suffix))
+        assert self.parquet_files, f"No {self.file_suffix} files found in {data_dir}"
         cache_file = os.path.join(data_dir, f"doc_counts_cache_{self._dataset_hash()}.json")
         if _dist_rank() == 0 and not os.path.exists(cache_file):
             self._count_docs()
