@@ -110,3 +110,19 @@ def test_fake_data_script_and_packed_inspector(tmp_path):
     pq.write_table(table, tmp_path / "packed.parquet")
     rep = inspect_packed_data(str(tmp_path / "packed.parquet"), WordTokenizer())
     assert "2 packs of 4 tokens" in rep and "consistency problems: 0" in rep and "first conversation" in rep
+
+
+def test_tokenizer_training_with_script_filter(tmp_path):
+    import tokenizer_train as tt
+    f = tt.ScriptFilter.from_preset("latin", 0.1)
+    assert f.should_keep_text("Hello world 123!") and not f.should_keep_text("Привет мир") and not f.should_keep_text("1234 !!")
+    assert f.should_keep_text("mostly latin text with one ж letter inside it")
+    rows = ["the quick brown fox jumps over the lazy dog"] * 200 + ["съешь ещё этих мягких булок"] * 50
+    pq.write_table(pa.table({"text": rows}), tmp_path / "c.parquet", row_group_size=64)
+    s = tt.ParquetSampler([tt.ParquetSampler.parse(f"{tmp_path}:0.5")], seed=1, text_filter=f)
+    tok = tt.train_tokenizer(s.sample_iterator(32), vocab_size=300)
+    assert 60 < s.seen < 190 and 0 < s.kept < s.seen
+    ids = tok.encode("the lazy dog").ids
+    assert tok.decode(ids).strip() == "the lazy dog" and tok.token_to_id("<bos>") == 0 and tok.token_to_id("<eos>") == 1
+    tt.main(["--data-path", f"{tmp_path}:1.0", "--output", str(tmp_path / "out" / "tok.json"), "--vocab-size", "280"])
+    assert (tmp_path / "out" / "tok.json").is_file()
