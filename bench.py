@@ -160,7 +160,8 @@ def run_ours(args):
     cfg = Config(model_name=MODEL, flavor=args.flavor, seq_len=SEQ, train_batch_size=MICRO_BATCH,
                  data_parallel_shard_degree=world, ac_mode=args.ac, selective_ac_option="op",
                  optimizer_groups=ADAMW_GROUPS, scheduler="linear_warmup_cosine", warmup_steps=100,
-                 train_num_steps=10_000, enable_checkpoint=False, synthetic_data=True)
+                 train_num_steps=10_000, enable_checkpoint=False, synthetic_data=True,
+                 fused_collectives=not args.no_fused_collectives)
     trainer = Trainer(cfg)
     vocab = trainer.model_args.vocab_size
     pool = host_batches(4, rank, vocab)
@@ -292,6 +293,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--flavor", default=FLAVOR)
     ap.add_argument("--ac", default="selective")
+    ap.add_argument("--no-fused-collectives", action="store_true",
+                    help="use NCCL reduce-scatter/all-gather instead of the fused peer-memory optimizer kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if not torch.cuda.is_available():
