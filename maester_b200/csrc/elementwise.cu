@@ -7,6 +7,7 @@
 #include "host_common.cuh"
 #include <cuda_bf16.h>
 #include <math.h>
+#include <stdlib.h>
 
 namespace {
 
@@ -201,6 +202,101 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(const __nv_bfloat16
       atomicAdd(dw + col, a0);
       atomicAdd(dw + col + 1, a1);
     }
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm backward, one pass
+// dx and dw from ONE read of dy and x: a persistent block per SM, one warp per row at a time, each lane
+// owning the vectors lane, lane+32, ... of every row it visits.  dy and x of the row stay in
+// registers between the reduction and the dx pass; dw partials stay in registers across all rows
+// of the lane, are combined per block in shared memory and leave as one atomic per column per block.
+template <int NV, bool CACHE, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) rmsnorm_bwd_fused_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres_add, __nv_bfloat16* __restrict__ dx,
+    float* __restrict__ dw, int M, int D, int unit_offset) {
+  extern __shared__ float dw_s[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  if (dw) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dw_s[i] = 0.f;
+    __syncthreads();
+  }
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  const float off = unit_offset ? 1.f : 0.f;
+  float acc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+  constexpr int WARPS = THREADS / 32;
+  for (int row = blockIdx.x * WARPS + warp; row < M; row += gridDim.x * WARPS) {
+    const size_t base = static_cast<size_t>(row) * D;
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + base);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + base);
+    const bf16x8* ar = dres_add ? reinterpret_cast<const bf16x8*>(dres_add + base) : nullptr;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + base);
+    const float rstd = rstd_in[row];
+    bf16x8 cg[CACHE ? NV : 1], cx[CACHE ? NV : 1];
+    if (CACHE) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          cg[i] = dyr[v];
+          cx[i] = xr[v];
+        }
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float g[8], xf[8], wf[8];
+        unpack8(CACHE ? cg[i] : dyr[v], g);
+        unpack8(CACHE ? cx[i] : xr[v], xf);
+        if (w) unpack8(wr[v], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = xf[e] * rstd;
+          dot += g[e] * (w ? wf[e] + off : 1.f) * xh;
+          acc[i][e] += g[e] * xh;
+        }
+      }
+    }
+    dot = warp_sum(dot) / static_cast<float>(D);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float g[8], xf[8], wf[8], o[8];
+        unpack8(CACHE ? cg[i] : dyr[v], g);
+        unpack8(CACHE ? cx[i] : xr[v], xf);
+        if (w) unpack8(wr[v], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[e] * (w ? wf[e] + off : 1.f) - xf[e] * rstd * dot);
+        if (ar) {
+          float a[8];
+          unpack8(ar[v], a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += a[e];
+        }
+        dxr[v] = pack8(o);
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) atomicAdd(&dw_s[v * 8 + e], acc[i][e]);
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) atomicAdd(dw + i, dw_s[i]);
   }
 }
 
@@ -590,7 +686,39 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, const
     const float lr = (*lr_ptr) * tt.lr_mult;
     const float decay = 1.f - lr * tt.wd;
     const float step_size = lr / bc1;
-    for (int i = threadIdx.x; i < ch.len; i += blockDim.x) {
+    // 128-bit path over the leading multiple of four elements (chunk offsets are 16-byte aligned
+    // whenever the flat layout aligns tensors, which the sharding runtime does)
+    const int len4 = ((ch.offset & 3) == 0) ? (ch.len & ~3) : 0;
+    for (int i = threadIdx.x * 4; i < len4; i += blockDim.x * 4) {
+      const long long idx = ch.offset + i;
+      const float4 g4 = *reinterpret_cast<const float4*>(g + idx);
+      const float4 m4 = *reinterpret_cast<const float4*>(m + idx);
+      const float4 v4 = *reinterpret_cast<const float4*>(v + idx);
+      const float4 p4 = *reinterpret_cast<const float4*>(p + idx);
+      const float gi[4] = {g4.x, g4.y, g4.z, g4.w}, mi[4] = {m4.x, m4.y, m4.z, m4.w};
+      const float vi[4] = {v4.x, v4.y, v4.z, v4.w}, pi[4] = {p4.x, p4.y, p4.z, p4.w};
+      float mo[4], vo[4], po[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float gr = gi[e] * grad_scale;
+        mo[e] = beta1 * mi[e] + (1.f - beta1) * gr;
+        vo[e] = beta2 * vi[e] + (1.f - beta2) * gr * gr;
+        const float denom = sqrtf(vo[e]) / bc2_sqrt + eps;
+        po[e] = pi[e] * decay - step_size * mo[e] / denom;
+      }
+      *reinterpret_cast<float4*>(m + idx) = make_float4(mo[0], mo[1], mo[2], mo[3]);
+      *reinterpret_cast<float4*>(v + idx) = make_float4(vo[0], vo[1], vo[2], vo[3]);
+      *reinterpret_cast<float4*>(p + idx) = make_float4(po[0], po[1], po[2], po[3]);
+      if (lp) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(po[0], po[1]), hi = __floats2bfloat162_rn(po[2], po[3]);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(lp + idx) = o;
+      }
+      if (zero_grad) *reinterpret_cast<float4*>(g_mut + idx) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int i = len4 + threadIdx.x; i < ch.len; i += blockDim.x) {
       const long long idx = ch.offset + i;
       const float gr = g[idx] * grad_scale;
       const float mm = beta1 * m[idx] + (1.f - beta1) * gr;
@@ -642,6 +770,27 @@ extern "C" int mb_rmsnorm_fwd(const void* x, const void* w, const void* res, voi
 extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres_add,
                               void* dx, float* dw, int M, int D, int unit_offset, cudaStream_t st) {
   if (D & 7) return -3;
+  const int nv = (D / 8 + 31) / 32;  // vectors per lane
+  if (nv <= 12 && M >= 8 * mbh::sm_count()) {
+    const int grid = mbh::sm_count();
+    const size_t smem = static_cast<size_t>(D) * sizeof(float);
+    static const int variant = getenv("MB_NORM_BWD_VARIANT") ? atoi(getenv("MB_NORM_BWD_VARIANT")) : 1;
+#define MB_NORM_BWD(NV, CACHE, THREADS)                                                                          \
+  rmsnorm_bwd_fused_kernel<NV, CACHE, THREADS><<<grid, THREADS, smem, st>>>(                                     \
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres_add, \
+      (__nv_bfloat16*)dx, dw, M, D, unit_offset)
+    if (variant == 0) {  // rows re-read from L1 for the second pass, 16 warps per SM
+      if (nv <= 4) MB_NORM_BWD(4, false, 512);
+      else if (nv <= 8) MB_NORM_BWD(8, false, 512);
+      else MB_NORM_BWD(12, false, 512);
+    } else {             // rows cached in registers, 8 warps per SM
+      if (nv <= 4) MB_NORM_BWD(4, true, 256);
+      else if (nv <= 8) MB_NORM_BWD(8, true, 256);
+      else MB_NORM_BWD(12, true, 256);
+    }
+#undef MB_NORM_BWD
+    return mbh::check_launch("rmsnorm_bwd_fused");
+  }
   rmsnorm_bwd_dx_kernel<<<(M + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                     (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres_add,
                                                     (__nv_bfloat16*)dx, M, D, unit_offset);

@@ -103,6 +103,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const int tm = (p.M + 2 * BM - 1) / (2 * BM), tn = (p.N + BN - 1) / BN;
   const int num_tiles = tm * tn;
   const int kblocks = (p.K + BK - 1) / BK;
+  // work unit u = (tile u % num_tiles, k-range u / num_tiles): all tiles' first ranges run before any
+  // second range, so partial sums of one tile rarely meet in the reduction atomics
+  const int splits = p.splits > 1 ? p.splits : 1;
+  const int num_units = num_tiles * splits;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_a);
@@ -131,12 +135,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += npairs) {
+      for (int u = pair; u < num_units && ok; u += npairs) {
         int mt, nt;
-        tile_coords(t, tm, tn, GROUP_M, mt, nt);
+        tile_coords(u % num_tiles, tm, tn, GROUP_M, mt, nt);
+        const int sp = u / num_tiles;
+        const int kb0 = sp * kblocks / splits, kb1 = (sp + 1) * kblocks / splits;
         const int m0 = mt * 2 * BM + static_cast<int>(cta) * BM;
         const int n0 = nt * BN + static_cast<int>(cta) * BNH;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1)) {
@@ -168,7 +174,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int t = pair; t < num_tiles && ok; t += npairs, ++tcount) {
+      for (int u = pair; u < num_units && ok; u += npairs, ++tcount) {
+        const int sp = u / num_tiles;
+        const int kb0 = sp * kblocks / splits, kb1 = (sp + 1) * kblocks / splits;
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1)) {
           atomicCAS(p.status, 0, ERR_WAIT_ACC_EMPTY);
@@ -177,7 +185,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full[s], ph)) {
@@ -194,7 +202,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                                      : make_smem_desc(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc(sb + k * 32, 16, 1024);
-            umma2_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma2_bf16_ss(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma2_commit_both(&empty[s]);
         }
@@ -206,9 +214,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const float alpha = p.alpha * (p.alpha_dev ? __ldg(p.alpha_dev) : 1.f);
     uint32_t tcount = 0;
     bool ok = true;
-    for (int t = pair; t < num_tiles && ok; t += npairs, ++tcount) {
+    for (int u = pair; u < num_units && ok; u += npairs, ++tcount) {
       int mt, nt;
-      tile_coords(t, tm, tn, GROUP_M, mt, nt);
+      tile_coords(u % num_tiles, tm, tn, GROUP_M, mt, nt);
       const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_ph)) {
         atomicCAS(p.status, 0, ERR_WAIT_ACC_FULL);
@@ -255,7 +263,7 @@ int launch2(const void* A, const void* B, const GemmParams& p, long long lda, lo
     cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     attr_set = true;
   }
-  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) * (p.splits > 1 ? p.splits : 1);
   const int max_pairs = mbh::sm_count() / 2;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cudaLaunchConfig_t cfg = {};
@@ -301,6 +309,25 @@ extern "C" int mb_gemm_bf16_2cta(const void* A, const void* B, void* C, const vo
   p.beta = beta;
   p.status = mbh::status().dev;
   if (!p.status) return -4;
+  p.splits = 1;
+  if (epi == EPI_F32_ACC && (ldc & 3) == 0) {
+    // Accumulating epilogue (weight gradients): few output tiles and a long contraction leave most of
+    // the last wave idle.  Cut the contraction so that tiles x splits fills the waves; partial sums
+    // meet in C through reduction atomics.  Cost model: waves x (k-blocks per unit + fixed overhead).
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const int pairs = mbh::sm_count() / 2;
+    const int kblocks = (K + BK - 1) / BK;
+    const int overhead = 8;
+    long long best = static_cast<long long>((tiles + pairs - 1) / pairs) * (kblocks + overhead);
+    for (int s = 2; s <= 16 && s * 8 <= kblocks; ++s) {
+      const long long cost = static_cast<long long>((tiles * s + pairs - 1) / pairs) * ((kblocks + s - 1) / s + overhead);
+      if (cost * 100 < best * 97) {
+        best = cost;
+        p.splits = s;
+      }
+    }
+    if (p.splits > 1) p.epi = EPI_F32_RED;
+  }
   if (!a_mn && !b_mn) return launch2<false, false>(A, B, p, lda, ldb, stream);
   if (!a_mn && b_mn) return launch2<false, true>(A, B, p, lda, ldb, stream);
   if (a_mn && !b_mn) return launch2<true, false>(A, B, p, lda, ldb, stream);

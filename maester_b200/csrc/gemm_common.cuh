@@ -10,6 +10,7 @@ enum EpiMode : int {
   EPI_F32 = 1,       // C(fp32) = alpha*acc
   EPI_F32_ACC = 2,   // C(fp32) += alpha*acc
   EPI_BF16_ADD = 3,  // C(bf16) = alpha*acc + beta*aux(bf16)
+  EPI_F32_RED = 4,   // C(fp32) += alpha*acc with reduction atomics (split-K partial sums; chosen internally)
 };
 
 struct GemmParams {
@@ -22,6 +23,7 @@ struct GemmParams {
   float beta;              // scale of aux in EPI_BF16_ADD
   const float* alpha_dev;  // optional device scalar multiplied into alpha
   int* status;
+  int splits;              // >1: the contraction is cut into this many ranges, each a separate work unit
 };
 
 // group GROUP_M row-tiles together so that concurrently running CTAs share operand tiles in L2
@@ -80,6 +82,18 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint3
     }
   } else {
     float* crow = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.epi == EPI_F32_RED) {
+      if (full_chunk && (p.ldc & 3) == 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(crow + j * 4), "f"(v[j * 4]),
+                       "f"(v[j * 4 + 1]), "f"(v[j * 4 + 2]), "f"(v[j * 4 + 3])
+                       : "memory");
+      } else {
+        for (int i = 0; i < 32 && col0 + i < p.N; ++i) atomicAdd(crow + i, v[i]);
+      }
+      return;
+    }
     if (full_chunk && (p.ldc & 3) == 0) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {

@@ -120,6 +120,8 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_gemm_bf16_grouped_contr": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _F, _P],
         "mb_fused_rs_adamw_ag": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _P],
         "mb_push_shards": [_P, _P, _P, _I, _P, _I, _P],
+        "mb_peer_scatter_rows": [_P, _P, _I, _P, _P, _I, _I, _L, _P, _P],
+        "mb_peer_gather_rows": [_P, _P, _I, _P, _P, _I, _I, _L, _P, _P],
         "mb_glu_fwd": [_P, _P, _L, _I, _I, _L, _P],
         "mb_glu_bwd": [_P, _P, _P, _L, _I, _I, _L, _P],
         "mb_embedding_fwd": [_P, _P, _P, _L, _I, _F, _I, _P],

@@ -228,6 +228,26 @@ def push_shards(master: torch.Tensor, symm_full, chunks: torch.Tensor, nchunks: 
                                   nchunks, _stream()), "push_shards")
 
 
+def peer_scatter_rows(src: torch.Tensor, symm_dst, dest_rank: torch.Tensor, dest_row: torch.Tensor, cap_rows: int,
+                      overflow: torch.Tensor) -> None:
+    """Write row i of ``src`` [n, dim] into rank dest_rank[i]'s symmetric buffer at row dest_row[i]."""
+    n, dim = src.shape
+    assert src.is_contiguous() and dest_rank.dtype == torch.int32 and dest_row.dtype == torch.int32
+    _ck(_lib.lib().mb_peer_scatter_rows(src.data_ptr(), symm_dst.ptr_array, symm_dst.world, dest_rank.data_ptr(),
+                                        dest_row.data_ptr(), n, dim, cap_rows, overflow.data_ptr(), _stream()),
+        "peer_scatter_rows")
+
+
+def peer_gather_rows(dst: torch.Tensor, symm_src, src_rank: torch.Tensor, src_row: torch.Tensor, cap_rows: int,
+                     overflow: torch.Tensor) -> None:
+    """Fill row i of ``dst`` [n, dim] from rank src_rank[i]'s symmetric buffer row src_row[i]."""
+    n, dim = dst.shape
+    assert dst.is_contiguous() and src_rank.dtype == torch.int32 and src_row.dtype == torch.int32
+    _ck(_lib.lib().mb_peer_gather_rows(dst.data_ptr(), symm_src.ptr_array, symm_src.world, src_rank.data_ptr(),
+                                       src_row.data_ptr(), n, dim, cap_rows, overflow.data_ptr(), _stream()),
+        "peer_gather_rows")
+
+
 def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:
     _ck(_lib.lib().mb_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), _stream()), "cast")
 

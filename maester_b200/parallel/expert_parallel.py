@@ -121,11 +121,15 @@ def _local_param(old: nn.Parameter, sl: tuple) -> nn.Parameter:
     return new
 
 
-def apply_ep(model: nn.Module, parallel_dims, use_peer_memory: bool = False) -> EPInfo:
+def apply_ep(model: nn.Module, parallel_dims, use_peer_memory: bool = False, capacity_factor: float = 2.0) -> EPInfo:
     """Keep ``E / ep`` experts per rank and route tokens between ranks (call before sharding)."""
     group = parallel_dims.mesh_group("ep")
     assert group is not None, "expert parallelism needs an 'ep' mesh dimension of size > 1"
     ep = EPInfo(group, dist.get_world_size(group), dist.get_rank(group))
+    shared = None
+    if use_peer_memory:  # one dispatcher for all blocks: they run one after another and share the workspaces
+        from maester_b200.parallel.peer_dispatch import PeerDispatcher
+        shared = PeerDispatcher(ep, capacity_factor)
     for moe in _moe_blocks(model):
         ex = moe.experts
         assert ex.num_experts % ep.size == 0, f"{ex.num_experts} experts do not divide over ep={ep.size}"
@@ -136,11 +140,7 @@ def apply_ep(model: nn.Module, parallel_dims, use_peer_memory: bool = False) -> 
             new.ep_local = True
             setattr(ex, name, new)
         ex.num_local_experts, ex.ep_rank, ex.ep_size = n_local, ep.rank, ep.size
-        if use_peer_memory:
-            from maester_b200.parallel.peer_dispatch import PeerDispatcher
-            moe.dispatcher = PeerDispatcher(ep)
-        else:
-            moe.dispatcher = AllToAllDispatcher(ep)
+        moe.dispatcher = shared if shared is not None else AllToAllDispatcher(ep)
     model.ep = ep
     return ep
 

@@ -113,7 +113,8 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
     if parallel_dims.ep_enabled:
         from maester_b200.parallel.expert_parallel import apply_ep
         assert has_moe, "expert_parallel_degree > 1 needs a mixture-of-experts model"
-        ep = apply_ep(model, parallel_dims, use_peer_memory=bool(getattr(cfg, "ep_peer_dispatch", False)))
+        ep = apply_ep(model, parallel_dims, use_peer_memory=bool(cfg.ep_peer_dispatch) and device_for_training().type == "cuda",
+                      capacity_factor=cfg.ep_capacity_factor)
     if parallel_dims.tp_enabled:
         if has_moe:  # as in the reference, only the MoE parts of DeepSeek / GLM-4.5 have a TP plan
             from maester_b200.parallel.expert_parallel import apply_expert_tp

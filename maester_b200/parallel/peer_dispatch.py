@@ -1,0 +1,159 @@
+"""Expert-parallel dispatch / combine over NVLink peer memory, without host synchronisation.
+
+Same contract as ``AllToAllDispatcher`` (expert_parallel.py).  What changes is who moves the rows:
+
+1. the per-expert slot counts of all ranks are all-gathered (a few hundred bytes; stays on the device);
+2. from that matrix every rank computes, with device tensor ops, where each of its slots lives on the
+   destination rank: ``dest_rank = expert // E_local`` and ``dest_row = start of the expert's
+   128-padded group on that rank + slots of lower ranks for that expert + position in my group``;
+3. ``peer_scatter_rows`` writes the rows into the destination ranks' symmetric buffers, the local
+   experts run their grouped GEMMs on the buffer with device-side group offsets, and
+   ``peer_gather_rows`` pulls every slot's result back (csrc/ep_comm.cu).
+
+Backward is the mirror image (gradients of the results are scattered, gradients of the inputs are
+gathered).  Cross-rank ordering is by stream-ordered barriers on the symmetric buffers' signal pads.
+Buffers hold ``capacity_factor x`` the balanced load; rows beyond that are dropped and counted in
+``overflow`` (read it with ``dropped()``; it costs a synchronisation, so only do so when logging).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from maester_b200.ops.functional import GROUP_ALIGN
+from maester_b200.parallel.symm import SymmBuffer
+
+
+class _Plan:
+    """Device-side routing plan of one MoE call."""
+    __slots__ = ("dest_rank", "dest_row", "offs", "n", "dim")
+
+
+class _Scatter(torch.autograd.Function):
+    """rows [n, dim] -> this rank's expert-major buffer [cap, dim] filled by all ranks."""
+
+    @staticmethod
+    def forward(ctx, rows, disp, plan, buf):
+        from maester_b200.ops import cuda as C
+        ctx.disp, ctx.plan = disp, plan
+        buf.tensor.zero_()
+        disp.barrier()                       # every rank's buffer is cleared
+        C.peer_scatter_rows(rows.contiguous(), buf, plan.dest_rank, plan.dest_row, disp.cap, disp.overflow)
+        disp.barrier()                       # every rank's rows have landed
+        return buf.tensor.view(disp.cap, plan.dim)
+
+    @staticmethod
+    def backward(ctx, grad_buf):
+        from maester_b200.ops import cuda as C
+        disp, plan = ctx.disp, ctx.plan
+        ws = disp.workspace(1, plan.dim)
+        ws.tensor.view(disp.cap, plan.dim).copy_(grad_buf)
+        disp.barrier()
+        grad_rows = torch.empty(plan.n, plan.dim, device=grad_buf.device, dtype=grad_buf.dtype)
+        C.peer_gather_rows(grad_rows, ws, plan.dest_rank, plan.dest_row, disp.cap, disp.overflow)
+        disp.barrier()                       # peers are done reading before the workspace is reused
+        return grad_rows, None, None, None
+
+
+class _Gather(torch.autograd.Function):
+    """expert outputs [cap, dim] on every rank -> rows [n, dim] of this rank's slots."""
+
+    @staticmethod
+    def forward(ctx, out_buf, disp, plan):
+        from maester_b200.ops import cuda as C
+        ctx.disp, ctx.plan = disp, plan
+        ws = disp.workspace(0, plan.dim)
+        ws.tensor.view(disp.cap, plan.dim).copy_(out_buf)
+        disp.barrier()
+        rows = torch.empty(plan.n, plan.dim, device=out_buf.device, dtype=out_buf.dtype)
+        C.peer_gather_rows(rows, ws, plan.dest_rank, plan.dest_row, disp.cap, disp.overflow)
+        disp.barrier()
+        return rows
+
+    @staticmethod
+    def backward(ctx, grad_rows):
+        from maester_b200.ops import cuda as C
+        disp, plan = ctx.disp, ctx.plan
+        ws = disp.workspace(0, plan.dim)
+        ws.tensor.zero_()                    # padding rows must carry finite (zero) gradients
+        disp.barrier()
+        C.peer_scatter_rows(grad_rows.contiguous(), ws, plan.dest_rank, plan.dest_row, disp.cap, disp.overflow)
+        disp.barrier()
+        # the result is consumed by the experts' backward before any other MoE call touches the workspace
+        return ws.tensor.view(disp.cap, plan.dim).clone(), None, None
+
+
+class PeerDispatcher:
+    def __init__(self, ep, capacity_factor: float = 2.0):
+        self.ep = ep
+        self.capacity_factor = capacity_factor
+        self.cap = 0
+        self._ws: dict[int, SymmBuffer] = {}
+        self._inputs: dict[int, SymmBuffer] = {}   # per MoE block: its input buffer is saved for backward
+        self.overflow: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ buffers
+    def _ensure(self, n_slots: int, n_local: int, dim: int, device: torch.device) -> None:
+        cap = int(self.capacity_factor * n_slots) + n_local * GROUP_ALIGN
+        cap = (cap + GROUP_ALIGN - 1) // GROUP_ALIGN * GROUP_ALIGN
+        if cap > self.cap:
+            assert self.cap == 0, "the number of routing slots per rank must not grow between steps"
+            self.cap = cap
+            self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
+            # symmetric allocations are collective: make them here, where all ranks are in step
+            for which in (0, 1):
+                self._ws[which] = SymmBuffer(self.cap * dim, torch.bfloat16, device, self.ep.group)
+
+    def workspace(self, which: int, dim: int) -> SymmBuffer:
+        return self._ws[which]
+
+    def input_buffer(self, moe, dim: int) -> SymmBuffer:
+        key = id(moe)
+        if key not in self._inputs:
+            self._inputs[key] = SymmBuffer(self.cap * dim, torch.bfloat16, self.overflow.device, self.ep.group)
+        return self._inputs[key]
+
+    def barrier(self) -> None:
+        self.workspace(0, 0).barrier()
+
+    def dropped(self) -> int:
+        return int(self.overflow.item()) if self.overflow is not None else 0
+
+    # ------------------------------------------------------------------ routing plan (device only)
+    def plan(self, counts: torch.Tensor, sorted_experts: torch.Tensor, n_local: int, dim: int) -> _Plan:
+        ep = self.ep
+        E = counts.numel()
+        allc = torch.empty(ep.size, E, dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(allc.view(-1), counts.contiguous(), group=ep.group)
+        tot = allc.sum(0)                                              # rows per expert over all ranks
+        padded = (tot + GROUP_ALIGN - 1) // GROUP_ALIGN * GROUP_ALIGN
+        pv = padded.view(ep.size, n_local)
+        group_start = (pv.cumsum(1) - pv).reshape(-1)                  # start of each expert's group on its rank
+        before_me = allc[:ep.rank].sum(0)                              # slots of lower ranks, per expert
+        my_start = counts.cumsum(0) - counts                           # start of my group per expert in my slot order
+        slot = torch.arange(sorted_experts.numel(), device=counts.device)
+        p = _Plan()
+        p.dest_rank = (sorted_experts // n_local).to(torch.int32)
+        p.dest_row = (group_start[sorted_experts] + before_me[sorted_experts] + (slot - my_start[sorted_experts])).to(torch.int32)
+        mine = pv[ep.rank]
+        offs = torch.zeros(n_local + 1, dtype=torch.int64, device=counts.device)
+        offs[1:] = mine.cumsum(0)
+        p.offs = offs.clamp_max(self.cap).to(torch.int32)
+        p.n, p.dim = sorted_experts.numel(), dim
+        return p
+
+    # ------------------------------------------------------------------ dispatcher contract
+    def __call__(self, moe, x, sorted_scores, token_idx, counts, sorted_experts):
+        n_local = moe.experts.num_local_experts
+        dim = x.shape[1]
+        self._ensure(token_idx.numel(), n_local, dim, x.device)
+        routed_in = x[token_idx]
+        if moe.score_before_experts:
+            routed_in = (routed_in.float() * sorted_scores[:, None]).to(x.dtype)
+        plan = self.plan(counts, sorted_experts, n_local, dim)
+        buf = _Scatter.apply(routed_in, self, plan, self.input_buffer(moe, dim))
+        out = moe.experts(buf, plan.offs)
+        routed_out = _Gather.apply(out, self, plan)
+        if not moe.score_before_experts:
+            routed_out = (routed_out.float() * sorted_scores[:, None]).to(x.dtype)
+        return routed_out

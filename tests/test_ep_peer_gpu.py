@@ -1,0 +1,64 @@
+"""Expert parallelism over peer memory (2 GPUs): same losses and weights as the all-to-all dispatcher."""
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+
+def _rank(rank, world, full, batches, peer):
+    import torch.distributed as dist
+    from test_expert_parallel_cpu import _cfg, _gather_params, _load
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_cfg(data_parallel_shard_degree=world, expert_parallel_degree=world, ep_peer_dispatch=peer,
+                      fused_collectives=False))
+    _load(tr, full)
+    losses = []
+    for b in batches:
+        mine = {k: v[tr.dp_rank * 2:(tr.dp_rank + 1) * 2] for k, v in b.items()}
+        losses.append(tr.train_step(mine).item())
+    dropped = 0
+    if peer:
+        from maester_b200.models.moe.moe import MoE
+        d = next(m.dispatcher for m in tr.model.modules() if isinstance(m, MoE))
+        dropped = d.dropped()
+    from maester_b200.ops import cuda as C
+    C.check_status()
+    return losses, {k: (v[0].float().cpu(), v[1], v[2]) for k, v in _gather_params(tr).items()}, dropped
+
+
+def _worker(rank, world, port, full, batches, peer, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        torch.save(_rank(rank, world, full, batches, peer), os.path.join(out_dir, f"r{rank}_{int(peer)}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_peer_dispatch_matches_all_to_all(tmp_path):
+    import torch.multiprocessing as mp
+    from test_expert_parallel_cpu import _cfg
+    from test_parallel_cpu import _batches, _free_port, _full_weights
+    full = _full_weights(_cfg(train_batch_size=4))
+    batches = _batches(3, 4, 32, 2000)
+    res = {}
+    for peer in (False, True):
+        mp.spawn(_worker, args=(2, _free_port(), full, batches, peer, str(tmp_path)), nprocs=2, join=True)
+        res[peer] = [torch.load(os.path.join(tmp_path, f"r{r}_{int(peer)}.pt"), weights_only=False) for r in range(2)]
+    for r in range(2):
+        a, b = res[False][r], res[True][r]
+        print(f"rank {r}: all-to-all {a[0]} peer {b[0]} dropped {b[2]}")
+        assert b[2] == 0
+        assert a[0] == pytest.approx(b[0], abs=2e-2)
+        for k in a[1]:
+            x, y = a[1][k][0], b[1][k][0]
+            assert ((x - y).norm() / (x.norm() + 1e-12)).item() < 2e-2, k
