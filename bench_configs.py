@@ -1,0 +1,112 @@
+"""Throughput of the secondary training configurations (the flagship one is ``bench.py``).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29540 \
+        bench_configs.py --preset deepseek-moe-ep8 --gpus 8 [--steps 8 --warmup 3] [--ep-peer] [--no-fused-collectives]
+
+Presets (shapes of the reference's headline configurations; synthetic packed data, random-init weights):
+
+* ``gemma3-1b``         Gemma-3 1B, seq 8192, micro-batch 4 per GPU, data-parallel sharding over all GPUs
+* ``llama3-8b-tp2``     Llama-3 8B, seq 8192, micro-batch 2 per data-parallel rank, TP=2 x FSDP
+* ``llama3-8b-cp2``     Llama-3 8B, seq 32768, micro-batch 1, context parallel 2 x FSDP
+* ``deepseek-moe-ep8``  16-layer DeepSeek-style MoE (64 routed experts, top-6), seq 4096, micro-batch 4 per GPU,
+                        expert parallel over all GPUs x FSDP
+
+Timing as in ``bench.py``: warm-up, then CUDA events around K steps between barriers, max over ranks,
+clocks sampled during the timed region; one JSON line from rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+import bench as B
+
+PRESETS = {
+    "gemma3-1b": dict(model_name="gemma3", flavor="1B", seq_len=8192, train_batch_size=4),
+    "llama3-8b-tp2": dict(model_name="llama3", flavor="8B", seq_len=8192, train_batch_size=2, tensor_parallel_degree=2),
+    "llama3-8b-cp2": dict(model_name="llama3", flavor="8B", seq_len=32768, train_batch_size=1, context_parallel_degree=2),
+    "deepseek-moe-ep8": dict(model_name="deepseek", flavor="bench16L", seq_len=4096, train_batch_size=4,
+                             expert_parallel="world"),
+}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--preset", required=True, choices=sorted(PRESETS))
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--ac", default="selective")
+    ap.add_argument("--ep-peer", action="store_true", help="expert-parallel exchange by peer-memory kernels")
+    ap.add_argument("--no-fused-collectives", action="store_true")
+    ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (0: the flavor's, or 128256)")
+    a = ap.parse_args()
+    a.warmup = max(a.warmup, 3)
+    if not torch.cuda.is_available():
+        print(json.dumps({"preset": a.preset, "unavailable": "no CUDA device"}))
+        return
+    world, rank, local_rank = B.dist_setup(a.gpus)
+    from maester_b200.config import Config
+    from maester_b200.datasets.synthetic import SyntheticLoader
+    from maester_b200.log_utils import init_logger
+    from maester_b200.ops import cuda as C
+    from maester_b200.trainer import Trainer
+
+    init_logger()
+    p = dict(PRESETS[a.preset])
+    ep = p.pop("expert_parallel", None)
+    tp, cp = p.get("tensor_parallel_degree", 1), p.get("context_parallel_degree", 1)
+    cfg = Config(**p, data_parallel_shard_degree=world // (tp * cp), expert_parallel_degree=world if ep == "world" else 1,
+                 ac_mode=a.ac, selective_ac_option="op", optimizer_groups=B.ADAMW_GROUPS, scheduler="linear_warmup_cosine",
+                 warmup_steps=100, train_num_steps=10_000, enable_checkpoint=False, synthetic_data=True,
+                 synthetic_vocab_size=a.vocab or 128256, fused_collectives=not a.no_fused_collectives,
+                 ep_peer_dispatch=a.ep_peer)
+    trainer = Trainer(cfg)
+    vocab = trainer.model_args.vocab_size
+    mb, seq = cfg.train_batch_size, cfg.seq_len
+    loader = SyntheticLoader(mb, seq, vocab, "geometric:1500", seed=0, rank=trainer.dp_rank, pin=True)
+    pool = [next(loader) for _ in range(4)]
+    dev_pool = [trainer.to_device(b) for b in pool]
+    torch.cuda.synchronize()
+    for i in range(a.warmup):
+        trainer.train_step(dev_pool[i % 4])
+    C.check_status()
+    sampler = B.ClockSampler(local_rank)
+    sampler.start()
+    l0 = C.launch_count
+    ms = B.timed_region(lambda i: trainer.train_step(dev_pool[i % 4]), a.steps, world)
+    launches = C.launch_count - l0
+    clocks = sampler.stop()
+    C.check_status()
+    losses = []
+
+    def e2e_step(i):
+        losses.append(trainer.train_step(pool[i % 4]).item())
+
+    ms_e2e = B.timed_region(e2e_step, a.steps, world)
+    dp = world // (tp * cp)
+    tokens = mb * seq * dp * a.steps
+    if rank == 0:
+        value = tokens / (ms / 1e3)
+        par = "+".join(s for s in (f"dp{dp}" if dp > 1 else "", f"tp{tp}" if tp > 1 else "", f"cp{cp}" if cp > 1 else "",
+                                   f"ep{world}" if ep else "") if s) or "single"
+        sys.stderr.write(f"[bench_configs] {a.preset}: {ms / a.steps:.1f} ms/step, {value:,.0f} tok/s, "
+                         f"MFU {trainer.mfu(value / world):.1f}% (of 2.25 PF)\n")
+        print(json.dumps({
+            "metric": "tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+            "config": {"preset": a.preset, "model": f"{cfg.model_name}-{cfg.flavor}", "global_batch": mb * dp, "seq_len": seq,
+                       "parallelism": par, "ep_exchange": ("peer-memory kernels" if a.ep_peer else "all_to_all") if ep else None,
+                       "fused_collectives": not a.no_fused_collectives},
+            "clocks": clocks, "gpu_launches": launches,
+            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
+                    "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in pool[0].values()),
+                    "d2h_bytes_per_step": 4, "last_loss": losses[-1]},
+        }), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -771,7 +771,7 @@ extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
                               void* dx, float* dw, int M, int D, int unit_offset, cudaStream_t st) {
   if (D & 7) return -3;
   const int nv = (D / 8 + 31) / 32;  // vectors per lane
-  if (nv <= 12 && M >= 8 * mbh::sm_count()) {
+  if (nv <= 16 && M >= 8 * mbh::sm_count()) {
     const int grid = mbh::sm_count();
     const size_t smem = static_cast<size_t>(D) * sizeof(float);
     static const int variant = getenv("MB_NORM_BWD_VARIANT") ? atoi(getenv("MB_NORM_BWD_VARIANT")) : 1;
@@ -782,11 +782,13 @@ extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
     if (variant == 0) {  // rows re-read from L1 for the second pass, 16 warps per SM
       if (nv <= 4) MB_NORM_BWD(4, false, 512);
       else if (nv <= 8) MB_NORM_BWD(8, false, 512);
-      else MB_NORM_BWD(12, false, 512);
+      else if (nv <= 12) MB_NORM_BWD(12, false, 512);
+      else MB_NORM_BWD(16, false, 256);
     } else {             // rows cached in registers, 8 warps per SM
       if (nv <= 4) MB_NORM_BWD(4, true, 256);
       else if (nv <= 8) MB_NORM_BWD(8, true, 256);
-      else MB_NORM_BWD(12, true, 256);
+      else if (nv <= 12) MB_NORM_BWD(12, true, 256);
+      else MB_NORM_BWD(16, false, 256);
     }
 #undef MB_NORM_BWD
     return mbh::check_launch("rmsnorm_bwd_fused");

@@ -217,7 +217,8 @@ class Transformer(nn.Module):
         tp = getattr(self, "tp", None)
         if tp is not None:
             from maester_b200.parallel.tensor_parallel import gather_seq, scatter_seq, vocab_parallel_cross_entropy
-            h = scatter_seq(h, tp)  # every rank embeds all tokens, keeps its sequence slice
+            tp.batch = B
+            h = scatter_seq(h, tp)  # every rank embeds all tokens, keeps its slice of the flattened tokens
         for layer in self.layers.values():
             h = layer(h, position_ids, self.inv_freq, self.rope_cs, document_ids)
         h = self.norm(h)

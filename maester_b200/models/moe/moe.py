@@ -162,6 +162,54 @@ class _RouterGemm(torch.autograd.Function):
         return dx, dw32.to(w.dtype)
 
 
+class _SlotGather(torch.autograd.Function):
+    """rows[p] = x[token of sorted slot p].  Every token owns exactly ``k`` slots, so the backward is a
+    gather back to slot order and a sum over k: no scatter-add, no atomics, deterministic."""
+
+    @staticmethod
+    def forward(ctx, x, token_idx, inv, k):
+        ctx.save_for_backward(inv)
+        ctx.k = k
+        return x.index_select(0, token_idx)
+
+    @staticmethod
+    def backward(ctx, g):
+        (inv,) = ctx.saved_tensors
+        dim = g.shape[1]
+        gx = g.index_select(0, inv).view(-1, ctx.k, dim).sum(dim=1, dtype=torch.float32).to(g.dtype)
+        return gx, None, None, None
+
+
+class _UniqueRowSelect(torch.autograd.Function):
+    """rows = buf[idx] for DISTINCT row indices: the backward is a plain row copy into zeros."""
+
+    @staticmethod
+    def forward(ctx, buf, idx):
+        ctx.save_for_backward(idx)
+        ctx.rows = buf.shape[0]
+        return buf.index_select(0, idx)
+
+    @staticmethod
+    def backward(ctx, g):
+        (idx,) = ctx.saved_tensors
+        return g.new_zeros(ctx.rows, g.shape[1]).index_copy_(0, idx, g), None
+
+
+class _SlotCombine(torch.autograd.Function):
+    """out[t] = sum over the k slots of token t of rows[sorted position of that slot]."""
+
+    @staticmethod
+    def forward(ctx, rows, token_idx, inv, k):
+        ctx.save_for_backward(token_idx)
+        dim = rows.shape[1]
+        return rows.index_select(0, inv).view(-1, k, dim).sum(dim=1, dtype=torch.float32).to(rows.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        (token_idx,) = ctx.saved_tensors
+        return g.index_select(0, token_idx), None, None, None
+
+
 class TokenReorderer(nn.Module):
     """Stable expert-major ordering of the T*k routing slots."""
 
@@ -172,6 +220,7 @@ class TokenReorderer(nn.Module):
     def forward(self, top_scores: torch.Tensor, selected: torch.Tensor):
         flat = selected.reshape(-1)
         order = torch.argsort(flat, stable=True)
+        self.last_order = order  # sorted position p holds original slot order[p] = token * top_k + j
         counts = torch.zeros(self.num_experts, device=flat.device, dtype=torch.int64)
         counts.scatter_add_(0, flat, torch.ones_like(flat, dtype=torch.int64))
         return top_scores.reshape(-1)[order], order // self.top_k, counts, flat[order]
@@ -216,6 +265,8 @@ class MoE(nn.Module):
             frac = counts_f / counts_f.sum().clamp_min(1.0)
             self.aux_loss = self.aux_loss_coeff * scores.shape[1] * (frac * scores.mean(dim=0)).sum()
         sorted_scores, token_idx, counts, sorted_experts = self.reorderer(top, idx)
+        order = self.reorderer.last_order
+        self._inv = torch.empty_like(order).scatter_(0, order, torch.arange(order.numel(), device=order.device))
 
         if self.dispatcher is not None:
             routed_out = self.dispatcher(self, x, sorted_scores, token_idx, counts, sorted_experts)
@@ -227,20 +278,25 @@ class MoE(nn.Module):
             dest = offs[:-1].to(torch.int64)[sorted_experts] + (slot - starts[sorted_experts])
             rows_cap = (T * self.top_k + self.router.num_experts * (GROUP_ALIGN - 1) + GROUP_ALIGN - 1) \
                 // GROUP_ALIGN * GROUP_ALIGN
-            routed_in = x[token_idx]
+            routed_in = self.gather_slots(x, token_idx)
             if self.score_before_experts:
                 routed_in = (routed_in.float() * sorted_scores[:, None]).to(x.dtype)
             buf = torch.zeros(rows_cap, dim, device=x.device, dtype=x.dtype).index_copy(0, dest, routed_in)
-            routed_out = self.experts(buf, offs)[dest]
+            routed_out = _UniqueRowSelect.apply(self.experts(buf, offs), dest)
             if not self.score_before_experts:
                 routed_out = (routed_out.float() * sorted_scores[:, None]).to(x.dtype)
 
-        out = self.shared_experts(x) if self.shared_experts is not None else torch.zeros_like(x)
-        out = out.index_add(0, token_idx, routed_out)
+        out = _SlotCombine.apply(routed_out, token_idx, self._inv, self.top_k)
+        if self.shared_experts is not None:
+            out = self.shared_experts(x, residual=out)
         if self.tp_group is not None:
             from maester_b200.parallel.expert_parallel import _ReduceFromTP
             out = _ReduceFromTP.apply(out, self.tp_group)
         return out.reshape(bs, slen, dim)
+
+    def gather_slots(self, x: torch.Tensor, token_idx: torch.Tensor) -> torch.Tensor:
+        """Rows of ``x`` in sorted-slot order (used by this block and by the expert-parallel dispatchers)."""
+        return _SlotGather.apply(x, token_idx, self._inv, self.top_k)
 
     def init_weights(self, init_std: float, buffer_device: torch.device | None = None) -> None:
         self.experts.init_weights(init_std)

@@ -68,7 +68,9 @@ def permute_to_local_experts(recv: torch.Tensor, recv_counts: torch.Tensor, n_lo
     max_len = (n + n_local * GROUP_ALIGN + GROUP_ALIGN - 1) // GROUP_ALIGN * GROUP_ALIGN
     perm, _, m_offsets = generate_permute_indices(recv_counts.reshape(-1), n_local, n_ranks, max_len, GROUP_ALIGN)
     idx = torch.where(perm < 0, torch.full_like(perm, n), perm).to(torch.int64)  # padding → the zero row
-    buf = torch.cat([recv, recv.new_zeros(1, dim)])[idx]
+    from maester_b200.models.moe.moe import _UniqueRowSelect
+    # indices repeat only for the zero row, whose gradient is discarded: a copy-based backward is exact
+    buf = _UniqueRowSelect.apply(torch.cat([recv, recv.new_zeros(1, dim)]), idx)
     offs = torch.cat([m_offsets.new_zeros(1), m_offsets]).to(torch.int32)
     return buf, offs, idx, n
 
@@ -84,7 +86,7 @@ class AllToAllDispatcher:
     def __call__(self, moe, x, sorted_scores, token_idx, counts, sorted_experts):
         ep = self.ep
         n_local = moe.experts.num_local_experts
-        routed_in = x[token_idx]
+        routed_in = moe.gather_slots(x, token_idx)
         if moe.score_before_experts:
             routed_in = (routed_in.float() * sorted_scores[:, None]).to(x.dtype)
         send_counts = counts.view(ep.size, n_local).contiguous()

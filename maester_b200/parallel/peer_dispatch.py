@@ -147,7 +147,7 @@ class PeerDispatcher:
         n_local = moe.experts.num_local_experts
         dim = x.shape[1]
         self._ensure(token_idx.numel(), n_local, dim, x.device)
-        routed_in = x[token_idx]
+        routed_in = moe.gather_slots(x, token_idx)
         if moe.score_before_experts:
             routed_in = (routed_in.float() * sorted_scores[:, None]).to(x.dtype)
         plan = self.plan(counts, sorted_experts, n_local, dim)

@@ -30,24 +30,29 @@ class TPInfo:
     size: int
     rank: int
     loss_parallel: bool = True
+    batch: int = 1  # batch size of the current forward (set by the model; restores [B, S, D] after a gather)
 
 
 # ------------------------------------------------------------------------------ primitives
+# "Sequence-sharded" activations are sharded along the FLATTENED token dimension: rank r holds rows
+# [r*T/tp, (r+1)*T/tp) of the [B*S, D] matrix, shaped [1, T/tp, D].  Token-local ops (norms, residual
+# adds) do not care, and gathers / reduce-scatters are plain contiguous collectives without any
+# permutation copy.
 def _all_gather_seq(x: torch.Tensor, tp: TPInfo) -> torch.Tensor:
-    """[B, S/tp, D] → [B, S, D]."""
-    B, s, D = x.shape
-    out = torch.empty(tp.size, B, s, D, device=x.device, dtype=x.dtype)
+    """[1, T/tp, D] → [B, S, D]."""
+    D = x.shape[-1]
+    t = x.numel() // D
+    out = torch.empty(tp.size * t, D, device=x.device, dtype=x.dtype)
     dist.all_gather_into_tensor(out.view(-1), x.contiguous().view(-1), group=tp.group)
-    return out.permute(1, 0, 2, 3).reshape(B, tp.size * s, D)
+    return out.view(tp.batch, -1, D)
 
 
 def _reduce_scatter_seq(x: torch.Tensor, tp: TPInfo) -> torch.Tensor:
-    """Sum over the group of [B, S, D], keep this rank's sequence slice [B, S/tp, D]."""
-    B, S, D = x.shape
-    s = S // tp.size
-    inp = x.reshape(B, tp.size, s, D).permute(1, 0, 2, 3).contiguous()
-    out = torch.empty(B, s, D, device=x.device, dtype=x.dtype)
-    dist.reduce_scatter_tensor(out.view(-1), inp.view(-1), op=dist.ReduceOp.SUM, group=tp.group)
+    """Sum over the group of [B, S, D], keep this rank's rows of the flattened tokens [1, T/tp, D]."""
+    D = x.shape[-1]
+    T = x.numel() // D
+    out = torch.empty(1, T // tp.size, D, device=x.device, dtype=x.dtype)
+    dist.reduce_scatter_tensor(out.view(-1), x.contiguous().view(-1), op=dist.ReduceOp.SUM, group=tp.group)
     return out
 
 
@@ -79,8 +84,9 @@ class _ScatterSeq(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, tp):
         ctx.tp = tp
-        s = x.shape[1] // tp.size
-        return x[:, tp.rank * s:(tp.rank + 1) * s].contiguous()
+        D = x.shape[-1]
+        t = (x.numel() // D) // tp.size
+        return x.reshape(-1, D)[tp.rank * t:(tp.rank + 1) * t].contiguous().view(1, t, D)
 
     @staticmethod
     def backward(ctx, g):
@@ -150,11 +156,20 @@ class _VocabParallelCE(torch.autograd.Function):
         dh = torch.empty_like(h)
         mg = getattr(w, "main_grad", None)
         dw = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        from maester_b200 import ops
+        native = ops.use_native(h, w) and w.shape[0] % 8 == 0 and h.shape[1] % 8 == 0
+        if native:
+            from maester_b200.ops import cuda as C
+            scale = gout.detach().to(torch.float32).reshape(1).contiguous()
         for i, r0 in enumerate(range(0, h.shape[0], _VocabParallelCE.CHUNK)):
             g = grads[i]
             r1 = r0 + g.shape[0]
-            dh[r0:r1] = ((g.float() @ w.float()) * gout).to(h.dtype)
-            dw.add_((g.float().t() @ h[r0:r1].float()) * gout)
+            if native:  # bf16 tensor-core GEMMs, fp32 accumulation straight into the gradient buffer
+                C.gemm(g, w, b_mn=True, out=dh[r0:r1], alpha_dev=scale)
+                C.gemm(g, h[r0:r1], a_mn=True, b_mn=True, out=dw, epi=C.EPI_F32_ACC, alpha_dev=scale)
+            else:
+                dh[r0:r1] = ((g.float() @ w.float()) * gout).to(h.dtype)
+                dw.add_((g.float().t() @ h[r0:r1].float()) * gout)
         # dH is a partial sum over the vocabulary shards
         dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=ctx.tp.group)
         return dh, (None if mg is not None else dw.to(w.dtype)), None, None
