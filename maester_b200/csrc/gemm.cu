@@ -337,6 +337,7 @@ extern "C" int mb_gemm_bf16(const void* A, const void* B, void* C, const void* a
   p.alpha_dev = alpha_dev;
   p.status = mbh::status().dev;
   p.splits = 1;
+  p.route_rows = 0;
   if (!p.status) return -4;
   GroupParams g = {GROUP_NONE, 0, nullptr, 0, 0};
   return dispatch(A, B, p, g, a_mn ? K : M, b_mn ? K : N, lda, ldb, a_mn, b_mn, stream);
@@ -366,6 +367,7 @@ extern "C" int mb_gemm_bf16_grouped_rows(const void* A, const void* B, void* C, 
   p.beta = 1.f;
   p.status = mbh::status().dev;
   p.splits = 1;
+  p.route_rows = 0;
   if (!p.status) return -4;
   GroupParams g = {GROUP_ROWS, num_groups, offs, b_mn ? K : N, 0};
   const long long b_rows = static_cast<long long>(num_groups) * (b_mn ? K : N);
@@ -395,6 +397,7 @@ extern "C" int mb_gemm_bf16_grouped_contr(const void* A, const void* B, void* C,
   p.beta = 1.f;
   p.status = mbh::status().dev;
   p.splits = 1;
+  p.route_rows = 0;
   if (!p.status) return -4;
   GroupParams g = {GROUP_CONTR, num_groups, offs, 0, static_cast<long long>(M) * ldc};
   return dispatch(A, B, p, g, rows_cap, rows_cap, lda, ldb, 1, 1, stream);

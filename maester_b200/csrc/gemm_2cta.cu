@@ -310,6 +310,7 @@ extern "C" int mb_gemm_bf16_2cta(const void* A, const void* B, void* C, const vo
   p.status = mbh::status().dev;
   if (!p.status) return -4;
   p.splits = 1;
+  p.route_rows = 0;
   if (epi == EPI_F32_ACC && (ldc & 3) == 0) {
     // Accumulating epilogue (weight gradients): few output tiles and a long contraction leave most of
     // the last wave idle.  Cut the contraction so that tiles x splits fills the waves; partial sums
@@ -328,6 +329,44 @@ extern "C" int mb_gemm_bf16_2cta(const void* A, const void* B, void* C, const vo
     }
     if (p.splits > 1) p.epi = EPI_F32_RED;
   }
+  if (!a_mn && !b_mn) return launch2<false, false>(A, B, p, lda, ldb, stream);
+  if (!a_mn && b_mn) return launch2<false, true>(A, B, p, lda, ldb, stream);
+  if (a_mn && !b_mn) return launch2<true, false>(A, B, p, lda, ldb, stream);
+  return launch2<true, true>(A, B, p, lda, ldb, stream);
+}
+
+// GEMM fused with a reduce-scatter over NVLink peer memory (row-parallel linears of tensor
+// parallelism, and the input-gradient GEMMs of column-parallel ones): every rank computes the full
+// [M, N] partial product, and the epilogue stores each 128-row slice of a tile straight into the
+// buffer of the rank that owns those rows (M / world consecutive rows per rank), in this rank's slot
+// of that buffer [world, M / world, N].  Tile by tile the stores overlap the math of the next tile;
+// the owner then sums its world slots (mb_sum_partials).  No atomics: the result is deterministic.
+// The caller brackets the launch with cross-rank barriers.
+extern "C" int mb_gemm_bf16_rs(const void* A, const void* B, void* const* peer_out, int world, int my_rank, int M,
+                               int N, int K, long long lda, long long ldb, long long ldc, int a_mn, int b_mn,
+                               float alpha, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 1 || world > 8 || M % world) return -3;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -3;
+  GemmParams p;
+  p.C = peer_out[my_rank];
+  p.aux = nullptr;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.ldaux = 0;
+  p.epi = EPI_BF16;
+  p.alpha = alpha;
+  p.alpha_dev = nullptr;
+  p.beta = 0.f;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  p.splits = 1;
+  for (int r = 0; r < 8; ++r) p.route_base[r] = r < world ? peer_out[r] : nullptr;
+  p.route_rows = M / world;
+  p.route_slot = my_rank;
   if (!a_mn && !b_mn) return launch2<false, false>(A, B, p, lda, ldb, stream);
   if (!a_mn && b_mn) return launch2<false, true>(A, B, p, lda, ldb, stream);
   if (a_mn && !b_mn) return launch2<true, false>(A, B, p, lda, ldb, stream);

@@ -24,6 +24,12 @@ struct GemmParams {
   const float* alpha_dev;  // optional device scalar multiplied into alpha
   int* status;
   int splits;              // >1: the contraction is cut into this many ranges, each a separate work unit
+  // Row routing of bf16 outputs (GEMM fused with a reduce-scatter over peer memory): output row r belongs to
+  // rank r / route_rows and is stored into that rank's buffer route_base[owner], in the slot of THIS
+  // rank: row  route_slot * route_rows + r % route_rows.  route_rows == 0 turns routing off.
+  void* route_base[8];
+  int route_rows;
+  int route_slot;
 };
 
 // group GROUP_M row-tiles together so that concurrently running CTAs share operand tiles in L2
@@ -48,6 +54,11 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint3
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
   if (p.epi == EPI_BF16 || p.epi == EPI_BF16_ADD) {
     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (p.route_rows > 0) {
+      const int owner = row / p.route_rows;
+      const long long slot_row = static_cast<long long>(p.route_slot) * p.route_rows + (row - owner * p.route_rows);
+      crow = reinterpret_cast<__nv_bfloat16*>(p.route_base[owner]) + slot_row * p.ldc + col0;
+    }
     if (p.epi == EPI_BF16_ADD) {
       const __nv_bfloat16* arow =
           reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;

@@ -83,14 +83,21 @@ class Attention(nn.Module):
 
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids, residual=None):
         from maester_b200.parallel.context_parallel import attention as cp_aware_attention
-        qkv = ops.linear(x, self._wqkv.get())
+        if self.tp_fused is not None:  # x is this rank's token shard: the all-gather lives in the projection
+            from maester_b200.parallel.fused_tp import ag_linear, linear_rs
+            qkv = ag_linear(x, self._wqkv.get(), self.tp_fused)
+        else:
+            qkv = ops.linear(x, self._wqkv.get())
         out = cp_aware_attention(self, qkv, None, None, position_ids, inv_freq, rope_cs, document_ids,
                                  self.n_heads, self.n_kv_heads, self.head_dim, layout="interleaved",
                                  scale=self.attn_scale, causal=True, window=None)
+        if self.tp_fused is not None:  # GEMM + reduce-scatter + residual in one pass over peer memory
+            return linear_rs(out, self.wo.weight, residual, self.tp_fused)
         return self.wo(out, residual=residual)
 
     cp_capable = True  # context parallelism may set .cp on instances
     cp = None
+    tp_fused = None    # set by apply_tp when the fused tensor-parallel kernels are usable
 
 
 class FeedForward(nn.Module):
@@ -114,9 +121,17 @@ class FeedForward(nn.Module):
 
     fused_param_order = ("w1", "w3", "w2")
 
+    tp_fused = None
+
     def forward(self, x, residual=None, recompute_act: bool = False):
-        gate_up = ops.linear(x, self._fused().get())
+        if self.tp_fused is not None:
+            from maester_b200.parallel.fused_tp import ag_linear, linear_rs
+            gate_up = ag_linear(x, self._fused().get(), self.tp_fused)
+        else:
+            gate_up = ops.linear(x, self._fused().get())
         act = maybe_checkpoint(lambda t: ops.glu(t, "silu"), recompute_act, gate_up)
+        if self.tp_fused is not None:
+            return linear_rs(act, self.w2.weight, residual, self.tp_fused)
         return self.w2(act, residual=residual)
 
     def init_weights(self, init_std: float) -> None:
@@ -140,7 +155,7 @@ class TransformerBlock(nn.Module):
 
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids):
         rc = self.selective_recompute
-        if self.tp is not None:
+        if self.tp is not None and self.attention.tp_fused is None:
             from maester_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
             a_in = gather_seq(maybe_checkpoint(self.attention_norm, rc, x), self.tp)
             h = x + reduce_scatter_seq(self.attention(a_in, position_ids, inv_freq, rope_cs, document_ids), self.tp)

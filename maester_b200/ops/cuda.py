@@ -248,6 +248,32 @@ def peer_gather_rows(dst: torch.Tensor, symm_src, src_rank: torch.Tensor, src_ro
         "peer_gather_rows")
 
 
+def gemm_rs(a: torch.Tensor, b: torch.Tensor, symm_out, my_rank: int, *, a_mn: bool = False, b_mn: bool = False,
+            alpha: float = 1.0) -> None:
+    """``op(A) @ op(B).T`` with the output rows scattered to their owner ranks' symmetric buffers
+    ``symm_out`` ([world, M/world, N] bf16 on every rank; this rank writes slot ``my_rank`` everywhere)."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    _ck(_lib.lib().mb_gemm_bf16_rs(a.data_ptr(), b.data_ptr(), symm_out.ptr_array, symm_out.world, my_rank, M, N, K,
+                                   _rows_pitch(a), _rows_pitch(b), N, int(a_mn), int(b_mn), float(alpha), _stream()),
+        "gemm_bf16_rs")
+
+
+def pull_sum(symm_parts, my_rank: int, res: torch.Tensor | None, out: torch.Tensor) -> None:
+    """out [M/world, N] = (res or 0) + sum over ranks of rows [my_rank*M/world, ...) of their [M, N] partials."""
+    assert out.is_contiguous() and (res is None or res.is_contiguous())
+    _ck(_lib.lib().mb_pull_sum(symm_parts.ptr_array, symm_parts.world, my_rank, _ptr(res), out.data_ptr(),
+                               out.shape[0], out.shape[1], _stream()), "pull_sum")
+
+
+def sum_partials(parts: torch.Tensor, res: torch.Tensor | None, out: torch.Tensor, world: int) -> None:
+    """out = (res or 0) + sum of the ``world`` slices of ``parts`` ([world * out.numel()] bf16)."""
+    assert out.is_contiguous() and (res is None or res.is_contiguous())
+    _ck(_lib.lib().mb_sum_partials(parts.data_ptr(), _ptr(res), out.data_ptr(), out.numel(), world, _stream()),
+        "sum_partials")
+
+
 def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:
     _ck(_lib.lib().mb_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), _stream()), "cast")
 

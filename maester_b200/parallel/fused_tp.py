@@ -1,0 +1,143 @@
+"""Tensor-parallel linears whose reduce-scatter is fused into the GEMM over NVLink peer memory.
+
+Megatron-style sequence parallelism needs, per transformer block and direction, two all-gathers and
+two reduce-scatters of a ``[tokens, dim]`` activation (reference plan:
+maester/parallelisms/parallelize_llama.py:107-181, executed there by DTensor + NCCL).  Every
+reduce-scatter follows a GEMM: the row-parallel ``wo`` / ``w2`` in forward, the input-gradient GEMMs of
+the column-parallel ``wq|wk|wv`` / ``w1|w3`` in backward.  ``FusedTP.gemm_rs`` runs that pair as ONE
+kernel: the tcgen05 GEMM's epilogue stores each finished tile's rows directly into the symmetric
+buffer of the rank that owns them (``mb_gemm_bf16_rs``), so the transfer of tile i overlaps the math
+of tile i+1; the owner then sums the ``tp`` partial slices together with the residual it would add
+anyway (``mb_sum_partials``).  Plain stores, no atomics: deterministic.  All-gathers stay NCCL.
+
+``ag_linear`` / ``linear_rs`` are the two autograd ops built on it; with them a tensor-parallel block
+runs the same code path as an unsharded one (the collectives live inside the first and last linear
+of attention and FFN).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch.autograd import Function
+
+from maester_b200.parallel.symm import SymmBuffer
+
+
+class FusedTP:
+    def __init__(self, tp, mode: str | None = None):
+        import os
+        self.tp = tp
+        self.mode = mode or os.environ.get("MB_TP_RS_MODE", "pull")
+        self.buf: SymmBuffer | None = None
+        self.pair: list[SymmBuffer] = []
+        self.calls = 0
+
+    def _ensure(self, numel: int, device: torch.device) -> SymmBuffer:
+        if self.buf is None or self.buf.tensor.numel() < numel:
+            assert self.buf is None, "activation size must not grow between calls (symmetric allocation is collective)"
+            self.buf = SymmBuffer(numel, torch.bfloat16, device, self.tp.group)
+        return self.buf
+
+    def gemm_rs(self, a: torch.Tensor, b: torch.Tensor, *, b_mn: bool, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """rows [rank*M/tp, (rank+1)*M/tp) of ``sum over ranks (a @ op(b))`` (+ residual) as [M/tp, N].
+
+        Two transports.  ``pull`` (default): the GEMM writes its full partial product into a local
+        symmetric buffer and the owner of each row block reads the block from every rank with 512-byte
+        coalesced loads while adding the residual; two buffers alternate, so one barrier per call.
+        ``push``: the GEMM epilogue stores rows into their owners' buffers tile by tile."""
+        from maester_b200.ops import cuda as C
+        tp = self.tp
+        M = a.shape[0]
+        N = b.shape[1] if b_mn else b.shape[0]
+        if self.mode == "pull":
+            if not self.pair:
+                self.pair = [SymmBuffer(M * N, torch.bfloat16, a.device, tp.group) for _ in range(2)]
+            assert self.pair[0].tensor.numel() >= M * N
+            buf = self.pair[self.calls & 1]
+            self.calls += 1
+            C.gemm(a, b, b_mn=b_mn, out=buf.tensor[:M * N].view(M, N))
+            buf.barrier()  # every rank's partial product is complete (and its previous pull has finished)
+            out = torch.empty(M // tp.size, N, device=a.device, dtype=a.dtype)
+            C.pull_sum(buf, tp.rank, residual, out)
+            return out
+        buf = self._ensure(M * N, a.device)
+        buf.barrier()  # every rank has consumed the previous partial sums
+        C.gemm_rs(a, b, buf, tp.rank, b_mn=b_mn)
+        buf.barrier()  # every rank's slices have landed
+        out = torch.empty(M // tp.size, N, device=a.device, dtype=a.dtype)
+        C.sum_partials(buf.tensor, residual, out, tp.size)
+        return out
+
+
+def _all_gather_rows(x2: torch.Tensor, tp) -> torch.Tensor:
+    out = torch.empty(tp.size * x2.shape[0], x2.shape[1], device=x2.device, dtype=x2.dtype)
+    dist.all_gather_into_tensor(out.view(-1), x2.contiguous().view(-1), group=tp.group)
+    return out
+
+
+def _wgrad(w, dy2, x2):
+    from maester_b200.ops import cuda as C
+    from maester_b200.ops.functional import _acc_or_return
+    return _acc_or_return(w, lambda buf, acc: C.gemm(dy2, x2, a_mn=True, b_mn=True, out=buf,
+                                                     epi=C.EPI_F32_ACC if acc else C.EPI_F32))
+
+
+class _AGLinear(Function):
+    """Column-parallel linear on a token-sharded input: ``all_gather(x) @ w.T``; the backward's input
+    gradient is a GEMM fused with the reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, x, w, fused: FusedTP):
+        from maester_b200.ops import cuda as C
+        tp = fused.tp
+        x_full = _all_gather_rows(x.reshape(-1, x.shape[-1]), tp)
+        ctx.save_for_backward(x_full, w)
+        ctx.fused, ctx.x_shape = fused, x.shape
+        return C.gemm(x_full, w).view(tp.batch, -1, w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w.shape[0])
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dx = ctx.fused.gemm_rs(dy2, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(w, dy2, x_full) if ctx.needs_input_grad[1] else None
+        return dx, dw, None
+
+
+class _LinearRS(Function):
+    """Row-parallel linear: ``reduce_scatter(x @ w.T) (+ residual)`` as one GEMM with a routed epilogue."""
+
+    @staticmethod
+    def forward(ctx, x, w, residual, fused: FusedTP):
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, w)
+        ctx.fused, ctx.x_shape, ctx.has_res = fused, x.shape, residual is not None
+        res2 = residual.reshape(-1, w.shape[0]).contiguous() if residual is not None else None
+        out = fused.gemm_rs(x2, w, b_mn=False, residual=res2)
+        return out.view(1, out.shape[0], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from maester_b200.ops import cuda as C
+        x2, w = ctx.saved_tensors
+        dy_full = _all_gather_rows(dy.reshape(-1, w.shape[0]), ctx.fused.tp)
+        dx = C.gemm(dy_full, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(w, dy_full, x2) if ctx.needs_input_grad[1] else None
+        return dx, dw, (dy if ctx.has_res else None), None
+
+
+def ag_linear(x: torch.Tensor, w: torch.Tensor, fused: FusedTP) -> torch.Tensor:
+    return _AGLinear.apply(x, w, fused)
+
+
+def linear_rs(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor | None, fused: FusedTP) -> torch.Tensor:
+    return _LinearRS.apply(x, w, residual, fused)
+
+
+def fused_tp_available(tp, device: torch.device) -> bool:
+    from maester_b200.parallel.symm import symmetric_memory_available
+    return device.type == "cuda" and tp.size <= 8 and symmetric_memory_available(tp.group)

@@ -207,6 +207,11 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
     n_kv = a.n_kv_heads or a.n_heads
     assert a.n_heads % tp.size == 0 and n_kv % tp.size == 0, "heads must divide by the TP degree"
     assert a.vocab_size % tp.size == 0, "vocabulary must divide by the TP degree"
+    fused = None
+    from maester_b200.parallel.fused_tp import FusedTP, fused_tp_available
+    from maester_b200.utils import device_for_training
+    if getattr(cfg, "fused_collectives", False) and fused_tp_available(tp, device_for_training()):
+        fused = FusedTP(tp)  # GEMM + reduce-scatter kernels over peer memory
     for layer in model.layers.values():
         att, ff = layer.attention, layer.feed_forward
         hd = att.head_dim
@@ -222,6 +227,8 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
         _reshape_linear(ff.w3, hidden // tp.size, a.dim)
         _reshape_linear(ff.w2, a.dim, hidden // tp.size)
         layer.tp = tp
+        if fused is not None:
+            att.tp_fused = ff.tp_fused = fused
         for norm in (layer.attention_norm, layer.ffn_norm):
             for p in norm.parameters():
                 p.tp_replicated = True
@@ -232,7 +239,7 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
         p.tp_replicated = True
     model.tp = tp
     logger.info(f"Applied tensor parallelism (degree {tp.size}, sequence parallel, "
-                f"loss parallel={tp.loss_parallel})")
+                f"loss parallel={tp.loss_parallel}, fused GEMM+reduce-scatter={fused is not None})")
 
 
 # ------------------------------------------------------------------------------ checkpoints / tests
