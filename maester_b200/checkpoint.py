@@ -210,4 +210,8 @@ class CheckpointManager:
 
     def _load(self, states: dict[str, Any], path: str) -> None:
         # tolerate keys written through a torch.compile wrapper ("._orig_mod")
-        dcp.load(states, checkpoint_id=path, no_dist=self._no_dist())
+        from torch.distributed.checkpoint.api import CheckpointException
+        try:
+            dcp.load(states, checkpoint_id=path, no_dist=self._no_dist())
+        except CheckpointException as e:  # derives from BaseException: turn it into an ordinary error
+            raise RuntimeError(f"checkpoint {path} is unreadable or does not match the model: {e}") from e

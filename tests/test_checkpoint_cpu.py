@@ -1,0 +1,184 @@
+"""DCP checkpoints of the sharding runtime: round trip, resume equality, resharding, expert layout,
+weights-only export, corrupted checkpoints (all on CPU, gloo for the multi-rank cases)."""
+import os
+import shutil
+
+import pytest
+import torch
+
+from test_parallel_cpu import ADAMW, _batches, _cfg, _close, _full_weights, _load_full, run_ranks
+
+
+def _mk(tmp, **kw):
+    return _cfg(enable_checkpoint=True, dump_dir=str(tmp), job_name="job", checkpoint_interval=2, **kw)
+
+
+def _trainer_with_ckpt(cfg):
+    from train import TrainState
+    from maester_b200.checkpoint import CheckpointManager
+    from maester_b200.trainer import Trainer
+    tr = Trainer(cfg)
+    state = TrainState()
+    ck = CheckpointManager(model=tr.model, optimizer=tr.optimizers, lr_scheduler=tr.scheduler, dataloader=None,
+                           states={"train_state": state}, cfg=cfg)
+    return tr, state, ck
+
+
+def _params(tr):
+    return {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+def _run_save_resume(rank, world, cfg_kw, tmp, full, batches):
+    """Train 2 steps, save, train 2 more; then a fresh trainer loads the checkpoint and trains the same 2."""
+    cfg = _mk(tmp, **cfg_kw)
+    tr, state, ck = _trainer_with_ckpt(cfg)
+    _load_full(tr, full)
+    mine = lambda b: {k: v[tr.dp_rank * 2:(tr.dp_rank + 1) * 2] for k, v in b.items()}
+    for b in batches[:2]:
+        tr.train_step(mine(b))
+        state.step += 1
+    ck.save(state.step)
+    after_save = _params(tr)
+    cont = [tr.train_step(mine(b)).item() for b in batches[2:]]
+    want = _params(tr)
+    tr2, state2, ck2 = _trainer_with_ckpt(cfg)
+    assert ck2.load() and state2.step == 2
+    restored = _params(tr2)
+    for k in after_save:
+        assert torch.equal(restored[k], after_save[k]), k
+    tr2.step = state2.step
+    resumed = [tr2.train_step(mine(b)).item() for b in batches[2:]]
+    got = _params(tr2)
+    assert resumed == pytest.approx(cont, abs=1e-6)
+    for k in want:
+        assert torch.allclose(got[k], want[k], atol=1e-6), k
+    return True
+
+
+def test_single_process_save_and_resume(tmp_path):
+    cfg1 = _cfg()
+    full = _full_weights(cfg1)
+    os.environ.pop("WORLD_SIZE", None)
+    assert _run_save_resume(0, 1, {}, tmp_path, full, _batches(4, 2, 64, 512))
+    assert sorted(os.listdir(tmp_path / "job" / "checkpoints")) == ["step-2"]
+
+
+def test_two_rank_fsdp_save_and_resume(tmp_path):
+    full = _full_weights(_cfg())
+    res = run_ranks(2, _run_save_resume, dict(data_parallel_shard_degree=2), str(tmp_path), full, _batches(4, 4, 64, 512))
+    assert res == [True, True]
+
+
+def _save_only(rank, world, cfg_kw, tmp, full, batches):
+    cfg = _mk(tmp, **cfg_kw)
+    tr, state, ck = _trainer_with_ckpt(cfg)
+    _load_full(tr, full)
+    for b in batches:
+        tr.train_step({k: v[tr.dp_rank * 2:(tr.dp_rank + 1) * 2] for k, v in b.items()})
+        state.step += 1
+    ck.save(state.step)
+    # unsharded view of the master weights for comparison
+    return {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+def test_checkpoint_written_by_two_ranks_loads_in_one_process(tmp_path):
+    """Resharding: the DTensor shard layout lets DCP load a 2-rank checkpoint into an unsharded model."""
+    full = _full_weights(_cfg())
+    res = run_ranks(2, _save_only, dict(data_parallel_shard_degree=2), str(tmp_path), full, _batches(2, 4, 64, 512))
+    os.environ.pop("WORLD_SIZE", None)
+    tr, state, ck = _trainer_with_ckpt(_mk(tmp_path))
+    assert ck.load(model_only=True)
+    got = _params(tr)
+    for k, v in res[0].items():
+        assert _close(got[k], v, tol=1e-2), k  # the 2-rank full view is bf16-free fp32 on CPU: equal up to rounding
+    from maester_b200.convert.io import read_dcp_model
+    flat = read_dcp_model(tmp_path / "job" / "checkpoints" / "step-2")
+    assert set(flat) >= set(res[0]) and all(flat[k].shape == res[0][k].shape for k in res[0])
+
+
+def test_final_export_is_weights_only_in_export_dtype(tmp_path):
+    os.environ.pop("WORLD_SIZE", None)
+    cfg = _mk(tmp_path, model_weights_only=True, export_dtype="bfloat16")
+    tr, state, ck = _trainer_with_ckpt(cfg)
+    tr.train_step(_batches(1, 2, 64, 512)[0])
+    ck.save(7, force=True)
+    from maester_b200.convert.io import read_dcp_model
+    flat = read_dcp_model(tmp_path / "job" / "checkpoints" / "step-7")
+    assert all(v.dtype == torch.bfloat16 for v in flat.values())
+    import torch.distributed.checkpoint as dcp
+    keys = dcp.FileSystemReader(str(tmp_path / "job" / "checkpoints" / "step-7")).read_metadata().state_dict_metadata
+    assert not any(k.startswith(("optimizer", "lr_scheduler", "train_state")) for k in keys)
+
+
+def test_seed_checkpoint_and_forced_load_path(tmp_path):
+    os.environ.pop("WORLD_SIZE", None)
+    cfg = _mk(tmp_path, model_weights_only=False)
+    tr, state, ck = _trainer_with_ckpt(cfg)
+    tr.train_step(_batches(1, 2, 64, 512)[0])
+    state.step = 5
+    ck.save(0, force=True)  # a step-0 ("seed") checkpoint: only the model is read back
+    tr2, state2, ck2 = _trainer_with_ckpt(cfg)
+    assert ck2.load(step=0) and state2.step == 0
+    for k, v in _params(tr).items():
+        assert torch.equal(_params(tr2)[k], v), k
+    forced = tmp_path / "elsewhere"
+    shutil.copytree(tmp_path / "job" / "checkpoints" / "step-0", forced)
+    tr3, state3, ck3 = _trainer_with_ckpt(_mk(tmp_path / "other", forced_load_path=str(forced)))
+    assert ck3.load() and state3.step == 0
+    for k, v in _params(tr).items():
+        assert torch.equal(_params(tr3)[k], v), k
+    with pytest.raises(ValueError):
+        _trainer_with_ckpt(_mk(tmp_path / "x", forced_load_path=str(tmp_path / "missing")))[2].load()
+
+
+def test_corrupted_checkpoint_is_detected(tmp_path):
+    os.environ.pop("WORLD_SIZE", None)
+    cfg = _mk(tmp_path)
+    tr, state, ck = _trainer_with_ckpt(cfg)
+    tr.train_step(_batches(1, 2, 64, 512)[0])
+    ck.save(2)
+    meta = tmp_path / "job" / "checkpoints" / "step-2" / ".metadata"
+    meta.write_bytes(meta.read_bytes()[:20])  # truncated metadata
+    tr2, state2, ck2 = _trainer_with_ckpt(cfg)
+    with pytest.raises(Exception):
+        ck2.load()
+
+
+def _ep_save_resume(rank, world, tmp, full, batches):
+    from test_expert_parallel_cpu import _cfg as ep_cfg, _load
+    from train import TrainState
+    from maester_b200.checkpoint import CheckpointManager
+    from maester_b200.trainer import Trainer
+    cfg = ep_cfg(data_parallel_shard_degree=world, expert_parallel_degree=2, enable_checkpoint=True, dump_dir=str(tmp),
+                 job_name="ep", checkpoint_interval=1)
+
+    def make():
+        tr = Trainer(cfg)
+        st = TrainState()
+        return tr, st, CheckpointManager(model=tr.model, optimizer=tr.optimizers, lr_scheduler=tr.scheduler,
+                                         dataloader=None, states={"train_state": st}, cfg=cfg)
+
+    tr, st, ck = make()
+    _load(tr, full)
+    mine = lambda b: {k: v[tr.dp_rank * 2:(tr.dp_rank + 1) * 2] for k, v in b.items()}
+    tr.train_step(mine(batches[0]))
+    st.step = 1
+    ck.save(1)
+    want_loss = tr.train_step(mine(batches[1])).item()
+    tr2, st2, ck2 = make()
+    assert ck2.load() and st2.step == 1
+    got_loss = tr2.train_step(mine(batches[1])).item()
+    assert got_loss == pytest.approx(want_loss, abs=1e-5)
+    return sum(1 for m in tr2.model.layers.values() if getattr(m, "moe_enabled", False))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_checkpoint_round_trip(tmp_path, world):
+    from test_expert_parallel_cpu import _cfg as ep_cfg
+    full = _full_weights(ep_cfg(train_batch_size=2 * world))
+    res = run_ranks(world, _ep_save_resume, str(tmp_path), full, _batches(2, 2 * world, 32, 2000))
+    assert all(r > 0 for r in res)
+    from maester_b200.convert.io import read_dcp_model
+    flat = read_dcp_model(tmp_path / "ep" / "checkpoints" / "step-1")
+    w1 = next(v for k, v in flat.items() if k.endswith("moe.experts.w1"))
+    assert w1.shape[0] == 8  # all experts, reassembled from the (ep x fsdp) shards
