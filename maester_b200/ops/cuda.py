@@ -260,6 +260,14 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, symm_out, my_rank: int, *, a_mn: b
         "gemm_bf16_rs")
 
 
+def wait_flag(flag: torch.Tensor, expect: int, timeout_ms: float, observed: torch.Tensor | None = None) -> None:
+    """Stream-ordered bounded wait until ``flag[0] >= expect`` (int32 device tensor, may be peer memory).
+    On expiry the library status word is set (``check_status`` raises) and the stream simply continues."""
+    assert flag.dtype == torch.int32 and (observed is None or observed.dtype == torch.int32)
+    _ck(_lib.lib().mb_wait_flag_probe(flag.data_ptr(), int(expect), float(timeout_ms), _ptr(observed), _stream()),
+        "wait_flag_probe")
+
+
 def pull_sum(symm_parts, my_rank: int, res: torch.Tensor | None, out: torch.Tensor) -> None:
     """out [M/world, N] = (res or 0) + sum over ranks of rows [my_rank*M/world, ...) of their [M, N] partials."""
     assert out.is_contiguous() and (res is None or res.is_contiguous())
