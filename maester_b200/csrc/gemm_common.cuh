@@ -30,6 +30,7 @@ struct GemmParams {
   void* route_base[8];
   int route_rows;
   int route_slot;
+  int group_m;             // CTA-pair kernel: row-tiles per rasterisation group (chosen by the launcher)
 };
 
 // group GROUP_M row-tiles together so that concurrently running CTAs share operand tiles in L2
