@@ -71,7 +71,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // [2]
   uint64_t* v_full = bars + 3;        // [2]
-  uint64_t* kv_empty = bars + 5;      // [2]
+  uint64_t* v_empty = bars + 5;       // [2]  V stage free: the P V product that read it has completed
+  uint64_t* k_empty = bars + 18;      // [2]  K stage free: the Q K^T product that read it has completed (earlier)
   uint64_t* s_full = bars + 7;        // [2]
   uint64_t* s_empty = bars + 9;       // [2]
   uint64_t* p_full = bars + 11;       // [2]
@@ -103,7 +104,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&k_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], SOFTMAX_THREADS);
       mbar_init(&p_full[i], SOFTMAX_THREADS);
@@ -130,21 +132,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c)
         tma_load_4d(smem + L::OFF_Q + c * (BQ * 128), &tmap_q, q_full, c * 64, h, q0, b);
-      for (int j = jb; j < je; ++j) {
-        const int n = j - jb, s = n & 1;
-        if (!mbar_wait(&kv_empty[s], ((n >> 1) & 1) ^ 1)) {
-          atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
-          break;
-        }
+      // K and V stages are released separately (K as soon as its scores exist, V only after the P V
+      // product), and K runs one block ahead of V, so that the load of K for block n+2 starts while
+      // block n is still in its softmax: the TMA latency stays off the critical path.
+      auto load_k = [&](int n) -> bool {
+        const int s = n & 1;
+        if (!mbar_wait(&k_empty[s], ((n >> 1) & 1) ^ 1)) return false;
         mbar_expect_tx(&k_full[s], L::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(smem + L::OFF_K + s * L::KV_BYTES + c * (BKV * 128), &tmap_k, &k_full[s], c * 64, kvh, j * BKV, b);
+          tma_load_4d(smem + L::OFF_K + s * L::KV_BYTES + c * (BKV * 128), &tmap_k, &k_full[s], c * 64, kvh, (jb + n) * BKV, b);
+        return true;
+      };
+      auto load_v = [&](int n) -> bool {
+        const int s = n & 1;
+        if (!mbar_wait(&v_empty[s], ((n >> 1) & 1) ^ 1)) return false;
         mbar_expect_tx(&v_full[s], L::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(smem + L::OFF_V + s * L::KV_BYTES + c * (BKV * 128), &tmap_v, &v_full[s], c * 64, kvh, j * BKV, b);
+          tma_load_4d(smem + L::OFF_V + s * L::KV_BYTES + c * (BKV * 128), &tmap_v, &v_full[s], c * 64, kvh, (jb + n) * BKV, b);
+        return true;
+      };
+      bool okp = true;
+      for (int n = 0; n < nblk && okp; ++n) {
+        okp = load_k(n);
+        if (okp && n >= 1) okp = load_v(n - 1);
       }
+      if (okp) okp = load_v(nblk - 1);
+      if (!okp) atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
     }
   } else if (warp == WARP_MMA) {
     // ---------------------------------------------------------------- MMA issuer
@@ -168,6 +183,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_bf16_ss(tmem_s + s * BKV, da, db, idesc_qk, k != 0);
         }
         umma_commit(&s_full[s]);
+        umma_commit(&k_empty[s]);
         return true;
       };
       if (ok) ok = issue_qk(0);
@@ -190,7 +206,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           const uint64_t db = make_smem_desc(sv + k * 2048, BKV * 128, 1024);
           umma_bf16_ss(tmem_o, da, db, idesc_pv, (n | k) != 0);
         }
-        umma_commit(&kv_empty[s]);
+        umma_commit(&v_empty[s]);
         umma_commit(&p_empty[s]);
         umma_commit(o_done);
       }
