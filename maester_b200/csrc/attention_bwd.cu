@@ -94,40 +94,54 @@ __device__ __forceinline__ void store_row32(uint8_t* tile, int rows_per_block, i
 }
 
 // ---------------------------------------------------------------------------------- dQ kernel
+// Per kv block n of 64:  S_n = Q K_n^T and dP_n = dO V_n^T into TMEM (two buffers each); the element-wise
+// warps read both, form dS_n = P * (dP - delta) * scale and write it back INTO THE dP BUFFER as packed
+// bf16 (tcgen05.st), from where it is the A operand of dQ += dS_n K_n (tcgen05.mma with A in tensor
+// memory).  No shared-memory staging of dS, which pays for a second K stage at head size 256; V is
+// released as soon as dP_n exists, K only after dQ_n, so the loads for block n+1 run during block n.
 constexpr int BKV = 64;
 
-template <int HD, int NST>
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+template <int HD, int NSTV>
 struct SmemDQ {
   static constexpr int Q_BYTES = 128 * HD * 2;
   static constexpr int KV_BYTES = BKV * HD * 2;
-  static constexpr int DS_BYTES = 128 * BKV * 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_DO = Q_BYTES;
-  static constexpr int OFF_K = 2 * Q_BYTES;
-  static constexpr int OFF_V = OFF_K + NST * KV_BYTES;
-  static constexpr int OFF_DS = OFF_V + NST * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_DS + 2 * DS_BYTES;
+  static constexpr int OFF_K = 2 * Q_BYTES;              // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;     // NSTV stages
+  static constexpr int OFF_BAR = OFF_V + NSTV * KV_BYTES;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
 
-template <int HD, int NST>
+template <int HD, int NSTV>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                    const BwdParams p) {
-  using L = SmemDQ<HD, NST>;
+  using L = SmemDQ<HD, NSTV>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* qdo_full = bars;       // 1
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* sdp_full = bars + 5;   // [2]
-  uint64_t* sdp_empty = bars + 7;  // [2]
-  uint64_t* ds_full = bars + 9;    // [2]
-  uint64_t* ds_empty = bars + 11;  // [2]
-  uint64_t* dq_done = bars + 13;   // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* k_full = bars + 1;     // [2]
+  uint64_t* k_empty = bars + 3;    // [2]  dQ_n has read K_n
+  uint64_t* v_full = bars + 5;     // [2]
+  uint64_t* v_empty = bars + 7;    // [2]  dP_n has read V_n
+  uint64_t* sdp_full = bars + 9;   // [2]  S_n and dP_n are in tensor memory
+  uint64_t* s_empty = bars + 11;   // [2]  the element-wise warps hold S_n in registers
+  uint64_t* ds_full = bars + 13;   // [2]  dS_n is in tensor memory
+  uint64_t* dp_empty = bars + 15;  // [2]  dQ_n has read dS_n: the dP buffer may be overwritten
+  uint64_t* dq_done = bars + 17;   // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.S + 127) / 128;
@@ -150,12 +164,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     mbar_init(qdo_full, 1);
     mbar_init(dq_done, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], EW_THREADS);
+      mbar_init(&s_empty[i], EW_THREADS);
       mbar_init(&ds_full[i], EW_THREADS);
-      mbar_init(&ds_empty[i], 1);
+      mbar_init(&dp_empty[i], 1);
     }
     mbar_fence_init();
   }
@@ -169,7 +185,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_dq = tmem_base;
   const uint32_t tmem_s = tmem_base + 256;            // 2 x 64
-  const uint32_t tmem_dp = tmem_base + 256 + 2 * BKV; // 2 x 64
+  const uint32_t tmem_dp = tmem_base + 256 + 2 * BKV; // 2 x 64; dS_n overwrites the start of each half
 
   if (warp == WARP_TMA) {
     if (lane == 0 && nblk > 0) {
@@ -179,19 +195,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         tma_load_4d(smem + L::OFF_Q + c * (128 * 128), &tmap_q, qdo_full, c * 64, h, q0, b);
         tma_load_4d(smem + L::OFF_DO + c * (128 * 128), &tmap_do, qdo_full, c * 64, h, q0, b);
       }
-      for (int n = 0; n < nblk; ++n) {
-        const int s = n % NST, use = n / NST;
-        if (!mbar_wait(&kv_empty[s], (use & 1) ^ 1)) {
-          atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
-          break;
-        }
-        mbar_expect_tx(&kv_full[s], 2 * L::KV_BYTES);
+      bool okp = true;
+      for (int n = 0; n < nblk && okp; ++n) {
+        const int sk = n & 1, sv = n % NSTV;
+        if (!mbar_wait(&k_empty[sk], ((n >> 1) & 1) ^ 1)) { okp = false; break; }
+        mbar_expect_tx(&k_full[sk], L::KV_BYTES);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c) {
-          tma_load_4d(smem + L::OFF_K + s * L::KV_BYTES + c * (BKV * 128), &tmap_k, &kv_full[s], c * 64, kvh, (jb + n) * BKV, b);
-          tma_load_4d(smem + L::OFF_V + s * L::KV_BYTES + c * (BKV * 128), &tmap_v, &kv_full[s], c * 64, kvh, (jb + n) * BKV, b);
-        }
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(smem + L::OFF_K + sk * L::KV_BYTES + c * (BKV * 128), &tmap_k, &k_full[sk], c * 64, kvh, (jb + n) * BKV, b);
+        if (!mbar_wait(&v_empty[sv], ((n / NSTV) & 1) ^ 1)) { okp = false; break; }
+        mbar_expect_tx(&v_full[sv], L::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(smem + L::OFF_V + sv * L::KV_BYTES + c * (BKV * 128), &tmap_v, &v_full[sv], c * 64, kvh, (jb + n) * BKV, b);
       }
+      if (!okp) atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
     }
   } else if (warp == WARP_MMA) {
     if (lane == 0 && nblk > 0) {
@@ -200,47 +218,53 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       const uint32_t sq = smem_u32(smem + L::OFF_Q), sdo = smem_u32(smem + L::OFF_DO);
       bool ok = mbar_wait(qdo_full, 0);
       auto issue_sdp = [&](int n) -> bool {
-        const int s = n % NST, use = n / NST, buf = n & 1;
-        if (!mbar_wait(&kv_full[s], use & 1)) return false;
-        if (!mbar_wait(&sdp_empty[buf], ((n >> 1) & 1) ^ 1)) return false;
+        const int sk_i = n & 1, sv_i = n % NSTV, buf = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        if (!mbar_wait(&v_full[sv_i], (n / NSTV) & 1)) return false;
+        if (!mbar_wait(&dp_empty[buf], ph ^ 1)) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + L::OFF_K + s * L::KV_BYTES);
-        const uint32_t sv = smem_u32(smem + L::OFF_V + s * L::KV_BYTES);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t blk = k >> 2, kk = k & 3;
-          umma_bf16_ss(tmem_s + buf * BKV, make_smem_desc(sq + blk * (128 * 128) + kk * 32, 16, 1024),
-                       make_smem_desc(sk + blk * (BKV * 128) + kk * 32, 16, 1024), idesc_s, k != 0);
-        }
+        const uint32_t sv = smem_u32(smem + L::OFF_V + sv_i * L::KV_BYTES);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t blk = k >> 2, kk = k & 3;
           umma_bf16_ss(tmem_dp + buf * BKV, make_smem_desc(sdo + blk * (128 * 128) + kk * 32, 16, 1024),
                        make_smem_desc(sv + blk * (BKV * 128) + kk * 32, 16, 1024), idesc_s, k != 0);
         }
+        umma_commit(&v_empty[sv_i]);
+        if (!mbar_wait(&k_full[sk_i], ph)) return false;
+        if (!mbar_wait(&s_empty[buf], ph ^ 1)) return false;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::OFF_K + sk_i * L::KV_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t blk = k >> 2, kk = k & 3;
+          umma_bf16_ss(tmem_s + buf * BKV, make_smem_desc(sq + blk * (128 * 128) + kk * 32, 16, 1024),
+                       make_smem_desc(sk + blk * (BKV * 128) + kk * 32, 16, 1024), idesc_s, k != 0);
+        }
         umma_commit(&sdp_full[buf]);
         return true;
       };
       if (ok) ok = issue_sdp(0);
       for (int n = 0; n < nblk && ok; ++n) {
-        if (NST > 1 && n + 1 < nblk) ok = issue_sdp(n + 1);
+        if (n + 1 < nblk) ok = issue_sdp(n + 1);
         if (!ok) break;
-        const int s = n % NST, buf = n & 1;
+        const int buf = n & 1;
         if (!mbar_wait(&ds_full[buf], (n >> 1) & 1)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t sds = smem_u32(smem + L::OFF_DS + buf * L::DS_BYTES);
-        const uint32_t sk = smem_u32(smem + L::OFF_K + s * L::KV_BYTES);
+        const uint32_t sk = smem_u32(smem + L::OFF_K + (n & 1) * L::KV_BYTES);
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k)
-          umma_bf16_ss(tmem_dq, make_smem_desc(sds + k * 32, 16, 1024),
-                       make_smem_desc(sk + k * 2048, BKV * 128, 1024), idesc_dq, (n | k) != 0);
-        umma_commit(&kv_empty[s]);
-        umma_commit(&ds_empty[buf]);
+        for (int k = 0; k < BKV / 16; ++k) {
+          // dS_n columns: kv 0..31 packed at the start of the first half of the dP buffer, kv 32..63 at the
+          // start of its second half (each element-wise thread overwrites only columns it has read itself)
+          const uint32_t a_tmem = tmem_dp + buf * BKV + (k >> 1) * 32 + (k & 1) * 8;
+          umma_bf16_ts(tmem_dq, a_tmem, make_smem_desc(sk + k * 2048, BKV * 128, 1024), idesc_dq, (n | k) != 0);
+        }
+        umma_commit(&k_empty[n & 1]);
+        umma_commit(&dp_empty[buf]);
         if (n == nblk - 1) umma_commit(dq_done);
-        if (NST == 1 && n + 1 < nblk) ok = issue_sdp(n + 1);
       }
       if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
     }
@@ -269,7 +293,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tmem_ld_32x32(tmem_dp + buf * BKV + half * 32 + lane_sel, rp);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&sdp_empty[buf]);  // scores are in registers: the MMA warp may refill this buffer
+      mbar_arrive(&s_empty[buf]);  // scores are in registers: the MMA warp may refill the S buffer
       const bool need_mask = (docb != nullptr) || (kv0 + BKV > p.S) || (p.causal && kv0 + BKV - 1 > q0) ||
                              (p.window >= 0 && (q0 + 127) - kv0 > p.window);
       float ds[32];
@@ -286,13 +310,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           if (is_masked(p, docb, q, kv, dq_doc, dk)) ds[i] = 0.f;
         }
       }
-      if (!mbar_wait(&ds_empty[buf], ((n >> 1) & 1) ^ 1)) {
-        atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
-        ok = false;
-        break;
-      }
-      store_row32(smem + L::OFF_DS + buf * L::DS_BYTES, 128, row, half * 32, ds);
-      fence_proxy_async_smem();
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) packed[i] = pack_bf16(ds[2 * i], ds[2 * i + 1]);
+      tmem_st_32x16(tmem_dp + buf * BKV + half * 32 + lane_sel, packed);
+      tmem_st_wait();
+      tc_fence_before();
       mbar_arrive(&ds_full[buf]);
     }
     if (ok && nblk > 0 && !mbar_wait(dq_done, 0)) {
