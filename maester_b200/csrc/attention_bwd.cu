@@ -359,20 +359,26 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------- dK/dV kernel
+// One CTA per 128 kv rows of one (batch, kv head[, half of the head dim when head_dim = 256]); it loops
+// over the q-heads of the GQA group and over query tiles of 64:
+//   S^T = K Q^T and dP^T = V dO^T into TMEM  ->  P^T and dS^T written back into the same TMEM buffers as
+//   packed bf16  ->  dV += P^T dO[:, slice] and dK += dS^T Q[:, slice] with the A operand in tensor memory.
+// Shared memory holds K and V (resident) and the query-side tiles split by when they are last needed:
+// the channels of this CTA's output slice (needed until dV / dK, two stages) and the other channels
+// (needed only for S^T / dP^T, one stage released early).  So the loads of tile n+1 run during tile n.
 constexpr int BQ2 = 64;
 
-template <int HD, int NSTQ>
+template <int HD, int DV>
 struct SmemKV {
+  static constexpr int EARLY = HD - DV;                  // channels not in this CTA's output slice
   static constexpr int KV_BYTES = 128 * HD * 2;
-  static constexpr int Q_BYTES = BQ2 * HD * 2;
-  static constexpr int PT_BYTES = 128 * BQ2 * 2;
+  static constexpr int LATE_BYTES = BQ2 * DV * 2;        // one of Q / dO, slice channels
+  static constexpr int EARLY_BYTES = BQ2 * EARLY * 2;    // one of Q / dO, other channels
   static constexpr int OFF_K = 0;
   static constexpr int OFF_V = KV_BYTES;
-  static constexpr int OFF_Q = 2 * KV_BYTES;
-  static constexpr int OFF_DO = OFF_Q + NSTQ * Q_BYTES;
-  static constexpr int OFF_PT = OFF_DO + NSTQ * Q_BYTES;
-  static constexpr int OFF_DST = OFF_PT + NSTQ * PT_BYTES;
-  static constexpr int OFF_STAT = OFF_DST + NSTQ * PT_BYTES;  // [2][2][BQ2] floats
+  static constexpr int OFF_QL = 2 * KV_BYTES;            // [2 stages][Q late | dO late]
+  static constexpr int OFF_QE = OFF_QL + 2 * 2 * LATE_BYTES;  // [Q early | dO early]
+  static constexpr int OFF_STAT = OFF_QE + 2 * EARLY_BYTES;   // [2][2][BQ2] floats
   static constexpr int OFF_BAR = OFF_STAT + 2 * 2 * BQ2 * 4;
   static constexpr int TOTAL = OFF_BAR + 256 + 1024;
 };
@@ -382,18 +388,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                      const BwdParams p) {
-  using L = SmemKV<HD, NSTQ>;
+  using L = SmemKV<HD, DV>;
   constexpr int NSPLIT = HD / DV;
+  constexpr bool HAS_EARLY = L::EARLY > 0;
+  constexpr int LATE_BLKS = DV / 64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
   uint64_t* kv_full = bars;         // 1
-  uint64_t* q_full = bars + 1;      // [2]
-  uint64_t* q_empty = bars + 3;     // [2]
-  uint64_t* sdp_full = bars + 5;    // [2]
-  uint64_t* sdp_empty = bars + 7;   // [2]
-  uint64_t* pt_full = bars + 9;     // [2]
-  uint64_t* pt_empty = bars + 11;   // [2]
+  uint64_t* ql_full = bars + 1;     // [2]  slice channels of Q and dO
+  uint64_t* ql_empty = bars + 3;    // [2]  dV_n and dK_n have read them
+  uint64_t* qe_full = bars + 5;     // 1    other channels
+  uint64_t* qe_empty = bars + 6;    // 1    S^T_n and dP^T_n have read them
+  uint64_t* sdp_full = bars + 7;    // [2]
+  uint64_t* pt_full = bars + 9;     // [2]  P^T_n and dS^T_n are in tensor memory
+  uint64_t* acc_free = bars + 11;   // [2]  dV_n and dK_n have read them: the S^T / dP^T buffers are free
   uint64_t* acc_done = bars + 13;   // 1
   uint64_t* stat_bar = bars + 14;   // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
@@ -407,6 +416,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int G = p.H / p.KV;
   const int kv0 = kb * 128;
   const int dv0 = split * DV;
+  const int lb0 = dv0 / 64;  // first 64-channel block of the output slice
   const int q_lo = p.causal ? kv0 : 0;
   int q_hi = p.S;
   if (p.q_hi_blk) q_hi = min(p.S, p.q_hi_blk[b * nkb + kb]);
@@ -422,13 +432,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     prefetch_tmap(&tmap_do);
     mbar_init(kv_full, 1);
     mbar_init(acc_done, 1);
+    mbar_init(qe_full, 1);
+    mbar_init(qe_empty, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&q_full[i], 1);
-      mbar_init(&q_empty[i], 1);
+      mbar_init(&ql_full[i], 1);
+      mbar_init(&ql_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], EW_THREADS);
       mbar_init(&pt_full[i], EW_THREADS);
-      mbar_init(&pt_empty[i], 1);
+      mbar_init(&acc_free[i], 1);
       mbar_init(&stat_bar[i], EW_THREADS);
     }
     mbar_fence_init();
@@ -443,8 +454,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_dk = tmem_base;          // DV <= 128 columns
   const uint32_t tmem_dv = tmem_base + 128;
-  const uint32_t tmem_st = tmem_base + 256;    // 2 x 64
-  const uint32_t tmem_dpt = tmem_base + 384;   // 2 x 64
+  const uint32_t tmem_st = tmem_base + 256;    // 2 x 64: S^T, then P^T (packed) at the start of each half
+  const uint32_t tmem_dpt = tmem_base + 384;   // 2 x 64: dP^T, then dS^T likewise
+
+  // shared-memory address of 64-channel block `blk` of the query-side tile (which = 0: Q, 1: dO)
+  auto q_block = [&](int stage, int which, int blk) -> uint32_t {
+    const bool late = blk >= lb0 && blk < lb0 + LATE_BLKS;
+    if (late)
+      return smem_u32(smem + L::OFF_QL + (stage * 2 + which) * L::LATE_BYTES + (blk - lb0) * (BQ2 * 128));
+    const int e = blk < lb0 ? blk : blk - LATE_BLKS;
+    return smem_u32(smem + L::OFF_QE + which * L::EARLY_BYTES + e * (BQ2 * 128));
+  };
 
   if (warp == WARP_TMA) {
     if (lane == 0 && ntot > 0) {
@@ -454,21 +474,33 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tma_load_4d(smem + L::OFF_K + c * (128 * 128), &tmap_k, kv_full, c * 64, kvh, kv0, b);
         tma_load_4d(smem + L::OFF_V + c * (128 * 128), &tmap_v, kv_full, c * 64, kvh, kv0, b);
       }
-      for (int n = 0; n < ntot; ++n) {
+      bool okp = true;
+      for (int n = 0; n < ntot && okp; ++n) {
         const int g = n / ntile, i = ib + n % ntile;
         const int h = kvh * G + g;
-        const int s = n % NSTQ, use = n / NSTQ;
-        if (!mbar_wait(&q_empty[s], (use & 1) ^ 1)) {
-          atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
-          break;
-        }
-        mbar_expect_tx(&q_full[s], 2 * L::Q_BYTES);
+        const int s = n & 1;
+        if (!mbar_wait(&ql_empty[s], ((n >> 1) & 1) ^ 1)) { okp = false; break; }
+        mbar_expect_tx(&ql_full[s], 2 * L::LATE_BYTES);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c) {
-          tma_load_4d(smem + L::OFF_Q + s * L::Q_BYTES + c * (BQ2 * 128), &tmap_q, &q_full[s], c * 64, h, i * BQ2, b);
-          tma_load_4d(smem + L::OFF_DO + s * L::Q_BYTES + c * (BQ2 * 128), &tmap_do, &q_full[s], c * 64, h, i * BQ2, b);
+        for (int c = 0; c < LATE_BLKS; ++c) {
+          tma_load_4d(smem + L::OFF_QL + (s * 2 + 0) * L::LATE_BYTES + c * (BQ2 * 128), &tmap_q, &ql_full[s],
+                      (lb0 + c) * 64, h, i * BQ2, b);
+          tma_load_4d(smem + L::OFF_QL + (s * 2 + 1) * L::LATE_BYTES + c * (BQ2 * 128), &tmap_do, &ql_full[s],
+                      (lb0 + c) * 64, h, i * BQ2, b);
+        }
+        if (HAS_EARLY) {
+          if (!mbar_wait(qe_empty, (n & 1) ^ 1)) { okp = false; break; }
+          mbar_expect_tx(qe_full, 2 * L::EARLY_BYTES);
+#pragma unroll
+          for (int c = 0; c < HD / 64; ++c) {
+            if (c >= lb0 && c < lb0 + LATE_BLKS) continue;
+            const int e = c < lb0 ? c : c - LATE_BLKS;
+            tma_load_4d(smem + L::OFF_QE + 0 * L::EARLY_BYTES + e * (BQ2 * 128), &tmap_q, qe_full, c * 64, h, i * BQ2, b);
+            tma_load_4d(smem + L::OFF_QE + 1 * L::EARLY_BYTES + e * (BQ2 * 128), &tmap_do, qe_full, c * 64, h, i * BQ2, b);
+          }
         }
       }
+      if (!okp) atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
     }
   } else if (warp == WARP_MMA) {
     if (lane == 0 && ntot > 0) {
@@ -477,54 +509,52 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V);
       bool ok = mbar_wait(kv_full, 0);
       auto issue_sdp = [&](int n) -> bool {
-        const int s = n % NSTQ, use = n / NSTQ, buf = n & 1;
-        if (!mbar_wait(&q_full[s], use & 1)) return false;
-        if (!mbar_wait(&sdp_empty[buf], ((n >> 1) & 1) ^ 1)) return false;
+        const int s = n & 1, buf = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        if (!mbar_wait(&ql_full[s], ph)) return false;
+        if (HAS_EARLY && !mbar_wait(qe_full, n & 1)) return false;
+        if (!mbar_wait(&acc_free[buf], ph ^ 1)) return false;
         tc_fence_after();
-        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::Q_BYTES);
-        const uint32_t sdo = smem_u32(smem + L::OFF_DO + s * L::Q_BYTES);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t blk = k >> 2, kk = k & 3;
           umma_bf16_ss(tmem_st + buf * BQ2, make_smem_desc(sk + blk * (128 * 128) + kk * 32, 16, 1024),
-                       make_smem_desc(sq + blk * (BQ2 * 128) + kk * 32, 16, 1024), idesc_st, k != 0);
+                       make_smem_desc(q_block(s, 0, blk) + kk * 32, 16, 1024), idesc_st, k != 0);
         }
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t blk = k >> 2, kk = k & 3;
           umma_bf16_ss(tmem_dpt + buf * BQ2, make_smem_desc(sv + blk * (128 * 128) + kk * 32, 16, 1024),
-                       make_smem_desc(sdo + blk * (BQ2 * 128) + kk * 32, 16, 1024), idesc_st, k != 0);
+                       make_smem_desc(q_block(s, 1, blk) + kk * 32, 16, 1024), idesc_st, k != 0);
         }
+        if (HAS_EARLY) umma_commit(qe_empty);
         umma_commit(&sdp_full[buf]);
         return true;
       };
       if (ok) ok = issue_sdp(0);
       for (int n = 0; n < ntot && ok; ++n) {
-        if (NSTQ > 1 && n + 1 < ntot) ok = issue_sdp(n + 1);
+        if (n + 1 < ntot) ok = issue_sdp(n + 1);
         if (!ok) break;
-        const int s = n % NSTQ, pb = n % NSTQ;
-        if (!mbar_wait(&pt_full[pb], (n / NSTQ) & 1)) {
+        const int s = n & 1, buf = n & 1;
+        if (!mbar_wait(&pt_full[buf], (n >> 1) & 1)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t spt = smem_u32(smem + L::OFF_PT + pb * L::PT_BYTES);
-        const uint32_t sdst = smem_u32(smem + L::OFF_DST + pb * L::PT_BYTES);
-        // B operands: the [BQ2 x DV] slice of dO / Q starting at channel dv0, MN-major
-        const uint32_t sdo = smem_u32(smem + L::OFF_DO + s * L::Q_BYTES) + (dv0 / 64) * (BQ2 * 128);
-        const uint32_t sq = smem_u32(smem + L::OFF_Q + s * L::Q_BYTES) + (dv0 / 64) * (BQ2 * 128);
+        // B operands: the [BQ2 x DV] slices of dO / Q (slice channels), MN-major
+        const uint32_t sq_l = smem_u32(smem + L::OFF_QL + (s * 2 + 0) * L::LATE_BYTES);
+        const uint32_t sdo_l = smem_u32(smem + L::OFF_QL + (s * 2 + 1) * L::LATE_BYTES);
 #pragma unroll
         for (int k = 0; k < BQ2 / 16; ++k)
-          umma_bf16_ss(tmem_dv, make_smem_desc(spt + k * 32, 16, 1024),
-                       make_smem_desc(sdo + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
+          umma_bf16_ts(tmem_dv, tmem_st + buf * BQ2 + (k >> 1) * 32 + (k & 1) * 8,
+                       make_smem_desc(sdo_l + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
 #pragma unroll
         for (int k = 0; k < BQ2 / 16; ++k)
-          umma_bf16_ss(tmem_dk, make_smem_desc(sdst + k * 32, 16, 1024),
-                       make_smem_desc(sq + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
-        umma_commit(&q_empty[s]);
-        umma_commit(&pt_empty[pb]);
+          umma_bf16_ts(tmem_dk, tmem_dpt + buf * BQ2 + (k >> 1) * 32 + (k & 1) * 8,
+                       make_smem_desc(sq_l + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
+        umma_commit(&ql_empty[s]);
+        umma_commit(&acc_free[buf]);
         if (n == ntot - 1) umma_commit(acc_done);
-        if (NSTQ == 1 && n + 1 < ntot) ok = issue_sdp(n + 1);
       }
       if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
     }
@@ -540,7 +570,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     for (int n = 0; n < ntot && ok; ++n) {
       const int g = n / ntile, i = ib + n % ntile;
       const int h = kvh * G + g;
-      const int buf = n & 1, pb = n % NSTQ;
+      const int buf = n & 1;
       const int q0 = i * BQ2;
       // stage lse (log2 domain; +inf past the end, which makes P = 0) and delta of this query tile
       if (threadIdx.x < 2 * BQ2) {
@@ -563,8 +593,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tmem_ld_32x32(tmem_st + buf * BQ2 + half * 32 + lane_sel, rs);
       tmem_ld_32x32(tmem_dpt + buf * BQ2 + half * 32 + lane_sel, rp);
       tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&sdp_empty[buf]);
       const float4* lse4 = reinterpret_cast<const float4*>(stat + buf * 2 * BQ2 + half * 32);
       const float4* del4 = reinterpret_cast<const float4*>(stat + buf * 2 * BQ2 + BQ2 + half * 32);
       const bool need_mask = (docb != nullptr) || (kv0 + 128 > p.S) || (p.causal && kv0 + 127 > q0) ||
@@ -593,15 +621,18 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           }
         }
       }
-      if (!mbar_wait(&pt_empty[pb], ((n / NSTQ) & 1) ^ 1)) {
-        atomicCAS(p.status, 0, ERR_WAIT_SOFTMAX);
-        ok = false;
-        break;
+      uint32_t pk[16], dk16[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        pk[j] = pack_bf16(pv[2 * j], pv[2 * j + 1]);
+        dk16[j] = pack_bf16(ds[2 * j], ds[2 * j + 1]);
       }
-      store_row32(smem + L::OFF_PT + pb * L::PT_BYTES, 128, row, half * 32, pv);
-      store_row32(smem + L::OFF_DST + pb * L::PT_BYTES, 128, row, half * 32, ds);
-      fence_proxy_async_smem();
-      mbar_arrive(&pt_full[pb]);
+      // each thread overwrites only columns it has read itself (the first 16 of its 32)
+      tmem_st_32x16(tmem_st + buf * BQ2 + half * 32 + lane_sel, pk);
+      tmem_st_32x16(tmem_dpt + buf * BQ2 + half * 32 + lane_sel, dk16);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&pt_full[buf]);
     }
     if (ok && ntot > 0 && !mbar_wait(acc_done, 0)) {
       atomicCAS(p.status, 0, ERR_WAIT_ACC_FULL);
@@ -685,7 +716,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, co
   if (e) return e;
   // ---- dK/dV
   if (make_maps(&tq, &tk, &tv, &tdo, q, k, v, dout, p.B, p.S, p.H, p.KV, HD, qs, ks, vs, BQ2, 128)) return -2;
-  using LK = SmemKV<HD, NSTQ>;
+  using LK = SmemKV<HD, DV>;
   static bool attr2 = false;
   if (!attr2) {
     cudaFuncSetAttribute(attn_bwd_dkdv_kernel<HD, DV, NSTQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, LK::TOTAL);
