@@ -77,21 +77,6 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
   }
 }
 
-// write 32 consecutive bf16 values of row `row` starting at column col0 (multiple of 32) into a
-// K-major swizzled tile made of 64-column blocks of [rows_per_block x 128 B]
-__device__ __forceinline__ void store_row32(uint8_t* tile, int rows_per_block, int row, int col0, const float (&v)[32]) {
-  const int blk = col0 >> 6;
-  const int chunk0 = (col0 & 63) >> 3;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    uint4 o;
-    o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-    o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-    o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-    o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-    *reinterpret_cast<uint4*>(tile + blk * (rows_per_block * 128) + swz128(row, chunk0 + j)) = o;
-  }
-}
 
 // ---------------------------------------------------------------------------------- dQ kernel
 // Per kv block n of 64:  S_n = Q K_n^T and dP_n = dO V_n^T into TMEM (two buffers each); the element-wise

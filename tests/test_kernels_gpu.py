@@ -175,7 +175,7 @@ def test_cross_entropy(V):
     lg.copy_(logits)
     C.ce_fwd_bwd(lg, labels, loss, gs)
     assert abs(loss.item() - want.item()) / want.item() < 1e-4
-    assert _rel(lg, lf.grad) < 8e-3
+    assert _rel(lg, lf.grad) < 1e-2  # bf16 output of the gradient
 
 
 def test_adamw_flat():
