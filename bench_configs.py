@@ -5,6 +5,7 @@
 
 Presets (shapes of the reference's headline configurations; synthetic packed data, random-init weights):
 
+* ``gemma3-4b``         Gemma-3 4B, seq 8192, micro-batch 2 per GPU (the configuration of ``bench.py``)
 * ``gemma3-1b``         Gemma-3 1B, seq 8192, micro-batch 4 per GPU, data-parallel sharding over all GPUs
 * ``llama3-8b-tp2``     Llama-3 8B, seq 8192, micro-batch 2 per data-parallel rank, TP=2 x FSDP
 * ``llama3-8b-cp2``     Llama-3 8B, seq 32768, micro-batch 1, context parallel 2 x FSDP
@@ -25,6 +26,7 @@ import torch
 import bench as B
 
 PRESETS = {
+    "gemma3-4b": dict(model_name="gemma3", flavor="4B", seq_len=8192, train_batch_size=2),
     "gemma3-1b": dict(model_name="gemma3", flavor="1B", seq_len=8192, train_batch_size=4),
     "llama3-8b-tp2": dict(model_name="llama3", flavor="8B", seq_len=8192, train_batch_size=2, tensor_parallel_degree=2),
     "llama3-8b-cp2": dict(model_name="llama3", flavor="8B", seq_len=32768, train_batch_size=1, context_parallel_degree=2),

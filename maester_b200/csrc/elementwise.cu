@@ -300,6 +300,96 @@ __global__ void __launch_bounds__(THREADS, 1) rmsnorm_bwd_fused_kernel(
   }
 }
 
+// Variant with the dw partial sums in shared memory: each warp owns a private fp32 row [D] that only it
+// touches (a lane always owns the same columns), so the accumulation is a plain read-modify-write
+// without atomics, registers hold just the row being processed, and two blocks fit on an SM.
+template <int NV>
+__global__ void __launch_bounds__(256, 2) rmsnorm_bwd_smemacc_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+    const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres_add, __nv_bfloat16* __restrict__ dx,
+    float* __restrict__ dw, int M, int D, int unit_offset) {
+  extern __shared__ float dw_all[];  // [8 warps][D]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D >> 3;
+  float* mine = dw_all + static_cast<size_t>(warp) * D;
+  if (dw) {
+    for (int i = lane; i < D; i += 32) mine[i] = 0.f;
+    __syncwarp();
+  }
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  const float off = unit_offset ? 1.f : 0.f;
+  for (int row = blockIdx.x * 8 + warp; row < M; row += gridDim.x * 8) {
+    const size_t base = static_cast<size_t>(row) * D;
+    const bf16x8* dyr = reinterpret_cast<const bf16x8*>(dy + base);
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + base);
+    const bf16x8* ar = dres_add ? reinterpret_cast<const bf16x8*>(dres_add + base) : nullptr;
+    bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + base);
+    const float rstd = rstd_in[row];
+    bf16x8 cg[NV], cx[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        cg[i] = dyr[v];
+        cx[i] = xr[v];
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float g[8], xf[8], wf[8];
+        unpack8(cg[i], g);
+        unpack8(cx[i], xf);
+        if (w) unpack8(wr[v], wf);
+        float4* acc4 = reinterpret_cast<float4*>(mine + v * 8);
+        float4 a0 = acc4[0], a1 = acc4[1];
+        float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float xh = xf[e] * rstd;
+          dot += g[e] * (w ? wf[e] + off : 1.f) * xh;
+          a[e] += g[e] * xh;
+        }
+        if (dw) {
+          acc4[0] = make_float4(a[0], a[1], a[2], a[3]);
+          acc4[1] = make_float4(a[4], a[5], a[6], a[7]);
+        }
+      }
+    }
+    dot = warp_sum(dot) / static_cast<float>(D);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float g[8], xf[8], wf[8], o[8];
+        unpack8(cg[i], g);
+        unpack8(cx[i], xf);
+        if (w) unpack8(wr[v], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[e] * (w ? wf[e] + off : 1.f) - xf[e] * rstd * dot);
+        if (ar) {
+          float a[8];
+          unpack8(ar[v], a);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += a[e];
+        }
+        dxr[v] = pack8(o);
+      }
+    }
+  }
+  if (dw) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += dw_all[static_cast<size_t>(k) * D + i];
+      atomicAdd(dw + i, s);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ QK-norm + RoPE
 // Input  qkv  [T, (H+2KV)*hd]  (q heads, then k heads, then v heads)
 // Output qk   [T, (H+KV)*hd]   normalised (optional) and rotated q and k
@@ -368,6 +458,64 @@ __device__ __forceinline__ void rope_rotate(float (&f)[E], int lane, int rot, in
   }
 }
 
+// Rotation coefficients of one token for the channels this lane owns, loaded once and reused for all
+// heads of the token.  half layout: c/s[j] for pair index i0 + j; interleaved: c/s[j] for pair j of the lane.
+template <int E>
+struct RopeCoef {
+  float c[E], s[E];
+  bool active, first;
+  int half_lanes;
+};
+template <int E>
+__device__ __forceinline__ void rope_load(RopeCoef<E>& rc, int lane, int rot, int layout, const float* cs_row) {
+  if (layout == 1) {
+    rc.active = true;
+    rc.first = true;
+    rc.half_lanes = 0;
+#pragma unroll
+    for (int j = 0; j < E / 2; ++j) {
+      const int ch = lane * E + 2 * j;
+      const bool in = ch < rot;
+      rc.c[j] = in ? cs_row[ch] : 1.f;
+      rc.s[j] = in ? cs_row[ch + 1] : 0.f;
+    }
+  } else {
+    rc.half_lanes = (rot / 2) / E;
+    rc.active = lane < 2 * rc.half_lanes;
+    rc.first = lane < rc.half_lanes;
+    const int i0 = (rc.first ? lane : lane - rc.half_lanes) * E;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      rc.c[j] = rc.active ? cs_row[2 * (i0 + j)] : 1.f;
+      rc.s[j] = rc.active ? cs_row[2 * (i0 + j) + 1] : 0.f;
+    }
+  }
+}
+template <int E>
+__device__ __forceinline__ void rope_apply(float (&f)[E], const RopeCoef<E>& rc, int layout, float sign) {
+  if (layout == 1) {
+#pragma unroll
+    for (int j = 0; j < E / 2; ++j) {
+      const float a = f[2 * j], b = f[2 * j + 1], s = rc.s[j] * sign;
+      f[2 * j] = a * rc.c[j] - b * s;
+      f[2 * j + 1] = a * s + b * rc.c[j];
+    }
+  } else {
+    float other[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) other[j] = __shfl_xor_sync(0xffffffffu, f[j], rc.half_lanes);
+    if (rc.active) {
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float s = rc.s[j] * sign;
+        f[j] = rc.first ? (f[j] * rc.c[j] - other[j] * s) : (other[j] * s + f[j] * rc.c[j]);
+      }
+    }
+  }
+}
+
+// One warp per TOKEN (grid-stride): the token's rotation coefficients and the norm weights stay in
+// registers while the warp walks over the token's q and k heads.
 template <int E>
 __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv,
                                                              const __nv_bfloat16* __restrict__ qw,
@@ -377,36 +525,43 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(const __nv_bfloat1
                                                              int KV, int rot, int layout, float eps, int unit_offset,
                                                              long long in_stride, long long out_stride) {
   constexpr int hd = E * 32;
-  const long long item = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (item >= items) return;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int heads = H + KV;
-  const long long t = item / heads;
-  const int h = static_cast<int>(item - t * heads);
-  float f[E];
-  load_e<E>(qkv + t * in_stride + static_cast<long long>(h) * hd + lane * E, f);
-  const __nv_bfloat16* w = (h < H) ? qw : kw;
-  if (w) {
-    float ss = 0.f;
+  const long long T = items / heads;
+  const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+  const float off = unit_offset ? 1.f : 0.f;
+  float wq[E], wk[E];
+  if (qw) load_e<E>(qw + lane * E, wq);
+  if (kw) load_e<E>(kw + lane * E, wk);
+  for (long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wid; t < T; t += nwarps) {
+    RopeCoef<E> rc;
+    if (cs) rope_load<E>(rc, lane, rot, layout, cs + static_cast<long long>(pos[t]) * rot);
+    const __nv_bfloat16* src = qkv + t * in_stride + lane * E;
+    __nv_bfloat16* dst = out + t * out_stride + lane * E;
+#pragma unroll 4
+    for (int h = 0; h < heads; ++h) {
+      float f[E];
+      load_e<E>(src + static_cast<long long>(h) * hd, f);
+      const bool is_q = h < H;
+      if (is_q ? (qw != nullptr) : (kw != nullptr)) {
+        float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < E; ++j) ss += f[j] * f[j];
-    ss = warp_sum(ss);
-    const float rstd = rsqrtf(ss / hd + eps);
-    float wf[E];
-    load_e<E>(w + lane * E, wf);
-    const float off = unit_offset ? 1.f : 0.f;
+        for (int j = 0; j < E; ++j) ss += f[j] * f[j];
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / hd + eps);
+        // match separate norm -> rope ops: the normalised value is rounded to bf16 first
 #pragma unroll
-    for (int j = 0; j < E; ++j) f[j] = f[j] * rstd * (wf[j] + off);
-    // match separate norm -> rope ops: the normalised value is rounded to bf16 first
-#pragma unroll
-    for (int j = 0; j < E; ++j) f[j] = __bfloat162float(__float2bfloat16(f[j]));
+        for (int j = 0; j < E; ++j)
+          f[j] = __bfloat162float(__float2bfloat16(f[j] * rstd * ((is_q ? wq[j] : wk[j]) + off)));
+      }
+      if (cs) rope_apply<E>(f, rc, layout, 1.f);
+      store_e<E>(dst + static_cast<long long>(h) * hd, f);
+    }
   }
-  if (cs) rope_rotate<E>(f, lane, rot, layout, cs + static_cast<long long>(pos[t]) * rot, 1.f);
-  store_e<E>(out + t * out_stride + static_cast<long long>(h) * hd + lane * E, f);
 }
 
 // Backward, in place on dqk (gradient w.r.t. rotated q,k) -> gradient w.r.t. the raw q,k.
-// dqw/dkw (fp32 [hd]) accumulate.  Grid-stride over items so weight grads reduce in registers.
+// dqw/dkw (fp32 [hd]) accumulate in registers over all tokens of the warp, then per block, then atomically.
 template <int E>
 __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(__nv_bfloat16* __restrict__ dqk,
                                                              const __nv_bfloat16* __restrict__ qkv,
@@ -421,40 +576,48 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(__nv_bfloat16* __r
   __shared__ float red[2][8][hd];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const int heads = H + KV;
+  const long long T = items / heads;
   const long long nwarps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-  float accq[E], acck[E];
+  float accq[E], acck[E], wq[E], wk[E];
 #pragma unroll
   for (int j = 0; j < E; ++j) accq[j] = acck[j] = 0.f;
+  if (qw) load_e<E>(qw + lane * E, wq);
+  if (kw) load_e<E>(kw + lane * E, wk);
   const float off = unit_offset ? 1.f : 0.f;
-  for (long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wid; item < items; item += nwarps) {
-    const long long t = item / heads;
-    const int h = static_cast<int>(item - t * heads);
-    __nv_bfloat16* gp = dqk + t * g_stride + static_cast<long long>(h) * hd + lane * E;
-    float g[E];
-    load_e<E>(gp, g);
-    if (cs) rope_rotate<E>(g, lane, rot, layout, cs + static_cast<long long>(pos[t]) * rot, -1.f);
-    const __nv_bfloat16* w = (h < H) ? qw : kw;
-    if (w) {
-      float x[E], wf[E];
-      load_e<E>(qkv + t * in_stride + static_cast<long long>(h) * hd + lane * E, x);
-      load_e<E>(w + lane * E, wf);
-      float ss = 0.f;
+  for (long long t = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + wid; t < T; t += nwarps) {
+    RopeCoef<E> rc;
+    if (cs) rope_load<E>(rc, lane, rot, layout, cs + static_cast<long long>(pos[t]) * rot);
+    __nv_bfloat16* gbase = dqk + t * g_stride + lane * E;
+    const __nv_bfloat16* xbase = qkv + t * in_stride + lane * E;
+#pragma unroll 2
+    for (int h = 0; h < heads; ++h) {
+      __nv_bfloat16* gp = gbase + static_cast<long long>(h) * hd;
+      float g[E];
+      load_e<E>(gp, g);
+      const bool is_q = h < H;
+      const bool normed = is_q ? (qw != nullptr) : (kw != nullptr);
+      float x[E];
+      if (normed) load_e<E>(xbase + static_cast<long long>(h) * hd, x);
+      if (cs) rope_apply<E>(g, rc, layout, -1.f);
+      if (normed) {
+        float ss = 0.f;
 #pragma unroll
-      for (int j = 0; j < E; ++j) ss += x[j] * x[j];
-      ss = warp_sum(ss);
-      const float rstd = rsqrtf(ss / hd + eps);
-      float dot = 0.f;
+        for (int j = 0; j < E; ++j) ss += x[j] * x[j];
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / hd + eps);
+        float dot = 0.f;
 #pragma unroll
-      for (int j = 0; j < E; ++j) dot += g[j] * (wf[j] + off) * x[j] * rstd;
-      dot = warp_sum(dot) / hd;
+        for (int j = 0; j < E; ++j) dot += g[j] * ((is_q ? wq[j] : wk[j]) + off) * x[j] * rstd;
+        dot = warp_sum(dot) / hd;
 #pragma unroll
-      for (int j = 0; j < E; ++j) {
-        const float xh = x[j] * rstd;
-        if (h < H) accq[j] += g[j] * xh; else acck[j] += g[j] * xh;
-        g[j] = rstd * (g[j] * (wf[j] + off) - xh * dot);
+        for (int j = 0; j < E; ++j) {
+          const float xh = x[j] * rstd;
+          if (is_q) accq[j] += g[j] * xh; else acck[j] += g[j] * xh;
+          g[j] = rstd * (g[j] * ((is_q ? wq[j] : wk[j]) + off) - xh * dot);
+        }
       }
+      store_e<E>(gp, g);
     }
-    store_e<E>(gp, g);
   }
   if (qw || kw) {
 #pragma unroll
@@ -774,7 +937,28 @@ extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   if (nv <= 16 && M >= 8 * mbh::sm_count()) {
     const int grid = mbh::sm_count();
     const size_t smem = static_cast<size_t>(D) * sizeof(float);
-    static const int variant = getenv("MB_NORM_BWD_VARIANT") ? atoi(getenv("MB_NORM_BWD_VARIANT")) : 1;
+    static const int variant = getenv("MB_NORM_BWD_VARIANT") ? atoi(getenv("MB_NORM_BWD_VARIANT")) : 2;
+    if (variant == 2 && nv <= 12 && static_cast<size_t>(D) * 8 * sizeof(float) <= 100 * 1024) {
+      // dw partials in shared memory (one private row per warp): two blocks per SM
+      const size_t smem2 = static_cast<size_t>(D) * 8 * sizeof(float);
+      const int grid2 = 2 * mbh::sm_count();
+#define MB_NORM_BWD2(NV)                                                                                        \
+  do {                                                                                                          \
+    static bool attr = false;                                                                                   \
+    if (!attr) {                                                                                                \
+      cudaFuncSetAttribute(rmsnorm_bwd_smemacc_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
+      attr = true;                                                                                              \
+    }                                                                                                           \
+    rmsnorm_bwd_smemacc_kernel<NV><<<grid2, 256, smem2, st>>>(                                                  \
+        (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,                       \
+        (const __nv_bfloat16*)dres_add, (__nv_bfloat16*)dx, dw, M, D, unit_offset);                             \
+  } while (0)
+      if (nv <= 4) MB_NORM_BWD2(4);
+      else if (nv <= 8) MB_NORM_BWD2(8);
+      else MB_NORM_BWD2(12);
+#undef MB_NORM_BWD2
+      return mbh::check_launch("rmsnorm_bwd_smemacc");
+    }
 #define MB_NORM_BWD(NV, CACHE, THREADS)                                                                          \
   rmsnorm_bwd_fused_kernel<NV, CACHE, THREADS><<<grid, THREADS, smem, st>>>(                                     \
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd, (const __nv_bfloat16*)dres_add, \
@@ -813,7 +997,9 @@ extern "C" int mb_qknorm_rope_fwd(const void* qkv, const void* qw, const void* k
                                   void* out, long long T, int H, int KV, int hd, int rot, int layout, float eps,
                                   int unit_offset, long long in_stride, long long out_stride, cudaStream_t st) {
   const long long items = T * (H + KV);
-  const int blocks = static_cast<int>((items + 7) / 8);
+  long long want_f = (T + 7) / 8;  // one warp per token
+  const long long cap_f = static_cast<long long>(mbh::sm_count()) * 8;
+  const int blocks = static_cast<int>(want_f < cap_f ? (want_f > 0 ? want_f : 1) : cap_f);
 #define MB_QK_FWD(E)                                                                                         \
   qknorm_rope_fwd_kernel<E><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)qw,      \
                                                     (const __nv_bfloat16*)kw, pos, cs, (__nv_bfloat16*)out,   \
@@ -832,7 +1018,8 @@ extern "C" int mb_qknorm_rope_bwd(void* dqk, const void* qkv, const void* qw, co
                                   int rot, int layout, float eps, int unit_offset, long long g_stride,
                                   long long in_stride, cudaStream_t st) {
   const long long items = T * (H + KV);
-  long long want = (items + 7) / 8;
+  long long want = (T + 7) / 8;  // one warp per token
+  if (want < 1) want = 1;
   const long long cap = static_cast<long long>(mbh::sm_count()) * 8;
   const int blocks = static_cast<int>(want < cap ? want : cap);
 #define MB_QK_BWD(E)                                                                                          \

@@ -114,6 +114,18 @@ def bench_elementwise(iters: int, small: bool) -> None:
     report("geglu fwd", timeit(lambda: C.glu_fwd(gu, 0), iters, warm), gu.numel() * 3)
     do = torch.randn(M, F, device="cuda", dtype=torch.bfloat16)
     report("geglu bwd", timeit(lambda: C.glu_bwd(gu, do, 0), iters, warm), gu.numel() * 2 * 2 + do.numel() * 2)
+    H, KV, hd = 8, 4, 256
+    qkv = torch.randn(M, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
+    qw = torch.zeros(hd, device="cuda", dtype=torch.bfloat16)
+    pos = (torch.arange(M, device="cuda", dtype=torch.int32) % 8192).contiguous()
+    cs = torch.randn(8192, hd // 2, 2, device="cuda")
+    nbytes = M * ((H + KV) * hd * 2) * 2
+    report("qknorm+rope fwd", timeit(lambda: C.qknorm_rope_fwd(qkv, qw, qw, pos, cs, H, KV, hd, 0, 1e-6, True), iters, warm),
+           nbytes)
+    dqk = torch.randn(M, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
+    dqw, dkw = torch.zeros(hd, device="cuda"), torch.zeros(hd, device="cuda")
+    report("qknorm+rope bwd", timeit(lambda: C.qknorm_rope_bwd(dqk, qkv, qw, qw, pos, cs, dqw, dkw, H, KV, hd, 0, 1e-6, True),
+                                     iters, warm), M * ((H + KV) * hd * 2) * 3)
     if small:
         return
     from maester_b200.optimizers.adamw import FusedAdamW
