@@ -44,8 +44,8 @@ __device__ __forceinline__ bf16x8 pack8(const float (&f)[8]) {
 // One warp per row.  y = [residual +] x * rsqrt(mean(x^2)+eps) * (w or 1+w).  D % 8 == 0.
 constexpr int NORM_MAXV = 16;  // vectors of 8 kept in registers per lane (D <= 4096)
 
-template <bool CACHE>
-__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+template <int NV>  // vectors of 8 kept in registers per lane; 0: no register cache (any D)
+__global__ void __launch_bounds__(256, NV > 0 && NV <= 8 ? 4 : (NV == 12 ? 3 : 2)) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x,
                                                          const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ res,
                                                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out,
@@ -58,11 +58,13 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
   const bf16x8* rr = res ? reinterpret_cast<const bf16x8*>(res + static_cast<size_t>(warp) * D) : nullptr;
   bf16x8* yr = reinterpret_cast<bf16x8*>(y + static_cast<size_t>(warp) * D);
   const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-  bf16x8 cache[CACHE ? NORM_MAXV : 1];
+  constexpr bool CACHE = NV > 0;
+  constexpr int NC = CACHE ? NV : 1;
+  bf16x8 cache[NC];
   float ss = 0.f;
   if (CACHE) {
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
+    for (int i = 0; i < NC; ++i) {
       const int v = lane + 32 * i;
       if (v < nvec) {
         cache[i] = xr[v];
@@ -108,7 +110,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
   };
   if (CACHE) {
 #pragma unroll
-    for (int i = 0; i < NORM_MAXV; ++i) {
+    for (int i = 0; i < NC; ++i) {
       const int v = lane + 32 * i;
       if (v < nvec) emit(v, cache[i]);
     }
@@ -919,14 +921,15 @@ extern "C" int mb_rmsnorm_fwd(const void* x, const void* w, const void* res, voi
                               float eps, int unit_offset, cudaStream_t st) {
   if (D & 7) return -3;
   const int blocks = (M + 7) / 8;
-  if ((D >> 3) <= NORM_MAXV * 32)
-    rmsnorm_fwd_kernel<true><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                     (const __nv_bfloat16*)res, (__nv_bfloat16*)y, rstd, M, D, eps,
-                                                     unit_offset);
-  else
-    rmsnorm_fwd_kernel<false><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
-                                                      (const __nv_bfloat16*)res, (__nv_bfloat16*)y, rstd, M, D, eps,
-                                                      unit_offset);
+  const int nv = (D / 8 + 31) / 32;
+#define MB_NORM_FWD(NV)                                                                                       \
+  rmsnorm_fwd_kernel<NV><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,            \
+                                                 (const __nv_bfloat16*)res, (__nv_bfloat16*)y, rstd, M, D, eps, \
+                                                 unit_offset)
+  // one instantiation for every D <= 4096: narrower register caches (more blocks per SM) measured slower
+  if (nv <= NORM_MAXV) MB_NORM_FWD(NORM_MAXV);
+  else MB_NORM_FWD(0);
+#undef MB_NORM_FWD
   return mbh::check_launch("rmsnorm_fwd");
 }
 
