@@ -46,6 +46,17 @@ def _as_dtensor(local: torch.Tensor, slot, sharded) -> torch.Tensor:
             return local
         from torch.distributed.tensor.placement_types import _StridedShard
         placements = [_StridedShard(0, split_factor=mesh.size(1)), Shard(0)]
+    elif sharded is not None and slot.tp_dim >= 0 and getattr(sharded, "tp_mesh", None) is not None:
+        # tensor-parallel slice (dim 0 or 1) of a parameter that is also sharded along dim 0 over the
+        # data-parallel ranks: the tp split comes first, so on dim 0 the data-parallel shard is strided
+        mesh = sharded.tp_mesh
+        from torch.distributed.tensor.placement_types import _StridedShard
+        if mesh.ndim == 1:
+            placements = [Shard(slot.tp_dim)]
+        elif slot.tp_dim == 0:
+            placements = [_StridedShard(0, split_factor=mesh.size(1)), Shard(0)]
+        else:
+            placements = [Shard(0), Shard(slot.tp_dim)]
     else:
         mesh = getattr(sharded, "device_mesh", None)
         if sharded is None or sharded.world == 1 or mesh is None:

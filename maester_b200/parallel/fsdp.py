@@ -47,6 +47,8 @@ class ParamSlot:
                                  # slice, sharded over the ranks that hold the same experts
     global_rows: int = 0         # dim 0 of the whole (all experts) tensor
     row_base: int = 0            # first global row of this rank's local slice (expert-parallel offset)
+    tp_dim: int = -1             # tensor-parallel slice dimension of this parameter (-1: not tensor-parallel)
+    tp_size: int = 1
 
     @property
     def padded_numel(self) -> int:
@@ -54,7 +56,12 @@ class ParamSlot:
 
     @property
     def global_shape(self) -> torch.Size:
-        return torch.Size((self.global_rows, *self.shape[1:])) if len(self.shape) else self.shape
+        if not len(self.shape):
+            return self.shape
+        dims = [self.global_rows, *self.shape[1:]]
+        if self.tp_dim >= 0:
+            dims[self.tp_dim] *= self.tp_size
+        return torch.Size(dims)
 
 
 @dataclass
@@ -205,7 +212,10 @@ class ShardedModel:
         dom = 1 if getattr(p, "ep_local", False) else 0
         chunk = (rows + self.domains[dom].world - 1) // self.domains[dom].world
         ep, er = (self.ep_size, self.ep_rank) if dom == 1 else (1, 0)
-        return ParamSlot(fqn, p, shape, rows, row_numel, chunk, dom=dom, global_rows=rows * ep, row_base=rows * er)
+        tp_dim = int(getattr(p, "tp_dim", -1))
+        tp_size = dist.get_world_size(self.tp_group) if (tp_dim >= 0 and self.tp_group is not None) else 1
+        return ParamSlot(fqn, p, shape, rows, row_numel, chunk, dom=dom, global_rows=rows * ep, row_base=rows * er,
+                         tp_dim=tp_dim if tp_size > 1 else -1, tp_size=tp_size)
 
     def _rebind_parameters(self) -> None:
         """Point every model parameter at its view of ``full`` and create the fp32 master shards."""

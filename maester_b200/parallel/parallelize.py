@@ -143,6 +143,10 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
     )
     sharded.device_mesh = world_mesh["dp_shard_cp"] if (shard_group is not None and world_mesh is not None) else None
     sharded.expert_mesh = _expert_checkpoint_mesh(world_mesh, parallel_dims) if ep is not None else None
+    sharded.tp_mesh = None  # (dp_shard, tp) or (tp,) sub-mesh describing tensor-parallel slices in checkpoints
+    if parallel_dims.tp_enabled and not has_moe and world_mesh is not None and not parallel_dims.cp_enabled:
+        names = [n for n in ("dp_shard", "tp") if n in (world_mesh.mesh_dim_names or ())]
+        sharded.tp_mesh = world_mesh[tuple(names)] if len(names) > 1 else world_mesh[names[0]]
     object.__setattr__(model, "_sharded", sharded)
     model.set_requires_gradient_sync = sharded.set_requires_gradient_sync
     # buffers that are still on the meta device (RoPE tables) are rebuilt by init_weights()

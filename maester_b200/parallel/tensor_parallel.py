@@ -188,9 +188,12 @@ def vocab_parallel_cross_entropy(h: torch.Tensor, w_local: torch.Tensor, labels:
 
 
 # ------------------------------------------------------------------------------ applying the plan
-def _reshape_linear(lin: nn.Module, out_features: int, in_features: int) -> None:
+def _reshape_linear(lin: nn.Module, out_features: int, in_features: int, tp_dim: int) -> None:
+    """Replace the weight by this rank's slice; ``tp_dim`` (0: output rows, 1: input columns) is kept on
+    the parameter so that checkpoints can describe the tensor-parallel layout."""
     lin.weight = nn.Parameter(torch.empty(out_features, in_features, device=lin.weight.device,
                                           dtype=lin.weight.dtype))
+    lin.weight.tp_dim = tp_dim
     lin.in_features, lin.out_features = in_features, out_features
 
 
@@ -217,15 +220,15 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
         hd = att.head_dim
         att.n_heads //= tp.size
         att.n_kv_heads //= tp.size
-        _reshape_linear(att.wq, att.n_heads * hd, a.dim)
-        _reshape_linear(att.wk, att.n_kv_heads * hd, a.dim)
-        _reshape_linear(att.wv, att.n_kv_heads * hd, a.dim)
-        _reshape_linear(att.wo, a.dim, att.n_heads * hd)
+        _reshape_linear(att.wq, att.n_heads * hd, a.dim, 0)
+        _reshape_linear(att.wk, att.n_kv_heads * hd, a.dim, 0)
+        _reshape_linear(att.wv, att.n_kv_heads * hd, a.dim, 0)
+        _reshape_linear(att.wo, a.dim, att.n_heads * hd, 1)
         hidden = ff.w1.out_features
         assert hidden % tp.size == 0
-        _reshape_linear(ff.w1, hidden // tp.size, a.dim)
-        _reshape_linear(ff.w3, hidden // tp.size, a.dim)
-        _reshape_linear(ff.w2, a.dim, hidden // tp.size)
+        _reshape_linear(ff.w1, hidden // tp.size, a.dim, 0)
+        _reshape_linear(ff.w3, hidden // tp.size, a.dim, 0)
+        _reshape_linear(ff.w2, a.dim, hidden // tp.size, 1)
         layer.tp = tp
         if fused is not None:
             att.tp_fused = ff.tp_fused = fused
@@ -233,7 +236,7 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
             for p in norm.parameters():
                 p.tp_replicated = True
     if not a.tied_embeddings:
-        _reshape_linear(model.output, a.vocab_size // tp.size, a.dim)
+        _reshape_linear(model.output, a.vocab_size // tp.size, a.dim, 0)
     model.tok_embeddings.weight.tp_replicated = True
     for p in model.norm.parameters():
         p.tp_replicated = True
