@@ -11,6 +11,7 @@ Presets (shapes of the reference's headline configurations; synthetic packed dat
 * ``llama3-8b-cp2``     Llama-3 8B, seq 32768, micro-batch 1, context parallel 2 x FSDP
 * ``deepseek-moe-ep8``  16-layer DeepSeek-style MoE (64 routed experts, top-6), seq 4096, micro-batch 4 per GPU,
                         expert parallel over all GPUs x FSDP
+* ``deepseek-moe-1gpu`` the same MoE block at 6 layers (fits one GPU without expert parallelism), seq 4096, micro-batch 4
 
 Timing as in ``bench.py``: warm-up, then CUDA events around K steps between barriers, max over ranks,
 clocks sampled during the timed region; one JSON line from rank 0.
@@ -32,6 +33,7 @@ PRESETS = {
     "llama3-8b-cp2": dict(model_name="llama3", flavor="8B", seq_len=32768, train_batch_size=1, context_parallel_degree=2),
     "deepseek-moe-ep8": dict(model_name="deepseek", flavor="bench16L", seq_len=4096, train_batch_size=4,
                              expert_parallel="world"),
+    "deepseek-moe-1gpu": dict(model_name="deepseek", flavor="bench6L", seq_len=4096, train_batch_size=4),
 }
 
 

@@ -29,4 +29,6 @@ deepseek_configs = {
                 mscale=1.0),
     # 16-layer MoE used as a benchmark configuration: 64 routed experts (ffn 1408) + 2 shared, top-6
     "bench16L": _ds(102400, 2048, 10944, 1408, 16, 16, _moe(64, 6), max_seq_len=4096),
+    # the same block at 6 layers: fits one GPU with fp32 master weights and Adam state (no expert parallelism)
+    "bench6L": _ds(102400, 2048, 10944, 1408, 6, 16, _moe(64, 6), max_seq_len=4096),
 }

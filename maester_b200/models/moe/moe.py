@@ -16,6 +16,7 @@ dispatch both synchronise).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Literal
 
@@ -25,7 +26,10 @@ import torch.nn.functional as F
 
 from maester_b200 import ops
 from maester_b200.models.layers import FusedWeight, Linear
-from maester_b200.ops.functional import GROUP_ALIGN, grouped_linear, padded_group_offsets
+from maester_b200.ops.functional import GROUP_ALIGN, grouped_swiglu, padded_group_offsets
+
+# routing, permutation and combine as native kernels (csrc/moe_route.cu); "0" keeps the ATen chain
+FUSED_ROUTING = os.environ.get("MB_MOE_FUSED_ROUTE", "1") != "0"
 
 
 @dataclass
@@ -76,10 +80,7 @@ class GroupedExperts(nn.Module):
 
     def forward(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
         """x: expert-major rows [rows_cap, dim] with zero padding rows; offs: padded int32 offsets."""
-        h1 = grouped_linear(x, self.w1, offs)
-        h3 = grouped_linear(x, self.w3, offs)
-        act = ops.glu(torch.cat([h1, h3], dim=-1), "silu")
-        return grouped_linear(act, self.w2, offs)
+        return grouped_swiglu(x, self.w1, self.w3, self.w2, offs)
 
     def init_weights(self, init_std: float) -> None:
         gen = None
@@ -210,6 +211,70 @@ class _SlotCombine(torch.autograd.Function):
         return g.index_select(0, token_idx), None, None, None
 
 
+class _FusedRoute(torch.autograd.Function):
+    """Scores, top-k and the whole routing plan in three launches (``csrc/moe_route.cu``).  Returns the gate
+    values [T, k] and the scores [T, E] (both differentiable); the plan object is appended to ``holder``."""
+
+    @staticmethod
+    def forward(ctx, logits, bias, k, softmax, norm, scale, force_balance, holder):
+        from maester_b200.ops import cuda as C
+        plan = C.moe_route(logits.contiguous(), bias, k, softmax, norm, scale, force_balance, GROUP_ALIGN)
+        holder.append(plan)
+        ctx.save_for_backward(plan.scores, plan.idx)
+        ctx.cfg = (softmax, norm, scale)
+        ctx.set_materialize_grads(False)
+        return plan.top, plan.scores
+
+    @staticmethod
+    def backward(ctx, d_top, d_scores):
+        from maester_b200.ops import cuda as C
+        scores, idx = ctx.saved_tensors
+        softmax, norm, scale = ctx.cfg
+        if d_top is None:
+            d_top = torch.zeros(idx.shape, device=scores.device, dtype=torch.float32)
+        return C.moe_route_bwd(d_top, d_scores, scores, idx, softmax, norm, scale), None, None, None, None, None, None, None
+
+
+class _RowsGather(torch.autograd.Function):
+    """Token rows -> tile-padded expert-major buffer (zeros in the padding), optionally times the gate value."""
+
+    @staticmethod
+    def forward(ctx, x, gate, row_slot, slot_row, k):
+        from maester_b200.ops import cuda as C
+        ctx.k = k
+        ctx.save_for_backward(x if gate is not None else None, gate, row_slot, slot_row)
+        return C.moe_rows_gather(x, row_slot, gate, k)
+
+    @staticmethod
+    def backward(ctx, g):
+        from maester_b200.ops import cuda as C
+        x, gate, row_slot, slot_row = ctx.saved_tensors
+        g = g.contiguous()
+        dx = C.moe_rows_combine(g, slot_row, gate, ctx.k)
+        dgate = C.moe_slot_dot(g, slot_row, x, ctx.k).view_as(gate) if gate is not None else None
+        return dx, dgate, None, None, None
+
+
+class _RowsCombine(torch.autograd.Function):
+    """Expert-major buffer -> one row per token: the sum of its k rows, optionally weighted by the gate values."""
+
+    @staticmethod
+    def forward(ctx, buf, gate, row_slot, slot_row, k):
+        from maester_b200.ops import cuda as C
+        ctx.k = k
+        ctx.save_for_backward(buf if gate is not None else None, gate, row_slot, slot_row)
+        return C.moe_rows_combine(buf, slot_row, gate, k)
+
+    @staticmethod
+    def backward(ctx, g):
+        from maester_b200.ops import cuda as C
+        buf, gate, row_slot, slot_row = ctx.saved_tensors
+        g = g.contiguous()
+        dbuf = C.moe_rows_gather(g, row_slot, gate, ctx.k)
+        dgate = C.moe_slot_dot(buf, slot_row, g, ctx.k).view_as(gate) if gate is not None else None
+        return dbuf, dgate, None, None, None
+
+
 class TokenReorderer(nn.Module):
     """Stable expert-major ordering of the T*k routing slots."""
 
@@ -257,6 +322,13 @@ class MoE(nn.Module):
         if self.tp_group is not None:  # hidden dimension sharded over tp: partial outputs, summed below
             from maester_b200.parallel.expert_parallel import _CopyToTP
             x = _CopyToTP.apply(x, self.tp_group)
+        if (FUSED_ROUTING and ops.use_native(x, self.router.gate.weight) and dim % 8 == 0
+                and self.router.num_experts <= 256 and self.top_k <= 8):
+            out = self._forward_fused(x.contiguous())
+            if self.tp_group is not None:
+                from maester_b200.parallel.expert_parallel import _ReduceFromTP
+                out = _ReduceFromTP.apply(out, self.tp_group)
+            return out.reshape(bs, slen, dim)
         top, idx, counts_f, scores = self.router(x, self.expert_bias)
         with torch.no_grad():
             self.tokens_per_expert.add_(counts_f)
@@ -293,6 +365,34 @@ class MoE(nn.Module):
             from maester_b200.parallel.expert_parallel import _ReduceFromTP
             out = _ReduceFromTP.apply(out, self.tp_group)
         return out.reshape(bs, slen, dim)
+
+    def _forward_fused(self, x: torch.Tensor) -> torch.Tensor:
+        """Same block with the routing chain, the permutation and the weighted combine as native kernels."""
+        r, k = self.router, self.top_k
+        logits = _RouterGemm.apply(x, r.gate.weight)
+        holder: list = []
+        top, scores = _FusedRoute.apply(logits, self.expert_bias, k, r.score_func == "softmax", r.route_norm,
+                                        float(r.route_scale), r._debug_force_load_balance, holder)
+        plan = holder[0]
+        with torch.no_grad():
+            self.tokens_per_expert.add_(plan.counts_f)
+        if self.aux_loss_coeff > 0 and self.training:
+            frac = plan.counts_f / float(plan.T * k)
+            self.aux_loss = self.aux_loss_coeff * r.num_experts * (frac * scores.mean(dim=0)).sum()
+        if self.dispatcher is not None:
+            L = plan.as_long()
+            self.reorderer.last_order, self._inv = L["order"], L["inv"]
+            sorted_scores = top.reshape(-1).index_select(0, L["order"])
+            routed_out = self.dispatcher(self, x, sorted_scores, L["token_idx"], L["counts"], L["sorted_experts"])
+            out = _SlotCombine.apply(routed_out, L["token_idx"], self._inv, k)
+        else:
+            before = self.score_before_experts
+            buf = _RowsGather.apply(x, top if before else None, plan.row_slot, plan.slot_row, k)
+            out = _RowsCombine.apply(self.experts(buf, plan.offs), None if before else top, plan.row_slot,
+                                     plan.slot_row, k)
+        if self.shared_experts is not None:
+            out = self.shared_experts(x, residual=out)
+        return out
 
     def gather_slots(self, x: torch.Tensor, token_idx: torch.Tensor) -> torch.Tensor:
         """Rows of ``x`` in sorted-slot order (used by this block and by the expert-parallel dispatchers)."""

@@ -345,3 +345,90 @@ def gemm_grouped_contr(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, out
                                               rows_cap, M, N, _rows_pitch(a), _rows_pitch(b), N, epi, float(alpha),
                                               _stream()), "gemm_grouped_contr")
     return out
+
+
+class RoutePlan:
+    """Device-side routing plan of one MoE block (all int32 / fp32 tensors, no host values)."""
+    __slots__ = ("T", "E", "k", "rows_cap", "scores", "top", "idx", "counts", "counts_f", "offs", "order", "inv",
+                 "slot_row", "row_slot", "sorted_scores", "token_idx", "sorted_experts", "_ints", "_sizes")
+
+    def as_long(self) -> dict[str, torch.Tensor]:
+        """int64 copies of the index vectors (one conversion launch) for code that indexes with them."""
+        names = ("counts", "offs", "order", "inv", "slot_row", "token_idx", "sorted_experts", "row_slot")
+        return dict(zip(names, torch.split(self._ints.long(), self._sizes)))
+
+
+def moe_route(logits: torch.Tensor, bias: torch.Tensor | None, k: int, softmax: bool, norm: bool, scale: float,
+              force_balance: bool, align: int) -> RoutePlan:
+    """Score function, (biased) top-k, histogram and a stable expert-major ordering of the T*k slots."""
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    dev = logits.device
+    p = RoutePlan()
+    p.T, p.E, p.k = T, E, k
+    p.rows_cap = (T * k + E * (align - 1) + align - 1) // align * align
+    n = T * k
+    f32 = dict(device=dev, dtype=torch.float32)
+    i32 = dict(device=dev, dtype=torch.int32)
+    p.scores = torch.empty(T, E, **f32)
+    p.top = torch.empty(T, k, **f32)
+    p.idx = torch.empty(T, k, **i32)
+    p.counts_f = torch.empty(E, **f32)
+    ints = torch.empty(E + (E + 1) + 5 * n + p.rows_cap, **i32)  # one allocation for the index vectors
+    p._ints, p._sizes = ints, [E, E + 1, n, n, n, n, n, p.rows_cap]
+    parts = torch.split(ints, p._sizes)
+    p.counts, p.offs, p.order, p.inv, p.slot_row, p.token_idx, p.sorted_experts, p.row_slot = parts
+    p.sorted_scores = torch.empty(n, **f32)
+    scratch = torch.empty((T + 63) // 64 * E + E, **i32)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == E
+    _ck(_lib.lib().mb_moe_route(logits.data_ptr(), _ptr(bias), T, E, k, int(softmax), int(norm), float(scale),
+                                int(force_balance), align, p.rows_cap, p.scores.data_ptr(), p.top.data_ptr(),
+                                p.idx.data_ptr(), p.counts.data_ptr(), p.counts_f.data_ptr(), p.offs.data_ptr(),
+                                p.order.data_ptr(), p.inv.data_ptr(), p.slot_row.data_ptr(), p.row_slot.data_ptr(),
+                                p.sorted_scores.data_ptr(), p.token_idx.data_ptr(), p.sorted_experts.data_ptr(),
+                                scratch.data_ptr(), _stream()), "moe_route")
+    return p
+
+
+def moe_route_bwd(d_top: torch.Tensor, d_scores: torch.Tensor | None, scores: torch.Tensor, idx: torch.Tensor,
+                  softmax: bool, norm: bool, scale: float) -> torch.Tensor:
+    T, E = scores.shape
+    k = idx.shape[1]
+    d_top = d_top.contiguous().float()
+    if d_scores is not None:
+        d_scores = d_scores.contiguous().float()
+    out = torch.empty_like(scores)
+    _ck(_lib.lib().mb_moe_route_bwd(d_top.data_ptr(), _ptr(d_scores), scores.data_ptr(), idx.data_ptr(), T, E, k,
+                                    int(softmax), int(norm), float(scale), out.data_ptr(), _stream()), "moe_route_bwd")
+    return out
+
+
+def moe_rows_gather(x: torch.Tensor, row_slot: torch.Tensor, slot_scale: torch.Tensor | None, k: int) -> torch.Tensor:
+    """buf[r] = x[row_slot[r] // k] (* slot_scale[row_slot[r]]); zero rows where row_slot[r] < 0."""
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and row_slot.dtype == torch.int32
+    rows, dim = row_slot.numel(), x.shape[1]
+    buf = torch.empty(rows, dim, device=x.device, dtype=x.dtype)
+    _ck(_lib.lib().mb_moe_rows_gather(x.data_ptr(), row_slot.data_ptr(), _ptr(slot_scale), k, rows, dim, buf.data_ptr(),
+                                      _stream()), "moe_rows_gather")
+    return buf
+
+
+def moe_rows_combine(buf: torch.Tensor, slot_row: torch.Tensor, slot_scale: torch.Tensor | None, k: int) -> torch.Tensor:
+    """out[t] = sum_j buf[slot_row[t*k+j]] (* slot_scale[t*k+j]) with fp32 accumulation."""
+    assert buf.dtype == torch.bfloat16 and buf.is_contiguous() and slot_row.dtype == torch.int32
+    T, dim = slot_row.numel() // k, buf.shape[1]
+    out = torch.empty(T, dim, device=buf.device, dtype=buf.dtype)
+    _ck(_lib.lib().mb_moe_rows_combine(buf.data_ptr(), slot_row.data_ptr(), _ptr(slot_scale), k, T, dim, buf.shape[0],
+                                       out.data_ptr(), _stream()), "moe_rows_combine")
+    return out
+
+
+def moe_slot_dot(buf: torch.Tensor, slot_row: torch.Tensor, g: torch.Tensor, k: int) -> torch.Tensor:
+    """d[t*k+j] = <buf[slot_row[t*k+j]], g[t]> in fp32."""
+    assert buf.dtype == torch.bfloat16 and g.dtype == torch.bfloat16 and buf.is_contiguous() and g.is_contiguous()
+    T, dim = g.shape
+    out = torch.empty(T * k, device=buf.device, dtype=torch.float32)
+    _ck(_lib.lib().mb_moe_slot_dot(buf.data_ptr(), slot_row.data_ptr(), g.data_ptr(), k, T, dim, buf.shape[0],
+                                   out.data_ptr(), _stream()), "moe_slot_dot")
+    return out

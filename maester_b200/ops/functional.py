@@ -401,6 +401,55 @@ class _GroupedLinear(Function):
         return dx, dw, None
 
 
+class _GroupedSwiGLU(Function):
+    """Whole expert FFN ``(silu(x w1) * (x w3)) w2`` over padded row groups.  Gate and up projections write the
+    two halves of one ``[rows, 2*hidden]`` buffer (no concatenation); the activation is recomputed in the
+    backward pass instead of being saved."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w3, w2, offs):
+        C = _C()
+        H = w1.shape[2]
+        h13 = torch.empty(x.shape[0], 2 * H, device=x.device, dtype=x.dtype)
+        C.gemm_grouped_rows(x, w1, offs, b_mn=True, out=h13[:, :H])
+        C.gemm_grouped_rows(x, w3, offs, b_mn=True, out=h13[:, H:])
+        ctx.save_for_backward(x, w1, w3, w2, offs, h13)
+        return C.gemm_grouped_rows(C.glu_fwd(h13, _ACT["silu"]), w2, offs, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _C()
+        x, w1, w3, w2, offs, h13 = ctx.saved_tensors
+        H = w1.shape[2]
+        dy = dy.contiguous()
+        act = C.glu_fwd(h13, _ACT["silu"])
+        dact = C.gemm_grouped_rows(dy, w2, offs, b_mn=False)
+        d13 = C.glu_bwd(h13, dact, _ACT["silu"])
+        del dact
+        grads = []
+        for w, a, b in ((w1, x, d13[:, :H]), (w3, x, d13[:, H:]), (w2, act, dy)):
+            mg = getattr(w, "main_grad", None)
+            buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+            C.gemm_grouped_contr(a, b, offs, buf)
+            grads.append(None if mg is not None else buf.to(w.dtype))
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = C.gemm_grouped_rows(d13[:, :H], w1, offs, b_mn=False)
+            dx.add_(C.gemm_grouped_rows(d13[:, H:], w3, offs, b_mn=False))
+        return dx, grads[0], grads[1], grads[2], None
+
+
+def grouped_swiglu(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, offs: torch.Tensor):
+    """Expert FFN over padded row groups: ``w1, w3: [E, dim, hidden]``, ``w2: [E, hidden, dim]``."""
+    H = w1.shape[2]
+    if (use_native(x, w1) and x.shape[0] % GROUP_ALIGN == 0 and w1.shape[1] % 64 == 0 and H % 64 == 0
+            and x.is_contiguous()):
+        return _GroupedSwiGLU.apply(x, w1, w3, w2, offs)
+    h1 = grouped_linear(x, w1, offs)
+    h3 = grouped_linear(x, w3, offs)
+    return grouped_linear(glu(torch.cat([h1, h3], dim=-1), "silu"), w2, offs)
+
+
 def grouped_linear(x: torch.Tensor, w: torch.Tensor, offs: torch.Tensor, counts: torch.Tensor | None = None):
     """``y[rows of group e] = x[rows of group e] @ w[e]`` with w: [E, in, out].
 
