@@ -90,6 +90,103 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
       : "memory");
 }
 
+// ---- all-gather fused into the GEMM: untiled bulk copies (no multicast) and the tile counters
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(gdst)), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ bool wait_counter(const int* p, int target) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_acquire_gpu(p) < target) {
+    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > MB_WAIT_TIMEOUT_NS) return false;
+  }
+  return true;
+}
+
+// One thread of a copying CTA: its share of every remote 256-row tile of A, in the order in which the computing
+// pairs reach the tiles (next rank's block first).  Shares are contiguous byte ranges; they move through the
+// ring of pipeline stages in pieces of at most one stage, loads running STAGES-1 pieces ahead of the stores.
+__device__ void ag_copy_rows(const GemmParams& p, uint8_t* smem, uint64_t* bars, int copier, int ncopiers, int tm) {
+  const int tiles_per_rank = tm / p.ag_world;
+  const long long row_bytes = p.ag_ld * 2;
+  const int rows_per = (2 * BM) / ncopiers;                 // rows of each tile handled by this CTA
+  const long long share = rows_per * row_bytes;
+  const int pieces_per_tile = static_cast<int>((share + STAGE_BYTES - 1) / STAGE_BYTES);
+  const int remote_tiles = tiles_per_rank * (p.ag_world - 1);
+  const long long n = static_cast<long long>(remote_tiles) * pieces_per_tile;
+  bool ok = true;
+  auto piece = [&](long long j, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, int& mt) {
+    const int t = static_cast<int>(j / pieces_per_tile), q = static_cast<int>(j % pieces_per_tile);
+    const int owner = (p.ag_rank + 1 + t / tiles_per_rank) % p.ag_world;
+    const int lt = t % tiles_per_rank;                      // tile inside the owner's block
+    mt = owner * tiles_per_rank + lt;
+    const long long off = (static_cast<long long>(lt) * 2 * BM + static_cast<long long>(copier) * rows_per) * row_bytes +
+                          static_cast<long long>(q) * STAGE_BYTES;
+    const long long left = share - static_cast<long long>(q) * STAGE_BYTES;
+    bytes = static_cast<uint32_t>(left < STAGE_BYTES ? left : STAGE_BYTES);
+    src = static_cast<const uint8_t*>(p.ag_src[owner]) + off;
+    dst = static_cast<uint8_t*>(p.ag_dst) + static_cast<long long>(owner) * tiles_per_rank * 2 * BM * row_bytes + off;
+  };
+  auto issue = [&](long long j) {
+    const uint8_t* src;
+    uint8_t* dst;
+    uint32_t bytes;
+    int mt;
+    piece(j, src, dst, bytes, mt);
+    const int s = static_cast<int>(j % STAGES);
+    mbar_expect_tx(&bars[s], bytes);
+    bulk_load(smem + s * STAGE_BYTES, src, bytes, &bars[s]);
+  };
+  long long issued = 0, done = 0;
+  for (long long j = 0; j < STAGES - 1 && j < n; ++j, ++issued) issue(j);
+  for (long long i = 0; i < n && ok; ++i) {
+    const int s = static_cast<int>(i % STAGES);
+    if (!mbar_wait(&bars[s], static_cast<uint32_t>((i / STAGES) & 1))) {
+      atomicCAS(p.status, 0, ERR_WAIT_PEER);
+      ok = false;
+      break;
+    }
+    done = i + 1;
+    const uint8_t* src;
+    uint8_t* dst;
+    uint32_t bytes;
+    int mt;
+    piece(i, src, dst, bytes, mt);
+    bulk_store(dst, smem + s * STAGE_BYTES, bytes);
+    tma_store_commit();
+    if ((i + 1) % pieces_per_tile == 0) {   // this CTA's share of tile mt is on its way: publish it once it has landed
+      tma_store_wait<0>();
+      asm volatile("fence.proxy.async;" ::: "memory");
+      red_release_gpu_add(p.ag_flags + mt, 1);
+    }
+    const long long j = i + STAGES - 1;
+    if (j < n) {
+      tma_store_wait_read<1>();             // the store that last read stage j % STAGES (piece i - 1) is done with it
+      issue(j);
+      ++issued;
+    }
+  }
+  tma_store_wait<0>();
+  // after a timeout: give the loads still in flight one more bounded wait each before the CTA may exit
+  for (long long i = done; i < issued; ++i)
+    (void)mbar_wait(&bars[i % STAGES], static_cast<uint32_t>((i / STAGES) & 1), 200000000ull);
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -113,6 +210,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   // second range, so partial sums of one tile rarely meet in the reduction atomics
   const int splits = p.splits > 1 ? p.splits : 1;
   const int num_units = num_tiles * splits;
+  // fused all-gather: the last `copiers` pairs copy; the tile order is rotated so that this rank's rows come first
+  const int copiers = p.ag_world > 1 ? p.ag_copiers : 0;
+  const int gpairs = npairs - copiers;
+  const int mt_rot = p.ag_world > 1 ? p.ag_rank * (tm / p.ag_world) : 0;
 
   if (threadIdx.x == 0) {
     prefetch_tmap(&tmap_a);
@@ -137,13 +238,26 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (pair < copiers) {  // lowest block indices: dispatched first
+    if (threadIdx.x == 0)
+      ag_copy_rows(p, smem, empty, pair * 2 + static_cast<int>(cta), 2 * copiers, tm);
+  } else if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int u = pair; u < num_units && ok; u += npairs) {
+      for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
         int mt, nt;
         tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
+        mt = (mt + mt_rot) % tm;
+        if (copiers > 0 && mt / (tm / p.ag_world) != p.ag_rank) {
+          // rows of another rank: every copying CTA has to have delivered its share of this tile
+          if (!wait_counter(p.ag_flags + mt, 2 * copiers)) {
+            atomicCAS(p.status, 0, ERR_WAIT_PEER);
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         const int sp = u / num_tiles;
         const int kb0 = sp * kblocks / splits, kb1 = (sp + 1) * kblocks / splits;
         const int m0 = mt * 2 * BM + static_cast<int>(cta) * BM;
@@ -180,7 +294,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int u = pair; u < num_units && ok; u += npairs, ++tcount) {
+      for (int u = pair - copiers; u < num_units && ok; u += gpairs, ++tcount) {
         const int sp = u / num_tiles;
         const int kb0 = sp * kblocks / splits, kb1 = (sp + 1) * kblocks / splits;
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
@@ -220,9 +334,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const float alpha = p.alpha * (p.alpha_dev ? __ldg(p.alpha_dev) : 1.f);
     uint32_t tcount = 0;
     bool ok = true;
-    for (int u = pair; u < num_units && ok; u += npairs, ++tcount) {
+    for (int u = pair - copiers; u < num_units && ok; u += gpairs, ++tcount) {
       int mt, nt;
       tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
+      mt = (mt + mt_rot) % tm;
       const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
       if (!mbar_wait(&acc_full[acc], acc_ph)) {
         atomicCAS(p.status, 0, ERR_WAIT_ACC_FULL);
@@ -287,8 +402,10 @@ int launch2(const void* A, const void* B, const GemmParams& p, long long lda, lo
     attr_set = true;
   }
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) * (p.splits > 1 ? p.splits : 1);
-  const int max_pairs = mbh::sm_count() / 2;
-  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  const int cop = p.ag_world > 1 ? p.ag_copiers : 0;  // pairs that copy instead of computing (fused all-gather)
+  const int max_pairs = mbh::sm_count() / 2 - cop;    // every CTA of the grid is resident: waiting on one another is safe
+  if (max_pairs < 1) return -3;
+  const int pairs = (tiles < max_pairs ? tiles : max_pairs) + cop;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.blockDim = dim3(THREADS, 1, 1);
@@ -394,4 +511,50 @@ extern "C" int mb_gemm_bf16_rs(const void* A, const void* B, void* const* peer_o
   if (!a_mn && b_mn) return launch2<false, true>(A, B, p, lda, ldb, stream);
   if (a_mn && !b_mn) return launch2<true, false>(A, B, p, lda, ldb, stream);
   return launch2<true, true>(A, B, p, lda, ldb, stream);
+}
+
+// All-gather fused into the GEMM (column-parallel linears of tensor parallelism with sequence-sharded
+// activations): C = A @ op(B)^T where A is [M, K] row-major and rows [r * M / world, (r + 1) * M / world) belong to
+// rank r.  `a_full` is this rank's [M, K] buffer whose own block is already in place; peer_src[r] points at rank
+// r's block ([M / world, K], contiguous) in peer-mapped memory.  `copiers` CTA pairs pull the remote blocks over
+// NVLink with bulk copies while the other pairs compute, starting with the local rows; a remote 256-row tile is
+// consumed as soon as its counter in `flags` ([M / 256] ints, zeroed here) shows that every share has landed.
+// The caller makes sure (cross-rank barrier) that the peers' blocks are complete before the launch and are
+// not overwritten before all ranks have finished.
+extern "C" int mb_gemm_bf16_ag(void* a_full, void* const* peer_src, int world, int my_rank, const void* B, void* C,
+                               int M, int N, int K, long long ldb, long long ldc, int b_mn, int copiers, int* flags,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (world < 2 || world > 8 || M % (world * 2 * BM) || (K & 7)) return -3;
+  if (copiers != 1 && copiers != 2 && copiers != 4 && copiers != 8) return -3;
+  if ((ldb & 7) || (reinterpret_cast<uintptr_t>(a_full) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  GemmParams p;
+  p.C = C;
+  p.aux = nullptr;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.ldaux = 0;
+  p.epi = EPI_BF16;
+  p.alpha = 1.f;
+  p.alpha_dev = nullptr;
+  p.beta = 0.f;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  p.splits = 1;
+  p.route_rows = 0;
+  p.ag_world = world;
+  p.ag_rank = my_rank;
+  p.ag_copiers = copiers;
+  for (int r = 0; r < 8; ++r) {
+    p.ag_src[r] = r < world ? peer_src[r] : nullptr;
+    if (r < world && r != my_rank && (!peer_src[r] || (reinterpret_cast<uintptr_t>(peer_src[r]) & 15))) return -3;
+  }
+  p.ag_dst = a_full;
+  p.ag_ld = K;
+  p.ag_flags = flags;
+  if (cudaMemsetAsync(flags, 0, sizeof(int) * (M / (2 * BM)), stream) != cudaSuccess) return -5;
+  if (b_mn) return launch2<false, true>(a_full, B, p, K, ldb, stream);
+  return launch2<false, false>(a_full, B, p, K, ldb, stream);
 }

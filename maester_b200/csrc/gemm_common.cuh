@@ -31,6 +31,18 @@ struct GemmParams {
   int route_rows;
   int route_slot;
   int group_m;             // CTA-pair kernel: row-tiles per rasterisation group (chosen by the launcher)
+  // All-gather fused into the GEMM (CTA-pair kernel, A row-major [M, K] whose M / ag_world-row blocks live on
+  // different ranks): the last ag_copiers CTA pairs of the grid do no math; they pull the other ranks' blocks
+  // from ag_src[r] into the local A with bulk copies staged through shared memory and count every finished
+  // share of a 256-row tile in ag_flags[tile].  The computing pairs start with the local block and wait for
+  // a remote tile's counter before its first load.  ag_world == 0 turns this off.
+  int ag_world = 0;
+  int ag_rank = 0;
+  int ag_copiers = 0;
+  const void* ag_src[8] = {};
+  void* ag_dst = nullptr;
+  long long ag_ld = 0;     // row pitch of A in elements (== K: blocks are contiguous)
+  int* ag_flags = nullptr; // [M / 256] counters, zeroed by the launcher before the kernel
 };
 
 // group GROUP_M row-tiles together so that concurrently running CTAs share operand tiles in L2

@@ -248,6 +248,50 @@ def peer_gather_rows(dst: torch.Tensor, symm_src, src_rank: torch.Tensor, src_ro
         "peer_gather_rows")
 
 
+def ep_plan(allc: torch.Tensor, me: int, n_local: int, idx: torch.Tensor, inv: torch.Tensor, align: int, cap: int):
+    """Destination (rank, row) of every routing slot from the all-gathered per-expert counts ``allc`` [ep, E];
+    also the padded group offsets [n_local + 1] of this rank's experts.  All on the device."""
+    ep, E = allc.shape
+    n = idx.numel()
+    assert allc.dtype == torch.int32 and idx.dtype == torch.int32 and inv.dtype == torch.int32 and allc.is_contiguous()
+    out = torch.empty(2 * n + n_local + 1, device=idx.device, dtype=torch.int32)
+    slot_rank, slot_row, offs = torch.split(out, [n, n, n_local + 1])
+    _ck(_lib.lib().mb_ep_plan(allc.data_ptr(), ep, me, E, n_local, idx.data_ptr(), inv.data_ptr(), n, align, cap,
+                              slot_rank.data_ptr(), slot_row.data_ptr(), offs.data_ptr(), _stream()), "ep_plan")
+    return slot_rank, slot_row, offs
+
+
+def peer_dispatch_rows(x: torch.Tensor, symm_dst, slot_rank: torch.Tensor, slot_row: torch.Tensor,
+                       slot_scale: torch.Tensor | None, k: int, cap_rows: int, overflow: torch.Tensor) -> None:
+    """Row t of ``x`` (times its gate value) into the buffers of the ranks that own its k experts."""
+    T, dim = x.shape
+    assert x.is_contiguous() and x.dtype == torch.bfloat16 and slot_rank.numel() == T * k
+    _ck(_lib.lib().mb_peer_dispatch_rows(x.data_ptr(), symm_dst.ptr_array, symm_dst.world, slot_rank.data_ptr(),
+                                         slot_row.data_ptr(), _ptr(slot_scale), T, k, dim, cap_rows, overflow.data_ptr(),
+                                         _stream()), "peer_dispatch_rows")
+
+
+def peer_combine_rows(symm_src, slot_rank: torch.Tensor, slot_row: torch.Tensor, slot_scale: torch.Tensor | None,
+                      T: int, k: int, dim: int, cap_rows: int, overflow: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum over the k slots of token t of the (weighted) rows read from the owning ranks' buffers."""
+    out = torch.empty(T, dim, device=slot_rank.device, dtype=torch.bfloat16)
+    _ck(_lib.lib().mb_peer_combine_rows(out.data_ptr(), symm_src.ptr_array, symm_src.world, slot_rank.data_ptr(),
+                                        slot_row.data_ptr(), _ptr(slot_scale), T, k, dim, cap_rows, overflow.data_ptr(),
+                                        _stream()), "peer_combine_rows")
+    return out
+
+
+def peer_slot_dot(symm_src, slot_rank: torch.Tensor, slot_row: torch.Tensor, g: torch.Tensor, k: int,
+                  cap_rows: int) -> torch.Tensor:
+    """d[t*k+j] = <row of slot (t, j) in its owner's buffer, g[t]> in fp32."""
+    T, dim = g.shape
+    assert g.is_contiguous() and g.dtype == torch.bfloat16
+    out = torch.empty(T * k, device=g.device, dtype=torch.float32)
+    _ck(_lib.lib().mb_peer_slot_dot(out.data_ptr(), symm_src.ptr_array, symm_src.world, slot_rank.data_ptr(),
+                                    slot_row.data_ptr(), g.data_ptr(), T, k, dim, cap_rows, _stream()), "peer_slot_dot")
+    return out
+
+
 def gemm_rs(a: torch.Tensor, b: torch.Tensor, symm_out, my_rank: int, *, a_mn: bool = False, b_mn: bool = False,
             alpha: float = 1.0) -> None:
     """``op(A) @ op(B).T`` with the output rows scattered to their owner ranks' symmetric buffers
@@ -258,6 +302,21 @@ def gemm_rs(a: torch.Tensor, b: torch.Tensor, symm_out, my_rank: int, *, a_mn: b
     _ck(_lib.lib().mb_gemm_bf16_rs(a.data_ptr(), b.data_ptr(), symm_out.ptr_array, symm_out.world, my_rank, M, N, K,
                                    _rows_pitch(a), _rows_pitch(b), N, int(a_mn), int(b_mn), float(alpha), _stream()),
         "gemm_bf16_rs")
+
+
+def gemm_ag(a_full: torch.Tensor, symm_blocks, my_rank: int, b: torch.Tensor, flags: torch.Tensor, *,
+            b_mn: bool = False, copiers: int = 4) -> torch.Tensor:
+    """``a_full @ op(b).T`` where ``a_full`` [M, K] holds only this rank's row block so far: the other ranks' blocks
+    are pulled from their symmetric buffers by ``copiers`` CTA pairs of the same kernel (fused all-gather)."""
+    M, K = a_full.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    assert a_full.is_contiguous() and a_full.dtype == torch.bfloat16 and (b.shape[0] if b_mn else b.shape[1]) == K
+    assert flags.dtype == torch.int32 and flags.numel() >= M // 256
+    out = torch.empty(M, N, device=a_full.device, dtype=torch.bfloat16)
+    _ck(_lib.lib().mb_gemm_bf16_ag(a_full.data_ptr(), symm_blocks.ptr_array, symm_blocks.world, my_rank, b.data_ptr(),
+                                   out.data_ptr(), M, N, K, _rows_pitch(b), N, int(b_mn), copiers, flags.data_ptr(),
+                                   _stream()), "gemm_ag")
+    return out
 
 
 def wait_flag(flag: torch.Tensor, expect: int, timeout_ms: float, observed: torch.Tensor | None = None) -> None:

@@ -8,7 +8,9 @@ the column-parallel ``wq|wk|wv`` / ``w1|w3`` in backward.  ``FusedTP.gemm_rs`` r
 kernel: the tcgen05 GEMM's epilogue stores each finished tile's rows directly into the symmetric
 buffer of the rank that owns them (``mb_gemm_bf16_rs``), so the transfer of tile i overlaps the math
 of tile i+1; the owner then sums the ``tp`` partial slices together with the residual it would add
-anyway (``mb_sum_partials``).  Plain stores, no atomics: deterministic.  All-gathers stay NCCL.
+anyway (``mb_sum_partials``).  Plain stores, no atomics: deterministic.  Every all-gather precedes a GEMM:
+``FusedTP.ag_gemm`` runs that pair as one kernel too (``mb_gemm_bf16_ag``: some CTA pairs of the GEMM grid pull
+the other ranks' row blocks with bulk copies while the rest multiply the local rows first).
 
 ``ag_linear`` / ``linear_rs`` are the two autograd ops built on it; with them a tensor-parallel block
 runs the same code path as an unsharded one (the collectives live inside the first and last linear
@@ -31,6 +33,12 @@ class FusedTP:
         self.buf: SymmBuffer | None = None
         self.pair: list[SymmBuffer] = []
         self.calls = 0
+        # all-gather -> GEMM: "fused" (copying CTA pairs inside the GEMM kernel) or "nccl"
+        self.ag_mode = os.environ.get("MB_TP_AG_MODE", "nccl")
+        self.ag_copiers = int(os.environ.get("MB_TP_AG_COPIERS", "4"))
+        self.ag_pair: list[SymmBuffer] = []
+        self.ag_flags: torch.Tensor | None = None
+        self.ag_calls = 0
 
     def _ensure(self, numel: int, device: torch.device) -> SymmBuffer:
         if self.buf is None or self.buf.tensor.numel() < numel:
@@ -69,6 +77,33 @@ class FusedTP:
         return out
 
 
+    def ag_gemm(self, x2: torch.Tensor, b: torch.Tensor, *, b_mn: bool) -> tuple[torch.Tensor, torch.Tensor]:
+        """``(all_gather(x2), all_gather(x2) @ op(b).T)`` with the gather inside the GEMM kernel
+        (``mb_gemm_bf16_ag``): every rank publishes its row block in a symmetric buffer; a few CTA pairs of the
+        GEMM pull the other blocks over NVLink with bulk copies while the rest multiply the local rows, and a
+        remote row tile is consumed as soon as its counter shows that it has landed.  Two buffers alternate,
+        so one cross-rank barrier per call.  Falls back to NCCL + GEMM for shapes the kernel does not take."""
+        from maester_b200.ops import cuda as C
+        tp = self.tp
+        Ml, K = x2.shape
+        M = Ml * tp.size
+        if self.ag_mode != "fused" or Ml % 256 or K % 8 or not x2.is_contiguous():
+            full = _all_gather_rows(x2, tp)
+            return full, C.gemm(full, b, b_mn=b_mn)
+        if not self.ag_pair:
+            self.ag_pair = [SymmBuffer(Ml * K, torch.bfloat16, x2.device, tp.group) for _ in range(2)]
+            self.ag_flags = torch.zeros(max(M // 256, 1), dtype=torch.int32, device=x2.device)
+        assert self.ag_pair[0].tensor.numel() >= Ml * K and self.ag_flags.numel() >= M // 256, \
+            "activation size must not grow between calls (symmetric allocation is collective)"
+        buf = self.ag_pair[self.ag_calls & 1]
+        self.ag_calls += 1
+        buf.tensor[:Ml * K].view(Ml, K).copy_(x2)
+        full = torch.empty(M, K, device=x2.device, dtype=x2.dtype)
+        full[tp.rank * Ml:(tp.rank + 1) * Ml].copy_(x2)
+        buf.barrier()  # every rank's block is published (and its reads of the other buffer's last use are over)
+        return full, C.gemm_ag(full, buf, tp.rank, b, self.ag_flags, b_mn=b_mn, copiers=self.ag_copiers)
+
+
 def _all_gather_rows(x2: torch.Tensor, tp) -> torch.Tensor:
     out = torch.empty(tp.size * x2.shape[0], x2.shape[1], device=x2.device, dtype=x2.dtype)
     dist.all_gather_into_tensor(out.view(-1), x2.contiguous().view(-1), group=tp.group)
@@ -90,10 +125,10 @@ class _AGLinear(Function):
     def forward(ctx, x, w, fused: FusedTP):
         from maester_b200.ops import cuda as C
         tp = fused.tp
-        x_full = _all_gather_rows(x.reshape(-1, x.shape[-1]), tp)
+        x_full, y = fused.ag_gemm(x.reshape(-1, x.shape[-1]).contiguous(), w, b_mn=False)
         ctx.save_for_backward(x_full, w)
         ctx.fused, ctx.x_shape = fused, x.shape
-        return C.gemm(x_full, w).view(tp.batch, -1, w.shape[0])
+        return y.view(tp.batch, -1, w.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
@@ -124,8 +159,12 @@ class _LinearRS(Function):
     def backward(ctx, dy):
         from maester_b200.ops import cuda as C
         x2, w = ctx.saved_tensors
-        dy_full = _all_gather_rows(dy.reshape(-1, w.shape[0]), ctx.fused.tp)
-        dx = C.gemm(dy_full, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dy2 = dy.reshape(-1, w.shape[0]).contiguous()
+        if ctx.needs_input_grad[0]:
+            dy_full, dx = ctx.fused.ag_gemm(dy2, w, b_mn=True)
+            dx = dx.view(ctx.x_shape)
+        else:
+            dy_full, dx = _all_gather_rows(dy2, ctx.fused.tp), None
         dw = _wgrad(w, dy_full, x2) if ctx.needs_input_grad[1] else None
         return dx, dw, (dy if ctx.has_res else None), None
 

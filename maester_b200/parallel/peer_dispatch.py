@@ -26,7 +26,7 @@ from maester_b200.parallel.symm import SymmBuffer
 
 class _Plan:
     """Device-side routing plan of one MoE call."""
-    __slots__ = ("dest_rank", "dest_row", "offs", "n", "dim")
+    __slots__ = ("dest_rank", "dest_row", "offs", "n", "dim", "slot_rank", "slot_row", "T", "k")
 
 
 class _Scatter(torch.autograd.Function):
@@ -80,6 +80,64 @@ class _Gather(torch.autograd.Function):
         C.peer_scatter_rows(grad_rows.contiguous(), ws, plan.dest_rank, plan.dest_row, disp.cap, disp.overflow)
         disp.barrier()
         # the result is consumed by the experts' backward before any other MoE call touches the workspace
+        return ws.tensor.view(disp.cap, plan.dim).clone(), None, None
+
+
+class _TokenScatter(torch.autograd.Function):
+    """Token rows [T, dim] (times their gate values) -> this rank's expert-major buffer, written by every rank
+    straight from its token rows: no [T*k, dim] tensor in sorted-slot order in between.  The backward is the
+    weighted combine of the buffer gradients plus, for the gate values, a dot product per slot."""
+
+    @staticmethod
+    def forward(ctx, x, gate, disp, plan, buf):
+        from maester_b200.ops import cuda as C
+        ctx.disp, ctx.plan = disp, plan
+        ctx.save_for_backward(x if gate is not None else None, gate)
+        buf.tensor.zero_()
+        disp.barrier()
+        C.peer_dispatch_rows(x, buf, plan.slot_rank, plan.slot_row, gate, plan.k, disp.cap, disp.overflow)
+        disp.barrier()
+        return buf.tensor.view(disp.cap, plan.dim)
+
+    @staticmethod
+    def backward(ctx, grad_buf):
+        from maester_b200.ops import cuda as C
+        disp, plan = ctx.disp, ctx.plan
+        x, gate = ctx.saved_tensors
+        ws = disp.workspace(1, plan.dim)
+        ws.tensor.view(disp.cap, plan.dim).copy_(grad_buf)
+        disp.barrier()
+        dx = C.peer_combine_rows(ws, plan.slot_rank, plan.slot_row, gate, plan.T, plan.k, plan.dim, disp.cap, disp.overflow)
+        dgate = None
+        if gate is not None:
+            dgate = C.peer_slot_dot(ws, plan.slot_rank, plan.slot_row, x, plan.k, disp.cap).view_as(gate)
+        disp.barrier()                       # peers are done reading before the workspace is reused
+        return dx, dgate, None, None, None
+
+
+class _TokenCombine(torch.autograd.Function):
+    """Expert outputs [cap, dim] on every rank -> out[t] = sum of the k rows of token t, read from their owners."""
+
+    @staticmethod
+    def forward(ctx, out_buf, disp, plan):
+        from maester_b200.ops import cuda as C
+        ctx.disp, ctx.plan = disp, plan
+        ws = disp.workspace(0, plan.dim)
+        ws.tensor.view(disp.cap, plan.dim).copy_(out_buf)
+        disp.barrier()
+        out = C.peer_combine_rows(ws, plan.slot_rank, plan.slot_row, None, plan.T, plan.k, plan.dim, disp.cap, disp.overflow)
+        disp.barrier()
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        from maester_b200.ops import cuda as C
+        disp, plan = ctx.disp, ctx.plan
+        ws = disp.workspace(0, plan.dim)
+        ws.tensor.zero_()                    # padding rows must carry finite (zero) gradients
+        disp.barrier()
+        C.peer_dispatch_rows(g.contiguous(), ws, plan.slot_rank, plan.slot_row, None, plan.k, disp.cap, disp.overflow)
+        disp.barrier()
         return ws.tensor.view(disp.cap, plan.dim).clone(), None, None
 
 
@@ -141,6 +199,26 @@ class PeerDispatcher:
         p.offs = offs.clamp_max(self.cap).to(torch.int32)
         p.n, p.dim = sorted_experts.numel(), dim
         return p
+
+    # ------------------------------------------------------------------ token-indexed path (native routing plan)
+    def fused(self, moe, x: torch.Tensor, route, gate: torch.Tensor) -> torch.Tensor:
+        """Dispatch, experts and combine for a block whose gate values multiply the expert INPUTS.  ``route`` is
+        the native routing plan of this rank's tokens (``ops.cuda.RoutePlan``), ``gate`` its [T, k] gate values.
+        One tiny all-gather of the per-expert counts, one plan kernel, then rows move between the ranks' buffers
+        directly from / to token order."""
+        from maester_b200.ops import cuda as C
+        ep = self.ep
+        n_local = moe.experts.num_local_experts
+        dim = x.shape[1]
+        self._ensure(route.T * route.k, n_local, dim, x.device)
+        allc = torch.empty(ep.size, route.E, dtype=torch.int32, device=x.device)
+        dist.all_gather_into_tensor(allc.view(-1), route.counts, group=ep.group)
+        p = _Plan()
+        p.slot_rank, p.slot_row, p.offs = C.ep_plan(allc, ep.rank, n_local, route.idx.view(-1), route.inv, GROUP_ALIGN,
+                                                    self.cap)
+        p.T, p.k, p.dim = route.T, route.k, dim
+        buf = _TokenScatter.apply(x, gate, self, p, self.input_buffer(moe, dim))
+        return _TokenCombine.apply(moe.experts(buf, p.offs), self, p)
 
     # ------------------------------------------------------------------ dispatcher contract
     def __call__(self, moe, x, sorted_scores, token_idx, counts, sorted_experts):

@@ -44,8 +44,12 @@ def _worker(rank, world, port, full, batches, peer, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_peer_dispatch_matches_all_to_all(tmp_path):
+@pytest.mark.parametrize("native_routing", ["1", "0"])
+def test_peer_dispatch_matches_all_to_all(tmp_path, native_routing, monkeypatch):
+    """native_routing=1: routing plan kernels + token-indexed peer dispatch / combine; 0: ATen routing chain and
+    the sorted-slot scatter / gather kernels."""
     import torch.multiprocessing as mp
+    monkeypatch.setenv("MB_MOE_FUSED_ROUTE", native_routing)  # read at import time by the spawned ranks
     from test_expert_parallel_cpu import _cfg
     from test_parallel_cpu import _batches, _free_port, _full_weights
     full = _full_weights(_cfg(train_batch_size=4))
