@@ -22,6 +22,7 @@ def _ds(vocab, dim, inter, moe_inter, layers, heads, moe, dense=1, q_lora=0, msc
 deepseek_configs = {
     "debug": _ds(129280, 512, 2048, 512, 8, 16, _moe(8, 3), flex=False, max_batch_size=32),
     "debug_flex": _ds(2000, 256, 1024, 256, 3, 16, _moe(8, 3)),
+    "debug_flex_gate_after": _ds(2000, 256, 1024, 256, 3, 16, _moe(8, 3, score_before_experts=False)),
     "16B": _ds(102400, 2048, 10944, 1408, 27, 16, _moe(64, 6)),
     "45B_custom": _ds(102400, 3072, 8192, 1408, 20, 128, _moe(160, 6, scale=16.0), q_lora=1536),
     "236B": _ds(102400, 5120, 12288, 1536, 60, 128, _moe(160, 6, scale=16.0), q_lora=1536),

@@ -379,7 +379,7 @@ class MoE(nn.Module):
         if self.aux_loss_coeff > 0 and self.training:
             frac = plan.counts_f / float(plan.T * k)
             self.aux_loss = self.aux_loss_coeff * r.num_experts * (frac * scores.mean(dim=0)).sum()
-        if self.dispatcher is not None and self.score_before_experts and hasattr(self.dispatcher, "fused"):
+        if self.dispatcher is not None and hasattr(self.dispatcher, "fused"):
             out = self.dispatcher.fused(self, x, plan, top)  # rows move between ranks straight from token order
         elif self.dispatcher is not None:
             L = plan.as_long()

@@ -155,14 +155,37 @@ def bench_grouped(iters: int, small: bool) -> None:
     C.check_status()
 
 
+def bench_moe(iters: int, small: bool) -> None:
+    """Routing plan and row kernels of the MoE block (DeepSeek-style: 64 experts, top-6, dim 2048)."""
+    _, bw_peak = _peaks()
+    T, E, k, D = (4096, 64, 6, 2048) if small else (16384, 64, 6, 2048)
+    logits = torch.randn(T, E, device="cuda")
+    warm = 0 if small else 3
+    t = timeit(lambda: C.moe_route(logits, None, k, True, False, 1.0, False, 128), iters, warm)
+    print(f"moe route T{T} E{E} top{k} (score + top-k + stable sort + offsets, 3 kernels + allocations): {t * 1e3:.1f} us")
+    p = C.moe_route(logits, None, k, True, False, 1.0, False, 128)
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: C.moe_rows_gather(x, p.row_slot, p.top, k), iters, warm)
+    nb = (T * D + p.rows_cap * D) * 2
+    print(f"moe rows gather -> [{p.rows_cap}, {D}]: {t * 1e3:.1f} us {nb / t / 1e6:.0f} GB/s ({nb / t / 1e6 / bw_peak:.2f} of measured)")
+    buf = torch.randn(p.rows_cap, D, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: C.moe_rows_combine(buf, p.slot_row, p.top, k), iters, warm)
+    nb = (T * k * D + T * D) * 2
+    print(f"moe rows combine -> [{T}, {D}]: {t * 1e3:.1f} us {nb / t / 1e6:.0f} GB/s ({nb / t / 1e6 / bw_peak:.2f} of measured)")
+    t = timeit(lambda: C.moe_slot_dot(buf, p.slot_row, x, k), iters, warm)
+    print(f"moe slot dot: {t * 1e3:.1f} us {nb / t / 1e6:.0f} GB/s ({nb / t / 1e6 / bw_peak:.2f} of measured)")
+    C.check_status()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "grouped", "all"])
+    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "grouped", "moe", "all"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true", help="one cold launch per kernel on a small case")
     a = ap.parse_args()
     iters = 1 if a.small else a.iters
-    table = {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "grouped": bench_grouped}
+    table = {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "grouped": bench_grouped,
+             "moe": bench_moe}
     for name, fn in table.items():
         if a.op in (name, "all"):
             fn(iters, a.small)

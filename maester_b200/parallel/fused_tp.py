@@ -34,8 +34,8 @@ class FusedTP:
         self.pair: list[SymmBuffer] = []
         self.calls = 0
         # all-gather -> GEMM: "fused" (copying CTA pairs inside the GEMM kernel) or "nccl"
-        self.ag_mode = os.environ.get("MB_TP_AG_MODE", "nccl")
-        self.ag_copiers = int(os.environ.get("MB_TP_AG_COPIERS", "4"))
+        self.ag_mode = os.environ.get("MB_TP_AG_MODE", "fused")
+        self.ag_copiers = int(os.environ.get("MB_TP_AG_COPIERS", "0"))  # CTA pairs that copy; 0: chosen per shape
         self.ag_pair: list[SymmBuffer] = []
         self.ag_flags: torch.Tensor | None = None
         self.ag_calls = 0
@@ -101,7 +101,17 @@ class FusedTP:
         full = torch.empty(M, K, device=x2.device, dtype=x2.dtype)
         full[tp.rank * Ml:(tp.rank + 1) * Ml].copy_(x2)
         buf.barrier()  # every rank's block is published (and its reads of the other buffer's last use are over)
-        return full, C.gemm_ag(full, buf, tp.rank, b, self.ag_flags, b_mn=b_mn, copiers=self.ag_copiers)
+        copiers = self.ag_copiers
+        if copiers <= 0:
+            # A copying CTA pair sustains about 64 GB/s over NVLink (its shared-memory ring bounds the bytes in
+            # flight); the blocks have to arrive at the rate at which the computing pairs consume rows, which
+            # for a fixed contraction depends on the output width only: pairs >= 27,000 / N (measured on B200:
+            # N = 3072 is fastest with 8 pairs, N = 14336 with 2).
+            N = b.shape[1] if b_mn else b.shape[0]
+            copiers = 1
+            while copiers < 8 and copiers * N < 27000:
+                copiers *= 2
+        return full, C.gemm_ag(full, buf, tp.rank, b, self.ag_flags, b_mn=b_mn, copiers=copiers)
 
 
 def _all_gather_rows(x2: torch.Tensor, tp) -> torch.Tensor:

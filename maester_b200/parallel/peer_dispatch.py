@@ -116,16 +116,18 @@ class _TokenScatter(torch.autograd.Function):
 
 
 class _TokenCombine(torch.autograd.Function):
-    """Expert outputs [cap, dim] on every rank -> out[t] = sum of the k rows of token t, read from their owners."""
+    """Expert outputs [cap, dim] on every rank -> out[t] = sum of the k rows of token t (times their gate values
+    when the block applies them after the experts), read from the rows' owners.  With gate values the outputs
+    stay in a per-block symmetric buffer until the backward pass, which needs them for the gate gradients."""
 
     @staticmethod
-    def forward(ctx, out_buf, disp, plan):
+    def forward(ctx, out_buf, gate, disp, plan, ws):
         from maester_b200.ops import cuda as C
-        ctx.disp, ctx.plan = disp, plan
-        ws = disp.workspace(0, plan.dim)
+        ctx.disp, ctx.plan, ctx.ws = disp, plan, ws
+        ctx.save_for_backward(gate)
         ws.tensor.view(disp.cap, plan.dim).copy_(out_buf)
         disp.barrier()
-        out = C.peer_combine_rows(ws, plan.slot_rank, plan.slot_row, None, plan.T, plan.k, plan.dim, disp.cap, disp.overflow)
+        out = C.peer_combine_rows(ws, plan.slot_rank, plan.slot_row, gate, plan.T, plan.k, plan.dim, disp.cap, disp.overflow)
         disp.barrier()
         return out
 
@@ -133,12 +135,17 @@ class _TokenCombine(torch.autograd.Function):
     def backward(ctx, g):
         from maester_b200.ops import cuda as C
         disp, plan = ctx.disp, ctx.plan
+        (gate,) = ctx.saved_tensors
+        g = g.contiguous()
+        dgate = None
+        if gate is not None:  # the owners' output buffers of this block are untouched since its forward pass
+            dgate = C.peer_slot_dot(ctx.ws, plan.slot_rank, plan.slot_row, g, plan.k, disp.cap).view_as(gate)
         ws = disp.workspace(0, plan.dim)
         ws.tensor.zero_()                    # padding rows must carry finite (zero) gradients
         disp.barrier()
-        C.peer_dispatch_rows(g.contiguous(), ws, plan.slot_rank, plan.slot_row, None, plan.k, disp.cap, disp.overflow)
+        C.peer_dispatch_rows(g, ws, plan.slot_rank, plan.slot_row, gate, plan.k, disp.cap, disp.overflow)
         disp.barrier()
-        return ws.tensor.view(disp.cap, plan.dim).clone(), None, None
+        return ws.tensor.view(disp.cap, plan.dim).clone(), dgate, None, None, None
 
 
 class PeerDispatcher:
@@ -148,6 +155,7 @@ class PeerDispatcher:
         self.cap = 0
         self._ws: dict[int, SymmBuffer] = {}
         self._inputs: dict[int, SymmBuffer] = {}   # per MoE block: its input buffer is saved for backward
+        self._outputs: dict[int, SymmBuffer] = {}  # per MoE block with gates after the experts: outputs kept likewise
         self.overflow: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ buffers
@@ -170,6 +178,12 @@ class PeerDispatcher:
         if key not in self._inputs:
             self._inputs[key] = SymmBuffer(self.cap * dim, torch.bfloat16, self.overflow.device, self.ep.group)
         return self._inputs[key]
+
+    def output_buffer(self, moe, dim: int) -> SymmBuffer:
+        key = id(moe)
+        if key not in self._outputs:
+            self._outputs[key] = SymmBuffer(self.cap * dim, torch.bfloat16, self.overflow.device, self.ep.group)
+        return self._outputs[key]
 
     def barrier(self) -> None:
         self.workspace(0, 0).barrier()
@@ -202,7 +216,7 @@ class PeerDispatcher:
 
     # ------------------------------------------------------------------ token-indexed path (native routing plan)
     def fused(self, moe, x: torch.Tensor, route, gate: torch.Tensor) -> torch.Tensor:
-        """Dispatch, experts and combine for a block whose gate values multiply the expert INPUTS.  ``route`` is
+        """Dispatch, experts and combine with the gate values applied where the block wants them.  ``route`` is
         the native routing plan of this rank's tokens (``ops.cuda.RoutePlan``), ``gate`` its [T, k] gate values.
         One tiny all-gather of the per-expert counts, one plan kernel, then rows move between the ranks' buffers
         directly from / to token order."""
@@ -217,8 +231,10 @@ class PeerDispatcher:
         p.slot_rank, p.slot_row, p.offs = C.ep_plan(allc, ep.rank, n_local, route.idx.view(-1), route.inv, GROUP_ALIGN,
                                                     self.cap)
         p.T, p.k, p.dim = route.T, route.k, dim
-        buf = _TokenScatter.apply(x, gate, self, p, self.input_buffer(moe, dim))
-        return _TokenCombine.apply(moe.experts(buf, p.offs), self, p)
+        before = moe.score_before_experts
+        buf = _TokenScatter.apply(x, gate if before else None, self, p, self.input_buffer(moe, dim))
+        out_ws = self.workspace(0, dim) if before else self.output_buffer(moe, dim)
+        return _TokenCombine.apply(moe.experts(buf, p.offs), None if before else gate, self, p, out_ws)
 
     # ------------------------------------------------------------------ dispatcher contract
     def __call__(self, moe, x, sorted_scores, token_idx, counts, sorted_experts):

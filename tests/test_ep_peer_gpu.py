@@ -10,12 +10,12 @@ pytestmark = pytest.mark.gpu
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
-def _rank(rank, world, full, batches, peer):
+def _rank(rank, world, full, batches, peer, flavor):
     import torch.distributed as dist
     from test_expert_parallel_cpu import _cfg, _gather_params, _load
     from maester_b200.trainer import Trainer
     tr = Trainer(_cfg(data_parallel_shard_degree=world, expert_parallel_degree=world, ep_peer_dispatch=peer,
-                      fused_collectives=False))
+                      fused_collectives=False, flavor=flavor))
     _load(tr, full)
     losses = []
     for b in batches:
@@ -31,32 +31,33 @@ def _rank(rank, world, full, batches, peer):
     return losses, {k: (v[0].float().cpu(), v[1], v[2]) for k, v in _gather_params(tr).items()}, dropped
 
 
-def _worker(rank, world, port, full, batches, peer, out_dir):
+def _worker(rank, world, port, full, batches, peer, out_dir, flavor):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        torch.save(_rank(rank, world, full, batches, peer), os.path.join(out_dir, f"r{rank}_{int(peer)}.pt"))
+        torch.save(_rank(rank, world, full, batches, peer, flavor), os.path.join(out_dir, f"r{rank}_{int(peer)}.pt"))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("native_routing", ["1", "0"])
-def test_peer_dispatch_matches_all_to_all(tmp_path, native_routing, monkeypatch):
-    """native_routing=1: routing plan kernels + token-indexed peer dispatch / combine; 0: ATen routing chain and
-    the sorted-slot scatter / gather kernels."""
+@pytest.mark.parametrize("native_routing,flavor", [("1", "debug_flex"), ("0", "debug_flex"),
+                                                   ("1", "debug_flex_gate_after")])
+def test_peer_dispatch_matches_all_to_all(tmp_path, native_routing, flavor, monkeypatch):
+    """native_routing=1: routing plan kernels + token-indexed peer dispatch / combine (gate values applied before
+    or after the experts); 0: ATen routing chain and the sorted-slot scatter / gather kernels."""
     import torch.multiprocessing as mp
     monkeypatch.setenv("MB_MOE_FUSED_ROUTE", native_routing)  # read at import time by the spawned ranks
     from test_expert_parallel_cpu import _cfg
     from test_parallel_cpu import _batches, _free_port, _full_weights
-    full = _full_weights(_cfg(train_batch_size=4))
+    full = _full_weights(_cfg(train_batch_size=4, flavor=flavor))
     batches = _batches(3, 4, 32, 2000)
     res = {}
     for peer in (False, True):
-        mp.spawn(_worker, args=(2, _free_port(), full, batches, peer, str(tmp_path)), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, _free_port(), full, batches, peer, str(tmp_path), flavor), nprocs=2, join=True)
         res[peer] = [torch.load(os.path.join(tmp_path, f"r{r}_{int(peer)}.pt"), weights_only=False) for r in range(2)]
     for r in range(2):
         a, b = res[False][r], res[True][r]
