@@ -399,6 +399,14 @@ extern "C" int mb_gemm_bf16_grouped_contr(const void* A, const void* B, void* C,
   p.splits = 1;
   p.route_rows = 0;
   if (!p.status) return -4;
+  // Short contractions (rows of one expert) make the accumulating epilogue's load-add-store the long pole of a
+  // tile; reduction atomics need no round trip.  Every element receives exactly one addition per call, so the
+  // result is the same as with load-add-store.  MB_GROUPED_RED=0 keeps the plain accumulate.
+  static const bool use_red = [] {
+    const char* e = getenv("MB_GROUPED_RED");
+    return !(e && e[0] == '0');
+  }();
+  if (use_red && epi == EPI_F32_ACC && (ldc & 3) == 0) p.epi = EPI_F32_RED;
   GroupParams g = {GROUP_CONTR, num_groups, offs, 0, static_cast<long long>(M) * ldc};
   return dispatch(A, B, p, g, rows_cap, rows_cap, lda, ldb, 1, 1, stream);
 }

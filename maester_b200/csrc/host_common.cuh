@@ -13,6 +13,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline EncodeTiledFn encode_fn() {
+  // The encode call is a driver-API call: it needs a context current on the calling thread.  A thread whose first
+  // CUDA work is one of our launchers (an autograd worker whose first backward node is a GEMM) has none yet;
+  // a runtime call binds the device's primary context to it.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;

@@ -14,6 +14,7 @@ kernel is future work).
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 import torch.nn as nn
@@ -24,6 +25,26 @@ from maester_b200.models.layers import Linear, maybe_checkpoint
 from maester_b200.models.moe import FeedForward, MoE
 from maester_b200.models.norms import RMSNorm
 from maester_b200.ops import reference as ref
+
+
+# RoPE + q|k|v packing + head-size padding of latent attention as one native kernel (csrc/mla_pack.cu)
+FUSED_MLA_PACK = os.environ.get("MB_MLA_PACK", "1") != "0"
+
+
+class _MLAPack(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, kvb, kpe, pos, inv_freq, dims):
+        from maester_b200.ops import cuda as C
+        ctx.save_for_backward(pos, inv_freq)
+        ctx.dims = dims
+        return C.mla_pack_fwd(q.contiguous(), kvb.contiguous(), kpe, pos, inv_freq, *dims)
+
+    @staticmethod
+    def backward(ctx, dout):
+        from maester_b200.ops import cuda as C
+        pos, inv_freq = ctx.saved_tensors
+        dq, dkvb, dkpe = C.mla_pack_bwd(dout.contiguous(), pos, inv_freq, *ctx.dims)
+        return dq, dkvb, dkpe, None, None, None
 
 
 def yarn_inv_freq(args: DeepSeekModelArgs, device=None) -> torch.Tensor:
@@ -72,6 +93,20 @@ class Attention(nn.Module):
         B, S, _ = x.shape
         H = self.n_heads
         q = self.wq(x) if self.q_lora_rank == 0 else self.wq_b(self.q_norm(self.wq_a(x)))
+        P = self.pad_dim
+        if (FUSED_MLA_PACK and ops.use_native(x) and position_ids is not None
+                and not (self.qk_nope_head_dim | self.qk_rope_head_dim | self.v_head_dim) & 7):
+            # RoPE, the shared k_pe broadcast, q|k|v packing and head-size padding in one kernel
+            kv_a = self.wkv_a(x)
+            kv_lat, k_pe = kv_a.split([self.kv_lora_rank, self.qk_rope_head_dim], dim=-1)
+            kvb = self.wkv_b(self.kv_norm(kv_lat))
+            dims = (H, self.qk_nope_head_dim, self.qk_rope_head_dim, self.v_head_dim, P)
+            qkv = _MLAPack.apply(q.reshape(B * S, -1), kvb.reshape(B * S, -1), k_pe.reshape(B * S, -1),
+                                 position_ids.reshape(-1).to(torch.int64), inv_freq.float().contiguous(), dims)
+            out = ops.attention_block(qkv.view(B, S, 3 * H * P), None, None, None, None, None, document_ids, H, H, P,
+                                      scale=self.softmax_scale, causal=True, window=None)
+            out = out.view(B, S, H, P)[..., : self.v_head_dim].reshape(B, S, H * self.v_head_dim)
+            return self.wo(out, residual=residual)
         q = q.view(B, S, H, self.qk_head_dim)
         q_nope, q_pe = q.split([self.qk_nope_head_dim, self.qk_rope_head_dim], dim=-1)
         q_pe = ref.apply_rope(q_pe, position_ids, inv_freq, "interleaved")
@@ -172,6 +207,8 @@ class DeepSeekModel(nn.Module):
         h = ops.embedding(tokens, self.tok_embeddings.weight)
         if position_ids is None:
             position_ids = torch.arange(S, device=tokens.device, dtype=torch.int32)[None].expand(B, S)
+        if tokens.is_cuda:  # the packing kernel wants one int64 position per token: convert once, not per layer
+            position_ids = position_ids.to(torch.int64).contiguous()
         for layer in self.layers.values():
             h = layer(h, position_ids, self.inv_freq, document_ids)
         h = self.norm(h)

@@ -248,6 +248,32 @@ def peer_gather_rows(dst: torch.Tensor, symm_src, src_rank: torch.Tensor, src_ro
         "peer_gather_rows")
 
 
+def mla_pack_fwd(q: torch.Tensor, kvb: torch.Tensor, kpe: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor,
+                 H: int, nope: int, rope: int, vdim: int, P: int) -> torch.Tensor:
+    """q [T, H*(nope+rope)], kvb [T, H*(nope+vdim)], kpe [T, rope] (row-strided view) -> packed [T, 3*H*P] with RoPE on
+    the rope channels (interleaved pairs) and zero padding up to the head size P of the attention kernel."""
+    T = q.shape[0]
+    assert q.is_contiguous() and kvb.is_contiguous() and kpe.stride(1) == 1 and pos.dtype == torch.int64
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rope
+    out = torch.empty(T, 3 * H * P, device=q.device, dtype=q.dtype)
+    _ck(_lib.lib().mb_mla_pack_fwd(q.data_ptr(), kvb.data_ptr(), kpe.data_ptr(), kpe.stride(0), pos.data_ptr(),
+                                   inv_freq.data_ptr(), T, H, nope, rope, vdim, P, out.data_ptr(), _stream()),
+        "mla_pack_fwd")
+    return out
+
+
+def mla_pack_bwd(dout: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor, H: int, nope: int, rope: int, vdim: int,
+                 P: int):
+    T = dout.shape[0]
+    assert dout.is_contiguous() and dout.shape[1] == 3 * H * P
+    dq = torch.empty(T, H * (nope + rope), device=dout.device, dtype=dout.dtype)
+    dkvb = torch.empty(T, H * (nope + vdim), device=dout.device, dtype=dout.dtype)
+    dkpe = torch.empty(T, rope, device=dout.device, dtype=dout.dtype)
+    _ck(_lib.lib().mb_mla_pack_bwd(dout.data_ptr(), pos.data_ptr(), inv_freq.data_ptr(), T, H, nope, rope, vdim, P,
+                                   dq.data_ptr(), dkvb.data_ptr(), dkpe.data_ptr(), _stream()), "mla_pack_bwd")
+    return dq, dkvb, dkpe
+
+
 def ep_plan(allc: torch.Tensor, me: int, n_local: int, idx: torch.Tensor, inv: torch.Tensor, align: int, cap: int):
     """Destination (rank, row) of every routing slot from the all-gathered per-expert counts ``allc`` [ep, E];
     also the padded group offsets [n_local + 1] of this rank's experts.  All on the device."""
