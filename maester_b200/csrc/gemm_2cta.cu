@@ -118,6 +118,18 @@ __device__ __forceinline__ bool wait_counter(const int* p, int target) {
   return true;
 }
 
+// k-block range of a work unit: slice `sp` of a split contraction, or (grouped weight gradients) the rows of group
+// `sp`, whose offsets are multiples of 128 rows
+__device__ __forceinline__ void unit_krange(const GemmParams& p, int sp, int kblocks, int splits, int& kb0, int& kb1) {
+  if (p.grp_offs) {
+    kb0 = p.grp_offs[sp] / BK;
+    kb1 = p.grp_offs[sp + 1] / BK;
+  } else {
+    kb0 = sp * kblocks / splits;
+    kb1 = (sp + 1) * kblocks / splits;
+  }
+}
+
 // One thread of a copying CTA: its share of every remote 256-row tile of A, in the order in which the computing
 // pairs reach the tiles (next rank's block first).  Shares are contiguous byte ranges; they move through the
 // ring of pipeline stages in pieces of at most one stage, loads running STAGES-1 pieces ahead of the stores.
@@ -209,7 +221,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   // work unit u = (tile u % num_tiles, k-range u / num_tiles): all tiles' first ranges run before any
   // second range, so partial sums of one tile rarely meet in the reduction atomics
   const int splits = p.splits > 1 ? p.splits : 1;
-  const int num_units = num_tiles * splits;
+  // grouped weight gradients: unit u = (tile u % num_tiles, group u / num_tiles), contraction over the group's rows
+  const int num_units = num_tiles * (p.grp_offs ? p.grp_count : splits);
   // fused all-gather: the last `copiers` pairs copy; the tile order is rotated so that this rank's rows come first
   const int copiers = p.ag_world > 1 ? p.ag_copiers : 0;
   const int gpairs = npairs - copiers;
@@ -258,8 +271,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           }
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-        const int sp = u / num_tiles;
-        const int kb0 = sp * kblocks / splits, kb1 = (sp + 1) * kblocks / splits;
+        int kb0, kb1;
+        unit_krange(p, u / num_tiles, kblocks, splits, kb0, kb1);
         const int m0 = mt * 2 * BM + static_cast<int>(cta) * BM;
         const int n0 = nt * BN + static_cast<int>(cta) * BNH;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -294,10 +307,12 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (int u = pair - copiers; u < num_units && ok; u += gpairs, ++tcount) {
-        const int sp = u / num_tiles;
-        const int kb0 = sp * kblocks / splits, kb1 = (sp + 1) * kblocks / splits;
+      for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
+        int kb0, kb1;
+        unit_krange(p, u / num_tiles, kblocks, splits, kb0, kb1);
+        if (kb0 == kb1) continue;  // a group without rows: no accumulator is produced (the epilogue skips it too)
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+        ++tcount;
         if (!mbar_wait(&acc_empty[acc], acc_ph ^ 1)) {
           atomicCAS(p.status, 0, ERR_WAIT_ACC_EMPTY);
           ok = false;
@@ -334,11 +349,19 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const float alpha = p.alpha * (p.alpha_dev ? __ldg(p.alpha_dev) : 1.f);
     uint32_t tcount = 0;
     bool ok = true;
-    for (int u = pair - copiers; u < num_units && ok; u += gpairs, ++tcount) {
+    long long c_off = 0;  // per-unit output base for grouped weight gradients
+    for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
       int mt, nt;
       tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
       mt = (mt + mt_rot) % tm;
+      if (p.grp_offs) {
+        int kb0, kb1;
+        unit_krange(p, u / num_tiles, kblocks, splits, kb0, kb1);
+        if (kb0 == kb1) continue;
+        c_off = static_cast<long long>(u / num_tiles) * p.grp_c_elems;
+      }
       const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
+      ++tcount;
       if (!mbar_wait(&acc_full[acc], acc_ph)) {
         atomicCAS(p.status, 0, ERR_WAIT_ACC_FULL);
         ok = false;
@@ -353,7 +376,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         uint32_t r[32];
         tmem_ld_32x32(taddr + c * 32, r);
         tmem_ld_wait();
-        store_acc_chunk(p, r, alpha, row, n0 + c * 32);
+        store_acc_chunk(p, r, alpha, row, n0 + c * 32, c_off);
       }
       tc_fence_before();
       mbar_arrive_leader(&acc_empty[acc]);
@@ -401,7 +424,8 @@ int launch2(const void* A, const void* B, const GemmParams& p, long long lda, lo
     cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     attr_set = true;
   }
-  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) * (p.splits > 1 ? p.splits : 1);
+  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) *
+                    (p.grp_offs ? p.grp_count : (p.splits > 1 ? p.splits : 1));
   const int cop = p.ag_world > 1 ? p.ag_copiers : 0;  // pairs that copy instead of computing (fused all-gather)
   const int max_pairs = mbh::sm_count() / 2 - cop;    // every CTA of the grid is resident: waiting on one another is safe
   if (max_pairs < 1) return -3;
@@ -557,4 +581,36 @@ extern "C" int mb_gemm_bf16_ag(void* a_full, void* const* peer_src, int world, i
   if (cudaMemsetAsync(flags, 0, sizeof(int) * (M / (2 * BM)), stream) != cudaSuccess) return -5;
   if (b_mn) return launch2<false, true>(a_full, B, p, K, ldb, stream);
   return launch2<false, false>(a_full, B, p, K, ldb, stream);
+}
+
+// Grouped GEMM over the contraction range on CTA pairs (weight gradients of stacked expert weights):
+//   C_g[M, N] (+)= A_g^T B_g with A: [rows_cap, M] and B: [rows_cap, N] row-major, rows grouped by offs (device,
+//   multiples of 128); C stacked [num_groups, M, N] with row pitch ldc.  epi: EPI_F32 / EPI_F32_ACC (fp32 output);
+//   the accumulating form uses reduction atomics, one addition per element per call.  Groups without rows are skipped.
+extern "C" int mb_gemm_bf16_2cta_grouped_contr(const void* A, const void* B, void* C, const int* offs, int num_groups,
+                                               int rows_cap, int M, int N, long long lda, long long ldb, long long ldc,
+                                               int epi, float alpha, cudaStream_t stream) {
+  if (rows_cap <= 0 || N <= 0 || M <= 0 || num_groups <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (rows_cap % 128) || (epi != EPI_F32 && epi != EPI_F32_ACC)) return -3;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  GemmParams p;
+  p.C = C;
+  p.aux = nullptr;
+  p.M = M;
+  p.N = N;
+  p.K = rows_cap;
+  p.ldc = ldc;
+  p.ldaux = 0;
+  p.epi = (epi == EPI_F32_ACC && (ldc & 3) == 0) ? EPI_F32_RED : epi;
+  p.alpha = alpha;
+  p.alpha_dev = nullptr;
+  p.beta = 1.f;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  p.splits = 1;
+  p.route_rows = 0;
+  p.grp_offs = offs;
+  p.grp_count = num_groups;
+  p.grp_c_elems = static_cast<long long>(M) * ldc;
+  return launch2<true, true>(A, B, p, lda, ldb, stream);
 }

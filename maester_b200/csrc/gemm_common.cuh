@@ -43,6 +43,11 @@ struct GemmParams {
   void* ag_dst = nullptr;
   long long ag_ld = 0;     // row pitch of A in elements (== K: blocks are contiguous)
   int* ag_flags = nullptr; // [M / 256] counters, zeroed by the launcher before the kernel
+  // Grouped weight gradients on the CTA-pair kernel: C_g[M, N] (+)= A_g^T B_g where group g owns the rows
+  // [grp_offs[g], grp_offs[g + 1]) of the contraction (multiples of 128); C_g starts grp_c_elems after C_{g-1}.
+  const int* grp_offs = nullptr;
+  int grp_count = 0;
+  long long grp_c_elems = 0;
 };
 
 // group GROUP_M row-tiles together so that concurrently running CTAs share operand tiles in L2
@@ -57,8 +62,9 @@ __device__ __forceinline__ void tile_coords(int t, int tm, int tn, int group_m, 
 }
 
 // Store 32 consecutive accumulator columns [col0, col0+32) of output row `row`.
+// `c_off` (elements) shifts the base of fp32 outputs (grouped weight gradients on the CTA-pair kernel).
 __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint32_t (&r)[32], float alpha, int row,
-                                                int col0) {
+                                                int col0, long long c_off = 0) {
   using namespace mb;
   if (row >= p.M || col0 >= p.N) return;
   const bool full_chunk = (col0 + 32 <= p.N);
@@ -105,7 +111,7 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint3
       for (int i = 0; i < 32 && col0 + i < p.N; ++i) crow[i] = __float2bfloat16(v[i]);
     }
   } else {
-    float* crow = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    float* crow = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
     if (p.epi == EPI_F32_RED) {
       if (full_chunk && (p.ldc & 3) == 0) {
 #pragma unroll

@@ -118,6 +118,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_gemm_bf16_2cta": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _I, _I, _F, _F, _P, _P],
         "mb_gemm_bf16_grouped_rows": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _I, _F, _P],
         "mb_gemm_bf16_grouped_contr": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _F, _P],
+        "mb_gemm_bf16_2cta_grouped_contr": [_P, _P, _P, _P, _I, _I, _I, _I, _L, _L, _L, _I, _F, _P],
         "mb_fused_rs_adamw_ag": [_P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _P],
         "mb_push_shards": [_P, _P, _P, _I, _P, _I, _P],
         "mb_peer_scatter_rows": [_P, _P, _I, _P, _P, _I, _I, _L, _P, _P],

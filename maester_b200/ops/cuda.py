@@ -28,6 +28,8 @@ _STATUS_NAMES = {
 
 launch_count = 0  # number of native kernel launches issued through this module
 GEMM_TWO_CTA = os.environ.get("MB_GEMM_2CTA", "1") != "0"
+# grouped weight gradients (contraction over an expert's rows) on the CTA-pair kernel
+GROUPED_CONTR_TWO_CTA = os.environ.get("MB_GROUPED_CONTR_2CTA", "1") != "0"
 
 
 def _stream() -> int:
@@ -426,9 +428,10 @@ def gemm_grouped_contr(a: torch.Tensor, b: torch.Tensor, offs: torch.Tensor, out
     N = b.shape[1]
     E = out.shape[0]
     assert out.shape == (E, M, N) and out.is_contiguous() and offs.dtype == torch.int32
-    _ck(_lib.lib().mb_gemm_bf16_grouped_contr(a.data_ptr(), b.data_ptr(), out.data_ptr(), offs.data_ptr(), E,
-                                              rows_cap, M, N, _rows_pitch(a), _rows_pitch(b), N, epi, float(alpha),
-                                              _stream()), "gemm_grouped_contr")
+    pair = GROUPED_CONTR_TWO_CTA and epi in (EPI_F32, EPI_F32_ACC) and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0
+    fn = _lib.lib().mb_gemm_bf16_2cta_grouped_contr if pair else _lib.lib().mb_gemm_bf16_grouped_contr
+    _ck(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), offs.data_ptr(), E, rows_cap, M, N, _rows_pitch(a), _rows_pitch(b),
+           N, epi, float(alpha), _stream()), "gemm_grouped_contr")
     return out
 
 
