@@ -46,6 +46,8 @@ class FusedAdamW(Optimizer):
         defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self._flat = None  # set by attach_flat()
+        self._eager = None  # set by eager_begin() for the duration of one step
+        self._unit_tables: dict = {}
 
     def attach_flat(self, master: torch.Tensor, grad: torch.Tensor, lowp: torch.Tensor | None, segments_by_param,
                     m: torch.Tensor | None = None, v: torch.Tensor | None = None):
@@ -68,17 +70,61 @@ class FusedAdamW(Optimizer):
 
     def _table(self):
         f = self._flat
-        key = tuple((g["lr"], g["weight_decay"]) for g in self.param_groups)
+        base_lr = self.param_groups[0]["lr"] or 1.0
+        # the chunk table holds lr RATIOS, so a schedule that scales every group alike never rebuilds it; the
+        # base learning rate lives in a one-element device tensor refreshed when it changes
+        key = tuple((round(g["lr"] / base_lr, 9), g["weight_decay"]) for g in self.param_groups)
         if f["table"] is None or f["table"][0] != key:
-            base_lr = self.param_groups[0]["lr"] or 1.0
             segs = []
             for g in self.param_groups:
                 for p in g["params"]:
                     off, n = f["seg"][p]
-                    segs.append((off, n, g["lr"] / base_lr if base_lr else 1.0, g["weight_decay"]))
+                    segs.append((off, n, g["lr"] / base_lr, g["weight_decay"]))
             dev = f["master"].device
             f["table"] = (key, build_chunk_table(segs, dev), torch.tensor([base_lr], device=dev, dtype=torch.float32))
+            f["table_lr"] = base_lr
+        if f.get("table_lr") != base_lr:
+            f["table"][2].fill_(base_lr)
+            f["table_lr"] = base_lr
         return f["table"][1], f["table"][2]
+
+    # ---- per-unit updates under the backward pass (peer-memory sharding runtime) -------------------------------
+    def eager_begin(self) -> bool:
+        """Announce the coming step before the backward pass that produces its gradients: fixes the step number,
+        learning rate and per-tensor table, and registers ``_eager_unit`` with the sharding runtime, which calls it
+        for every unit as soon as the unit's gradients are complete on all ranks."""
+        f = self._flat
+        sharded = f.get("sharded") if f is not None else None
+        if sharded is None or not sharded.fused or not f["master"].is_cuda:
+            return False
+        st = self.state[self.param_groups[0]["params"][0]]
+        (_, tensors, _), lr_t = self._table()
+        self._eager = dict(step=int(st["step"].item()) + 1, tensors=tensors, lr_t=lr_t, done=set())
+        if self._eager_unit not in sharded.eager_hooks:
+            sharded.eager_hooks.append(self._eager_unit)
+        return True
+
+    @torch.no_grad()
+    def _eager_unit(self, u) -> None:
+        e, f = self._eager, self._flat
+        if e is None or id(u) in e["done"]:
+            return
+        from maester_b200.ops import cuda as C
+        sharded = f["sharded"]
+        tab = self._unit_tables.get(id(u))
+        if tab is None:  # chunk records of this optimizer's parameters inside the unit (geometry only: cached)
+            order = [p for g in self.param_groups for p in g["params"]]
+            tensor_of = {id(p): i for i, p in enumerate(order)}
+            mine = [sl.master for sl in u.slots if id(sl.master) in tensor_of]
+            tab = sharded.fused_chunk_table(mine, tensor_of) if mine else (None, 0)
+            self._unit_tables[id(u)] = tab
+        fchunks, fn = tab
+        if fn:
+            g0 = self.param_groups[0]
+            b1, b2 = g0["betas"]
+            C.fused_rs_adamw_ag(sharded.symm_grad, sharded.symm_full, f["master"], f["m"], f["v"], f["grad"], fchunks,
+                                e["tensors"], fn, e["lr_t"], b1, b2, g0["eps"], e["step"], sharded.divide)
+        e["done"].add(id(u))
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -93,7 +139,14 @@ class FusedAdamW(Optimizer):
             (chunks, tensors, nch), lr_t = self._table()
             b1, b2 = g0["betas"]
             sharded = f.get("sharded")
-            if sharded is not None and sharded.fused:
+            if sharded is not None and sharded.fused and self._eager is not None:
+                # the units were updated one by one under the backward pass; run the ones whose hook did not fire
+                st_step = self._eager["step"]
+                for u in sharded.units:
+                    if id(u) not in self._eager["done"]:
+                        self._eager_unit(u)
+                self._eager = None
+            elif sharded is not None and sharded.fused:
                 # reduce-scatter + update + all-gather in one kernel over the peers' buffers
                 if f.get("fused_table") is None or f["fused_table"][0] is not chunks:
                     order = [p for g in self.param_groups for p in g["params"]]

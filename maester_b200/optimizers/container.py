@@ -13,6 +13,7 @@ state-dict keys are the model's fully-qualified parameter names either way.
 from __future__ import annotations
 
 import importlib
+import os
 from typing import Any
 
 import torch
@@ -21,6 +22,9 @@ from torch.optim import Optimizer
 
 from maester_b200.log_utils import logger
 from maester_b200.optimizers.adamw import FusedAdamW
+
+# peer-memory sharding runtime: update each unit under the backward pass ("0": one kernel for all units in step())
+EAGER_UNIT_UPDATES = os.environ.get("MB_FSDP_EAGER", "1") != "0"
 
 
 def _named_trainable(model: torch.nn.Module) -> list[tuple[str, torch.nn.Parameter]]:
@@ -47,6 +51,22 @@ class OptimizersContainer(Optimizer, Stateful):
         self._hook_stats: dict[str, Any] = {}
 
     # -- stepping
+    def announce_step(self) -> bool:
+        """Call before the backward pass whose gradients the next ``step()`` consumes (the last micro-batch), when
+        nothing has to look at the complete gradient first (no clipping by the global norm).  With the peer-memory
+        sharding runtime every unit is then reduced, updated and re-gathered by its own kernel launch as soon as
+        its gradients are complete, under the backward pass of the earlier blocks, instead of all at once in
+        ``step()``.  Returns whether that mode is on for this step."""
+        sharded = getattr(self.model, "_sharded", None)
+        if sharded is None or not sharded.fused or not EAGER_UNIT_UPDATES:
+            return False
+        if not all(isinstance(o, FusedAdamW) and o._flat is not None for o in self.optimizers):
+            return False
+        if not all(o.eager_begin() for o in self.optimizers):
+            return False
+        sharded.eager_active = True
+        return True
+
     def step(self, closure=None):  # hooks registered on the container wrap this method
         loss = None
         sharded = getattr(self.model, "_sharded", None)
@@ -59,6 +79,10 @@ class OptimizersContainer(Optimizer, Stateful):
             out = opt.step(closure) if closure is not None else opt.step()
             loss = out if out is not None else loss
         if sharded is not None:
+            if sharded.eager_active:
+                sharded.eager_active = False
+                for u in sharded.units:
+                    u.eager_done = False
             sharded.lowp_fresh = sharded.device.type == "cuda" and all(
                 isinstance(o, FusedAdamW) and o._flat is not None for o in self.optimizers)
             sharded.gather_params()

@@ -85,6 +85,7 @@ class Unit:
     gather_event: torch.cuda.Event | None = None
     gathered: bool = True
     grads_pending: bool = False
+    eager_done: bool = False     # fused mode: this step's update of the unit already ran under the backward pass
 
 
 def _ordered_params(module: nn.Module, prefix: str, seen: set, skip_modules: set):
@@ -175,6 +176,8 @@ class ShardedModel:
         # ---- buffers
         self.fused = False
         self.symm_full = self.symm_grad = None
+        self.eager_hooks: list = []   # fused mode: callables(unit) that run the optimizer kernel for one unit
+        self.eager_active = False     # set for the backward pass whose gradients the next optimizer step consumes
         if fused_comm and not self.has_experts and self.world > 1 and self.rep_world == 1 and param_dtype == torch.bfloat16 and all(
                 sl.padded_numel % 4 == 0 for u in self.units for sl in u.slots):
             from maester_b200.parallel.symm import SymmBuffer, symmetric_memory_available
@@ -342,7 +345,12 @@ class ShardedModel:
             if tp_sync and getattr(sl.param, "tp_replicated", False):
                 dist.all_reduce(sl.param.main_grad, group=self.tp_group)
         if self.world * self.rep_world == 1 or self.fused:
-            return  # fused mode: the optimizer kernel reduces straight from the peers' gradient buffers
+            # fused mode: the optimizer kernel reduces straight from the peers' gradient buffers, for this unit
+            # right away (on the side stream, under the backward pass of the earlier blocks) when the optimizers
+            # have announced the step, else for all units at the optimizer step
+            if self.fused and self.eager_active and self.eager_hooks:
+                self._eager_update(u)
+            return
         stream = self.comm_stream
         if stream is not None:
             stream.wait_stream(torch.cuda.current_stream())
@@ -470,6 +478,18 @@ class ShardedModel:
         for i, r in enumerate(recs):
             arr[i] = r
         return torch.from_numpy(arr.view(np.uint8).copy()).to(self.device), len(recs)
+
+    def _eager_update(self, u: Unit) -> None:
+        """Reduce-scatter + optimizer update + all-gather of one unit as soon as its gradients are complete.
+        The cross-rank barrier in front says that every rank has finished this unit's backward pass: its gradient
+        buffers are final and nobody reads its parameters any more, so the kernel may overwrite them everywhere."""
+        stream = self.comm_stream
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self.symm_grad.barrier()
+            for hook in self.eager_hooks:
+                hook(u)
+        u.eager_done = True
 
     def pre_optimizer_step(self) -> None:
         """Fused mode: all ranks' gradient buffers must be complete before any rank reduces them."""

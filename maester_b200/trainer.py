@@ -136,10 +136,13 @@ class Trainer:
         skip_sync = self.grad_accum > 1 and not self.cfg.gradient_accumulation_sync_each_step
         losses = []
         batches = list(batches)
+        clip = bool(self.cfg.max_grad_norm and self.cfg.max_grad_norm > 0 and getattr(self.cfg, "clip_gradients", False))
         for i, batch in enumerate(batches):
             self.global_micro_step += 1
             torch.manual_seed(self.global_micro_step + self.dp_rank)
             sync = (i == len(batches) - 1) if skip_sync else True
+            if i == len(batches) - 1 and not clip and hasattr(self.optimizers, "announce_step"):
+                self.optimizers.announce_step()  # units may be updated as soon as their gradients are complete
             losses.append(self.forward_backward(batch, sync))
         if self.cfg.max_grad_norm and self.cfg.max_grad_norm > 0 and getattr(self.cfg, "clip_gradients", False):
             params = [p for g in self.optimizers.param_groups for p in g["params"]]

@@ -56,7 +56,11 @@ def _worker(rank, world, port, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fused_optimizer_collective_matches_nccl_path():
+@pytest.mark.parametrize("per_unit", ["1", "0"])
+def test_fused_optimizer_collective_matches_nccl_path(per_unit, monkeypatch):
+    """per_unit=1: every unit is reduced, updated and re-gathered under the backward pass as soon as its gradients
+    are complete; 0: one kernel over all units at the optimizer step."""
+    monkeypatch.setenv("MB_FSDP_EAGER", per_unit)  # read at import time by the spawned ranks
     world = 2
     with tempfile.TemporaryDirectory() as d:
         mp.spawn(_worker, args=(world, _free_port(), d), nprocs=world, join=True)
