@@ -18,6 +18,11 @@ gradient-sync toggle for accumulation) with a layout chosen for 180 GB GPUs:
   step, consumed by forward pre-hooks) and ONE reduce-scatter per unit, launched from backward hooks
   so it overlaps the backward of the preceding unit.
 
+* with peer-mapped (symmetric) buffers the reduce-scatter, the AdamW update and the all-gather of a unit are one
+  kernel (``csrc/comm.cu``) that reads the peers' gradient buffers and writes the peers' parameter buffers through
+  NVSwitch; it is launched per unit from the same backward hooks once the optimizers have announced the step
+  (``_eager_update``), so it runs under the backward pass of the earlier blocks.
+
 With one rank the shard and full buffers coincide and no communication code runs.
 """
 from __future__ import annotations

@@ -36,6 +36,71 @@ def nvtx_range(name: str):
         yield
 
 
+class KernelTimers:
+    """NVTX ranges and CUDA-event timers around every native launcher of ``maester_b200.ops.cuda``.
+
+    ``with KernelTimers() as kt: trainer.train_step(batch)`` wraps the module's launcher functions for the duration
+    of the block: each call is bracketed by an NVTX range named after the launcher and by two CUDA events on the
+    launching stream.  ``kt.report()`` synchronises once and returns ``{launcher: (calls, device milliseconds)}``
+    sorted by time; ``kt.report(group=...)`` additionally takes the maximum over the ranks of a process group, the way
+    multi-GPU numbers are quoted.  The wrappers add two event records per call, so use it for attribution, not for
+    headline numbers.  ``module`` and ``names`` exist for tests (any module with callables works, also without CUDA).
+    """
+
+    def __init__(self, module=None, names: list[str] | None = None):
+        if module is None:
+            from maester_b200.ops import cuda as module
+        self.module = module
+        self.names = names or [n for n, f in vars(module).items()
+                               if callable(f) and not n.startswith("_") and getattr(f, "__module__", None) == module.__name__
+                               and not isinstance(f, type) and n not in ("check_status",)]
+        self._saved: dict = {}
+        self._events: dict[str, list] = {}
+        self.calls: dict[str, int] = {}
+        self._cuda = torch.cuda.is_available()
+
+    def _wrap(self, name: str, fn):
+        def timed(*a, **kw):
+            self.calls[name] = self.calls.get(name, 0) + 1
+            if not self._cuda:
+                return fn(*a, **kw)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.nvtx.range_push(f"mb::{name}")
+            e0.record()
+            try:
+                return fn(*a, **kw)
+            finally:
+                e1.record()
+                torch.cuda.nvtx.range_pop()
+                self._events.setdefault(name, []).append((e0, e1))
+        timed.__wrapped__ = fn
+        return timed
+
+    def __enter__(self):
+        for n in self.names:
+            self._saved[n] = getattr(self.module, n)
+            setattr(self.module, n, self._wrap(n, self._saved[n]))
+        return self
+
+    def __exit__(self, *exc):
+        for n, f in self._saved.items():
+            setattr(self.module, n, f)
+        self._saved.clear()
+        return False
+
+    def report(self, group=None) -> dict[str, tuple[int, float]]:
+        if self._cuda:
+            torch.cuda.synchronize()
+        names = sorted(self.calls)
+        ms = [sum(a.elapsed_time(b) for a, b in self._events.get(n, [])) for n in names]
+        if group is not None and dist.is_initialized() and names:
+            t = torch.tensor(ms, dtype=torch.float64, device="cuda" if self._cuda else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+            ms = t.tolist()
+        out = {n: (self.calls[n], float(m)) for n, m in zip(names, ms)}
+        return dict(sorted(out.items(), key=lambda kv: -kv[1][1]))
+
+
 @contextlib.contextmanager
 def maybe_enable_profiling(cfg, *, global_step: int = 0):
     if not cfg.enable_profiling:
