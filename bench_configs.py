@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 
 import torch
@@ -35,6 +36,8 @@ PRESETS = {
                              expert_parallel="world"),
     "deepseek-moe-1gpu": dict(model_name="deepseek", flavor="bench6L", seq_len=4096, train_batch_size=4),
 }
+# smallest world size whose GPUs hold the configuration (sharded fp32 state + activations within 180 GB each)
+MIN_GPUS = {"llama3-8b-cp2": 4, "deepseek-moe-ep8": 8}
 
 
 def main() -> None:
@@ -51,6 +54,12 @@ def main() -> None:
     a.warmup = max(a.warmup, 3)
     if not torch.cuda.is_available():
         print(json.dumps({"preset": a.preset, "unavailable": "no CUDA device"}))
+        return
+    need = MIN_GPUS.get(a.preset, 1)
+    if int(os.environ.get("WORLD_SIZE", a.gpus)) < need:  # refuse before anything is allocated
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"preset": a.preset, "unavailable": f"needs at least {need} GPUs: the fp32 state of the "
+                              "whole model does not fit the memory of fewer"}))
         return
     world, rank, local_rank = B.dist_setup(a.gpus)
     from maester_b200.config import Config
