@@ -119,6 +119,82 @@ __global__ void __launch_bounds__(256, NV > 0 && NV <= 8 ? 4 : (NV == 12 ? 3 : 2
   }
 }
 
+// Streaming form of the forward kernel: a fixed grid of warps walks the rows, and the loads of a warp's next row are
+// issued before the arithmetic and the stores of its current row, so every warp always has a row of loads in flight.
+template <int NV>
+__global__ void __launch_bounds__(128, 3) rmsnorm_fwd_stream_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                    const __nv_bfloat16* __restrict__ w,
+                                                                    const __nv_bfloat16* __restrict__ res,
+                                                                    __nv_bfloat16* __restrict__ y,
+                                                                    float* __restrict__ rstd_out, int M, int D, float eps,
+                                                                    int unit_offset) {
+  const int lane = threadIdx.x & 31;
+  const int nw = gridDim.x * (blockDim.x >> 5);
+  const int nvec = D >> 3;
+  const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
+  const float off = unit_offset ? 1.f : 0.f;
+  bf16x8 cur[NV], nxt[NV];
+  int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (row >= M) return;
+  {
+    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + static_cast<size_t>(row) * D);
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (lane + 32 * i < nvec) cur[i] = xr[lane + 32 * i];
+  }
+  for (; row < M; row += nw) {
+    const int next = row + nw;
+    if (next < M) {
+      const bf16x8* xn = reinterpret_cast<const bf16x8*>(x + static_cast<size_t>(next) * D);
+#pragma unroll
+      for (int i = 0; i < NV; ++i)
+        if (lane + 32 * i < nvec) nxt[i] = xn[lane + 32 * i];
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      if (lane + 32 * i < nvec) {
+        float f[8];
+        unpack8(cur[i], f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    const bf16x8* rr = res ? reinterpret_cast<const bf16x8*>(res + static_cast<size_t>(row) * D) : nullptr;
+    bf16x8* yr = reinterpret_cast<bf16x8*>(y + static_cast<size_t>(row) * D);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float f[8], wf[8];
+        unpack8(cur[i], f);
+        if (w) {
+          unpack8(wr[v], wf);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) wf[e] = 1.f - off;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = f[e] * rstd * (wf[e] + off);
+        if (rr) {  // rounded to bf16 before the residual add, as separate ops would do
+          bf16x8 yn = pack8(f);
+          float g[8], r[8];
+          unpack8(yn, g);
+          unpack8(rr[v], r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = g[e] + r[e];
+        }
+        yr[v] = pack8(f);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) cur[i] = nxt[i];
+  }
+}
+
 // ------------------------------------------------------------------ RMSNorm backward: dx
 // dx = rstd * (w' * dy - xhat * mean(xhat * w' * dy)),  xhat = x * rstd,  w' = w or 1+w.
 // If dres_add is non-null, dx is accumulated onto it (dx_out = dres_add + dx): used to merge the
@@ -309,7 +385,7 @@ template <int NV>
 __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_smemacc_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
     const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dres_add, __nv_bfloat16* __restrict__ dx,
-    float* __restrict__ dw, int M, int D, int unit_offset) {
+    float* __restrict__ dw, int M, int D, int unit_offset, int prefetch_next) {
   extern __shared__ float dw_all[];  // [8 warps][D]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nvec = D >> 3;
@@ -334,6 +410,18 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_smemacc_kernel(
       if (v < nvec) {
         cg[i] = dyr[v];
         cx[i] = xr[v];
+      }
+    }
+    if (prefetch_next && row + gridDim.x * 8 < M && (lane & 7) == 0) {
+      // pull this warp's next row towards L2 while the current one is processed (one request per 128-byte line)
+      const size_t nb = static_cast<size_t>(row + gridDim.x * 8) * D;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(dy + nb + v * 8));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(x + nb + v * 8));
+        }
       }
     }
     float dot = 0.f;
@@ -926,6 +1014,20 @@ extern "C" int mb_rmsnorm_fwd(const void* x, const void* w, const void* res, voi
   rmsnorm_fwd_kernel<NV><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,            \
                                                  (const __nv_bfloat16*)res, (__nv_bfloat16*)y, rstd, M, D, eps, \
                                                  unit_offset)
+  static const int variant = getenv("MB_NORM_FWD_VARIANT") ? atoi(getenv("MB_NORM_FWD_VARIANT")) : 0;
+  if (variant == 1 && nv <= 12 && M >= 16 * mbh::sm_count()) {
+    const int grid = 3 * mbh::sm_count();  // three 4-warp blocks per SM (register-limited)
+#define MB_NORM_FWD_S(NV)                                                                                              \
+  rmsnorm_fwd_stream_kernel<NV><<<grid, 128, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w,                \
+                                                      (const __nv_bfloat16*)res, (__nv_bfloat16*)y, rstd, M, D, eps,    \
+                                                      unit_offset)
+    if (nv <= 4) MB_NORM_FWD_S(4);
+    else if (nv <= 8) MB_NORM_FWD_S(8);
+    else if (nv <= 10) MB_NORM_FWD_S(10);
+    else MB_NORM_FWD_S(12);
+#undef MB_NORM_FWD_S
+    return mbh::check_launch("rmsnorm_fwd_stream");
+  }
   // one instantiation for every D <= 4096: narrower register caches (more blocks per SM) measured slower
   if (nv <= NORM_MAXV) MB_NORM_FWD(NORM_MAXV);
   else MB_NORM_FWD(0);
@@ -954,8 +1056,9 @@ extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
     }                                                                                                           \
     rmsnorm_bwd_smemacc_kernel<NV><<<grid2, 256, smem2, st>>>(                                                  \
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,                       \
-        (const __nv_bfloat16*)dres_add, (__nv_bfloat16*)dx, dw, M, D, unit_offset);                             \
+        (const __nv_bfloat16*)dres_add, (__nv_bfloat16*)dx, dw, M, D, unit_offset, prefetch_next);              \
   } while (0)
+      static const int prefetch_next = getenv("MB_NORM_BWD_PREFETCH") ? atoi(getenv("MB_NORM_BWD_PREFETCH")) : 0;
       if (nv <= 4) MB_NORM_BWD2(4);
       else if (nv <= 8) MB_NORM_BWD2(8);
       else MB_NORM_BWD2(12);
