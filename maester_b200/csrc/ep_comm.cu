@@ -113,6 +113,25 @@ ep_plan_kernel(const int* __restrict__ allc, int ep, int me, int E, int n_local,
   }
 }
 
+// Zero the padding rows of this rank's expert-major buffer: rows [offs[l] + rows of expert l, offs[l + 1]) for every
+// local expert l.  The rows in front are overwritten by the dispatch, the rows behind the last group are never read,
+// so clearing the whole buffer (twice the balanced load) is not needed.  grid = (n_local, row slices).
+__global__ void __launch_bounds__(256)
+ep_zero_padding_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ allc, int ep, int me, int E, int n_local,
+                       const int* __restrict__ offs, int dim, long long cap) {
+  const int l = blockIdx.x;
+  int tot = 0;
+  for (int r = 0; r < ep; ++r) tot += allc[r * E + me * n_local + l];
+  long long lo = static_cast<long long>(offs[l]) + tot, hi = offs[l + 1];
+  if (hi > cap) hi = cap;
+  const int nvec = dim >> 3;
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  for (long long r = lo + blockIdx.y; r < hi; r += gridDim.y) {
+    uint4* row = reinterpret_cast<uint4*>(buf + r * dim);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) row[v] = z;
+  }
+}
+
 __device__ __forceinline__ void ep_unpack8(const uint4& u, float* f) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
 #pragma unroll
@@ -292,6 +311,15 @@ extern "C" int mb_ep_plan(const int* allc, int ep, int me, int E, int n_local, c
   ep_plan_kernel<<<want < 1 ? 1 : (want < capb ? want : capb), 256, 0, st>>>(allc, ep, me, E, n_local, idx, inv, n_slots,
                                                                             align, cap, slot_rank, slot_row, offs);
   return mbh::check_launch("ep_plan");
+}
+
+// buf: this rank's [cap, dim] expert-major buffer; allc / offs as for mb_ep_plan.
+extern "C" int mb_ep_zero_padding(void* buf, const int* allc, int ep, int me, int E, int n_local, const int* offs,
+                                  int dim, long long cap, cudaStream_t st) {
+  if ((dim & 7) || n_local < 1 || ep * n_local != E || me < 0 || me >= ep) return -3;
+  ep_zero_padding_kernel<<<dim3(n_local, 32), 256, 0, st>>>(static_cast<__nv_bfloat16*>(buf), allc, ep, me, E, n_local,
+                                                            offs, dim, cap);
+  return mbh::check_launch("ep_zero_padding");
 }
 
 extern "C" int mb_peer_dispatch_rows(const void* x, void* const* peer_ptrs, int world, const int* slot_rank,

@@ -78,9 +78,10 @@ class GroupedExperts(nn.Module):
         self.w2 = nn.Parameter(torch.empty(num_experts, hidden_dim, dim))
         self.w3 = nn.Parameter(torch.empty(num_experts, dim, hidden_dim))
 
-    def forward(self, x: torch.Tensor, offs: torch.Tensor) -> torch.Tensor:
-        """x: expert-major rows [rows_cap, dim] with zero padding rows; offs: padded int32 offsets."""
-        return grouped_swiglu(x, self.w1, self.w3, self.w2, offs)
+    def forward(self, x: torch.Tensor, offs: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """x: expert-major rows [rows_cap, dim] with zero padding rows; offs: padded int32 offsets; out: optional
+        preallocated result buffer (used when it can be written directly)."""
+        return grouped_swiglu(x, self.w1, self.w3, self.w2, offs, out)
 
     def init_weights(self, init_std: float) -> None:
         gen = None

@@ -126,6 +126,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_mla_pack_fwd": [_P, _P, _P, _L, _P, _P, _L, _I, _I, _I, _I, _I, _P, _P],
         "mb_mla_pack_bwd": [_P, _P, _P, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P],
         "mb_ep_plan": [_P, _I, _I, _I, _I, _P, _P, _I, _I, _L, _P, _P, _P, _P],
+        "mb_ep_zero_padding": [_P, _P, _I, _I, _I, _I, _P, _I, _L, _P],
         "mb_peer_dispatch_rows": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _L, _P, _P],
         "mb_peer_combine_rows": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _L, _P, _P],
         "mb_peer_slot_dot": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _L, _P],

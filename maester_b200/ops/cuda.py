@@ -289,6 +289,15 @@ def ep_plan(allc: torch.Tensor, me: int, n_local: int, idx: torch.Tensor, inv: t
     return slot_rank, slot_row, offs
 
 
+def ep_zero_padding(buf: torch.Tensor, allc: torch.Tensor, me: int, n_local: int, offs: torch.Tensor, dim: int,
+                    cap: int) -> None:
+    """Zero only the padding rows of the local experts' groups in this rank's [cap, dim] expert-major buffer."""
+    ep, E = allc.shape
+    assert buf.dtype == torch.bfloat16 and buf.numel() >= cap * dim and offs.dtype == torch.int32
+    _ck(_lib.lib().mb_ep_zero_padding(buf.data_ptr(), allc.data_ptr(), ep, me, E, n_local, offs.data_ptr(), dim, cap,
+                                      _stream()), "ep_zero_padding")
+
+
 def peer_dispatch_rows(x: torch.Tensor, symm_dst, slot_rank: torch.Tensor, slot_row: torch.Tensor,
                        slot_scale: torch.Tensor | None, k: int, cap_rows: int, overflow: torch.Tensor) -> None:
     """Row t of ``x`` (times its gate value) into the buffers of the ranks that own its k experts."""

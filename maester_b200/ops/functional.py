@@ -407,14 +407,16 @@ class _GroupedSwiGLU(Function):
     backward pass instead of being saved."""
 
     @staticmethod
-    def forward(ctx, x, w1, w3, w2, offs):
+    def forward(ctx, x, w1, w3, w2, offs, out_box=None):
+        # out_box: optional one-element list holding a preallocated [rows, dim] output (e.g. a peer-visible buffer)
         C = _C()
         H = w1.shape[2]
         h13 = torch.empty(x.shape[0], 2 * H, device=x.device, dtype=x.dtype)
         C.gemm_grouped_rows(x, w1, offs, b_mn=True, out=h13[:, :H])
         C.gemm_grouped_rows(x, w3, offs, b_mn=True, out=h13[:, H:])
         ctx.save_for_backward(x, w1, w3, w2, offs, h13)
-        return C.gemm_grouped_rows(C.glu_fwd(h13, _ACT["silu"]), w2, offs, b_mn=True)
+        out = out_box[0] if out_box else None
+        return C.gemm_grouped_rows(C.glu_fwd(h13, _ACT["silu"]), w2, offs, b_mn=True, out=out)
 
     @staticmethod
     def backward(ctx, dy):
@@ -436,15 +438,17 @@ class _GroupedSwiGLU(Function):
         if ctx.needs_input_grad[0]:
             dx = C.gemm_grouped_rows(d13[:, :H], w1, offs, b_mn=False)
             dx.add_(C.gemm_grouped_rows(d13[:, H:], w3, offs, b_mn=False))
-        return dx, grads[0], grads[1], grads[2], None
+        return dx, grads[0], grads[1], grads[2], None, None
 
 
-def grouped_swiglu(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, offs: torch.Tensor):
-    """Expert FFN over padded row groups: ``w1, w3: [E, dim, hidden]``, ``w2: [E, hidden, dim]``."""
+def grouped_swiglu(x: torch.Tensor, w1: torch.Tensor, w3: torch.Tensor, w2: torch.Tensor, offs: torch.Tensor,
+                   out: torch.Tensor | None = None):
+    """Expert FFN over padded row groups: ``w1, w3: [E, dim, hidden]``, ``w2: [E, hidden, dim]``.  ``out`` (optional,
+    [rows, dim], contiguous) receives the result on the native path; the returned tensor is the result either way."""
     H = w1.shape[2]
     if (use_native(x, w1) and x.shape[0] % GROUP_ALIGN == 0 and w1.shape[1] % 64 == 0 and H % 64 == 0
             and x.is_contiguous()):
-        return _GroupedSwiGLU.apply(x, w1, w3, w2, offs)
+        return _GroupedSwiGLU.apply(x, w1, w3, w2, offs, [out] if out is not None else None)
     h1 = grouped_linear(x, w1, offs)
     h3 = grouped_linear(x, w3, offs)
     return grouped_linear(glu(torch.cat([h1, h3], dim=-1), "silu"), w2, offs)

@@ -26,7 +26,13 @@ from maester_b200.parallel.symm import SymmBuffer
 
 class _Plan:
     """Device-side routing plan of one MoE call."""
-    __slots__ = ("dest_rank", "dest_row", "offs", "n", "dim", "slot_rank", "slot_row", "T", "k")
+    __slots__ = ("dest_rank", "dest_row", "offs", "n", "dim", "slot_rank", "slot_row", "T", "k", "allc", "n_local")
+
+    def zero_padding(self, disp, buf) -> None:
+        """Clear the padding rows of the local experts' groups in ``buf`` (the rows in front are overwritten by the
+        dispatch, the rows behind the last group are never read), instead of the whole twice-oversized buffer."""
+        from maester_b200.ops import cuda as C
+        C.ep_zero_padding(buf.tensor, self.allc, disp.ep.rank, self.n_local, self.offs, self.dim, disp.cap)
 
 
 class _Scatter(torch.autograd.Function):
@@ -93,7 +99,7 @@ class _TokenScatter(torch.autograd.Function):
         from maester_b200.ops import cuda as C
         ctx.disp, ctx.plan = disp, plan
         ctx.save_for_backward(x if gate is not None else None, gate)
-        buf.tensor.zero_()
+        plan.zero_padding(disp, buf)
         disp.barrier()
         C.peer_dispatch_rows(x, buf, plan.slot_rank, plan.slot_row, gate, plan.k, disp.cap, disp.overflow)
         disp.barrier()
@@ -125,7 +131,8 @@ class _TokenCombine(torch.autograd.Function):
         from maester_b200.ops import cuda as C
         ctx.disp, ctx.plan, ctx.ws = disp, plan, ws
         ctx.save_for_backward(gate)
-        ws.tensor.view(disp.cap, plan.dim).copy_(out_buf)
+        if out_buf.data_ptr() != ws.tensor.data_ptr():  # not already written in place by the last expert GEMM
+            ws.tensor.view(disp.cap, plan.dim).copy_(out_buf)
         disp.barrier()
         out = C.peer_combine_rows(ws, plan.slot_rank, plan.slot_row, gate, plan.T, plan.k, plan.dim, disp.cap, disp.overflow)
         disp.barrier()
@@ -141,7 +148,7 @@ class _TokenCombine(torch.autograd.Function):
         if gate is not None:  # the owners' output buffers of this block are untouched since its forward pass
             dgate = C.peer_slot_dot(ctx.ws, plan.slot_rank, plan.slot_row, g, plan.k, disp.cap).view_as(gate)
         ws = disp.workspace(0, plan.dim)
-        ws.tensor.zero_()                    # padding rows must carry finite (zero) gradients
+        plan.zero_padding(disp, ws)          # padding rows must carry finite (zero) gradients
         disp.barrier()
         C.peer_dispatch_rows(g, ws, plan.slot_rank, plan.slot_row, gate, plan.k, disp.cap, disp.overflow)
         disp.barrier()
@@ -231,10 +238,13 @@ class PeerDispatcher:
         p.slot_rank, p.slot_row, p.offs = C.ep_plan(allc, ep.rank, n_local, route.idx.view(-1), route.inv, GROUP_ALIGN,
                                                     self.cap)
         p.T, p.k, p.dim = route.T, route.k, dim
+        p.allc, p.n_local = allc, n_local
         before = moe.score_before_experts
         buf = _TokenScatter.apply(x, gate if before else None, self, p, self.input_buffer(moe, dim))
         out_ws = self.workspace(0, dim) if before else self.output_buffer(moe, dim)
-        return _TokenCombine.apply(moe.experts(buf, p.offs), None if before else gate, self, p, out_ws)
+        # the last expert GEMM writes straight into the peer-visible buffer the combine reads from
+        y = moe.experts(buf, p.offs, out=out_ws.tensor[:self.cap * dim].view(self.cap, dim))
+        return _TokenCombine.apply(y, None if before else gate, self, p, out_ws)
 
     # ------------------------------------------------------------------ dispatcher contract
     def __call__(self, moe, x, sorted_scores, token_idx, counts, sorted_experts):
