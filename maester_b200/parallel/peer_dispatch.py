@@ -10,6 +10,13 @@ Same contract as ``AllToAllDispatcher`` (expert_parallel.py).  What changes is w
    experts run their grouped GEMMs on the buffer with device-side group offsets, and
    ``peer_gather_rows`` pulls every slot's result back (csrc/ep_comm.cu).
 
+With the native routing plan (``ops.cuda.RoutePlan``) the block takes the token-indexed form of the same
+exchange (``PeerDispatcher.fused``): ``mb_ep_plan`` computes every slot's (rank, row) in one kernel,
+``peer_dispatch_rows`` writes each token's row (times its gate value) straight from token order into the owners'
+buffers, ``peer_combine_rows`` sums a token's k expert rows read from their owners, ``peer_slot_dot`` yields the
+gate gradients, only the padding rows of the expert groups are cleared, and the last expert GEMM writes into the
+peer-visible buffer itself: no ``[T*k, dim]`` tensor in sorted order, no full-buffer memset, no staging copy.
+
 Backward is the mirror image (gradients of the results are scattered, gradients of the inputs are
 gathered).  Cross-rank ordering is by stream-ordered barriers on the symmetric buffers' signal pads.
 Buffers hold ``capacity_factor x`` the balanced load; rows beyond that are dropped and counted in
