@@ -1,4 +1,4 @@
-"""Kernel micro-benchmarks: ``python -m maester_b200.ops.kernel_bench <op> [--iters N] [--small]``.
+"""Kernel micro-benchmarks: ``python -m benchmarks.kernel_bench <op> [--iters N] [--small]``.
 
 ``op``: ``gemm`` (forward / dgrad / wgrad layouts of the Gemma-3 4B projections, 1-CTA and CTA-pair
 kernels next to ``torch.matmul``), ``attention`` (forward and backward for head sizes 256 and 128,
@@ -21,7 +21,7 @@ from maester_b200.ops.functional import kv_block_lower_bounds, q_block_upper_bou
 
 
 def _peaks() -> tuple[float, float]:
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             d = json.load(f)

@@ -1,7 +1,7 @@
 """Micro-benchmark of the tensor-parallel linears: collective fused into the GEMM kernel vs NCCL + GEMM.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29560 \
-        -m maester_b200.parallel.tp_bench [--tokens 16384] [--dim 4096] [--iters 20] [--copiers 1,2,4,8]
+        -m benchmarks.tp_bench [--tokens 16384] [--dim 4096] [--iters 20] [--copiers 1,2,4,8]
 
 Shapes default to Llama-3 8B with TP = world size (sequence-sharded activations ``[tokens / tp, dim]``): the
 column-parallel ``wq|wk|wv`` and ``w1|w3`` (all-gather -> GEMM) and the row-parallel ``wo`` and ``w2``

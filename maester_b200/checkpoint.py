@@ -29,28 +29,47 @@ from maester_b200.config import TORCH_DTYPE_MAP
 from maester_b200.log_utils import logger
 
 
+def _check_device_status() -> None:
+    """A kernel whose bounded wait ran out leaves garbage behind: refuse to write it to disk."""
+    if torch.cuda.is_available():
+        from maester_b200.ops import cuda as C
+        C.check_status(sync=True)
+
+
 class IntervalType(enum.Enum):
     SECONDS = enum.auto()
     STEPS = enum.auto()
 
 
 def _as_dtensor(local: torch.Tensor, slot, sharded) -> torch.Tensor:
-    """Present this rank's dim-0 rows as a DTensor (plain tensor when the model is not distributed).
-    Expert-parallel tensors are sharded twice along dim 0: over ``ep``, then over the ranks that hold
-    the same experts."""
-    from torch.distributed.tensor import DTensor, Shard
+    """Present this rank's piece of a parameter (or of its optimizer state) as a DTensor over the mesh dimensions
+    that split it, so that DCP writes whole tensors and can reshard on load.  A plain tensor is returned only when
+    nothing splits the parameter (one process, or a data-parallel group of one without tensor parallelism).
 
-    if sharded is not None and slot.dom == 1:
-        mesh = getattr(sharded, "expert_mesh", None)
+    Splits, outermost first: experts over ``dp_shard_in_ep`` (expert parallelism) and each rank's experts over
+    ``dp_shard_mod_ep`` (the ranks holding the same experts): a strided shard plus a shard on dim 0; dense parameters
+    over ``dp_shard_cp`` on dim 0; on top of either, the tensor-parallel slice along ``slot.tp_dim`` over ``tp`` (a
+    slice of dim 0 makes the data-parallel shard of dim 0 strided).  Parameters that are replicated over ``tp`` are
+    published over the data-parallel mesh only; DCP keeps one copy of identical pieces."""
+    from torch.distributed.tensor import DTensor, Shard
+    from torch.distributed.tensor.placement_types import _StridedShard
+
+    if sharded is None:
+        return local
+    meshes = getattr(sharded, "ckpt_meshes", None) or {}
+    tp = slot.tp_dim >= 0
+    if slot.dom == 1:
+        mesh = meshes.get("expert_tp" if tp else "expert")
         if mesh is None:
-            return local
-        from torch.distributed.tensor.placement_types import _StridedShard
+            raise NotImplementedError(f"no checkpoint mesh for the expert parameter {slot.fqn}")
         placements = [_StridedShard(0, split_factor=mesh.size(1)), Shard(0)]
-    elif sharded is not None and slot.tp_dim >= 0 and getattr(sharded, "tp_mesh", None) is not None:
-        # tensor-parallel slice (dim 0 or 1) of a parameter that is also sharded along dim 0 over the
-        # data-parallel ranks: the tp split comes first, so on dim 0 the data-parallel shard is strided
-        mesh = sharded.tp_mesh
-        from torch.distributed.tensor.placement_types import _StridedShard
+        if tp:
+            assert slot.tp_dim > 0, "expert tensors are tensor-parallel along their hidden dimension"
+            placements.append(Shard(slot.tp_dim))
+    elif tp:
+        mesh = meshes.get("dense_tp")
+        if mesh is None:
+            raise NotImplementedError(f"no checkpoint mesh for the tensor-parallel parameter {slot.fqn}")
         if mesh.ndim == 1:
             placements = [Shard(slot.tp_dim)]
         elif slot.tp_dim == 0:
@@ -58,8 +77,8 @@ def _as_dtensor(local: torch.Tensor, slot, sharded) -> torch.Tensor:
         else:
             placements = [Shard(0), Shard(slot.tp_dim)]
     else:
-        mesh = getattr(sharded, "device_mesh", None)
-        if sharded is None or sharded.world == 1 or mesh is None:
+        mesh = meshes.get("dense")
+        if mesh is None or sharded.world == 1:
             return local
         placements = [Shard(0)]
     shape = slot.global_shape
@@ -159,11 +178,13 @@ class CheckpointManager:
     def _no_dist(self) -> bool:
         return not dist.is_initialized()
 
+    def will_save(self, curr_step: int, force: bool = False) -> bool:
+        return bool(self.enable_checkpoint and (force or curr_step % self.interval == 0))
+
     def save(self, curr_step: int, force: bool = False) -> None:
-        if not self.enable_checkpoint:
+        if not self.will_save(curr_step, force):
             return
-        if not force and curr_step % self.interval != 0:
-            return
+        _check_device_status()  # raises before anything is written
         states: dict[str, Any] = self.states
         if force and self.model_weights_only:
             sd = self.states["model"].state_dict()

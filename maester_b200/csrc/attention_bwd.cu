@@ -690,11 +690,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, co
   // ---- dQ
   if (make_maps(&tq, &tk, &tv, &tdo, q, k, v, dout, p.B, p.S, p.H, p.KV, HD, qs, ks, vs, 128, BKV)) return -2;
   using LQ = SmemDQ<HD, NST>;
-  static bool attr1 = false;
-  if (!attr1) {
-    cudaFuncSetAttribute(attn_bwd_dq_kernel<HD, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize, LQ::TOTAL);
-    attr1 = true;
-  }
+  MB_SET_MAX_SMEM_ONCE((attn_bwd_dq_kernel<HD, NST>), LQ::TOTAL);
   dim3 g1((p.S + 127) / 128, p.H, p.B);
   attn_bwd_dq_kernel<HD, NST><<<g1, BWD_THREADS, LQ::TOTAL, st>>>(tq, tk, tv, tdo, p);
   int e = mbh::check_launch("attn_bwd_dq");
@@ -702,11 +698,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, co
   // ---- dK/dV
   if (make_maps(&tq, &tk, &tv, &tdo, q, k, v, dout, p.B, p.S, p.H, p.KV, HD, qs, ks, vs, BQ2, 128)) return -2;
   using LK = SmemKV<HD, DV>;
-  static bool attr2 = false;
-  if (!attr2) {
-    cudaFuncSetAttribute(attn_bwd_dkdv_kernel<HD, DV, NSTQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, LK::TOTAL);
-    attr2 = true;
-  }
+  MB_SET_MAX_SMEM_ONCE((attn_bwd_dkdv_kernel<HD, DV, NSTQ>), LK::TOTAL);
   dim3 g2((p.S + 127) / 128, p.KV * (HD / DV), p.B);
   attn_bwd_dkdv_kernel<HD, DV, NSTQ><<<g2, BWD_THREADS, LK::TOTAL, st>>>(tq, tk, tv, tdo, p);
   return mbh::check_launch("attn_bwd_dkdv");
@@ -763,7 +755,7 @@ static __device__ int g_noalloc_status;
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
 struct NoallocDevice {
-  bool ready = false;
+  std::atomic<bool> ready{false};
   float* delta = nullptr;  // device address of g_noalloc_delta on that GPU
   int* status = nullptr;   // device address of g_noalloc_status
 };
@@ -773,7 +765,7 @@ NoallocDevice g_noalloc_dev[NOALLOC_MAX_DEVICES];
 // the runtime; the address a kernel can use has to be asked for.
 int noalloc_setup(int dev) {
   NoallocDevice& d = g_noalloc_dev[dev];
-  if (d.ready) return 0;
+  if (d.ready.load(std::memory_order_acquire)) return 0;
   void* p = nullptr;
   cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_delta);
   if (e != cudaSuccess || !p) {
@@ -789,7 +781,7 @@ int noalloc_setup(int dev) {
     return MB_NOALLOC_SETUP_FAILED;
   }
   d.status = static_cast<int*>(p);
-  d.ready = true;
+  d.ready.store(true, std::memory_order_release);
   return 0;
 }
 
@@ -840,4 +832,14 @@ extern "C" int mb_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
   if (hd == 128) return launch_bwd<128, 2, 128, 2>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
   if (hd == 64) return launch_bwd<64, 2, 64, 2>(q, k, v, dout, p, q_tok_stride, k_tok_stride, v_tok_stride, st);
   return -3;
+}
+
+extern "C" int mb_noalloc_status(void) {
+  int code = 0;
+  if (cudaMemcpyFromSymbol(&code, g_noalloc_status, sizeof(int)) != cudaSuccess) return MB_NOALLOC_SETUP_FAILED;
+  if (code != 0) {
+    const int zero = 0;
+    if (cudaMemcpyToSymbol(g_noalloc_status, &zero, sizeof(int)) != cudaSuccess) return MB_NOALLOC_SETUP_FAILED;
+  }
+  return code;
 }

@@ -388,11 +388,7 @@ int launch_fwd(const void* q, const void* k, const void* v, const AttnParams& p,
   const uint32_t bk[4] = {64, 1, BKV, 1};
   if (mbh::make_tmap_bf16_nd(&tk, k, 4, dk, sk, bk)) return -2;
   if (mbh::make_tmap_bf16_nd(&tv, v, 4, dk, sv, bk)) return -2;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(attn_fwd_kernel<HD, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-    attr_set = true;
-  }
+  MB_SET_MAX_SMEM_ONCE((attn_fwd_kernel<HD, BKV>), L::TOTAL);
   dim3 grid((p.S + BQ - 1) / BQ, p.H, p.B);
   attn_fwd_kernel<HD, BKV><<<grid, ATT_THREADS, L::TOTAL, st>>>(tq, tk, tv, p);
   return mbh::check_launch("attn_fwd");

@@ -1038,11 +1038,7 @@ extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
       const int grid2 = 2 * mbh::sm_count();
 #define MB_NORM_BWD2(NV)                                                                                        \
   do {                                                                                                          \
-    static bool attr = false;                                                                                   \
-    if (!attr) {                                                                                                \
-      cudaFuncSetAttribute(rmsnorm_bwd_smemacc_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); \
-      attr = true;                                                                                              \
-    }                                                                                                           \
+    MB_SET_MAX_SMEM_ONCE(rmsnorm_bwd_smemacc_kernel<NV>, 100 * 1024);                                           \
     rmsnorm_bwd_smemacc_kernel<NV><<<grid2, 256, smem2, st>>>(                                                  \
         (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, rstd,                       \
         (const __nv_bfloat16*)dres_add, (__nv_bfloat16*)dx, dw, M, D, unit_offset);                             \

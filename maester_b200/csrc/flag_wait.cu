@@ -40,7 +40,45 @@ __global__ void wait_flag_probe_kernel(const int* flag, int expect, unsigned lon
   }
 }
 
+// Cross-GPU barrier over a table of per-rank signal pads that every rank can address.  Rank `me` stores the
+// epoch into slot [base + me] of every rank's pad and then waits until slot [base + p] of its own pad has reached
+// the epoch for every p.  Epochs only grow, so the pads never need clearing between barriers.  The release store
+// after a system-scope fence publishes everything earlier kernels of this stream wrote (to local or peer memory);
+// the acquire loads order the peers' writes before the kernels that follow on this stream.  Plain peer loads and
+// stores only; every wait gives up at the deadline and records ERR_WAIT_PEER.
+constexpr int BARRIER_MAX_RANKS = 64;
+struct PadTable {
+  int* pad[BARRIER_MAX_RANKS];
+};
+
+__global__ void symm_barrier_kernel(const PadTable pads, int world, int me, int base, int epoch,
+                                    unsigned long long timeout_ns, int* status) {
+  const int p = threadIdx.x;
+  if (p < world) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(pads.pad[p] + base + me), "r"(epoch) : "memory");
+    if (!wait_flag_bounded(pads.pad[me] + base + p, epoch, timeout_ns)) atomicCAS(status, 0, ERR_WAIT_PEER);
+  }
+}
+
 }  // namespace
+
+// Stream-ordered barrier over `world` ranks (this one is `me`).  pads[r] is rank r's signal pad as mapped into
+// this process; slots [base, base + world) of every pad belong to this barrier channel; `epoch` must be the same
+// on every rank and larger than in the previous call on this channel.  timeout_ms is clamped to 10 minutes.
+extern "C" int mb_symm_barrier(void* const* pads, int world, int me, int base, int epoch, float timeout_ms,
+                               cudaStream_t st) {
+  int* status = mbh::status().dev;
+  if (!status) return -4;
+  if (world < 1 || world > BARRIER_MAX_RANKS || me < 0 || me >= world) return -3;
+  PadTable t;
+  for (int r = 0; r < world; ++r) t.pad[r] = static_cast<int*>(pads[r]);
+  if (timeout_ms < 1.f) timeout_ms = 1.f;
+  if (timeout_ms > 600000.f) timeout_ms = 600000.f;
+  symm_barrier_kernel<<<1, BARRIER_MAX_RANKS, 0, st>>>(t, world, me, base, epoch,
+                                                       static_cast<unsigned long long>(timeout_ms * 1e6), status);
+  return mbh::check_launch("symm_barrier");
+}
 
 // Waits (on the stream) until *flag >= expect or timeout_ms elapses; on expiry the library status becomes
 // ERR_WAIT_PEER.  observed (device int, may be null) receives 1 / 0.  timeout_ms is clamped to 10 s.

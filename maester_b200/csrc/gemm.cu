@@ -290,11 +290,7 @@ int launch(const void* A, const void* B, const GemmParams& p, const GroupParams&
   if (!B_MN) e = mbh::make_tmap_bf16_2d(&tb, B, p.K, b_rows, ldb, 64, BN);
   else e = mbh::make_tmap_bf16_2d(&tb, B, p.N, b_rows, ldb, 64, BK);
   if (e) return e;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    attr_set = true;
-  }
+  MB_SET_MAX_SMEM_ONCE((gemm_bf16_kernel<A_MN, B_MN>), SMEM_BYTES);
   int grid = mbh::sm_count();
   if (g.mode == GROUP_NONE) {
     const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);

@@ -419,11 +419,7 @@ int launch2(const void* A, const void* B, const GemmParams& p, long long lda, lo
   if (e) return e;
   GemmParams pp = p;
   pp.group_m = choose_group_m(p.M, p.N, p.K);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaFuncSetAttribute(gemm_bf16_2cta_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    attr_set = true;
-  }
+  MB_SET_MAX_SMEM_ONCE((gemm_bf16_2cta_kernel<A_MN, B_MN>), SMEM_BYTES);
   const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) *
                     (p.grp_offs ? p.grp_count : (p.splits > 1 ? p.splits : 1));
   const int cop = p.ag_world > 1 ? p.ag_copiers : 0;  // pairs that copy instead of computing (fused all-gather)

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <atomic>
 
 namespace mbh {
 
@@ -12,15 +13,35 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-inline EncodeTiledFn encode_fn() {
-  // The encode call is a driver-API call: it needs a context current on the calling thread.  A thread whose first
-  // CUDA work is one of our launchers (an autograd worker whose first backward node is a GEMM) has none yet;
-  // a runtime call binds the device's primary context to it.
+// The encode call is a driver-API call: it needs a context current on the calling thread.  A thread whose first
+// CUDA work is one of our launchers (an autograd worker whose first backward node is a GEMM) may have none yet.
+// cudaSetDevice on the current device binds the primary context (CUDA 12 initialises it there); only if the
+// driver still reports no current context does the classic cudaFree(nullptr), which releases nothing, run.
+inline void bind_context_to_thread() {
   static thread_local bool bound = false;
-  if (!bound) {
-    cudaFree(nullptr);
-    bound = true;
+  if (bound) return;
+  bound = true;
+  typedef CUresult (*CtxGetCurrentFn)(CUcontext*);
+  static CtxGetCurrentFn get_current = nullptr;
+  if (!get_current) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      get_current = reinterpret_cast<CtxGetCurrentFn>(p);
   }
+  CUcontext ctx = nullptr;
+  if (get_current && get_current(&ctx) == CUDA_SUCCESS && ctx) return;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaSetDevice(dev);
+  ctx = nullptr;
+  if (get_current && get_current(&ctx) == CUDA_SUCCESS && ctx) return;
+  cudaFree(nullptr);
+}
+
+inline EncodeTiledFn encode_fn() {
+  bind_context_to_thread();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;
@@ -100,15 +121,36 @@ inline Status& status() {
   return s;
 }
 
-inline int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  }
-  return n;
+// Per-device caches: a process may drive several GPUs, and function attributes and SM counts belong to the
+// device that is current at the launch.
+constexpr int MAX_DEVICES = 64;
+inline int current_device() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev < 0 || dev >= MAX_DEVICES) ? 0 : dev;
 }
+
+inline int sm_count() {
+  static std::atomic<int> n[MAX_DEVICES];
+  const int dev = current_device();
+  int v = n[dev].load(std::memory_order_relaxed);
+  if (!v) {
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    n[dev].store(v, std::memory_order_relaxed);
+  }
+  return v;
+}
+
+// Raises a kernel's dynamic shared-memory limit once per device (one bit per device in a per-call-site mask).
+#define MB_SET_MAX_SMEM_ONCE(kernel, bytes)                                                                  \
+  do {                                                                                                       \
+    static std::atomic<unsigned long long> mb_done_{0};                                                      \
+    const unsigned long long mb_bit_ = 1ull << mbh::current_device();                                        \
+    if (!(mb_done_.load(std::memory_order_acquire) & mb_bit_)) {                                             \
+      cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);                      \
+      mb_done_.fetch_or(mb_bit_, std::memory_order_release);                                                 \
+    }                                                                                                        \
+  } while (0)
 
 inline int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();

@@ -135,6 +135,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_sum_partials": [_P, _P, _P, _L, _I, _P],
         "mb_pull_sum": [_P, _I, _I, _P, _P, _L, _L, _P],
         "mb_wait_flag_probe": [_P, _I, _F, _P, _P],
+        "mb_symm_barrier": [_P, _I, _I, _I, _I, _F, _P],
         "mb_moe_route": [_P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _L] + [_P] * 15,
         "mb_moe_route_bwd": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P, _P],
         "mb_moe_rows_gather": [_P, _P, _P, _I, _L, _I, _P, _P],

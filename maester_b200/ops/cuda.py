@@ -364,6 +364,12 @@ def wait_flag(flag: torch.Tensor, expect: int, timeout_ms: float, observed: torc
         "wait_flag_probe")
 
 
+def symm_barrier(pad_array, world: int, me: int, base: int, epoch: int, timeout_ms: float) -> None:
+    """Stream-ordered cross-rank barrier on per-rank signal pads (``pad_array``: ``void*[world]``); bounded wait."""
+    _ck(_lib.lib().mb_symm_barrier(pad_array, int(world), int(me), int(base), int(epoch), float(timeout_ms),
+                                   _stream()), "symm_barrier")
+
+
 def pull_sum(symm_parts, my_rank: int, res: torch.Tensor | None, out: torch.Tensor) -> None:
     """out [M/world, N] = (res or 0) + sum over ranks of rows [my_rank*M/world, ...) of their [M, N] partials."""
     assert out.is_contiguous() and (res is None or res.is_contiguous())

@@ -40,6 +40,7 @@ class EPInfo:
     group: object
     size: int
     rank: int
+    peer_dispatcher: object = None
 
 
 class _AllToAll(torch.autograd.Function):
@@ -120,6 +121,8 @@ def _local_param(old: nn.Parameter, sl: tuple) -> nn.Parameter:
     for attr in ("ep_local", "tp_replicated"):
         if getattr(old, attr, False):
             setattr(new, attr, True)
+    if hasattr(old, "tp_dim"):
+        new.tp_dim = old.tp_dim
     return new
 
 
@@ -144,6 +147,7 @@ def apply_ep(model: nn.Module, parallel_dims, use_peer_memory: bool = False, cap
         ex.num_local_experts, ex.ep_rank, ex.ep_size = n_local, ep.rank, ep.size
         moe.dispatcher = shared if shared is not None else AllToAllDispatcher(ep)
     model.ep = ep
+    ep.peer_dispatcher = shared  # None with the all-to-all dispatcher (which never drops rows)
     return ep
 
 
@@ -193,6 +197,7 @@ def apply_expert_tp(model: nn.Module, parallel_dims) -> None:
         ex.w1 = _local_param(ex.w1, (slice(None), slice(None), cols))
         ex.w3 = _local_param(ex.w3, (slice(None), slice(None), cols))
         ex.w2 = _local_param(ex.w2, (slice(None), cols))
+        ex.w1.tp_dim, ex.w3.tp_dim, ex.w2.tp_dim = 2, 2, 1  # which dimension the checkpoint reassembles over tp
         sh = moe.shared_experts
         if sh is not None:
             hs = sh.w1.weight.shape[0]
@@ -201,6 +206,7 @@ def apply_expert_tp(model: nn.Module, parallel_dims) -> None:
             sh.w1.weight = _local_param(sh.w1.weight, (r,))
             sh.w3.weight = _local_param(sh.w3.weight, (r,))
             sh.w2.weight = _local_param(sh.w2.weight, (slice(None), r))
+            sh.w1.weight.tp_dim, sh.w3.weight.tp_dim, sh.w2.weight.tp_dim = 0, 0, 1
             from maester_b200.models.layers import FusedWeight
             sh._w13 = FusedWeight([sh.w1, sh.w3])
         moe.router.gate.weight.tp_replicated = True

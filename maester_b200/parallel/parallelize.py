@@ -142,26 +142,33 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
         ep_size=ep.size if ep is not None else 1, ep_rank=ep.rank if ep is not None else 0,
     )
     sharded.device_mesh = world_mesh["dp_shard_cp"] if (shard_group is not None and world_mesh is not None) else None
-    sharded.expert_mesh = _expert_checkpoint_mesh(world_mesh, parallel_dims) if ep is not None else None
-    sharded.tp_mesh = None  # (dp_shard, tp) or (tp,) sub-mesh describing tensor-parallel slices in checkpoints
-    if parallel_dims.tp_enabled and not has_moe and world_mesh is not None and not parallel_dims.cp_enabled:
-        names = [n for n in ("dp_shard", "tp") if n in (world_mesh.mesh_dim_names or ())]
-        sharded.tp_mesh = world_mesh[tuple(names)] if len(names) > 1 else world_mesh[names[0]]
+    sharded.ckpt_meshes = _checkpoint_meshes(world_mesh, parallel_dims, ep is not None)
     object.__setattr__(model, "_sharded", sharded)
     model.set_requires_gradient_sync = sharded.set_requires_gradient_sync
     # buffers that are still on the meta device (RoPE tables) are rebuilt by init_weights()
     return model
 
 
-def _expert_checkpoint_mesh(world_mesh, parallel_dims):
-    """2-D sub-mesh ``(dp_shard_mod_ep, dp_shard_in_ep)`` for checkpointing expert tensors ``[E, ...]``:
-    experts are split over ``ep`` first and each rank's slice over the ranks holding the same experts,
-    which is a strided shard on the first mesh dimension and a plain shard on the second (the layout
-    FSDP2 on top of expert parallelism produces).  ``None`` with tensor-parallel experts (their
-    checkpoints are per-rank)."""
-    if world_mesh is None or parallel_dims.tp_enabled:
-        return None
-    return world_mesh["dp_shard_mod_ep", "dp_shard_in_ep"]
+def _checkpoint_meshes(world_mesh, parallel_dims, has_ep: bool) -> dict:
+    """Sub-meshes over which checkpointed tensors are split (see ``checkpoint._as_dtensor``):
+    ``dense``: ``(dp_shard_cp,)``; ``dense_tp``: ``(dp_shard_cp, tp)`` or ``(tp,)``; ``expert``:
+    ``(dp_shard_mod_ep, dp_shard_in_ep)`` (the layout FSDP2 on top of expert parallelism produces);
+    ``expert_tp``: the same with ``tp`` appended."""
+    out: dict = {}
+    if world_mesh is None:
+        return out
+    names = set(world_mesh.mesh_dim_names or ())
+    if parallel_dims.fsdp_enabled:
+        out["dense"] = world_mesh["dp_shard_cp"]
+    if parallel_dims.tp_enabled:
+        out["dense_tp"] = world_mesh["dp_shard_cp", "tp"] if parallel_dims.fsdp_enabled else world_mesh["tp"]
+    if has_ep:
+        in_ep = ("dp_shard_in_ep",) if "dp_shard_in_ep" in names else ()
+        if in_ep:
+            out["expert"] = world_mesh[("dp_shard_mod_ep",) + in_ep]
+            if parallel_dims.tp_enabled:
+                out["expert_tp"] = world_mesh[("dp_shard_mod_ep",) + in_ep + ("tp",)]
+    return out
 
 
 def materialize(model: nn.Module) -> None:

@@ -203,7 +203,12 @@ class PeerDispatcher:
         self.workspace(0, 0).barrier()
 
     def dropped(self) -> int:
+        """Rows dropped over capacity since the last reset (synchronises with the device: call when logging)."""
         return int(self.overflow.item()) if self.overflow is not None else 0
+
+    def reset_dropped(self) -> None:
+        if self.overflow is not None:
+            self.overflow.zero_()
 
     # ------------------------------------------------------------------ routing plan (device only)
     def plan(self, counts: torch.Tensor, sorted_experts: torch.Tensor, n_local: int, dim: int) -> _Plan:

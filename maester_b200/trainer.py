@@ -41,6 +41,8 @@ def build_model_args(cfg: Config, vocab_size: int | None = None):
             raise ValueError("flavor has no vocab_size: pass a tokenizer or set synthetic_vocab_size")
         args.vocab_size = vocab_size
     args.max_seq_len = cfg.seq_len
+    if cfg.moe_aux_loss_coeff > 0 and hasattr(args, "moe_args"):
+        args.moe_args.aux_loss_coeff = cfg.moe_aux_loss_coeff
     if cfg.enable_mup:
         args.enable_mup = True
         args.mup_input_alpha = cfg.mup_input_alpha
@@ -95,6 +97,65 @@ class Trainer:
         self.grad_accum = max(1, cfg.gradient_accumulation_steps)
         self.global_micro_step = 0
         self.step = 0
+        self.heartbeat = None
+        if cfg.step_heartbeat and dist.is_initialized() and world_size > 1:
+            from maester_b200.heartbeat import StepHeartbeat
+            self.heartbeat = StepHeartbeat()
+        self.activation_stats: dict[str, list] = {}
+        if cfg.enable_mup and cfg.mup_log_coord_check:
+            self._register_coord_check_hooks()
+
+    # ------------------------------------------------------------------ muP coordinate check
+    def _register_coord_check_hooks(self) -> None:
+        """Forward hooks that record mean |activation| of the embedding, attention / feed-forward projections and the
+        output head on log steps (reference train.py:209-235); ``pop_activation_stats`` turns them into
+        ``act/<key>_abs_mean`` metrics."""
+        def hook(key):
+            def fn(mod, inp, out):
+                if (self.step + 1) % self.cfg.log_freq == 0 or self.step == 0:
+                    self.activation_stats.setdefault(key, []).append(out.detach().abs().float().mean())
+            return fn
+
+        n = 0
+        for name, mod in self.model.named_modules():
+            key = None
+            if name == "tok_embeddings":
+                key = "tok_embed"
+            elif "attention." in name and name.endswith((".wq", ".wk", ".wv", ".wo")):
+                key = "attn"
+            elif "feed_forward." in name and name.endswith((".w1", ".w2", ".w3")):
+                key = "ffn"
+            elif name == "output":
+                key = "output"
+            if key is not None:
+                mod.register_forward_hook(hook(key))
+                n += 1
+        logger.info(f"Activation hooks registered for {n} modules")
+
+    def pop_activation_stats(self) -> dict[str, float]:
+        out = {f"act/{k}_abs_mean": float(torch.stack(v).mean().item()) for k, v in self.activation_stats.items() if v}
+        self.activation_stats = {}
+        return out
+
+    # ------------------------------------------------------------------ health between steps
+    def check_device_status(self, sync: bool = False) -> None:
+        """Raise if a kernel gave up on a bounded wait since the last check (its output is then garbage).  Call where
+        the host has just synchronised (after reading losses) and, with ``sync=True``, before saving a checkpoint."""
+        if self.device.type == "cuda":
+            from maester_b200.ops import cuda as C
+            C.check_status(sync=sync)
+
+    def pop_dropped_rows(self) -> int | None:
+        """Rows the peer-memory expert dispatcher dropped over capacity since the last call (None without it)."""
+        disp = getattr(getattr(self.model, "ep", None), "peer_dispatcher", None)
+        if disp is None:
+            return None
+        n = int(disp.dropped())
+        disp.reset_dropped()
+        if n:
+            logger.warning(f"expert-parallel peer dispatch dropped {n} rows over capacity "
+                           f"(ep_capacity_factor={self.cfg.ep_capacity_factor}); the all-to-all dispatcher never drops")
+        return n
 
     # ------------------------------------------------------------------ one optimizer step
     def to_device(self, batch: dict[str, Any]) -> dict[str, Any]:
@@ -136,7 +197,10 @@ class Trainer:
         skip_sync = self.grad_accum > 1 and not self.cfg.gradient_accumulation_sync_each_step
         losses = []
         batches = list(batches)
-        clip = bool(self.cfg.max_grad_norm and self.cfg.max_grad_norm > 0 and getattr(self.cfg, "clip_gradients", False))
+        clip = bool(self.cfg.clip_gradients and self.cfg.max_grad_norm and self.cfg.max_grad_norm > 0)
+        if self.heartbeat is not None:  # nobody launches kernels towards a peer that is gone
+            self.heartbeat.beat(self.step + 1)
+            self.heartbeat.check(self.step + 1, timeout_s=self.cfg.heartbeat_timeout_seconds)
         for i, batch in enumerate(batches):
             self.global_micro_step += 1
             torch.manual_seed(self.global_micro_step + self.dp_rank)
@@ -144,7 +208,7 @@ class Trainer:
             if i == len(batches) - 1 and not clip and hasattr(self.optimizers, "announce_step"):
                 self.optimizers.announce_step()  # units may be updated as soon as their gradients are complete
             losses.append(self.forward_backward(batch, sync))
-        if self.cfg.max_grad_norm and self.cfg.max_grad_norm > 0 and getattr(self.cfg, "clip_gradients", False):
+        if clip:
             params = [p for g in self.optimizers.param_groups for p in g["params"]]
             clip_grad_norm(params, self.cfg.max_grad_norm, group=self.sharded.group if self.sharded else None)
         self.optimizers.step()

@@ -184,11 +184,11 @@ def test_expert_parallel_checkpoint_round_trip(tmp_path, world):
     assert w1.shape[0] == 8  # all experts, reassembled from the (ep x fsdp) shards
 
 
-def _tp_save(rank, world, tmp, full, batches, dp):
+def _tp_save(rank, world, tmp, full, batches, dp, cp=1):
     from maester_b200.trainer import Trainer
     from train import TrainState
     from maester_b200.checkpoint import CheckpointManager
-    cfg = _mk(tmp, tensor_parallel_degree=2, data_parallel_shard_degree=dp)
+    cfg = _mk(tmp, tensor_parallel_degree=2, data_parallel_shard_degree=dp, context_parallel_degree=cp)
     tr = Trainer(cfg)
     import torch.distributed as dist
     g = tr.parallel_dims.mesh_group("tp")
@@ -200,11 +200,12 @@ def _tp_save(rank, world, tmp, full, batches, dp):
     return True
 
 
-@pytest.mark.parametrize("world,dp", [(2, 1), (4, 2)])
-def test_tensor_parallel_checkpoint_reassembles_full_weights(tmp_path, world, dp):
-    """TP slices (x data-parallel shards) are published as DTensors, so the checkpoint holds whole tensors."""
+@pytest.mark.parametrize("world,dp,cp", [(2, 1, 1), (4, 2, 1), (4, 1, 2)])
+def test_tensor_parallel_checkpoint_reassembles_full_weights(tmp_path, world, dp, cp):
+    """TP slices (x data-parallel shards, x context-parallel shards) are published as DTensors, so the checkpoint
+    holds whole tensors."""
     full = _full_weights(_cfg())
-    run_ranks(world, _tp_save, str(tmp_path), full, _batches(1, 2, 64, 512), dp)
+    run_ranks(world, _tp_save, str(tmp_path), full, _batches(1, 2, 64, 512), dp, cp)
     from maester_b200.convert.io import read_dcp_model
     flat = read_dcp_model(tmp_path / "job" / "checkpoints" / "step-2")
     for k, v in full.items():
@@ -212,3 +213,50 @@ def test_tensor_parallel_checkpoint_reassembles_full_weights(tmp_path, world, dp
             assert flat[k].shape == v.shape, k
             assert torch.equal(flat[k], v.float()), k
     assert {"layers.0.attention.wq.weight", "layers.0.attention.wo.weight", "layers.0.feed_forward.w2.weight"} <= set(flat)
+
+
+def _expert_tp_save(rank, world, tmp, full, cfg_kw):
+    from test_expert_parallel_cpu import _cfg as ep_cfg, _load
+    from train import TrainState
+    from maester_b200.checkpoint import CheckpointManager
+    from maester_b200.trainer import Trainer
+    import torch.distributed as dist
+    cfg = ep_cfg(enable_checkpoint=True, dump_dir=str(tmp), job_name="etp", checkpoint_interval=1, **cfg_kw)
+    tr = Trainer(cfg)
+    g = tr.parallel_dims.mesh_group("tp")
+    _load(tr, full, (dist.get_rank(g), dist.get_world_size(g)))
+    st = TrainState()
+    ck = CheckpointManager(model=tr.model, optimizer=tr.optimizers, lr_scheduler=tr.scheduler, dataloader=None,
+                           states={"train_state": st}, cfg=cfg)
+    ck.save(1)
+    # a fresh trainer restores exactly this rank's pieces
+    before = {sl.fqn: sl.master.data.clone() for u in tr.sharded.units for sl in u.slots}
+    tr2 = Trainer(cfg)
+    st2 = TrainState()
+    ck2 = CheckpointManager(model=tr2.model, optimizer=tr2.optimizers, lr_scheduler=tr2.scheduler, dataloader=None,
+                            states={"train_state": st2}, cfg=cfg)
+    assert ck2.load()
+    for u in tr2.sharded.units:
+        for sl in u.slots:
+            assert torch.equal(sl.master.data, before[sl.fqn]), sl.fqn
+    return True
+
+
+@pytest.mark.parametrize("world,kw", [
+    (2, dict(tensor_parallel_degree=2)),                                                          # TP-only experts
+    (4, dict(tensor_parallel_degree=2, data_parallel_shard_degree=2, expert_parallel_degree=4)),  # EP x TP
+])
+def test_tensor_parallel_expert_checkpoint_holds_whole_tensors(tmp_path, world, kw):
+    """Experts sliced over tp (alone or under expert parallelism) reassemble to the unsharded tensors."""
+    from test_expert_parallel_cpu import _cfg as ep_cfg
+    full = _full_weights(ep_cfg())
+    run_ranks(world, _expert_tp_save, str(tmp_path), full, kw)
+    from maester_b200.convert.io import read_dcp_model
+    flat = read_dcp_model(tmp_path / "etp" / "checkpoints" / "step-1")
+    checked = 0
+    for k, v in full.items():
+        if k in flat:
+            assert flat[k].shape == v.shape, (k, flat[k].shape, v.shape)
+            assert torch.equal(flat[k], v.float()), k
+            checked += 1
+    assert checked > 10 and any(k.endswith("moe.experts.w2") for k in flat)

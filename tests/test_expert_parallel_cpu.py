@@ -96,3 +96,19 @@ def test_tensor_parallel_experts_match_single_process():
     want_losses, want = _single(cfg1, full, batches)
     res = run_ranks(2, _ep_rank, dict(tensor_parallel_degree=2), full, batches, 2)
     _check(res, want_losses, want, 2, 1)
+
+
+def test_expert_parallel_with_tensor_parallel_experts_matches_single_process():
+    """ep 4 x tp 2 on four ranks (two data-parallel ranks of two tensor-parallel ranks each): experts are split over
+    the two ``dp_shard_in_ep`` ranks and every expert's hidden dimension over ``tp``
+    (reference ExpertTensorParallel: maester/parallelisms/expert_parallel.py:167-213)."""
+    cfg1 = _cfg(train_batch_size=4)
+    full = _full_weights(cfg1)
+    batches = _batches(2, 4, 32, 2000)
+    want_losses, want = _single(cfg1, full, batches)
+    res = run_ranks(4, _ep_rank, dict(data_parallel_shard_degree=2, tensor_parallel_degree=2, expert_parallel_degree=4),
+                    full, batches, 2)
+    # the two tensor-parallel ranks of a data-parallel rank see the same batch and report the same loss
+    mean = [sum(r[0][i] for r in res) / 4 for i in range(len(want_losses))]
+    assert mean == pytest.approx(want_losses, abs=2e-4)
+    _check(res, want_losses, want, 4, 2)

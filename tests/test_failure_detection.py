@@ -186,3 +186,60 @@ def test_bounded_wait_expires_sets_status_and_leaves_the_context_usable():
     ref = a.float() @ b.float().t()
     assert (C.gemm(a, b).float() - ref).abs().max().item() < 0.5  # kernels still run after the expiry
     C.check_status()
+
+
+@pytest.mark.gpu
+def test_cross_rank_barrier_gives_up_when_a_peer_never_arrives():
+    """The library's own barrier kernel on a local table of signal pads: with the peer's arrival already posted it
+    passes; with a peer that never posts it returns at the deadline with the status word set, and later kernels run."""
+    import ctypes
+
+    from maester_b200.ops import cuda as C
+    C.check_status()
+    pads = torch.zeros(2, 64, dtype=torch.int32, device="cuda")  # pads[r]: signal pad of rank r
+    table = (ctypes.c_void_p * 2)(pads[0].data_ptr(), pads[1].data_ptr())
+    pads[0, 1] = 1                                   # "rank 1" has already posted epoch 1 into rank 0's pad
+    C.symm_barrier(table, 2, 0, 0, 1, timeout_ms=300.0)
+    C.check_status()
+    assert pads[:, 0].tolist() == [1, 1]             # rank 0's arrival reached both pads
+    t0 = time.time()
+    C.symm_barrier(table, 2, 0, 0, 2, timeout_ms=300.0)   # nobody posts epoch 2 for rank 1
+    with pytest.raises(RuntimeError, match="status 5"):
+        C.check_status()
+    assert time.time() - t0 < 5
+    x = torch.randn(128, 64, device="cuda", dtype=torch.bfloat16)
+    assert torch.isfinite(C.gemm(x, x).float()).all()
+    C.check_status()
+
+
+def test_a_failed_kernel_status_blocks_the_checkpoint(tmp_path, monkeypatch):
+    """If a kernel gave up on a bounded wait, its output is garbage: ``save`` must raise before writing anything."""
+    import maester_b200.checkpoint as ckpt
+    from test_checkpoint_cpu import _mk, _trainer_with_ckpt
+    tr, state, ck = _trainer_with_ckpt(_mk(tmp_path))
+
+    def bad():
+        raise RuntimeError("maester_b200 kernel reported status 5: timed out waiting on a peer GPU's flag")
+
+    monkeypatch.setattr(ckpt, "_check_device_status", bad)
+    with pytest.raises(RuntimeError, match="status 5"):
+        ck.save(2)
+    assert not (tmp_path / "job" / "checkpoints" / "step-2").exists()
+    monkeypatch.undo()
+    ck.save(2)
+    assert (tmp_path / "job" / "checkpoints" / "step-2" / ".metadata").exists()
+
+
+@pytest.mark.gpu
+def test_an_expired_wait_blocks_the_checkpoint_on_the_gpu(tmp_path):
+    from maester_b200.ops import cuda as C
+    from test_checkpoint_cpu import _mk, _trainer_with_ckpt
+    C.check_status()
+    tr, state, ck = _trainer_with_ckpt(_mk(tmp_path))
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    C.wait_flag(flag, 1, timeout_ms=100.0)  # nothing sets the flag: the wait runs out
+    with pytest.raises(RuntimeError, match="status 5"):
+        ck.save(2)
+    assert not (tmp_path / "job" / "checkpoints" / "step-2").exists()
+    ck.save(2)  # the failed check cleared the status word
+    assert (tmp_path / "job" / "checkpoints" / "step-2" / ".metadata").exists()

@@ -81,3 +81,29 @@ def test_noalloc_rejects_oversized_problem():
     rc = fn(None, None, None, None, None, None, None, None, None, None, 2, 16384, 64, 8, 128,
             0, 0, 0, 0, 1, -1, 0.1, None, None)
     assert rc == MB_NOALLOC_TOO_LARGE
+
+
+def test_noalloc_builtin_status_word_can_be_read_and_cleared():
+    """Without a caller-provided status word the kernels report into a word inside the library;
+    ``mb_noalloc_status`` reads and clears it (0 after a healthy call)."""
+    from maester_b200.ops import _lib
+
+    lib = ctypes.CDLL(str(_lib.build()))
+    lib.mb_noalloc_status.restype = _I
+    fn = _symbol()
+    B, S, H, KV, hd = 1, 256, 2, 1, 128
+    torch.manual_seed(5)
+    qkv = (torch.randn(B, S, (H + 2 * KV) * hd, device="cuda") * 0.5).to(torch.bfloat16)
+    q = qkv[..., : H * hd].view(B, S, H, hd)
+    k = qkv[..., H * hd:(H + KV) * hd].view(B, S, KV, hd)
+    v = qkv[..., (H + KV) * hd:].view(B, S, KV, hd)
+    from maester_b200.ops import cuda as C
+    out, lse = C.attn_fwd(q, k, v, hd ** -0.5, True, None)
+    dout = torch.randn_like(out)
+    got = torch.zeros(B * S, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
+    rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+            got.data_ptr(), None, None, None, B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
+            got.stride(0), 1, -1, hd ** -0.5, None, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert lib.mb_noalloc_status() == 0
+    assert torch.isfinite(got.float()).all() and got.float().abs().sum() > 0

@@ -157,6 +157,7 @@ def main() -> None:
 
                 if train_state.step == 1 or train_state.step % cfg.log_freq == 0:
                     losses = torch.stack(losses_since_last_log).tolist()  # one device->host transfer
+                    trainer.check_device_status()  # the host has just synchronised: a kernel that gave up shows here
                     avg_loss, max_loss = float(np.mean(losses)), float(np.max(losses))
                     if pd.dp_enabled:
                         global_avg_loss = dist_mean(avg_loss, trainer.dp_group).item()
@@ -201,6 +202,10 @@ def main() -> None:
                         metrics["padding/std_length"] = lengths.std().item() if lengths.numel() > 1 else 0.0
                     if weight_scale_stats:
                         metrics.update(weight_scale_stats)
+                    metrics.update(trainer.pop_activation_stats())
+                    dropped = trainer.pop_dropped_rows()
+                    if dropped is not None:
+                        metrics["moe/dropped_rows"] = dropped
                     hook_stats = getattr(trainer.optimizers, "_hook_stats", None)
                     if hook_stats:
                         metrics.update(hook_stats)
@@ -218,7 +223,10 @@ def main() -> None:
                     time_last_log = timer()
                     gpu_memory_monitor.reset_peak_stats()
 
-                checkpoint.save(train_state.step, force=(train_state.step == cfg.train_num_steps))
+                last = train_state.step == cfg.train_num_steps
+                if checkpoint.will_save(train_state.step, force=last):
+                    trainer.check_device_status(sync=True)  # never persist weights a failed kernel may have corrupted
+                checkpoint.save(train_state.step, force=last)
                 if torch_profiler is not None:
                     torch_profiler.step()
                 if memory_profiler is not None:
