@@ -17,7 +17,7 @@ import os
 import torch
 
 from maester_b200.ops import cuda as C
-from maester_b200.ops.functional import kv_block_lower_bounds, q_block_upper_bounds
+from maester_b200.ops.functional import attention_plan
 
 
 def _peaks() -> tuple[float, float]:
@@ -81,14 +81,13 @@ def bench_attention(iters: int, small: bool) -> None:
         q = qkv[..., :H * hd].view(B, S, H, hd)
         k = qkv[..., H * hd:(H + KV) * hd].view(B, S, KV, hd)
         v = qkv[..., (H + KV) * hd:].view(B, S, KV, hd)
-        lo = kv_block_lower_bounds(S, 128, window, None, "cuda", batch=B)
-        hi = q_block_upper_bounds(S, 128, window, None, "cuda", batch=B)
-        out, lse = C.attn_fwd(q, k, v, hd ** -0.5, True, window, None, lo)
+        plan = attention_plan(S, window, None, "cuda", batch=B)
+        out, lse = C.attn_fwd(q, k, v, hd ** -0.5, True, window, plan)
         dout = torch.randn_like(out)
         dqkv = torch.empty_like(qkv).view(B * S, -1)
         fl = 4 * B * H * hd * S * (S / 2 if window is None else window)
-        tf = timeit(lambda: C.attn_fwd(q, k, v, hd ** -0.5, True, window, None, lo), iters, warm)
-        tb = timeit(lambda: C.attn_bwd(q, k, v, out, dout, lse, dqkv, hd ** -0.5, True, window, None, lo, hi), iters, warm)
+        tf = timeit(lambda: C.attn_fwd(q, k, v, hd ** -0.5, True, window, plan), iters, warm)
+        tb = timeit(lambda: C.attn_bwd(q, k, v, out, dout, lse, dqkv, hd ** -0.5, True, window, plan), iters, warm)
         print(f"attention H{H} KV{KV} hd{hd} window={window} B{B} S{S}: fwd {tf:.3f} ms {fl / tf / 1e9:5.0f} TF "
               f"({fl / tf / 1e9 / tf_peak:.2f} of measured) | bwd {tb:.3f} ms {2.5 * fl / tb / 1e9:5.0f} TF "
               f"({2.5 * fl / tb / 1e9 / tf_peak:.2f} of measured)")

@@ -8,18 +8,28 @@
 //                    of 64: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T to shared memory, then
 //                    dV += P^T dO and dK += dS^T Q.  The 256-wide head is split in two CTAs because
 //                    dK, dV, S^T and dP^T must share the 512 TMEM columns.
-// P is recomputed from the saved log-sum-exp.  Masks as in the forward kernel.
+// P is recomputed from the saved log-sum-exp.  Masks as in the forward kernel: per-row intervals (kv_start for
+// query rows, q_end for kv rows) when given, else window / causal bounds computed here plus an element-wise
+// document-id comparison.
 // Gradients are written into one packed buffer [T, (H + 2 KV) * hd] (q heads, k heads, v heads).
 #include "host_common.cuh"
 #include "sm100.cuh"
+#include <limits.h>
 #include <math.h>
+#include <atomic>
 
 namespace {
 using namespace mb;
 
-constexpr int BWD_THREADS = 320;     // warps 0-7: element-wise stage (two threads per row), 8: TMA, 9: MMA
+constexpr int BWD_THREADS = 352;     // warps 0-7: element-wise stage (two threads per row), 8: TMA, 9-10: MMA issue
 constexpr int EW_THREADS = 256;
 constexpr int WARP_TMA = 8, WARP_MMA = 9;
+// MMA issue: one thread cannot issue faster than one MMA per ~54 cycles (measured) while an M128 N64 K16 product
+// takes 32, so two threads issue, split by role: warp 9 issues the score products (S or S^T) of every block, warp 10
+// the dP (dP^T) products and the accumulating products (dQ, or dV and dK).  Every mbarrier therefore still has
+// consumers that see all of its phases in order.  Products of different threads that touch the same tensor-memory
+// buffer are ordered by "issued" barriers (arrive after issuing, tcgen05 fences on both sides): the pipe executes
+// in issue order.
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) {
@@ -36,19 +46,13 @@ struct BwdParams {
   const int* doc;        // [B,S] or null
   const int* kv_lo_blk;  // [B, ceil(S/128)] or null   (dQ kernel)
   const int* q_hi_blk;   // [B, ceil(S/128)] or null   (dK/dV kernel): exclusive upper bound on q
+  const int* kv_start;   // [B, S] or null: lowest kv index a query row may attend to (window, document start folded in)
+  const int* q_end;      // [B, S] or null: exclusive upper bound on the query rows that may attend to a kv row
   int B, S, H, KV;
   int causal, window;
   float scale, scale_log2;
   int* status;
 };
-
-__device__ __forceinline__ bool is_masked(const BwdParams& p, const int* docb, int q, int kv, int dq, int dk) {
-  bool bad = (kv >= p.S) | (q >= p.S);
-  if (p.causal) bad |= kv > q;
-  if (p.window >= 0) bad |= (q - kv) > p.window;
-  if (docb) bad |= dq != dk;
-  return bad;
-}
 
 // ---------------------------------------------------------------------------------- delta
 __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
@@ -153,7 +157,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
-      mbar_init(&sdp_full[i], 1);
+      mbar_init(&sdp_full[i], 2);  // one commit from each issuing thread (S_n and dP_n)
       mbar_init(&s_empty[i], EW_THREADS);
       mbar_init(&ds_full[i], EW_THREADS);
       mbar_init(&dp_empty[i], 1);
@@ -197,58 +201,73 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       if (!okp) atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
     }
   } else if (warp == WARP_MMA) {
+    // ---- issuer A: S_n = Q K_n^T for every block
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
-      const uint32_t sq = smem_u32(smem + L::OFF_Q), sdo = smem_u32(smem + L::OFF_DO);
+      const uint64_t dq0 = make_smem_desc(smem_u32(smem + L::OFF_Q), 16, 1024);
       bool ok = mbar_wait(qdo_full, 0);
-      auto issue_sdp = [&](int n) -> bool {
-        const int sk_i = n & 1, sv_i = n % NSTV, buf = n & 1;
-        const uint32_t ph = (n >> 1) & 1;
-        if (!mbar_wait(&v_full[sv_i], (n / NSTV) & 1)) return false;
-        if (!mbar_wait(&dp_empty[buf], ph ^ 1)) return false;
-        tc_fence_after();
-        const uint32_t sv = smem_u32(smem + L::OFF_V + sv_i * L::KV_BYTES);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t blk = k >> 2, kk = k & 3;
-          umma_bf16_ss(tmem_dp + buf * BKV, make_smem_desc(sdo + blk * (128 * 128) + kk * 32, 16, 1024),
-                       make_smem_desc(sv + blk * (BKV * 128) + kk * 32, 16, 1024), idesc_s, k != 0);
-        }
-        umma_commit(&v_empty[sv_i]);
-        if (!mbar_wait(&k_full[sk_i], ph)) return false;
-        if (!mbar_wait(&s_empty[buf], ph ^ 1)) return false;
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + L::OFF_K + sk_i * L::KV_BYTES);
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t blk = k >> 2, kk = k & 3;
-          umma_bf16_ss(tmem_s + buf * BKV, make_smem_desc(sq + blk * (128 * 128) + kk * 32, 16, 1024),
-                       make_smem_desc(sk + blk * (BKV * 128) + kk * 32, 16, 1024), idesc_s, k != 0);
-        }
-        umma_commit(&sdp_full[buf]);
-        return true;
-      };
-      if (ok) ok = issue_sdp(0);
       for (int n = 0; n < nblk && ok; ++n) {
-        if (n + 1 < nblk) ok = issue_sdp(n + 1);
-        if (!ok) break;
-        const int buf = n & 1;
-        if (!mbar_wait(&ds_full[buf], (n >> 1) & 1)) {
+        const int sk_i = n & 1, buf = n & 1;
+        const uint32_t ph = (n >> 1) & 1;
+        if (!mbar_wait(&k_full[sk_i], ph) || !mbar_wait(&s_empty[buf], ph ^ 1)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + L::OFF_K + (n & 1) * L::KV_BYTES);
+        // descriptors are built once per tile and stepped by constants (the issuing thread is the bottleneck)
+        const uint64_t dk0 = make_smem_desc(smem_u32(smem + L::OFF_K + sk_i * L::KV_BYTES), 16, 1024);
+        umma_bf16_ss_c<false>(tmem_s + buf * BKV, dq0, dk0, idesc_s);
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          // dS_n columns: kv 0..31 packed at the start of the first half of the dP buffer, kv 32..63 at the
-          // start of its second half (each element-wise thread overwrites only columns it has read itself)
-          const uint32_t a_tmem = tmem_dp + buf * BKV + (k >> 1) * 32 + (k & 1) * 8;
-          umma_bf16_ts(tmem_dq, a_tmem, make_smem_desc(sk + k * 2048, BKV * 128, 1024), idesc_dq, (n | k) != 0);
+        for (int k = 1; k < HD / 16; ++k)
+          umma_bf16_ss_c<true>(tmem_s + buf * BKV, smem_desc_advance(dq0, (k >> 2) * (128 * 128) + (k & 3) * 32),
+                               smem_desc_advance(dk0, (k >> 2) * (BKV * 128) + (k & 3) * 32), idesc_s);
+        umma_commit(&sdp_full[buf]);
+      }
+      if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
+    }
+  } else if (warp == WARP_MMA + 1) {
+    // ---- issuer B: dP_n = dO V_n^T (one block ahead) and dQ += dS_n K_n
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, BKV, false, false);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
+      const uint64_t ddo0 = make_smem_desc(smem_u32(smem + L::OFF_DO), 16, 1024);
+      bool ok = mbar_wait(qdo_full, 0);
+      auto issue_dp = [&](int n) -> bool {
+        const int sv_i = n % NSTV, buf = n & 1;
+        if (!mbar_wait(&v_full[sv_i], (n / NSTV) & 1)) return false;
+        // (the dP buffer was last read by the dQ product of block n-2, issued earlier by this same thread: no wait)
+        tc_fence_after();
+        const uint64_t dv0 = make_smem_desc(smem_u32(smem + L::OFF_V + sv_i * L::KV_BYTES), 16, 1024);
+        umma_bf16_ss_c<false>(tmem_dp + buf * BKV, ddo0, dv0, idesc_s);
+#pragma unroll
+        for (int k = 1; k < HD / 16; ++k)
+          umma_bf16_ss_c<true>(tmem_dp + buf * BKV, smem_desc_advance(ddo0, (k >> 2) * (128 * 128) + (k & 3) * 32),
+                               smem_desc_advance(dv0, (k >> 2) * (BKV * 128) + (k & 3) * 32), idesc_s);
+        umma_commit(&v_empty[sv_i]);
+        umma_commit(&sdp_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_dp(0);
+      for (int n = 0; n < nblk && ok; ++n) {
+        if (n + 1 < nblk) ok = issue_dp(n + 1);
+        if (!ok) break;
+        const int buf = n & 1;
+        // K_n has landed (the other thread waited for it too; this makes the TMA writes visible to this thread's MMAs)
+        if (!mbar_wait(&ds_full[buf], (n >> 1) & 1) || !mbar_wait(&k_full[n & 1], (n >> 1) & 1)) {
+          ok = false;
+          break;
         }
+        tc_fence_after();
+        // dS_n columns: kv 0..31 packed at the start of the first half of the dP buffer, kv 32..63 at the
+        // start of its second half (each element-wise thread overwrites only columns it has read itself)
+        const uint64_t dkm0 = make_smem_desc(smem_u32(smem + L::OFF_K + (n & 1) * L::KV_BYTES), BKV * 128, 1024);
+        const uint32_t a0 = tmem_dp + buf * BKV;
+        umma_bf16_ts(tmem_dq, a0, dkm0, idesc_dq, n != 0);
+#pragma unroll
+        for (int k = 1; k < BKV / 16; ++k)
+          umma_bf16_ts_c<true>(tmem_dq, a0 + (k >> 1) * 32 + (k & 1) * 8, smem_desc_advance(dkm0, k * 2048), idesc_dq);
+        // K_n is free once dQ_n has read it (S_n, issued by the other thread, completed before dS_n existed)
         umma_commit(&k_empty[n & 1]);
-        umma_commit(&dp_empty[buf]);
         if (n == nblk - 1) umma_commit(dq_done);
       }
       if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
@@ -258,8 +277,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     const int row = (warp & 3) * 32 + lane;
     const int q = q0 + row;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int* docb = p.doc ? p.doc + static_cast<long long>(b) * p.S : nullptr;
+    // masks: one admissible kv interval [lo_q, hi_q] per query row (see the forward kernel); the element-wise
+    // document comparison only runs when document ids are given without the interval form
+    const int* docb = (p.doc && !p.kv_start) ? p.doc + static_cast<long long>(b) * p.S : nullptr;
     const int dq_doc = (docb && q < p.S) ? docb[q] : 0;
+    int lo_q, hi_q;
+    if (q >= p.S) {
+      lo_q = INT_MAX;
+      hi_q = -1;
+    } else {
+      hi_q = p.causal ? q : p.S - 1;
+      if (p.kv_start) lo_q = p.kv_start[static_cast<long long>(b) * p.S + q];
+      else lo_q = p.window >= 0 ? max(0, q - p.window) : 0;
+    }
+    int w_lo_max = lo_q, w_hi_min = hi_q;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) {
+      w_lo_max = max(w_lo_max, __shfl_xor_sync(0xffffffffu, w_lo_max, sh));
+      w_hi_min = min(w_hi_min, __shfl_xor_sync(0xffffffffu, w_hi_min, sh));
+    }
     const long long stat_idx = (static_cast<long long>(b) * p.H + h) * p.S + q;
     const float lse2 = (q < p.S) ? p.lse[stat_idx] * LOG2E : INFINITY;  // rows past the end give P = 0
     const float delta = (q < p.S) ? p.delta[stat_idx] : 0.f;
@@ -279,8 +315,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[buf]);  // scores are in registers: the MMA warp may refill the S buffer
-      const bool need_mask = (docb != nullptr) || (kv0 + BKV > p.S) || (p.causal && kv0 + BKV - 1 > q0) ||
-                             (p.window >= 0 && (q0 + 127) - kv0 > p.window);
+      const bool need_mask = (docb != nullptr) || kv0 < w_lo_max || kv0 + BKV - 1 > w_hi_min;
       float ds[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
@@ -291,8 +326,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int kv = kv0 + half * 32 + i;
-          const int dk = (docb && kv < p.S) ? docb[kv] : 0;
-          if (is_masked(p, docb, q, kv, dq_doc, dk)) ds[i] = 0.f;
+          bool bad = (kv < lo_q) | (kv > hi_q);
+          if (docb && kv < p.S) bad |= docb[kv] != dq_doc;
+          if (bad) ds[i] = 0.f;
         }
       }
       uint32_t packed[16];
@@ -391,6 +427,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* acc_done = bars + 13;   // 1
   uint64_t* stat_bar = bars + 14;   // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* acc_issued = bars + 18; // [2]  the dV / dK products that read the S^T / dP^T buffers have been issued
   float* stat = reinterpret_cast<float*>(smem + L::OFF_STAT);  // [buf][0: lse2, 1: delta][BQ2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -417,12 +454,14 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     prefetch_tmap(&tmap_do);
     mbar_init(kv_full, 1);
     mbar_init(acc_done, 1);
+    mbar_init(&acc_issued[0], 1);
+    mbar_init(&acc_issued[1], 1);
     mbar_init(qe_full, 1);
-    mbar_init(qe_empty, 1);
+    mbar_init(qe_empty, 2);   // S^T_n (issuer A) and dP^T_n (issuer B) have read the early region
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ql_full[i], 1);
       mbar_init(&ql_empty[i], 1);
-      mbar_init(&sdp_full[i], 1);
+      mbar_init(&sdp_full[i], 2);  // one commit from each issuing thread
       mbar_init(&pt_full[i], EW_THREADS);
       mbar_init(&acc_free[i], 1);
       mbar_init(&stat_bar[i], EW_THREADS);
@@ -441,15 +480,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const uint32_t tmem_dv = tmem_base + 128;
   const uint32_t tmem_st = tmem_base + 256;    // 2 x 64: S^T, then P^T (packed) at the start of each half
   const uint32_t tmem_dpt = tmem_base + 384;   // 2 x 64: dP^T, then dS^T likewise
-
-  // shared-memory address of 64-channel block `blk` of the query-side tile (which = 0: Q, 1: dO)
-  auto q_block = [&](int stage, int which, int blk) -> uint32_t {
-    const bool late = blk >= lb0 && blk < lb0 + LATE_BLKS;
-    if (late)
-      return smem_u32(smem + L::OFF_QL + (stage * 2 + which) * L::LATE_BYTES + (blk - lb0) * (BQ2 * 128));
-    const int e = blk < lb0 ? blk : blk - LATE_BLKS;
-    return smem_u32(smem + L::OFF_QE + which * L::EARLY_BYTES + e * (BQ2 * 128));
-  };
 
   if (warp == WARP_TMA) {
     if (lane == 0 && ntot > 0) {
@@ -487,59 +517,77 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       }
       if (!okp) atomicCAS(p.status, 0, ERR_WAIT_EMPTY);
     }
-  } else if (warp == WARP_MMA) {
+  } else if (warp >= WARP_MMA) {
+    // issuer A (warp 9): S^T_n = K Q_n^T for every tile.  Issuer B (warp 10): dP^T_n = V dO_n^T (one tile ahead) and
+    // dV += P^T_n dO_n, dK += dS^T_n Q_n.
+    const bool is_a = warp == WARP_MMA;
     if (lane == 0 && ntot > 0) {
       constexpr uint32_t idesc_st = make_idesc_bf16(128, BQ2, false, false);
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, DV, false, true);
-      const uint32_t sk = smem_u32(smem + L::OFF_K), sv = smem_u32(smem + L::OFF_V);
+      static_assert(NSPLIT <= 2, "block-to-region mapping below assumes at most two channel splits");
+      const uint64_t da0 = make_smem_desc(smem_u32(smem + (is_a ? L::OFF_K : L::OFF_V)), 16, 1024);
+      const int which = is_a ? 0 : 1;  // query-side operand: Q for S^T, dO for dP^T
       bool ok = mbar_wait(kv_full, 0);
-      auto issue_sdp = [&](int n) -> bool {
+      // S^T_n (A) or dP^T_n (B): 128 kv rows x BQ2 query columns, contraction over all channels.  The query-side
+      // tile sits in two regions: with two channel splits the first LATE_BLKS 64-channel blocks are the slice
+      // ("late") region for split 0 and the other ("early") region for split 1, and vice versa.
+      auto issue_scores = [&](int n) -> bool {
         const int s = n & 1, buf = n & 1;
         const uint32_t ph = (n >> 1) & 1;
         if (!mbar_wait(&ql_full[s], ph)) return false;
         if (HAS_EARLY && !mbar_wait(qe_full, n & 1)) return false;
-        if (!mbar_wait(&acc_free[buf], ph ^ 1)) return false;
+        // the buffer was last read by dV_(n-2) / dK_(n-2): issued by B itself, or (for A) announced by B
+        if (is_a && n >= 2 && !mbar_wait(&acc_issued[buf], ((n - 2) >> 1) & 1)) return false;
         tc_fence_after();
+        const uint64_t late = make_smem_desc(smem_u32(smem + L::OFF_QL + (s * 2 + which) * L::LATE_BYTES), 16, 1024);
+        const uint64_t early = HAS_EARLY ? make_smem_desc(smem_u32(smem + L::OFF_QE + which * L::EARLY_BYTES), 16, 1024) : late;
+        const uint64_t lo_half = (!HAS_EARLY || split == 0) ? late : early;
+        const uint64_t hi_half = (!HAS_EARLY || split == 0) ? early : late;
+        const uint32_t d_t = (is_a ? tmem_st : tmem_dpt) + buf * BQ2;
+        umma_bf16_ss_c<false>(d_t, da0, lo_half, idesc_st);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t blk = k >> 2, kk = k & 3;
-          umma_bf16_ss(tmem_st + buf * BQ2, make_smem_desc(sk + blk * (128 * 128) + kk * 32, 16, 1024),
-                       make_smem_desc(q_block(s, 0, blk) + kk * 32, 16, 1024), idesc_st, k != 0);
+        for (int k = 1; k < HD / 16; ++k) {
+          const int blk = k >> 2, kk = k & 3;
+          const bool in_lo = !HAS_EARLY || blk < LATE_BLKS;
+          const uint64_t db = smem_desc_advance(in_lo ? lo_half : hi_half,
+                                                (in_lo ? blk : blk - LATE_BLKS) * (BQ2 * 128) + kk * 32);
+          umma_bf16_ss_c<true>(d_t, smem_desc_advance(da0, blk * (128 * 128) + kk * 32), db, idesc_st);
         }
-#pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t blk = k >> 2, kk = k & 3;
-          umma_bf16_ss(tmem_dpt + buf * BQ2, make_smem_desc(sv + blk * (128 * 128) + kk * 32, 16, 1024),
-                       make_smem_desc(q_block(s, 1, blk) + kk * 32, 16, 1024), idesc_st, k != 0);
-        }
-        if (HAS_EARLY) umma_commit(qe_empty);
-        umma_commit(&sdp_full[buf]);
+        if (HAS_EARLY) umma_commit(qe_empty);   // two arrivals per tile: S^T and dP^T have read the early region
+        umma_commit(&sdp_full[buf]);            // two arrivals per tile
         return true;
       };
-      if (ok) ok = issue_sdp(0);
-      for (int n = 0; n < ntot && ok; ++n) {
-        if (n + 1 < ntot) ok = issue_sdp(n + 1);
-        if (!ok) break;
-        const int s = n & 1, buf = n & 1;
-        if (!mbar_wait(&pt_full[buf], (n >> 1) & 1)) {
-          ok = false;
-          break;
+      if (is_a) {
+        for (int n = 0; n < ntot && ok; ++n) ok = issue_scores(n);
+      } else {
+        if (ok) ok = issue_scores(0);
+        for (int n = 0; n < ntot && ok; ++n) {
+          if (n + 1 < ntot) ok = issue_scores(n + 1);
+          if (!ok) break;
+          const int s = n & 1, buf = n & 1;
+          if (!mbar_wait(&pt_full[buf], (n >> 1) & 1)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          // B operands: the [BQ2 x DV] slices of dO / Q (slice channels), MN-major
+          const uint64_t dql = make_smem_desc(smem_u32(smem + L::OFF_QL + (s * 2 + 0) * L::LATE_BYTES), BQ2 * 128, 1024);
+          const uint64_t ddol = make_smem_desc(smem_u32(smem + L::OFF_QL + (s * 2 + 1) * L::LATE_BYTES), BQ2 * 128, 1024);
+          umma_bf16_ts(tmem_dv, tmem_st + buf * BQ2, ddol, idesc_acc, n != 0);
+#pragma unroll
+          for (int k = 1; k < BQ2 / 16; ++k)
+            umma_bf16_ts_c<true>(tmem_dv, tmem_st + buf * BQ2 + (k >> 1) * 32 + (k & 1) * 8,
+                                 smem_desc_advance(ddol, k * 2048), idesc_acc);
+          umma_bf16_ts(tmem_dk, tmem_dpt + buf * BQ2, dql, idesc_acc, n != 0);
+#pragma unroll
+          for (int k = 1; k < BQ2 / 16; ++k)
+            umma_bf16_ts_c<true>(tmem_dk, tmem_dpt + buf * BQ2 + (k >> 1) * 32 + (k & 1) * 8,
+                                 smem_desc_advance(dql, k * 2048), idesc_acc);
+          tc_fence_before();
+          mbar_arrive(&acc_issued[buf]);  // A may now overwrite the S^T buffer of this parity (it enters the pipe later)
+          umma_commit(&ql_empty[s]);
+          if (n == ntot - 1) umma_commit(acc_done);
         }
-        tc_fence_after();
-        // B operands: the [BQ2 x DV] slices of dO / Q (slice channels), MN-major
-        const uint32_t sq_l = smem_u32(smem + L::OFF_QL + (s * 2 + 0) * L::LATE_BYTES);
-        const uint32_t sdo_l = smem_u32(smem + L::OFF_QL + (s * 2 + 1) * L::LATE_BYTES);
-#pragma unroll
-        for (int k = 0; k < BQ2 / 16; ++k)
-          umma_bf16_ts(tmem_dv, tmem_st + buf * BQ2 + (k >> 1) * 32 + (k & 1) * 8,
-                       make_smem_desc(sdo_l + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
-#pragma unroll
-        for (int k = 0; k < BQ2 / 16; ++k)
-          umma_bf16_ts(tmem_dk, tmem_dpt + buf * BQ2 + (k >> 1) * 32 + (k & 1) * 8,
-                       make_smem_desc(sq_l + k * 2048, BQ2 * 128, 1024), idesc_acc, (n | k) != 0);
-        umma_commit(&ql_empty[s]);
-        umma_commit(&acc_free[buf]);
-        if (n == ntot - 1) umma_commit(acc_done);
       }
       if (!ok) atomicCAS(p.status, 0, ERR_WAIT_MISC);
     }
@@ -549,8 +597,24 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const int row = (warp & 3) * 32 + lane;
     const int kv = kv0 + row;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const int* docb = p.doc ? p.doc + static_cast<long long>(b) * p.S : nullptr;
+    // masks: the query rows that may attend to this kv row form the interval [qlo_kv, qhi_kv)
+    const int* docb = (p.doc && !p.q_end) ? p.doc + static_cast<long long>(b) * p.S : nullptr;
     const int dk_doc = (docb && kv < p.S) ? docb[kv] : 0;
+    int qlo_kv, qhi_kv;
+    if (kv >= p.S) {
+      qlo_kv = INT_MAX;
+      qhi_kv = 0;
+    } else {
+      qlo_kv = p.causal ? kv : 0;
+      if (p.q_end) qhi_kv = min(p.S, p.q_end[static_cast<long long>(b) * p.S + kv]);
+      else qhi_kv = p.window >= 0 ? min(p.S, kv + p.window + 1) : p.S;
+    }
+    int w_qlo_max = qlo_kv, w_qhi_min = qhi_kv;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) {
+      w_qlo_max = max(w_qlo_max, __shfl_xor_sync(0xffffffffu, w_qlo_max, sh));
+      w_qhi_min = min(w_qhi_min, __shfl_xor_sync(0xffffffffu, w_qhi_min, sh));
+    }
     bool ok = true;
     for (int n = 0; n < ntot && ok; ++n) {
       const int g = n / ntile, i = ib + n % ntile;
@@ -580,8 +644,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tmem_ld_wait();
       const float4* lse4 = reinterpret_cast<const float4*>(stat + buf * 2 * BQ2 + half * 32);
       const float4* del4 = reinterpret_cast<const float4*>(stat + buf * 2 * BQ2 + BQ2 + half * 32);
-      const bool need_mask = (docb != nullptr) || (kv0 + 128 > p.S) || (p.causal && kv0 + 127 > q0) ||
-                             (p.window >= 0 && (q0 + BQ2 - 1) - kv0 > p.window);
+      const bool need_mask = (docb != nullptr) || q0 < w_qlo_max || q0 + BQ2 > w_qhi_min;
       float pv[32], ds[32];
 #pragma unroll
       for (int j4 = 0; j4 < 8; ++j4) {
@@ -599,8 +662,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int qq = q0 + half * 32 + j;
-          const int dq_doc = (docb && qq < p.S) ? docb[qq] : 0;
-          if (is_masked(p, docb, qq, kv, dq_doc, dk_doc)) {
+          bool bad = (qq < qlo_kv) | (qq >= qhi_kv);
+          if (docb && qq < p.S) bad |= docb[qq] != dk_doc;
+          if (bad) {
             pv[j] = 0.f;
             ds[j] = 0.f;
           }
@@ -710,7 +774,8 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* dout, co
 // delta_ws: fp32 [B,H,S] scratch; dqkv: packed gradient buffer with row pitch g_stride.
 extern "C" int mb_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                            const float* lse, float* delta_ws, void* dqkv, const int* doc, const int* kv_lo_blk,
-                           const int* q_hi_blk, int B, int S, int H, int KV, int hd, long long q_tok_stride,
+                           const int* q_hi_blk, const int* kv_start, const int* q_end, int B, int S, int H, int KV,
+                           int hd, long long q_tok_stride,
                            long long k_tok_stride, long long v_tok_stride, long long g_stride, int causal,
                            int window, float scale, cudaStream_t st) {
   BwdParams p;
@@ -721,6 +786,8 @@ extern "C" int mb_attn_bwd(const void* q, const void* k, const void* v, const vo
   p.doc = doc;
   p.kv_lo_blk = kv_lo_blk;
   p.q_hi_blk = q_hi_blk;
+  p.kv_start = kv_start;
+  p.q_end = q_end;
   p.B = B;
   p.S = S;
   p.H = H;
@@ -731,6 +798,7 @@ extern "C" int mb_attn_bwd(const void* q, const void* k, const void* v, const vo
   p.scale_log2 = scale * LOG2E;
   p.status = mbh::status().dev;
   if (!p.status) return -4;
+  if ((kv_start != nullptr) != (q_end != nullptr) || (kv_start && !causal)) return -3;
   if ((q_tok_stride & 7) || (k_tok_stride & 7) || (v_tok_stride & 7) || (g_stride & 7)) return -3;
   const long long items = static_cast<long long>(B) * S * H;
   attn_delta_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, st>>>(
@@ -814,6 +882,8 @@ extern "C" int mb_attn_bwd_noalloc(const void* q, const void* k, const void* v, 
   p.doc = doc;
   p.kv_lo_blk = kv_lo_blk;
   p.q_hi_blk = q_hi_blk;
+  p.kv_start = nullptr;
+  p.q_end = nullptr;
   p.B = B;
   p.S = S;
   p.H = H;

@@ -274,7 +274,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         int kb0, kb1;
         unit_krange(p, u / num_tiles, kblocks, splits, kb0, kb1);
         const int m0 = mt * 2 * BM + static_cast<int>(cta) * BM;
-        const int n0 = nt * BN + static_cast<int>(cta) * BNH;
+        // gated forward: the even CTA stages 128 gate rows of the fused weight, the odd CTA the matching up rows
+        const int n0 = p.glu_mode == 1 ? nt * BNH + static_cast<int>(cta) * p.glu_F : nt * BN + static_cast<int>(cta) * BNH;
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -371,12 +372,31 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       const int row = mt * 2 * BM + static_cast<int>(cta) * BM + q * 32 + lane;
       const int n0 = nt * BN;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.glu_mode == 1) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        store_acc_chunk(p, r, alpha, row, n0 + c * 32, c_off);
+        for (int c = 0; c < BNH / 32; ++c) {  // columns [0, 128): gate units nt*128 .., columns [128, 256): the same up units
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(taddr + c * 32, rg);
+          tmem_ld_32x32(taddr + BNH + c * 32, ru);
+          tmem_ld_wait();
+          store_glu_fwd_chunk(p, rg, ru, alpha, row, nt * BNH + c * 32);
+        }
+      } else if (p.glu_mode == 2) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          store_glu_bwd_chunk(p, r, alpha, row, n0 + c * 32);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          store_acc_chunk(p, r, alpha, row, n0 + c * 32, c_off);
+        }
       }
       tc_fence_before();
       mbar_arrive_leader(&acc_empty[acc]);
@@ -609,4 +629,73 @@ extern "C" int mb_gemm_bf16_2cta_grouped_contr(const void* A, const void* B, voi
   p.grp_count = num_groups;
   p.grp_c_elems = static_cast<long long>(M) * ldc;
   return launch2<true, true>(A, B, p, lda, ldb, stream);
+}
+
+// Gated linear unit fused into the GEMM epilogue (see GemmParams::glu_mode).
+//  forward : gate_up[M, 2F] (may be null) and act_out[M, F] from x[M, K] and the fused weight w[2F, K]:
+//            act_out = act(x w_gate^T) * (x w_up^T).  F must be a multiple of 128.
+//  backward: d_gate_up[M, 2F] from dy[M, K], the down-projection weight w[K, F] (b_mn layout) and the saved
+//            gate_up: d(act) = dy w, then the activation's derivative.  F must be a multiple of 32.
+extern "C" int mb_gemm_glu_fwd(const void* x, const void* w, void* gate_up, void* act_out, int M, int F, int K,
+                               long long ldx, long long ldw, long long ldgu, long long ldo, int act,
+                               cudaStream_t stream) {
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if ((F % BNH) || (ldx & 7) || (ldw & 7) || (ldgu & 7) || (ldo & 7)) return -3;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(gate_up) & 15) || (reinterpret_cast<uintptr_t>(act_out) & 15))
+    return -3;
+  GemmParams p;
+  p.C = gate_up;
+  p.aux = nullptr;
+  p.M = M;
+  p.N = 2 * F;
+  p.K = K;
+  p.ldc = ldgu;
+  p.ldaux = 0;
+  p.epi = EPI_BF16;
+  p.alpha = 1.f;
+  p.alpha_dev = nullptr;
+  p.beta = 0.f;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  p.splits = 1;
+  p.route_rows = 0;
+  p.glu_mode = 1;
+  p.glu_act = act;
+  p.glu_F = F;
+  p.glu_out = act_out;
+  p.glu_ldo = ldo;
+  return launch2<false, false>(x, w, p, ldx, ldw, stream);
+}
+
+extern "C" int mb_gemm_glu_bwd(const void* dy, const void* w, const void* gate_up, void* d_gate_up, int M, int F,
+                               int K, long long lddy, long long ldw, long long ldgu, long long lddgu, int act,
+                               cudaStream_t stream) {
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if ((F % 32) || (lddy & 7) || (ldw & 7) || (ldgu & 7) || (lddgu & 7)) return -3;
+  if ((reinterpret_cast<uintptr_t>(dy) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(gate_up) & 15) || (reinterpret_cast<uintptr_t>(d_gate_up) & 15))
+    return -3;
+  GemmParams p;
+  p.C = d_gate_up;
+  p.aux = nullptr;
+  p.M = M;
+  p.N = F;
+  p.K = K;
+  p.ldc = lddgu;
+  p.ldaux = 0;
+  p.epi = EPI_BF16;
+  p.alpha = 1.f;
+  p.alpha_dev = nullptr;
+  p.beta = 0.f;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  p.splits = 1;
+  p.route_rows = 0;
+  p.glu_mode = 2;
+  p.glu_act = act;
+  p.glu_F = F;
+  p.glu_in = gate_up;
+  p.glu_ldi = ldgu;
+  return launch2<false, true>(dy, w, p, lddy, ldw, stream);
 }

@@ -48,7 +48,108 @@ struct GemmParams {
   const int* grp_offs = nullptr;
   int grp_count = 0;
   long long grp_c_elems = 0;
+  // Gated-linear-unit epilogues (CTA-pair kernel).
+  //  glu_mode 1 (forward): B is the fused weight [gate rows | up rows] with glu_F rows each and N = 2 glu_F.  A
+  //    tile takes 128 gate rows (even CTA's half of B) and the matching 128 up rows (odd CTA's half), so one
+  //    accumulator row holds gate_j and up_j for 128 values of j: the epilogue stores both (C = [gate | up], bf16)
+  //    and act(gate_j) * up_j into glu_out [M, glu_F] (row pitch glu_ldo).
+  //  glu_mode 2 (backward): the accumulator is d(act) [M, N = glu_F]; the epilogue reads gate_j and up_j from
+  //    glu_in [M, 2 glu_F] (row pitch glu_ldi) and stores d(gate_j) = d * up_j * act'(gate_j) and
+  //    d(up_j) = d * act(gate_j) into C [M, 2 glu_F].
+  int glu_mode = 0;
+  int glu_act = 0;         // 0: tanh-GELU, 1: SiLU
+  int glu_F = 0;
+  void* glu_out = nullptr;
+  long long glu_ldo = 0;
+  const void* glu_in = nullptr;
+  long long glu_ldi = 0;
 };
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// act(g) and act'(g) for the gated units (tanh-GELU with the hardware tanh, SiLU)
+__device__ __forceinline__ void glu_act_and_grad(int act, float g, float& a, float& da) {
+  if (act == 0) {
+    const float k = 0.7978845608028654f;
+    const float inner = k * (g + 0.044715f * g * g * g);
+    const float th = tanh_approx(inner);
+    a = 0.5f * g * (1.f + th);
+    da = 0.5f * (1.f + th) + 0.5f * g * (1.f - th * th) * k * (1.f + 3.f * 0.044715f * g * g);
+  } else {
+    const float sg = 1.f / (1.f + __expf(-g));
+    a = g * sg;
+    da = sg * (1.f + g * (1.f - sg));
+  }
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+// 32 accumulator columns of gate and the matching 32 of up for output row `row`, units j0 .. j0+31:
+// stores [gate | up] into C and act(gate) * up into glu_out.  glu_F is a multiple of 128, so chunks are whole.
+__device__ __forceinline__ void store_glu_fwd_chunk(const GemmParams& p, const uint32_t (&rg)[32],
+                                                    const uint32_t (&ru)[32], float alpha, int row, int j0) {
+  using namespace mb;
+  if (row >= p.M) return;
+  __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
+  __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.glu_out) + static_cast<long long>(row) * p.glu_ldo + j0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float g[8], u[8], o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      g[e] = bf16_round(__uint_as_float(rg[j * 8 + e]) * alpha);  // the activation sees what the backward pass will read
+      u[e] = bf16_round(__uint_as_float(ru[j * 8 + e]) * alpha);
+      float a, da;
+      glu_act_and_grad(p.glu_act, g[e], a, da);
+      o[e] = a * u[e];
+    }
+    uint4 vg, vu, vo;
+    vg.x = pack_bf16(g[0], g[1]); vg.y = pack_bf16(g[2], g[3]); vg.z = pack_bf16(g[4], g[5]); vg.w = pack_bf16(g[6], g[7]);
+    vu.x = pack_bf16(u[0], u[1]); vu.y = pack_bf16(u[2], u[3]); vu.z = pack_bf16(u[4], u[5]); vu.w = pack_bf16(u[6], u[7]);
+    vo.x = pack_bf16(o[0], o[1]); vo.y = pack_bf16(o[2], o[3]); vo.z = pack_bf16(o[4], o[5]); vo.w = pack_bf16(o[6], o[7]);
+    if (p.C) {
+      reinterpret_cast<uint4*>(crow + j0)[j] = vg;
+      reinterpret_cast<uint4*>(crow + p.glu_F + j0)[j] = vu;
+    }
+    reinterpret_cast<uint4*>(orow)[j] = vo;
+  }
+}
+
+// 32 accumulator columns of d(act) for output row `row`, units j0 .. j0+31 -> d(gate), d(up) into C [M, 2 glu_F].
+__device__ __forceinline__ void store_glu_bwd_chunk(const GemmParams& p, const uint32_t (&r)[32], float alpha, int row,
+                                                    int j0) {
+  using namespace mb;
+  if (row >= p.M || j0 >= p.N) return;
+  const __nv_bfloat16* irow = reinterpret_cast<const __nv_bfloat16*>(p.glu_in) + static_cast<long long>(row) * p.glu_ldi;
+  __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint4 g4 = reinterpret_cast<const uint4*>(irow + j0)[j];
+    const uint4 u4 = reinterpret_cast<const uint4*>(irow + p.glu_F + j0)[j];
+    const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* ub = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    float dg[8], du[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 g = __bfloat1622float2(gb[e]), u = __bfloat1622float2(ub[e]);
+      const float d0 = __uint_as_float(r[j * 8 + 2 * e]) * alpha, d1 = __uint_as_float(r[j * 8 + 2 * e + 1]) * alpha;
+      float a, da;
+      glu_act_and_grad(p.glu_act, g.x, a, da);
+      dg[2 * e] = d0 * u.x * da;
+      du[2 * e] = d0 * a;
+      glu_act_and_grad(p.glu_act, g.y, a, da);
+      dg[2 * e + 1] = d1 * u.y * da;
+      du[2 * e + 1] = d1 * a;
+    }
+    uint4 vg, vu;
+    vg.x = pack_bf16(dg[0], dg[1]); vg.y = pack_bf16(dg[2], dg[3]); vg.z = pack_bf16(dg[4], dg[5]); vg.w = pack_bf16(dg[6], dg[7]);
+    vu.x = pack_bf16(du[0], du[1]); vu.y = pack_bf16(du[2], du[3]); vu.z = pack_bf16(du[4], du[5]); vu.w = pack_bf16(du[6], du[7]);
+    reinterpret_cast<uint4*>(crow + j0)[j] = vg;
+    reinterpret_cast<uint4*>(crow + p.glu_F + j0)[j] = vu;
+  }
+}
 
 // group GROUP_M row-tiles together so that concurrently running CTAs share operand tiles in L2
 __device__ __forceinline__ void tile_coords(int t, int tm, int tn, int group_m, int& mt, int& nt) {

@@ -90,9 +90,8 @@ class GemmaMLP(nn.Module):
         self._gate_up = FusedWeight([self.gate_proj, self.up_proj])
 
     def forward(self, x: torch.Tensor, recompute_act: bool = False) -> torch.Tensor:
-        gate_up = ops.linear(x, self._gate_up.get())
-        act = maybe_checkpoint(lambda t: ops.glu(t, "gelu_tanh"), recompute_act, gate_up)
-        return self.down_proj(act)
+        # one autograd node: the gated activation lives in the GEMM epilogues (forward and backward)
+        return ops.glu_mlp(x, self._gate_up.get(), self.down_proj.weight, "gelu_tanh")
 
     def init_weights(self, init_std: float) -> None:
         for lin in (self.gate_proj, self.up_proj, self.down_proj):

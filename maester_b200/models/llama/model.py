@@ -128,7 +128,7 @@ class FeedForward(nn.Module):
             from maester_b200.parallel.fused_tp import ag_linear, linear_rs
             gate_up = ag_linear(x, self._fused().get(), self.tp_fused)
         else:
-            gate_up = ops.linear(x, self._fused().get())
+            return ops.glu_mlp(x, self._fused().get(), self.w2.weight, "silu", residual=residual)
         act = maybe_checkpoint(lambda t: ops.glu(t, "silu"), recompute_act, gate_up)
         if self.tp_fused is not None:
             return linear_rs(act, self.w2.weight, residual, self.tp_fused)

@@ -3,6 +3,7 @@ from maester_b200.ops.functional import (  # noqa: F401
     attention_block,
     embedding,
     glu,
+    glu_mlp,
     kv_block_lower_bounds,
     linear,
     linear_cross_entropy,

@@ -173,6 +173,28 @@ def glu_bwd(gate_up: torch.Tensor, dout: torch.Tensor, act: int) -> torch.Tensor
     return din.view(gate_up.shape)
 
 
+def gemm_glu_fwd(x: torch.Tensor, w_gu: torch.Tensor, act: int):
+    """``gate_up = x @ w_gu.T`` ([M, 2F]) and ``act(gate) * up`` ([M, F]) from one GEMM (CTA-pair kernel)."""
+    M, K = x.shape
+    F = w_gu.shape[0] // 2
+    gate_up = torch.empty(M, 2 * F, device=x.device, dtype=x.dtype)
+    out = torch.empty(M, F, device=x.device, dtype=x.dtype)
+    _ck(_lib.lib().mb_gemm_glu_fwd(x.data_ptr(), w_gu.data_ptr(), gate_up.data_ptr(), out.data_ptr(), M, F, K,
+                                   _rows_pitch(x), _rows_pitch(w_gu), 2 * F, F, int(act), _stream()), "gemm_glu_fwd")
+    return gate_up, out
+
+
+def gemm_glu_bwd(dy: torch.Tensor, w_down: torch.Tensor, gate_up: torch.Tensor, act: int) -> torch.Tensor:
+    """``d[gate | up]`` ([M, 2F]) from ``d(act) = dy @ w_down`` (never stored) and the saved ``gate_up``."""
+    M, D = dy.shape
+    F = w_down.shape[1]
+    d_gu = torch.empty(M, 2 * F, device=dy.device, dtype=dy.dtype)
+    _ck(_lib.lib().mb_gemm_glu_bwd(dy.data_ptr(), w_down.data_ptr(), gate_up.data_ptr(), d_gu.data_ptr(), M, F, D,
+                                   _rows_pitch(dy), _rows_pitch(w_down), _rows_pitch(gate_up), 2 * F, int(act),
+                                   _stream()), "gemm_glu_bwd")
+    return d_gu
+
+
 def embedding_fwd(tokens: torch.Tensor, w: torch.Tensor, scale: float | None) -> torch.Tensor:
     tok = tokens.reshape(-1).to(torch.int64).contiguous()
     D = w.shape[1]
@@ -388,31 +410,40 @@ def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:
     _ck(_lib.lib().mb_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), float(scale), _stream()), "cast")
 
 
+def _plan_ptrs(plan):
+    if plan is None:
+        return None, None, None, None, None
+    return _ptr(plan.doc), _ptr(plan.lo_blk), _ptr(plan.hi_blk), _ptr(plan.kv_start), _ptr(plan.q_end)
+
+
 def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, causal: bool, window: int | None,
-             doc: torch.Tensor | None, kv_lo_blk: torch.Tensor | None):
-    """q: [B,S,H,hd] (last two dims dense, token stride arbitrary); k, v: [B,S,KV,hd]."""
+             plan=None):
+    """q: [B,S,H,hd] (last two dims dense, token stride arbitrary); k, v: [B,S,KV,hd].  ``plan`` is the
+    ``ops.functional.AttnPlan`` of the mask (None: causal / window bounds only)."""
     B, S, H, hd = q.shape
     KV = k.shape[2]
     for t in (q, k, v):
         assert t.stride(3) == 1 and t.stride(2) == hd and t.stride(0) == S * t.stride(1)
     out = torch.empty(B, S, H, hd, device=q.device, dtype=q.dtype)
     lse = torch.empty(B, H, S, device=q.device, dtype=torch.float32)
-    _ck(_lib.lib().mb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), _ptr(doc),
-                               _ptr(kv_lo_blk), B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
+    doc, lo, _, kv_start, _ = _plan_ptrs(plan)
+    _ck(_lib.lib().mb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), doc, lo,
+                               kv_start, B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
                                int(causal), -1 if window is None or window <= 0 else int(window), float(scale),
                                _stream()), "attn_fwd")
     return out, lse
 
 
-def attn_bwd(q, k, v, out, dout, lse, dqkv, scale, causal, window, doc, kv_lo_blk, q_hi_blk=None) -> None:
+def attn_bwd(q, k, v, out, dout, lse, dqkv, scale, causal, window, plan=None) -> None:
     """Fills ``dqkv`` [B*S, (H+2KV)*hd] with the gradients of q, k (post norm/rope) and v."""
     B, S, H, hd = q.shape
     KV = k.shape[2]
     assert out.is_contiguous() and dout.is_contiguous() and dqkv.stride(1) == 1
     delta = torch.empty(B, H, S, device=q.device, dtype=torch.float32)
+    doc, lo, hi, kv_start, q_end = _plan_ptrs(plan)
     _ck(_lib.lib().mb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(),
-                               lse.data_ptr(), delta.data_ptr(), dqkv.data_ptr(), _ptr(doc), _ptr(kv_lo_blk),
-                               _ptr(q_hi_blk), B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
+                               lse.data_ptr(), delta.data_ptr(), dqkv.data_ptr(), doc, lo, hi, kv_start, q_end,
+                               B, S, H, KV, hd, q.stride(1), k.stride(1), v.stride(1),
                                dqkv.stride(0), int(causal), -1 if window is None or window <= 0 else int(window),
                                float(scale), _stream()), "attn_bwd")
 

@@ -136,6 +136,68 @@ def glu(gate_up: torch.Tensor, activation: str) -> torch.Tensor:
     return ref.geglu(gate_up) if activation == "gelu_tanh" else ref.swiglu(gate_up)
 
 
+class _GluMLP(Function):
+    """``down(act(x w_gate^T) * (x w_up^T)) [+ residual]`` with the gated activation fused into the GEMM epilogues.
+
+    Forward: the gate|up projection is one GEMM over the fused weight whose epilogue holds ``gate_j`` and ``up_j`` of
+    the same unit in one accumulator row and writes both ``[gate | up]`` (kept for the backward pass) and the
+    activation.  Backward: the input-gradient GEMM of the down projection produces ``d(act)`` in tensor memory and its
+    epilogue applies the activation's derivative, so ``d(act)`` never exists in global memory and no stand-alone
+    element-wise pass runs in either direction."""
+
+    @staticmethod
+    def forward(ctx, x, w_gu, w_down, residual, act, save_act):
+        C = _C()
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if x2.stride(1) != 1:
+            x2 = x2.contiguous()
+        gate_up, a = C.gemm_glu_fwd(x2, w_gu, act)
+        D = w_down.shape[0]
+        if residual is None:
+            y = C.gemm(a, w_down)
+        else:
+            y = C.gemm(a, w_down, epi=C.EPI_BF16_ADD, aux=residual.reshape(-1, D))
+        ctx.save_for_backward(x2, w_gu, w_down, gate_up, a if save_act else None)
+        ctx.act, ctx.x_shape, ctx.has_res = act, x.shape, residual is not None
+        return y.view(*x.shape[:-1], D)
+
+    @staticmethod
+    def backward(ctx, dy):
+        C = _C()
+        x2, w_gu, w_down, gate_up, a = ctx.saved_tensors
+        D = w_down.shape[0]
+        dy2 = dy.reshape(-1, D)
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        if a is None:
+            a = C.glu_fwd(gate_up, ctx.act)
+        d_gu = C.gemm_glu_bwd(dy2, w_down, gate_up, ctx.act)
+        dw_down = None
+        if ctx.needs_input_grad[2]:
+            dw_down = _acc_or_return(w_down, lambda buf, acc: C.gemm(dy2, a, a_mn=True, b_mn=True, out=buf,
+                                                                      epi=C.EPI_F32_ACC if acc else C.EPI_F32))
+        del a
+        dx = C.gemm(d_gu, w_gu, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw_gu = None
+        if ctx.needs_input_grad[1]:
+            dw_gu = _acc_or_return(w_gu, lambda buf, acc: C.gemm(d_gu, x2, a_mn=True, b_mn=True, out=buf,
+                                                                  epi=C.EPI_F32_ACC if acc else C.EPI_F32))
+        return dx, dw_gu, dw_down, (dy if ctx.has_res else None), None, None
+
+
+def glu_mlp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str,
+            residual: torch.Tensor | None = None, save_act: bool = True) -> torch.Tensor:
+    """Gated MLP ``down(act(gate) * up) [+ residual]`` with ``w_gate_up = [w_gate; w_up]`` ([2F, K]) and
+    ``w_down`` [D, F].  ``save_act=False`` recomputes the activation in the backward pass instead of keeping it."""
+    F2 = w_gate_up.shape[0]
+    if use_native(x, w_gate_up) and (F2 // 2) % 128 == 0 and w_gate_up.is_contiguous() and w_down.is_contiguous() \
+            and x.shape[-1] % 8 == 0 and _C().GEMM_TWO_CTA:
+        return _GluMLP.apply(x, w_gate_up, w_down, residual, _ACT[activation], save_act)
+    act = glu(linear(x, w_gate_up), activation)
+    return linear(act, w_down, residual)
+
+
 # --------------------------------------------------------------------------- embedding
 class _Embedding(Function):
     @staticmethod
@@ -160,6 +222,26 @@ def embedding(tokens: torch.Tensor, w: torch.Tensor, scale: float | None = None)
 
 
 # --------------------------------------------------------------------------- attention
+def _run_starts(doc: torch.Tensor) -> torch.Tensor:
+    """[B, S] int32: index of the first token of the contiguous run of equal ids that contains each token."""
+    S = doc.shape[1]
+    idx = torch.arange(S, device=doc.device, dtype=torch.int32)
+    change = torch.ones_like(doc, dtype=torch.bool)
+    change[:, 1:] = doc[:, 1:] != doc[:, :-1]
+    return torch.where(change, idx[None], torch.zeros_like(doc)).cummax(dim=1).values.to(torch.int32)
+
+
+def _run_ends(doc: torch.Tensor) -> torch.Tensor:
+    """[B, S] int32: one past the last token of the run that contains each token."""
+    S = doc.shape[1]
+    idx = torch.arange(S, device=doc.device, dtype=torch.int32)
+    change = torch.zeros_like(doc, dtype=torch.bool)
+    change[:, 1:] = doc[:, 1:] != doc[:, :-1]
+    nxt = torch.where(change, idx[None], torch.full_like(doc, S))
+    suffix = nxt.flip(1).cummin(dim=1).values.flip(1)      # smallest run start at or after each position
+    return torch.cat([suffix[:, 1:], torch.full_like(suffix[:, :1], S)], dim=1).to(torch.int32)
+
+
 def kv_block_lower_bounds(S: int, block_q: int, window: int | None, doc: torch.Tensor | None, device,
                           batch: int = 1) -> torch.Tensor | None:
     """Per (batch, query block) lowest kv index any row of the block may attend to.
@@ -168,49 +250,85 @@ def kv_block_lower_bounds(S: int, block_q: int, window: int | None, doc: torch.T
     ``max(start of its document, q - window)`` and the block takes the minimum over its rows.
     No host synchronisation.
     """
-    if doc is None and (window is None or window <= 0):
-        return None
-    idx = torch.arange(S, device=device, dtype=torch.int32)
-    if doc is not None:
-        d = doc.to(torch.int32)
-        change = torch.ones_like(d, dtype=torch.bool)
-        change[:, 1:] = d[:, 1:] != d[:, :-1]
-        start = torch.where(change, idx[None], torch.zeros_like(d)).cummax(dim=1).values
-    else:
-        start = torch.zeros(batch, S, device=device, dtype=torch.int32)
-    if window is not None and window > 0:
-        start = torch.maximum(start, (idx - window).clamp_min(0)[None].expand_as(start))
-    nqb = (S + block_q - 1) // block_q
-    pad = nqb * block_q - S
-    if pad:
-        start = torch.nn.functional.pad(start, (0, pad), value=S)
-    return start.view(start.shape[0], nqb, block_q).amin(dim=2).to(torch.int32).contiguous()
+    plan = attention_plan(S, window, doc, device, batch=batch, block=block_q)
+    return plan.lo_blk
 
 
 def q_block_upper_bounds(S: int, block_kv: int, window: int | None, doc: torch.Tensor | None, device,
                          batch: int = 1) -> torch.Tensor | None:
     """Per (batch, kv block) exclusive upper bound on the query index that may attend to the block:
     ``min(end of the kv row's document, kv + window + 1)`` maximised over the block's rows."""
-    if doc is None and (window is None or window <= 0):
-        return None
+    plan = attention_plan(S, window, doc, device, batch=batch, block=block_kv)
+    return plan.hi_blk
+
+
+class AttnPlan:
+    """Mask description for the attention kernels, built once per (document ids, window) and shared by every
+    layer of a step.  With causal attention over packed documents (contiguous runs of equal ids) the mask
+    ``kv <= q  and  q - kv <= window  and  doc[q] == doc[kv]`` is one interval per row:
+
+    * ``kv_start[b, q]``: lowest admissible kv index of query row q = max(start of its document, q - window);
+    * ``q_end[b, kv]``: one past the highest query row that may attend to kv = min(end of its document,
+      kv + window + 1);
+    * ``lo_blk`` / ``hi_blk``: the same bounds per block of 128 rows (minimum / maximum over the block), used to
+      skip whole kv / query blocks.
+
+    ``doc`` is kept only for non-causal attention, where the kernels compare ids element by element.
+    All fields are None when there is neither a window nor document ids."""
+
+    __slots__ = ("kv_start", "q_end", "lo_blk", "hi_blk", "doc")
+
+    def __init__(self, kv_start=None, q_end=None, lo_blk=None, hi_blk=None, doc=None):
+        self.kv_start, self.q_end, self.lo_blk, self.hi_blk, self.doc = kv_start, q_end, lo_blk, hi_blk, doc
+
+
+def attention_plan(S: int, window: int | None, doc: torch.Tensor | None, device, batch: int = 1,
+                   causal: bool = True, block: int = 128) -> AttnPlan:
+    """Build the mask arrays on the device (a dozen small kernels, no host synchronisation)."""
+    has_window = window is not None and window > 0
+    if doc is None and not has_window:
+        return AttnPlan()
     idx = torch.arange(S, device=device, dtype=torch.int32)
     if doc is not None:
-        d = doc.to(torch.int32)
-        change = torch.zeros_like(d, dtype=torch.bool)
-        change[:, 1:] = d[:, 1:] != d[:, :-1]
-        nxt = torch.where(change, idx[None], torch.full_like(d, S))
-        # end[kv] = smallest run start strictly after kv
-        suffix = nxt.flip(1).cummin(dim=1).values.flip(1)
-        end = torch.cat([suffix[:, 1:], torch.full_like(suffix[:, :1], S)], dim=1)
+        d = doc.to(device=device, dtype=torch.int32)
+        start, end = _run_starts(d), _run_ends(d)
     else:
+        start = torch.zeros(batch, S, device=device, dtype=torch.int32)
         end = torch.full((batch, S), S, device=device, dtype=torch.int32)
-    if window is not None and window > 0:
+    if has_window:
+        start = torch.maximum(start, (idx - window).clamp_min(0)[None].expand_as(start))
         end = torch.minimum(end, (idx + window + 1).clamp_max(S)[None].expand_as(end))
-    nkb = (S + block_kv - 1) // block_kv
-    pad = nkb * block_kv - S
-    if pad:
-        end = torch.nn.functional.pad(end, (0, pad), value=0)
-    return end.view(end.shape[0], nkb, block_kv).amax(dim=2).to(torch.int32).contiguous()
+    nb = (S + block - 1) // block
+    pad = nb * block - S
+    sp = torch.nn.functional.pad(start, (0, pad), value=S) if pad else start
+    ep = torch.nn.functional.pad(end, (0, pad), value=0) if pad else end
+    lo = sp.view(sp.shape[0], nb, block).amin(dim=2).to(torch.int32).contiguous()
+    hi = ep.view(ep.shape[0], nb, block).amax(dim=2).to(torch.int32).contiguous()
+    if causal:
+        return AttnPlan(start.contiguous(), end.contiguous(), lo, hi, None)
+    # without the causal bound a row may also look ahead inside its document: the interval arrays above do not
+    # describe that, so the kernels fall back to comparing ids (block bounds stay valid as lower / upper bounds
+    # only for the causal part, so they are dropped too)
+    return AttnPlan(None, None, None, None, None if doc is None else doc.to(device=device, dtype=torch.int32).contiguous())
+
+
+_PLAN_CACHE: dict = {}
+
+
+def cached_attention_plan(S: int, window: int | None, doc: torch.Tensor | None, device, batch: int,
+                          causal: bool) -> AttnPlan:
+    """``attention_plan`` memoised on the identity and version of the document-id tensor: all layers of a step
+    (and the backward pass) share two plans, one for the windowed and one for the global layers."""
+    key = (None if doc is None else (doc.data_ptr(), doc._version, tuple(doc.shape)), S, window if window else 0,
+           batch, bool(causal), str(device))
+    hit = _PLAN_CACHE.get(key)
+    if hit is not None and (doc is None or hit[0] is doc):
+        return hit[1]
+    plan = attention_plan(S, window, doc, device, batch=batch, causal=causal)
+    if len(_PLAN_CACHE) >= 8:
+        _PLAN_CACHE.pop(next(iter(_PLAN_CACHE)))
+    _PLAN_CACHE[key] = (doc, plan)  # holding ``doc`` keeps its address from being reused by another tensor
+    return plan
 
 
 def rope_table(inv_freq: torch.Tensor, max_pos: int, attn_factor: float = 1.0) -> torch.Tensor:
@@ -236,17 +354,17 @@ class _AttnBlock(Function):
         q = qk[:, : H * hd].view(B, S, H, hd)
         k = qk[:, H * hd:(H + KV) * hd].view(B, S, KV, hd)
         v = qkv2[:, (H + KV) * hd:].view(B, S, KV, hd)
-        doc32 = doc.to(torch.int32).contiguous() if doc is not None else None
-        lo = kv_block_lower_bounds(S, 128, window, doc32, qkv.device, batch=B)
-        out, lse = C.attn_fwd(q, k, v, scale, causal, window, doc32, lo)
-        ctx.save_for_backward(qkv2, qk if need_qk else None, qw, kw, pos32, cs, doc32, lo, out, lse)
+        plan = cached_attention_plan(S, window, doc, qkv.device, B, causal)
+        out, lse = C.attn_fwd(q, k, v, scale, causal, window, plan)
+        ctx.save_for_backward(qkv2, qk if need_qk else None, qw, kw, pos32, cs, out, lse)
+        ctx.plan = plan
         ctx.cfg = (B, S, H, KV, hd, layout, eps, unit_offset, scale, causal, window, need_qk)
         return out.view(B, S, H * hd)
 
     @staticmethod
     def backward(ctx, dout):
         C = _C()
-        qkv2, qk, qw, kw, pos32, cs, doc32, lo, out, lse = ctx.saved_tensors
+        qkv2, qk, qw, kw, pos32, cs, out, lse = ctx.saved_tensors
         B, S, H, KV, hd, layout, eps, unit_offset, scale, causal, window, need_qk = ctx.cfg
         if qk is None:
             qk = qkv2
@@ -254,9 +372,7 @@ class _AttnBlock(Function):
         k = qk[:, H * hd:(H + KV) * hd].view(B, S, KV, hd)
         v = qkv2[:, (H + KV) * hd:].view(B, S, KV, hd)
         dqkv = torch.empty(B * S, (H + 2 * KV) * hd, device=dout.device, dtype=dout.dtype)
-        hi = q_block_upper_bounds(S, 128, window, doc32, dout.device, batch=B)
-        C.attn_bwd(q, k, v, out, dout.reshape(B, S, H, hd).contiguous(), lse, dqkv, scale, causal, window, doc32,
-                   lo, hi)
+        C.attn_bwd(q, k, v, out, dout.reshape(B, S, H, hd).contiguous(), lse, dqkv, scale, causal, window, ctx.plan)
         dqw = dkw = None
         if need_qk:
             mq = getattr(qw, "main_grad", None) if qw is not None else None

@@ -144,6 +144,38 @@ def test_glu(act):
     assert _rel(C.glu_bwd(x, d, act), xf.grad) < 5e-3
 
 
+@pytest.mark.parametrize("act,name", [(0, "gelu_tanh"), (1, "silu")])
+@pytest.mark.parametrize("M,K,F,D", [(256, 128, 128, 64), (1000, 320, 384, 136), (2048, 2560, 1024, 2560)])
+def test_glu_mlp_fused_epilogues(act, name, M, K, F, D):
+    """Gate|up GEMM with the activation in its epilogue, and the down projection's input-gradient GEMM with the
+    activation's derivative in its epilogue, against the fp32 definition (values and all gradients)."""
+    from maester_b200.ops import cuda as C
+    from maester_b200.ops.functional import glu_mlp
+    torch.manual_seed(4)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w_gu = (torch.randn(2 * F, K, device="cuda") * K ** -0.5).to(torch.bfloat16).requires_grad_(True)
+    w_d = (torch.randn(D, F, device="cuda") * F ** -0.5).to(torch.bfloat16).requires_grad_(True)
+    res = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    gate_up, a = C.gemm_glu_fwd(x.detach(), w_gu.detach(), act)
+    gu_ref = x.detach().float() @ w_gu.detach().float().T
+    assert _rel(gate_up, gu_ref) < 5e-3
+    g, u = gate_up.float().chunk(2, dim=-1)
+    a_ref = (torch.nn.functional.gelu(g, approximate="tanh") if act == 0 else torch.nn.functional.silu(g)) * u
+    assert _rel(a, a_ref) < 6e-3
+    assert (a.float() - a_ref).abs().max().item() < 2e-2 * a_ref.abs().max().item() + 1e-2
+    y = glu_mlp(x, w_gu, w_d, name, residual=res)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xf, wf, df = (t.detach().float().requires_grad_(True) for t in (x, w_gu, w_d))
+    gf, uf = (xf @ wf.T).chunk(2, dim=-1)
+    af = (torch.nn.functional.gelu(gf, approximate="tanh") if act == 0 else torch.nn.functional.silu(gf)) * uf
+    yf = af @ df.T + res.float()
+    yf.backward(dy.float())
+    assert _rel(y, yf) < 8e-3
+    for name_, got, want in (("dx", x.grad, xf.grad), ("dw_gu", w_gu.grad, wf.grad), ("dw_down", w_d.grad, df.grad)):
+        assert _rel(got, want) < 1.5e-2, (name_, _rel(got, want))
+
+
 def test_embedding():
     from maester_b200.ops import cuda as C
     w = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16)
@@ -202,7 +234,7 @@ def test_adamw_flat():
 
 def _attn_case(B, S, H, KV, hd, causal, window, docs):
     from maester_b200.ops import cuda as C
-    from maester_b200.ops.functional import kv_block_lower_bounds
+    from maester_b200.ops.functional import attention_plan
     torch.manual_seed(2)
     qkv = torch.randn(B, S, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
     q = qkv[..., : H * hd].view(B, S, H, hd)
@@ -212,20 +244,22 @@ def _attn_case(B, S, H, KV, hd, causal, window, docs):
     if docs:
         doc = torch.zeros(B, S, dtype=torch.int32, device="cuda")
         for b in range(B):
-            cuts = sorted(torch.randint(1, S, (3,)).tolist())
+            cuts = sorted(torch.randint(1, max(2, S), (3,)).tolist())
             for c in cuts:
                 doc[b, c:] += 1
     scale = hd ** -0.5
-    lo = kv_block_lower_bounds(S, 128, window, doc, device="cuda", batch=B)
-    out, lse = C.attn_fwd(q, k, v, scale, causal, window, doc, lo)
+    plan = attention_plan(S, window, doc, "cuda", batch=B, causal=causal)
+    out, lse = C.attn_fwd(q, k, v, scale, causal, window, plan)
     C.check_status()
     want, wlse = ref.attention(q, k, v, scale, causal, window, doc, return_lse=True)
     assert _rel(out, want) < 1e-2, _rel(out, want)
+    assert (out.float() - want.float()).abs().max().item() < 6e-2  # no wrong row hides in a norm
     assert (lse - wlse).abs().max().item() < 2e-2
 
 
 @pytest.mark.parametrize("hd", [64, 128, 256])
-@pytest.mark.parametrize("causal,window,docs", [(True, None, False), (True, 100, False), (True, None, True), (True, 64, True), (False, None, False)])
+@pytest.mark.parametrize("causal,window,docs", [(True, None, False), (True, 100, False), (True, None, True), (True, 64, True), (False, None, False),
+                                                (False, None, True)])
 def test_attention_fwd(hd, causal, window, docs):
     _attn_case(2, 384, 4, 2, hd, causal, window, docs)
 
@@ -233,6 +267,64 @@ def test_attention_fwd(hd, causal, window, docs):
 def test_attention_fwd_ragged_len():
     _attn_case(1, 200, 2, 1, 128, True, None, False)
     _attn_case(1, 333, 2, 2, 256, True, 50, True)
+    _attn_case(1, 64, 2, 2, 256, True, None, False)      # a single kv block: the second softmax set stays idle
+    _attn_case(1, 1, 2, 1, 128, True, None, True)        # one token
+    _attn_case(2, 1100, 4, 2, 256, True, 300, True)      # many blocks, window wider than a document
+
+
+def _packed_docs(B, S, mean, seed):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    doc = torch.zeros(B, S, dtype=torch.int32)
+    for b in range(B):
+        i = d = 0
+        while i < S:
+            j = min(S, i + max(1, int(rng.geometric(1.0 / mean))))
+            doc[b, i:j] = d
+            i, d = j, d + 1
+    return doc.cuda()
+
+
+@pytest.mark.parametrize("window", [None, 1024])
+def test_attention_benchmark_shape_fwd_bwd(window):
+    """The shape of the headline benchmark (sequence 8192, 8 query / 4 kv heads of 256, window 1024 or global,
+    geometric documents) against the fp32 definition, element by element: a wrong row or a mask slip at a tile
+    boundary of a long sequence cannot hide in a norm.  The oracle runs one head group at a time to bound memory."""
+    from maester_b200.ops import cuda as C
+    from maester_b200.ops.functional import attention_plan
+    B, S, H, KV, hd = 1, 8192, 8, 4, 256
+    torch.manual_seed(7)
+    doc = _packed_docs(B, S, 700.0, 3)
+    qkv = (torch.randn(B, S, (H + 2 * KV) * hd, device="cuda") * 0.7).to(torch.bfloat16)
+    q = qkv[..., : H * hd].view(B, S, H, hd)
+    k = qkv[..., H * hd:(H + KV) * hd].view(B, S, KV, hd)
+    v = qkv[..., (H + KV) * hd:].view(B, S, KV, hd)
+    scale = hd ** -0.5
+    plan = attention_plan(S, window, doc, "cuda", batch=B)
+    out, lse = C.attn_fwd(q, k, v, scale, True, window, plan)
+    dout = (torch.randn_like(out) * 0.5)
+    dqkv = torch.zeros(B * S, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
+    C.attn_bwd(q, k, v, out, dout, lse, dqkv, scale, True, window, plan)
+    C.check_status()
+    G = H // KV
+    for g in range(KV):  # oracle per kv head (its G query heads), fp32, dense mask
+        qf = q[:, :, g * G:(g + 1) * G].float().detach().requires_grad_(True)
+        kf = k[:, :, g:g + 1].float().detach().requires_grad_(True)
+        vf = v[:, :, g:g + 1].float().detach().requires_grad_(True)
+        want, wlse = ref.attention(qf, kf, vf, scale, True, window, doc, return_lse=True)
+        want.backward(dout[:, :, g * G:(g + 1) * G].float())
+        got = out[:, :, g * G:(g + 1) * G].float()
+        assert (got - want).abs().max().item() < 4e-2, (g, (got - want).abs().max().item())
+        assert _rel(got, want) < 1e-2
+        assert (lse[:, g * G:(g + 1) * G] - wlse).abs().max().item() < 2e-2
+        d = dqkv.view(B, S, -1).float()
+        dq = d[..., g * G * hd:(g + 1) * G * hd].view(B, S, G, hd)
+        dk = d[..., (H + g) * hd:(H + g + 1) * hd].view(B, S, 1, hd)
+        dv = d[..., (H + KV + g) * hd:(H + KV + g + 1) * hd].view(B, S, 1, hd)
+        for name, a, w in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+            assert _rel(a, w) < 2e-2, (name, g, _rel(a, w))
+            assert (a - w).abs().max().item() < 0.05 * w.abs().max().item() + 2e-2, (name, g)
+        del qf, kf, vf, want
 
 
 def _attn_bwd_case(B, S, H, KV, hd, causal, window, docs):

@@ -50,11 +50,13 @@ def _case(fn, seed, B, S, H, KV, hd, window):
     scale = hd ** -0.5
     lo = kv_block_lower_bounds(S, 128, window, doc, "cuda", batch=B)
     hi = q_block_upper_bounds(S, 128, window, doc, "cuda", batch=B)
-    out, lse = C.attn_fwd(q, k, v, scale, True, window, doc, lo)
+    from maester_b200.ops.functional import attention_plan
+    plan = attention_plan(S, window, doc, "cuda", batch=B)
+    out, lse = C.attn_fwd(q, k, v, scale, True, window, plan)
     dout = torch.randn_like(out)
 
     want = torch.zeros(B * S, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
-    C.attn_bwd(q, k, v, out, dout, lse, want, scale, True, window, doc, lo, hi)
+    C.attn_bwd(q, k, v, out, dout, lse, want, scale, True, window, plan)
 
     got = torch.zeros_like(want)
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
