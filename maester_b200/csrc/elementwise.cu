@@ -1175,6 +1175,59 @@ extern "C" int mb_adamw(float* p, float* g, float* m, float* v, void* lp, const 
   return mbh::check_launch("adamw");
 }
 
+// ------------------------------------------------------------------ multi-tensor squared norms
+// One launch for every tensor of a flat fp32 buffer: out[t] += sum of squares of tensor t's elements (and, when
+// `scale` is given, the buffer is multiplied by *scale in the same pass, which is the clipping step).  Work is
+// described by the chunk table of the optimizer ({offset, length, tensor}); each block reduces one chunk at a time
+// and adds one value per chunk to its tensor's slot.  Replaces a foreach-norm (one reduction kernel per tensor
+// plus a stack) in gradient clipping and in the weight-scale monitor.
+__global__ void __launch_bounds__(256) multi_sqnorm_kernel(float* __restrict__ x, const AdamChunk* __restrict__ chunks,
+                                                          int nchunks, float* __restrict__ out,
+                                                          const float* __restrict__ scale) {
+  __shared__ float red[8];
+  const float sc = scale ? *scale : 1.f;
+  for (int ci = blockIdx.x; ci < nchunks; ci += gridDim.x) {
+    const AdamChunk ch = chunks[ci];
+    float* base = x + ch.offset;
+    float acc = 0.f;
+    const int n4 = ((reinterpret_cast<uintptr_t>(base) & 15) == 0) ? (ch.len >> 2) : 0;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      float4 v = reinterpret_cast<float4*>(base)[i];
+      if (out) acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      if (scale) {
+        v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
+        reinterpret_cast<float4*>(base)[i] = v;
+      }
+    }
+    for (int i = n4 * 4 + threadIdx.x; i < ch.len; i += blockDim.x) {
+      const float v = base[i];
+      if (out) acc += v * v;
+      if (scale) base[i] = v * sc;
+    }
+    if (out) {
+      acc = warp_sum(acc);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+        t = warp_sum(t);
+        if (threadIdx.x == 0) atomicAdd(out + ch.tensor, t);
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// x: flat fp32 buffer; chunks as for mb_adamw; out: [n_tensors] fp32 accumulators (may be null: scale only);
+// scale: device scalar the buffer is multiplied by (may be null: norms only).
+extern "C" int mb_multi_sqnorm(float* x, const void* chunks, int nchunks, float* out, const float* scale,
+                               cudaStream_t st) {
+  if (nchunks <= 0) return 0;
+  const int blocks = nchunks < mbh::sm_count() * 8 ? nchunks : mbh::sm_count() * 8;
+  multi_sqnorm_kernel<<<blocks, 256, 0, st>>>(x, (const AdamChunk*)chunks, nchunks, out, scale);
+  return mbh::check_launch("multi_sqnorm");
+}
+
 extern "C" int mb_cast_f32_bf16(const float* x, void* y, long long n, float scale, cudaStream_t st) {
   cast_f32_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, (__nv_bfloat16*)y, n, scale);
   return mbh::check_launch("cast_f32_bf16");

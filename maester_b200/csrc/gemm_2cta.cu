@@ -216,7 +216,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   const uint32_t cta = cluster_ctarank();        // 0 = even CTA (issues the MMAs), 1 = partner
   const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
   const int tm = (p.M + 2 * BM - 1) / (2 * BM), tn = (p.N + BN - 1) / BN;
-  const int num_tiles = tm * tn;
+  const int num_tiles = p.syrk ? tm * (tm + 1) / 2 : tm * tn;  // symmetric update: tiles on and below the diagonal
   const int kblocks = (p.K + BK - 1) / BK;
   // work unit u = (tile u % num_tiles, k-range u / num_tiles): all tiles' first ranges run before any
   // second range, so partial sums of one tile rarely meet in the reduction atomics
@@ -260,7 +260,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = true;
       for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
         int mt, nt;
-        tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
+        if (p.syrk) tri_coords(u % num_tiles, mt, nt);
+        else tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
         mt = (mt + mt_rot) % tm;
         if (copiers > 0 && mt / (tm / p.ag_world) != p.ag_rank) {
           // rows of another rank: every copying CTA has to have delivered its share of this tile
@@ -353,7 +354,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     long long c_off = 0;  // per-unit output base for grouped weight gradients
     for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
       int mt, nt;
-      tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
+      if (p.syrk) tri_coords(u % num_tiles, mt, nt);
+      else tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
       mt = (mt + mt_rot) % tm;
       if (p.grp_offs) {
         int kb0, kb1;
@@ -396,6 +398,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
           store_acc_chunk(p, r, alpha, row, n0 + c * 32, c_off);
+          if (p.syrk && nt < mt) store_acc_chunk_mirrored(p, r, alpha, row, n0 + c * 32);
         }
       }
       tc_fence_before();
@@ -440,7 +443,8 @@ int launch2(const void* A, const void* B, const GemmParams& p, long long lda, lo
   GemmParams pp = p;
   pp.group_m = choose_group_m(p.M, p.N, p.K);
   MB_SET_MAX_SMEM_ONCE((gemm_bf16_2cta_kernel<A_MN, B_MN>), SMEM_BYTES);
-  const int tiles = ((p.M + 2 * BM - 1) / (2 * BM)) * ((p.N + BN - 1) / BN) *
+  const int tm_h = (p.M + 2 * BM - 1) / (2 * BM);
+  const int tiles = (p.syrk ? tm_h * (tm_h + 1) / 2 : tm_h * ((p.N + BN - 1) / BN)) *
                     (p.grp_offs ? p.grp_count : (p.splits > 1 ? p.splits : 1));
   const int cop = p.ag_world > 1 ? p.ag_copiers : 0;  // pairs that copy instead of computing (fused all-gather)
   const int max_pairs = mbh::sm_count() / 2 - cop;    // every CTA of the grid is resident: waiting on one another is safe
@@ -698,4 +702,32 @@ extern "C" int mb_gemm_glu_bwd(const void* dy, const void* w, const void* gate_u
   p.glu_in = gate_up;
   p.glu_ldi = ldgu;
   return launch2<false, true>(dy, w, p, lddy, ldw, stream);
+}
+
+// Symmetric rank-k update on CTA pairs: C[M, M] = alpha * A A^T (+ beta * aux), A: [M, K] row-major bf16, C and aux
+// bf16.  Only the 256x256 tiles on and below the diagonal are computed (about half of the FLOPs of the full product);
+// tiles below the diagonal are stored twice, once transposed.  The reference does the same with its Triton kernel
+// (maester/optimizers/muon_/syrk.py:9-125).
+extern "C" int mb_syrk_bf16(const void* A, void* C, const void* aux, int M, int K, long long lda, long long ldc,
+                            long long ldaux, float alpha, float beta, cudaStream_t stream) {
+  if (M <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (reinterpret_cast<uintptr_t>(A) & 15)) return -3;
+  GemmParams p;
+  p.C = C;
+  p.aux = aux;
+  p.M = M;
+  p.N = M;
+  p.K = K;
+  p.ldc = ldc;
+  p.ldaux = ldaux;
+  p.epi = aux ? EPI_BF16_ADD : EPI_BF16;
+  p.alpha = alpha;
+  p.alpha_dev = nullptr;
+  p.beta = beta;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  p.splits = 1;
+  p.route_rows = 0;
+  p.syrk = 1;
+  return launch2<false, false>(A, A, p, lda, lda, stream);
 }

@@ -56,6 +56,9 @@ struct GemmParams {
   //  glu_mode 2 (backward): the accumulator is d(act) [M, N = glu_F]; the epilogue reads gate_j and up_j from
   //    glu_in [M, 2 glu_F] (row pitch glu_ldi) and stores d(gate_j) = d * up_j * act'(gate_j) and
   //    d(up_j) = d * act(gate_j) into C [M, 2 glu_F].
+  // Symmetric rank-k update (C = alpha * A A^T [+ beta * aux], M == N, bf16 out): only the tiles on and below the
+  // diagonal are computed; every tile below the diagonal is also stored transposed into its mirror position.
+  int syrk = 0;
   int glu_mode = 0;
   int glu_act = 0;         // 0: tanh-GELU, 1: SiLU
   int glu_F = 0;
@@ -160,6 +163,33 @@ __device__ __forceinline__ void tile_coords(int t, int tm, int tn, int group_m, 
   const int r = t - g * group_size;
   mt = first_m + r % gm;
   nt = r / gm;
+}
+
+// Lower-triangular tile enumeration: t in [0, T (T + 1) / 2) -> (mt, nt) with nt <= mt, row by row.
+__device__ __forceinline__ void tri_coords(int t, int& mt, int& nt) {
+  int m = static_cast<int>((sqrtf(8.f * static_cast<float>(t) + 1.f) - 1.f) * 0.5f);
+  while ((m + 1) * (m + 2) / 2 <= t) ++m;   // guard the float estimate
+  while (m * (m + 1) / 2 > t) --m;
+  mt = m;
+  nt = t - m * (m + 1) / 2;
+}
+
+// Mirror of store_acc_chunk for the symmetric update: the 32 values of row `row`, columns [col0, col0+32), also go
+// to C[col0 + i][row].  Across a warp the 32 rows are consecutive, so every store instruction writes 64 contiguous bytes.
+__device__ __forceinline__ void store_acc_chunk_mirrored(const GemmParams& p, const uint32_t (&r)[32], float alpha,
+                                                         int row, int col0) {
+  if (row >= p.M) return;
+  __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C);
+  const __nv_bfloat16* aux = reinterpret_cast<const __nv_bfloat16*>(p.aux);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int col = col0 + i;
+    if (col >= p.N) break;
+    float v = __uint_as_float(r[i]) * alpha;
+    // the mirrored element takes the aux value of its own position, so a non-symmetric aux stays exact
+    if (p.epi == EPI_BF16_ADD) v += p.beta * __bfloat162float(aux[static_cast<long long>(col) * p.ldaux + row]);
+    c[static_cast<long long>(col) * p.ldc + row] = __float2bfloat16(v);
+  }
 }
 
 // Store 32 consecutive accumulator columns [col0, col0+32) of output row `row`.

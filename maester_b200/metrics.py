@@ -137,6 +137,24 @@ class WeightScaleMonitor:
         self.step += 1
         if self.step % self.log_freq != 0:
             return None
+        sharded = getattr(self.model, "_sharded", None)
+        if sharded is not None:
+            # one multi-tensor launch over the flat master shards, then the all-reduces of one small vector
+            slots = sharded._slot_list()
+            keep = [i for i, sl in enumerate(slots) if sl.master.requires_grad and not any(s in sl.fqn for s in self.ignored)]
+            if not keep:
+                return {}
+            sq = sharded.global_sqnorms("master")
+            # expert tensors: this rank's experts only (the norm was summed over the ranks holding the same experts)
+            full = torch.tensor([max(1, math.prod(slots[i].global_shape) // (sharded.ep_size if slots[i].dom == 1 else 1))
+                                 for i in keep], device=sq.device, dtype=torch.float32)
+            rms = (sq[torch.tensor(keep, device=sq.device)] / full).sqrt().tolist()
+            stats = {}
+            for i, r in zip(keep, rms):
+                g = clean_param_name(slots[i].fqn)
+                self.weight_stats[g].append(r)
+                stats[f"{g}/weight_rms"] = r
+            return stats
         named = [(n, p) for n, p in self._named() if p.numel() > 0]
         if not named:
             return {}

@@ -141,6 +141,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_moe_rows_gather": [_P, _P, _P, _I, _L, _I, _P, _P],
         "mb_moe_rows_combine": [_P, _P, _P, _I, _I, _I, _L, _P, _P],
         "mb_moe_slot_dot": [_P, _P, _P, _I, _I, _I, _L, _P, _P],
+        "mb_syrk_bf16": [_P, _P, _P, _I, _I, _L, _L, _L, _F, _F, _P],
         "mb_gemm_glu_fwd": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _P],
         "mb_gemm_glu_bwd": [_P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _I, _P],
         "mb_glu_fwd": [_P, _P, _L, _I, _I, _L, _P],
@@ -149,6 +150,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_embedding_bwd": [_P, _P, _P, _L, _I, _F, _P],
         "mb_ce_fwd_bwd": [_P, _P, _P, _P, _F, _L, _I, _L, _I, _I, _P, _P],
         "mb_adamw": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _I, _P],
+        "mb_multi_sqnorm": [_P, _P, _I, _P, _P, _P],
         "mb_cast_f32_bf16": [_P, _P, _L, _F, _P],
         "mb_attn_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _I, _F, _P],
         "mb_attn_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,

@@ -173,6 +173,16 @@ def glu_bwd(gate_up: torch.Tensor, dout: torch.Tensor, act: int) -> torch.Tensor
     return din.view(gate_up.shape)
 
 
+def syrk(a: torch.Tensor, aux: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
+    """``alpha * a @ a.T (+ beta * aux)`` (bf16): only the tiles on and below the diagonal are computed, the rest
+    is mirrored by the epilogue."""
+    M, K = a.shape
+    out = torch.empty(M, M, device=a.device, dtype=a.dtype)
+    _ck(_lib.lib().mb_syrk_bf16(a.data_ptr(), out.data_ptr(), _ptr(aux), M, K, _rows_pitch(a), M,
+                                _rows_pitch(aux) if aux is not None else 0, float(alpha), float(beta), _stream()), "syrk")
+    return out
+
+
 def gemm_glu_fwd(x: torch.Tensor, w_gu: torch.Tensor, act: int):
     """``gate_up = x @ w_gu.T`` ([M, 2F]) and ``act(gate) * up`` ([M, F]) from one GEMM (CTA-pair kernel)."""
     M, K = x.shape
@@ -404,6 +414,15 @@ def sum_partials(parts: torch.Tensor, res: torch.Tensor | None, out: torch.Tenso
     assert out.is_contiguous() and (res is None or res.is_contiguous())
     _ck(_lib.lib().mb_sum_partials(parts.data_ptr(), _ptr(res), out.data_ptr(), out.numel(), world, _stream()),
         "sum_partials")
+
+
+def multi_sqnorm(flat: torch.Tensor, chunks: torch.Tensor, nchunks: int, out: torch.Tensor | None,
+                 scale: torch.Tensor | None = None) -> None:
+    """``out[t] += sum(x_t ** 2)`` for every tensor t of the flat fp32 buffer (one launch; chunk table as for AdamW);
+    with ``scale`` (device scalar) the buffer is also multiplied by it."""
+    assert flat.dtype == torch.float32 and (out is None or out.dtype == torch.float32)
+    _ck(_lib.lib().mb_multi_sqnorm(flat.data_ptr(), chunks.data_ptr(), int(nchunks), _ptr(out), _ptr(scale), _stream()),
+        "multi_sqnorm")
 
 
 def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:

@@ -33,14 +33,13 @@ NS_COEFFS = (3.4445, -4.7750, 2.0315)
 def syrk(a: torch.Tensor, c: torch.Tensor | None = None, alpha: float = 1.0, beta: float = 0.0) -> torch.Tensor:
     """``alpha·A·Aᵀ + beta·C`` (reference kernel: maester/optimizers/muon_/syrk.py:143-169).
 
-    Runs on the native GEMM for bf16 CUDA inputs; the product is computed in full (a triangular
-    tile schedule with mirrored stores is a possible refinement, the result is symmetric either way).
+    For bf16 CUDA inputs this is the CTA-pair GEMM with a triangular tile schedule: only the 256x256 tiles on and
+    below the diagonal are computed and the epilogue also stores each of them transposed, as the reference kernel
+    does with its lower-triangular blocks.
     """
-    if a.is_cuda and a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0:
+    if a.is_cuda and a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.is_contiguous():
         from maester_b200.ops import cuda as C
-        if c is not None and beta != 0.0:
-            return C.gemm(a, a, epi=C.EPI_BF16_ADD, aux=c, alpha=alpha, beta=beta)
-        return C.gemm(a, a, alpha=alpha)
+        return C.syrk(a, c if (c is not None and beta != 0.0) else None, alpha, beta)
     out = alpha * (a @ a.mT)
     return out + beta * c if (c is not None and beta != 0.0) else out
 
@@ -57,8 +56,8 @@ def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.T
         x = x.t().contiguous()
     x = (x / (x.norm() + eps)).contiguous()
     for _ in range(steps):
-        A = C.gemm(x, x)                                                   # X Xᵀ            [m, m]
-        Bm = C.gemm(A, A, epi=C.EPI_BF16_ADD, aux=A, alpha=c, beta=b)      # c·A·A + b·A     (A symmetric)
+        A = C.syrk(x)                                                      # X Xᵀ            [m, m], lower tiles + mirror
+        Bm = C.syrk(A, A, alpha=c, beta=b)                                 # c·A·Aᵀ + b·A    (A symmetric: A·A = A·Aᵀ)
         x = C.gemm(Bm, x, b_mn=True, epi=C.EPI_BF16_ADD, aux=x, alpha=1.0, beta=a)  # B·X + a·X
     return x.t().contiguous() if transposed else x
 

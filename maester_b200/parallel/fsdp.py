@@ -275,6 +275,89 @@ class ShardedModel:
         """{master parameter: (offset, numel)} into the flat shard buffers (for the fused optimizer)."""
         return {sl.master: (sl.shard_off, sl.master.numel()) for u in self.units for sl in u.slots}
 
+    # ------------------------------------------------------------------ per-tensor norms over the flat shard buffers
+    def _slot_list(self) -> list[ParamSlot]:
+        return [sl for u in self.units for sl in u.slots]
+
+    def _norm_table(self):
+        """Chunk table {offset, length, tensor = slot index} over every slot's shard (cached: geometry only)."""
+        if getattr(self, "_norm_tab", None) is None:
+            from maester_b200.optimizers.adamw import build_chunk_table
+            segs = [(sl.shard_off, sl.master.numel(), 1.0, 0.0) for sl in self._slot_list() if sl.master.numel() > 0]
+            idx = [i for i, sl in enumerate(self._slot_list()) if sl.master.numel() > 0]
+            chunks, _, n = build_chunk_table(segs, self.device)
+            self._norm_tab = (chunks, n, torch.tensor(idx, device=self.device, dtype=torch.long))
+        return self._norm_tab
+
+    @torch.no_grad()
+    def shard_sqnorms(self, which: str = "grad") -> torch.Tensor:
+        """fp32 [n_slots]: sum of squares of this rank's shard of every parameter (``which`` = "grad" | "master").
+        One native launch on CUDA (multi-tensor kernel over the flat buffer), a loop of torch reductions on CPU."""
+        flat = self.shard_grad if which == "grad" else self.master
+        slots = self._slot_list()
+        out = torch.zeros(len(slots), device=self.device, dtype=torch.float32)
+        if self._use_cuda and flat.dtype == torch.float32:
+            from maester_b200.ops import cuda as C
+            chunks, n, idx = self._norm_table()
+            if n:
+                dense = torch.zeros(idx.numel(), device=self.device, dtype=torch.float32)
+                C.multi_sqnorm(flat, chunks, n, dense)
+                out[idx] = dense
+            return out
+        for i, sl in enumerate(slots):
+            n = sl.master.numel()
+            if n:
+                out[i] = flat[sl.shard_off: sl.shard_off + n].float().pow(2).sum()
+        return out
+
+    @torch.no_grad()
+    def global_sqnorms(self, which: str = "grad") -> torch.Tensor:
+        """Per-parameter sums of squares over all ranks that hold a piece of the parameter: data-parallel shards (each
+        slot's own sharding domain) and tensor-parallel slices; replicas are counted once."""
+        sq = self.shard_sqnorms(which)
+        if not dist.is_initialized():
+            return sq
+        slots = self._slot_list()
+        for d, dom in enumerate(self.domains):
+            if dom.world > 1:
+                mask = torch.tensor([sl.dom == d for sl in slots], device=self.device)
+                if bool(mask.any()):
+                    part = torch.where(mask, sq, torch.zeros_like(sq))
+                    dist.all_reduce(part, group=dom.group)
+                    sq = torch.where(mask, part, sq)
+        if self.tp_group is not None and dist.get_world_size(self.tp_group) > 1:
+            mask = torch.tensor([sl.tp_dim >= 0 for sl in slots], device=self.device)
+            if bool(mask.any()):
+                part = torch.where(mask, sq, torch.zeros_like(sq))
+                dist.all_reduce(part, group=self.tp_group)
+                sq = torch.where(mask, part, sq)
+        return sq
+
+    @torch.no_grad()
+    def clip_grad_norm(self, max_norm: float) -> torch.Tensor:
+        """Scale the reduced gradient shards so that the global L2 norm is at most ``max_norm``; returns the norm
+        before clipping (the reference's ``clip_grad_norm``, maester/utils.py:245-288, on the flat buffers: one norm
+        launch, the all-reduces of a few hundred floats, one scale launch)."""
+        sq = self.global_sqnorms("grad")
+        if self.ep_size > 1 and dist.is_initialized():
+            # expert tensors differ between expert-parallel ranks: add the other ranks' experts
+            slots = self._slot_list()
+            mask = torch.tensor([sl.dom == 1 for sl in slots], device=self.device)
+            if bool(mask.any()) and getattr(self, "ep_group", None) is not None:
+                part = torch.where(mask, sq, torch.zeros_like(sq))
+                dist.all_reduce(part, group=self.ep_group)
+                sq = torch.where(mask, part, sq)
+        total = sq.sum().sqrt()
+        coef = torch.clamp(max_norm / (total + 1e-6), max=1.0).reshape(1)
+        if self._use_cuda and self.shard_grad.dtype == torch.float32:
+            from maester_b200.ops import cuda as C
+            chunks, n, _ = self._norm_table()
+            if n:
+                C.multi_sqnorm(self.shard_grad, chunks, n, None, coef)
+        else:
+            self.shard_grad.mul_(coef)
+        return total
+
     # ------------------------------------------------------------------ initialisation
     @torch.no_grad()
     def init_master_from_full(self) -> None:

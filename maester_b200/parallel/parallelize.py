@@ -143,6 +143,7 @@ def parallelize(model: nn.Module, world_mesh, parallel_dims, cfg) -> nn.Module:
     )
     sharded.device_mesh = world_mesh["dp_shard_cp"] if (shard_group is not None and world_mesh is not None) else None
     sharded.ckpt_meshes = _checkpoint_meshes(world_mesh, parallel_dims, ep is not None)
+    sharded.ep_group = ep.group if ep is not None else None
     object.__setattr__(model, "_sharded", sharded)
     model.set_requires_gradient_sync = sharded.set_requires_gradient_sync
     # buffers that are still on the meta device (RoPE tables) are rebuilt by init_weights()

@@ -209,8 +209,11 @@ class Trainer:
                 self.optimizers.announce_step()  # units may be updated as soon as their gradients are complete
             losses.append(self.forward_backward(batch, sync))
         if clip:
-            params = [p for g in self.optimizers.param_groups for p in g["params"]]
-            clip_grad_norm(params, self.cfg.max_grad_norm, group=self.sharded.group if self.sharded else None)
+            if self.sharded is not None:
+                self.last_grad_norm = self.sharded.clip_grad_norm(self.cfg.max_grad_norm)
+            else:
+                params = [p for g in self.optimizers.param_groups for p in g["params"]]
+                self.last_grad_norm = clip_grad_norm(params, self.cfg.max_grad_norm, group=False)
         self.optimizers.step()
         self.scheduler.step()
         self.step += 1

@@ -425,3 +425,51 @@ def test_linear_cross_entropy_fused():
     assert abs(loss.item() - want.item()) < 2e-2
     assert _rel(h.grad, hf.grad) < 2e-2
     assert _rel(w.grad, wf.grad) < 2e-2
+
+
+@pytest.mark.parametrize("M,K", [(256, 64), (1000, 328), (2560, 2560)])
+def test_syrk_triangular_schedule(M, K):
+    """A A^T (+ beta C) computed on the tiles below the diagonal and mirrored equals the full product."""
+    from maester_b200.ops import cuda as C
+    torch.manual_seed(1)
+    a = (torch.randn(M, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    want = a.float() @ a.float().T
+    got = C.syrk(a)
+    assert _rel(got, want) < 5e-3
+    assert torch.equal(got, got.T.contiguous())          # exactly symmetric: the mirror is a copy
+    aux = torch.randn(M, M, device="cuda", dtype=torch.bfloat16)
+    got2 = C.syrk(a, aux, alpha=-2.0, beta=0.5)
+    assert _rel(got2, -2.0 * want + 0.5 * aux.float()) < 5e-3
+
+
+def test_newton_schulz_on_triangular_syrk():
+    from maester_b200.optimizers.muon import newton_schulz
+    torch.manual_seed(2)
+    g = torch.randn(512, 1280, device="cuda")
+    got = newton_schulz(g.to(torch.bfloat16), steps=5).float()
+    want = ref.newton_schulz(g, 5, 1e-7).float()
+    assert _rel(got, want) < 6e-2
+    s = torch.linalg.svdvals(got)
+    assert 0.5 < s.min().item() and s.max().item() < 1.3  # close to an orthogonal factor
+
+
+def test_multi_tensor_sqnorm_and_scale():
+    from maester_b200.ops import cuda as C
+    from maester_b200.optimizers.adamw import build_chunk_table
+    torch.manual_seed(3)
+    sizes = [5, 32768, 70001, 1, 123457]
+    flat = torch.randn(sum(sizes) + 64, device="cuda")
+    segs, off = [], 3   # an odd start: unaligned chunks take the scalar path
+    for n in sizes:
+        segs.append((off, n, 1.0, 0.0))
+        off += n
+    chunks, _, nch = build_chunk_table(segs, "cuda")
+    out = torch.zeros(len(sizes), device="cuda")
+    C.multi_sqnorm(flat, chunks, nch, out)
+    want = torch.stack([flat[o:o + n].double().pow(2).sum() for o, n, _, _ in segs]).float()
+    assert torch.allclose(out, want, rtol=1e-5)
+    before = flat.clone()
+    C.multi_sqnorm(flat, chunks, nch, None, torch.tensor([0.25], device="cuda"))
+    for o, n, _, _ in segs:
+        assert torch.equal(flat[o:o + n], before[o:o + n] * 0.25)
+    assert torch.equal(flat[:3], before[:3])

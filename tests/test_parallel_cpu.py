@@ -171,3 +171,22 @@ def test_gradient_accumulation_equals_one_big_batch():
     res = run_ranks(2, _accum_rank, full, b)
     for k in want:
         assert _close(res[0][1][k], want[k]), k
+
+
+def test_gradient_clipping_on_sharded_buffers_matches_single_process():
+    """Clipping on the flat shard buffers (per-tensor norms, all-reduce over the sharding group, one scale) gives the
+    same losses and weights on two ranks as in one process, and the clip is active (tiny max norm)."""
+    kw = dict(clip_gradients=True, max_grad_norm=0.05)
+    cfg1 = _cfg(train_batch_size=4, **kw)
+    full = _full_weights(cfg1)
+    batches = _batches(3, 4, 64, 512)
+    want_losses, want_params = _single(cfg1, full, batches)
+    unclipped_losses, _ = _single(_cfg(train_batch_size=4), full, batches)
+    assert abs(unclipped_losses[-1] - want_losses[-1]) > 1e-4  # the clip changed the trajectory
+    res = run_ranks(2, _fsdp_rank, dict(data_parallel_shard_degree=2, **kw), full, batches)
+    for r in range(2):
+        _, params = res[r]
+        for k in want_params:
+            assert _close(params[k], want_params[k]), k
+    mean_losses = [(a + b) / 2 for a, b in zip(res[0][0], res[1][0])]
+    assert mean_losses == pytest.approx(want_losses, abs=1e-4)
