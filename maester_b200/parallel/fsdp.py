@@ -24,6 +24,19 @@ gradient-sync toggle for accumulation) with a layout chosen for 180 GB GPUs:
   (``_eager_update``), so it runs under the backward pass of the earlier blocks.
 
 With one rank the shard and full buffers coincide and no communication code runs.
+
+Resharding mode (``reshard=True``; the reference's ``fsdp_reshard_after_forward`` / ``CPUOffloadPolicy``,
+parallelize_llama.py:265-286, parallelize_deepseek.py:264-300).  For models whose whole bf16 copy plus a whole fp32
+gradient buffer (6 bytes per parameter per GPU) would not fit, a block's parameters exist in full only while the block
+runs: every rank keeps just its rows (``shard_lp``), the blocks share ``STAGES`` staging buffers of the largest block's
+size (block i always uses buffer i % STAGES, so parameter views never move), a block is all-gathered into its buffer on
+the side stream while the previous block computes (forward) or while the next block's backward runs (backward), and
+its fp32 gradients live in a matching staging buffer that is reduce-scattered into the owner's shard and cleared as
+soon as the backward pass has left the block.  Only the root unit (embedding, final norm, head) stays gathered for
+the whole step.  Per GPU this needs ``2 bytes x (root + STAGES blocks)`` and ``4 bytes x (root + STAGES blocks)``
+instead of ``6 bytes x all parameters``.  Gradient accumulation reduces after every micro-batch in this mode (the
+staging buffers are reused), and ``cpu_offload`` keeps the fp32 master weights, gradient shards and optimizer state
+in pinned host memory with the optimizer step running there.
 """
 from __future__ import annotations
 
@@ -117,7 +130,8 @@ class ShardedModel:
     def __init__(self, model: nn.Module, unit_modules: list[tuple[str, nn.Module]], *, device: torch.device,
                  param_dtype: torch.dtype = torch.bfloat16, reduce_dtype: torch.dtype = torch.float32,
                  shard_group=None, replicate_group=None, gradient_divide_factor: float | None = None,
-                 tp_group=None, fused_comm: bool = False, expert_group=None, ep_size: int = 1, ep_rank: int = 0):
+                 tp_group=None, fused_comm: bool = False, expert_group=None, ep_size: int = 1, ep_rank: int = 0,
+                 reshard: bool = False, cpu_offload: bool = False):
         self.model = model
         self.device = device
         self.param_dtype, self.reduce_dtype = param_dtype, reduce_dtype
@@ -178,6 +192,22 @@ class ShardedModel:
                 u.shard_mid = s
         self.full_numel, self.shard_numel = f, s
 
+        # ---- resharding mode (dense data-parallel sharding only)
+        self.reshard = bool(reshard) and self.world > 1 and not self.has_experts
+        if reshard and not self.reshard and self.world > 1:
+            logger.warning("resharding is not available with expert-parallel parameters: keeping the model resident")
+        self.cpu_offload = bool(cpu_offload) and self.reshard
+        if cpu_offload and not self.cpu_offload:
+            logger.warning("enable_cpu_offload needs the resharding mode (fsdp_reshard_after_forward != 'never', "
+                           "data-parallel shard degree > 1): ignored")
+        self.resharded = False          # becomes True once the weights are initialised and the full buffer is dropped
+        self.stage: list[torch.Tensor] = []
+        self.gstage: list[torch.Tensor] = []
+        self.slot_owner: list[int] = []
+        self.gslot_event: list = []
+        if self.reshard:
+            fused_comm = False          # the per-block gather / reduce-scatter below replace the fused step kernel
+
         # ---- buffers
         self.fused = False
         self.symm_full = self.symm_grad = None
@@ -195,9 +225,16 @@ class ShardedModel:
                     logger.warning(f"symmetric memory unavailable, using NCCL collectives: {e}")
                     self.symm_full = self.symm_grad = None
         self.full = self.symm_full.tensor.zero_() if self.fused else torch.zeros(f, dtype=param_dtype, device=device)
-        self.master = torch.zeros(s, dtype=torch.float32, device=device)
-        self.shard_grad = torch.zeros(s, dtype=torch.float32, device=device)
-        if self.world > 1:
+        state_dev = torch.device("cpu") if self.cpu_offload else device
+        pin = self.cpu_offload and self._use_cuda
+        self.master = torch.zeros(s, dtype=torch.float32, device=state_dev, pin_memory=pin)
+        self.shard_grad = torch.zeros(s, dtype=torch.float32, device=state_dev, pin_memory=pin)
+        if self.reshard:
+            # until the weights are initialised the parameters are views of a temporary full buffer; gradients only
+            # exist in the staging buffers created by _enter_reshard()
+            self.full_grad = None
+            self.shard_lp = torch.zeros(s, dtype=param_dtype, device=device)
+        elif self.world > 1:
             self.full_grad = self.symm_grad.tensor.zero_() if self.fused else \
                 torch.zeros(f, dtype=torch.float32, device=device)
             self.shard_lp = torch.zeros(s if not self.fused else 1, dtype=param_dtype, device=device)
@@ -230,15 +267,18 @@ class ShardedModel:
         for u in self.units:
             for sl in u.slots:
                 n = sl.rows * sl.row_numel
-                view = self.full[sl.full_off: sl.full_off + n].view(sl.shape)
-                gview = self.full_grad[sl.full_off: sl.full_off + n].view(sl.shape)
+                pbuf, gbuf, base = self._unit_buffers(u)
+                view = pbuf[sl.full_off - base: sl.full_off - base + n].view(sl.shape)
                 new = nn.Parameter(view, requires_grad=sl.param.requires_grad)
-                new.main_grad = gview
+                if gbuf is not None:
+                    new.main_grad = gbuf[sl.full_off - base: sl.full_off - base + n].view(sl.shape)
                 for attr in ("tp_replicated", "ep_local"):
                     if getattr(sl.param, attr, False):
                         setattr(new, attr, True)
                 self._replace_param(sl.param, new)
                 sl.param = new
+                if sl.master is not None:
+                    continue  # second binding (entering the resharding mode): the optimizers keep the shards they have
                 lo, hi = self._own_rows(sl)
                 m = self.master[sl.shard_off: sl.shard_off + (hi - lo) * sl.row_numel]
                 g = self.shard_grad[sl.shard_off: sl.shard_off + (hi - lo) * sl.row_numel]
@@ -247,6 +287,42 @@ class ShardedModel:
                 mp.grad = g.view(shard_shape)
                 mp.fqn = sl.fqn
                 sl.master = mp
+
+    def _unit_buffers(self, u: Unit):
+        """(parameter buffer, gradient buffer or None, offset of the buffers' element 0 in the flat numbering)."""
+        if not self.resharded:
+            return self.full, self.full_grad, 0
+        if u is self.root:
+            return self.root_full, self.root_grad, u.full_lo
+        k = self.units.index(u) % self.STAGES
+        return self.stage[k], self.gstage[k], u.full_lo
+
+    STAGES = 2
+
+    def _enter_reshard(self) -> None:
+        """Drop the full parameter buffer: bind every block to its staging buffers, keep only the root gathered."""
+        blocks = self.units[:-1]
+        cap = max((u.full_hi - u.full_lo for u in blocks), default=0)
+        dev = self.device
+        self.stage = [torch.zeros(cap, dtype=self.param_dtype, device=dev) for _ in range(self.STAGES)]
+        self.gstage = [torch.zeros(cap, dtype=torch.float32, device=dev) for _ in range(self.STAGES)]
+        r = self.root
+        self.root_full = self.full[r.full_lo:r.full_hi].clone()
+        self.root_grad = torch.zeros(r.full_hi - r.full_lo, dtype=torch.float32, device=dev)
+        self.full = None
+        self.resharded = True
+        self.slot_owner = [-1] * self.STAGES
+        self.gslot_event = [None] * self.STAGES
+        self._rebind_parameters()
+        if hasattr(self, "_by_master"):
+            del self._by_master
+        if self._use_cuda:
+            torch.cuda.empty_cache()
+        logger.info(
+            f"ShardedModel: resharding mode, {self.STAGES} staging buffers of {cap * 2 / 2**20:.0f} MiB (+ fp32 gradients), "
+            f"root unit resident ({(r.full_hi - r.full_lo) * 2 / 2**30:.2f} GiB), "
+            f"optimizer state on {'the host' if self.cpu_offload else 'the device'}"
+        )
 
     def _replace_param(self, old: nn.Parameter, new: nn.Parameter) -> None:
         """Swap a Parameter object everywhere it is registered (tied weights appear more than once)."""
@@ -296,7 +372,13 @@ class ShardedModel:
         flat = self.shard_grad if which == "grad" else self.master
         slots = self._slot_list()
         out = torch.zeros(len(slots), device=self.device, dtype=torch.float32)
-        if self._use_cuda and flat.dtype == torch.float32:
+        if flat.device != self.device:  # optimizer state offloaded to the host: reduce there
+            for i, sl in enumerate(slots):
+                n = sl.master.numel()
+                if n:
+                    out[i] = flat[sl.shard_off: sl.shard_off + n].pow(2).sum().to(self.device)
+            return out
+        if flat.is_cuda and flat.dtype == torch.float32:
             from maester_b200.ops import cuda as C
             chunks, n, idx = self._norm_table()
             if n:
@@ -349,13 +431,13 @@ class ShardedModel:
                 sq = torch.where(mask, part, sq)
         total = sq.sum().sqrt()
         coef = torch.clamp(max_norm / (total + 1e-6), max=1.0).reshape(1)
-        if self._use_cuda and self.shard_grad.dtype == torch.float32:
+        if self.shard_grad.is_cuda and self.shard_grad.dtype == torch.float32:
             from maester_b200.ops import cuda as C
             chunks, n, _ = self._norm_table()
             if n:
                 C.multi_sqnorm(self.shard_grad, chunks, n, None, coef)
         else:
-            self.shard_grad.mul_(coef)
+            self.shard_grad.mul_(coef.to(self.shard_grad.device))
         return total
 
     # ------------------------------------------------------------------ initialisation
@@ -386,13 +468,38 @@ class ShardedModel:
                     src = sl.param.data.reshape(sl.rows, -1)[lo:hi]
                     sl.master.data.view(hi - lo, -1).copy_(src)
         self.lowp_fresh = True
+        if self.reshard and not self.resharded:
+            self._shards_to_lowp()
+            self._enter_reshard()
+
+    @torch.no_grad()
+    def _shards_to_lowp(self) -> None:
+        """bf16 copy of this rank's master rows (what the per-block all-gathers send)."""
+        self.shard_lp.copy_(self.master, non_blocking=True)
+
+    @torch.no_grad()
+    def load_full_weights(self, weights: dict[str, torch.Tensor]) -> None:
+        """Load unsharded weights (by parameter name; already sliced for this rank's tensor / expert parallel part):
+        every rank keeps its rows in the fp32 master shards and refreshes the compute-dtype copies.  Works in both
+        modes; in the resharding mode the full model is never materialised."""
+        for u in self.units:
+            for sl in u.slots:
+                w = weights[sl.fqn].to(torch.float32)
+                lo, hi = self._own_rows(sl)
+                if hi > lo:
+                    sl.master.data.view(hi - lo, -1).copy_(w.reshape(sl.rows, -1)[lo:hi])
+        self.lowp_fresh = False
+        if self.reshard and not self.resharded:
+            self._shards_to_lowp()
+            self._enter_reshard()
+        self.gather_params()
 
     # ------------------------------------------------------------------ hooks
     def _install_hooks(self) -> None:
         if self.world * self.rep_world == 1:
             return
         for i, u in enumerate(self.units[:-1]):
-            u.module.register_forward_pre_hook(lambda m, a, u=u: self._wait_gather(u))
+            u.module.register_forward_pre_hook(lambda m, a, u=u, i=i: self._pre_forward(u, i))
             u.module.register_full_backward_pre_hook(lambda m, g, i=i: self._on_backward_reach(i))
         def root_pre_forward(m, a):  # must return None: a returned value would replace the inputs
             self._wait_gather(self.root)
@@ -405,24 +512,83 @@ class ShardedModel:
             torch.cuda.current_stream().wait_event(u.gather_event) if self._use_cuda else None
             u.gather_event = None
 
+    def _pre_forward(self, u: Unit, i: int) -> None:
+        if not self.resharded:
+            self._wait_gather(u)
+            return
+        # resharding mode (also reached when a checkpointed block is recomputed inside the backward pass)
+        self._ensure_block(i)
+        if not self._in_backward and i + 1 < len(self.units) - 1:
+            self._prefetch_block(i + 1)
+
     def _on_backward_reach(self, i: int) -> None:
         # backward has reached unit i, so unit i+1 (the one after it in forward order) is complete
-        if i + 1 < len(self.units) - 1:
+        nblocks = len(self.units) - 1
+        if self.resharded:
+            self._in_backward = True
+            self._ensure_block(i)
+            k = i % self.STAGES
+            if self.gslot_event[k] is not None and self._use_cuda:  # this block's gradient staging buffer is clear again
+                torch.cuda.current_stream().wait_event(self.gslot_event[k])
+                self.gslot_event[k] = None
+        if i + 1 < nblocks:
             self._reduce_unit(self.units[i + 1])
+        if self.resharded and i - 1 >= 0:
+            self._prefetch_block(i - 1)
+
+    # ------------------------------------------------------------------ resharding mode: per-block all-gather
+    _in_backward = False
+
+    @torch.no_grad()
+    def _gather_block(self, i: int) -> None:
+        """All-gather block i's parameters from the ranks' bf16 shards into its staging buffer (side stream)."""
+        u = self.units[i]
+        k = i % self.STAGES
+        stream = self.comm_stream
+        if stream is not None:
+            stream.wait_stream(torch.cuda.current_stream())  # the buffer's previous owner has finished computing
+        ctx = torch.cuda.stream(stream) if stream is not None else _null()
+        buf = self.stage[k]
+        with ctx, torch.autograd._unsafe_preserve_version_counter(buf):
+            # (tensors saved for the backward pass are views of this buffer: block i always returns to the same
+            # addresses, so refilling it must not look like an in-place modification to autograd)
+            dom = self.domains[0]
+            n_shard = u.shard_hi - u.shard_lo
+            recv = torch.empty(dom.world * n_shard, dtype=self.param_dtype, device=self.device)
+            dist.all_gather_into_tensor(recv, self.shard_lp[u.shard_lo:u.shard_hi], group=dom.group)
+            rv = recv.view(dom.world, n_shard)
+            for sl in u.slots:
+                o = sl.full_off - u.full_lo
+                buf[o: o + sl.padded_numel * dom.world].view(dom.world, sl.padded_numel).copy_(
+                    rv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel])
+            if stream is not None:
+                u.gather_event = torch.cuda.Event()
+                u.gather_event.record(stream)
+        self.slot_owner[k] = i
+
+    def _prefetch_block(self, i: int) -> None:
+        if self.slot_owner[i % self.STAGES] != i:
+            self._gather_block(i)
+
+    def _ensure_block(self, i: int) -> None:
+        if self.slot_owner[i % self.STAGES] != i:
+            self._gather_block(i)
+        self._wait_gather(self.units[i])
 
     # ------------------------------------------------------------------ collectives
     def set_requires_gradient_sync(self, flag: bool) -> None:
         self.require_sync = flag
 
     def mark_backward_start(self) -> None:
+        self._in_backward = False  # called from the root's forward pre-hook: a new forward / backward pair begins
         for u in self.units:
             u.grads_pending = True
 
     @torch.no_grad()
     def _reduce_unit(self, u: Unit) -> None:
         """Reduce-scatter (and replicate all-reduce) of one unit's accumulated fp32 gradients."""
-        if not u.grads_pending or not self.require_sync:
-            return
+        if not u.grads_pending or not (self.require_sync or self.resharded):
+            return  # (the resharding mode reduces after every micro-batch: its staging buffers are reused)
         u.grads_pending = False
         tp_sync = self.tp_group is not None and dist.get_world_size(self.tp_group) > 1
         for sl in u.slots:  # gradients that ordinary autograd left in .grad (plain-PyTorch op path)
@@ -444,6 +610,9 @@ class ShardedModel:
             stream.wait_stream(torch.cuda.current_stream())
         ctx = torch.cuda.stream(stream) if stream is not None else _null()
         with ctx:
+            if self.resharded:
+                self._reduce_unit_resharded(u)
+                return
             shard = self.shard_grad[u.shard_lo:u.shard_hi]
             for dom, lo, hi, slots in self._segments(u):
                 seg = self.shard_grad[lo:hi]
@@ -470,6 +639,35 @@ class ShardedModel:
             if self.rep_world > 1:
                 dist.all_reduce(shard, op=dist.ReduceOp.SUM, group=self.replicate_group)
             shard.mul_(1.0 / self.divide)
+
+    def _reduce_unit_resharded(self, u: Unit) -> None:
+        """Resharding mode: reduce-scatter the unit's gradient staging buffer, ADD the result (divided) to this rank's
+        gradient shard, clear the staging buffer for the block that uses it next.  Runs on the side stream."""
+        _, gbuf, base = self._unit_buffers(u)
+        dom = self.domains[0]
+        n_shard = u.shard_hi - u.shard_lo
+        send = torch.empty(dom.world * n_shard, dtype=self.reduce_dtype, device=self.device)
+        sv = send.view(dom.world, n_shard)
+        for sl in u.slots:
+            o = sl.full_off - base
+            src = gbuf[o: o + sl.padded_numel * dom.world]
+            sv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel].copy_(
+                src.view(dom.world, sl.padded_numel))
+        gbuf[: u.full_hi - u.full_lo].zero_()
+        out = torch.empty(n_shard, dtype=self.reduce_dtype, device=self.device)
+        dist.reduce_scatter_tensor(out, send, op=dist.ReduceOp.SUM, group=dom.group)
+        if self.rep_world > 1:
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.replicate_group)
+        seg = self.shard_grad[u.shard_lo:u.shard_hi]
+        if seg.device != out.device:   # optimizer state on the host
+            seg.add_(out.to(torch.float32).cpu(), alpha=1.0 / self.divide)
+        else:
+            seg.add_(out.to(torch.float32), alpha=1.0 / self.divide)
+        if u is not self.root and self.comm_stream is not None:
+            k = self.units.index(u) % self.STAGES
+            ev = torch.cuda.Event()
+            ev.record(self.comm_stream)
+            self.gslot_event[k] = ev
 
     def _segments(self, u: Unit):
         """(domain, shard range, slots) of a unit: dense parameters first, then expert-parallel ones."""
@@ -506,6 +704,30 @@ class ShardedModel:
     def gather_params(self) -> None:
         """After the optimizer step: cast the updated master shards and all-gather them into ``full``,
         one unit at a time on the side stream; forward pre-hooks wait per unit."""
+        if self.resharded:
+            # every rank refreshes the bf16 copy of its rows; blocks are gathered when they run, the root unit now
+            if not self.lowp_fresh or self.cpu_offload:
+                self._shards_to_lowp()
+            self.lowp_fresh = False
+            self.slot_owner = [-1] * self.STAGES
+            stream = self.comm_stream
+            if stream is not None:
+                stream.wait_stream(torch.cuda.current_stream())
+            ctx = torch.cuda.stream(stream) if stream is not None else _null()
+            u, dom = self.root, self.domains[0]
+            with ctx, torch.autograd._unsafe_preserve_version_counter(self.root_full):
+                n_shard = u.shard_hi - u.shard_lo
+                recv = torch.empty(dom.world * n_shard, dtype=self.param_dtype, device=self.device)
+                dist.all_gather_into_tensor(recv, self.shard_lp[u.shard_lo:u.shard_hi], group=dom.group)
+                rv = recv.view(dom.world, n_shard)
+                for sl in u.slots:
+                    o = sl.full_off - u.full_lo
+                    self.root_full[o: o + sl.padded_numel * dom.world].view(dom.world, sl.padded_numel).copy_(
+                        rv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel])
+                if stream is not None:
+                    u.gather_event = torch.cuda.Event()
+                    u.gather_event.record(stream)
+            return
         if self.fused:
             if not self.lowp_fresh:  # no fused optimizer step wrote the parameters: push the shards
                 from maester_b200.ops import cuda as C
@@ -587,6 +809,8 @@ class ShardedModel:
     @torch.no_grad()
     def zero_grad(self) -> None:
         self.shard_grad.zero_()
+        if self.resharded:
+            return  # the staging buffers are cleared by the reduce-scatter that empties them
         if self.full_grad is not self.shard_grad:
             self.full_grad.zero_()
 

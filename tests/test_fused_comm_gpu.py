@@ -72,3 +72,46 @@ def test_fused_optimizer_collective_matches_nccl_path(per_unit, monkeypatch):
                   f"rel_full={rel_full:.2e} rel_master={rel_master:.2e}")
             assert fused_losses == pytest.approx(nccl_losses, abs=2e-2)
             assert rel_master < 2e-3 and rel_full < 5e-3
+
+
+def _reshard_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from maester_b200.config import Config
+    from maester_b200.datasets.synthetic import SyntheticLoader
+    from maester_b200.ops import cuda as C
+    from maester_b200.trainer import Trainer
+    out = {}
+    for mode in ("never", "always"):
+        torch.manual_seed(0)
+        torch.cuda.reset_peak_memory_stats()
+        cfg = Config(model_name="gemma3", flavor="debug", seq_len=512, train_batch_size=2,
+                     data_parallel_shard_degree=world, ac_mode="selective", enable_checkpoint=False,
+                     optimizer_groups=ADAMW, scheduler="constant", fused_collectives=False,
+                     fsdp_reshard_after_forward=mode)
+        tr = Trainer(cfg)
+        assert tr.sharded.resharded == (mode == "always")
+        loader = SyntheticLoader(2, 512, tr.model_args.vocab_size, "uniform:16:256", seed=3, rank=rank)
+        losses = [tr.train_step(next(loader)).item() for _ in range(4)]
+        C.check_status()
+        out[mode] = (losses, tr.sharded.master.clone())
+        del tr
+    rel = ((out["never"][1] - out["always"][1]).norm() / out["never"][1].norm()).item()
+    torch.save((out["never"][0], out["always"][0], rel), os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_resharding_mode_trains_like_the_resident_mode():
+    """Blocks gathered into two staging buffers when they run (side stream, prefetch) and gradients reduce-scattered
+    block by block give the same losses and master weights as keeping the whole model and gradient buffer resident."""
+    world = 2
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_reshard_worker, args=(world, _free_port(), d), nprocs=world, join=True)
+        for r in range(world):
+            resident, resharded, rel = torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False)
+            assert resharded == pytest.approx(resident, abs=2e-2)
+            assert rel < 2e-3

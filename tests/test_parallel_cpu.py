@@ -190,3 +190,49 @@ def test_gradient_clipping_on_sharded_buffers_matches_single_process():
             assert _close(params[k], want_params[k]), k
     mean_losses = [(a + b) / 2 for a, b in zip(res[0][0], res[1][0])]
     assert mean_losses == pytest.approx(want_losses, abs=1e-4)
+
+
+def _reshard_rank(rank, world, cfg_kw, full, batches, accum):
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_cfg(**cfg_kw))
+    assert tr.sharded.resharded and tr.sharded.full is None
+    tr.sharded.load_full_weights(full)
+    losses = []
+    for b in batches:
+        mine = {k: v[rank * 2 * accum:(rank + 1) * 2 * accum] for k, v in b.items()}
+        micro = [{k: v[j * 2:(j + 1) * 2] for k, v in mine.items()} for j in range(accum)]
+        losses.append(tr.train_step(micro if accum > 1 else micro[0]).item())
+    # reassemble this rank's view of the weights from the master shards of both ranks is done by the caller
+    return losses, {sl.fqn: (sl.master.data.clone(), sl.shape) for u in tr.sharded.units for sl in u.slots}
+
+
+@pytest.mark.parametrize("ac,accum,offload", [("none", 1, False), ("full", 1, False), ("none", 2, False), ("none", 1, True)])
+def test_resharding_mode_matches_single_process(ac, accum, offload):
+    """fsdp_reshard_after_forward=always: blocks are gathered into two staging buffers when they run and their
+    gradients are reduce-scattered block by block; losses and weights equal the single-process run, with full
+    activation recomputation (the block is re-gathered for its recomputation), with gradient accumulation (reduced
+    after every micro-batch) and with the optimizer state kept on the host."""
+    per_rank = 2 * accum
+    cfg1 = _cfg(train_batch_size=2, gradient_accumulation_steps=2 * accum, ac_mode=ac)
+    full = _full_weights(cfg1)
+    batches = _batches(3, 2 * per_rank, 64, 512)
+
+    from maester_b200.trainer import Trainer
+    tr = Trainer(cfg1)
+    _load_full(tr, full)
+    want_losses = []
+    for b in batches:
+        micro = [{k: v[j * 2:(j + 1) * 2] for k, v in b.items()} for j in range(2 * accum)]
+        want_losses.append(tr.train_step(micro).item())
+    want = {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+    kw = dict(data_parallel_shard_degree=2, fsdp_reshard_after_forward="always", ac_mode=ac,
+              gradient_accumulation_steps=accum, enable_cpu_offload=offload)
+    res = run_ranks(2, _reshard_rank, kw, full, batches, accum)
+    mean_losses = [(a + b) / 2 for a, b in zip(res[0][0], res[1][0])]
+    assert mean_losses == pytest.approx(want_losses, abs=1e-4)
+    for fqn, w in want.items():
+        pieces = [res[r][1][fqn][0].reshape(-1, *w.shape[1:]) if w.dim() > 0 else res[r][1][fqn][0].reshape(1)
+                  for r in range(2)]
+        got = torch.cat(pieces, dim=0)[: max(1, w.shape[0] if w.dim() > 0 else 1)].reshape(w.shape)
+        assert _close(got, w), fqn
