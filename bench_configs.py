@@ -50,6 +50,11 @@ def main() -> None:
     ap.add_argument("--ep-peer", action="store_true", help="expert-parallel exchange by peer-memory kernels")
     ap.add_argument("--no-fused-collectives", action="store_true")
     ap.add_argument("--vocab", type=int, default=0, help="override the vocabulary size (0: the flavor's, or 128256)")
+    ap.add_argument("--cp-mode", default="alltoall", choices=["alltoall", "ring"], help="context-parallel attention form")
+    ap.add_argument("--docs", default=None, help="document lengths of the synthetic data (default geometric:1500; "
+                    "the ring form needs 'full': one document per row)")
+    ap.add_argument("--reshard", default="default", choices=["default", "never", "always"],
+                    help="fsdp_reshard_after_forward")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     if not torch.cuda.is_available():
@@ -76,11 +81,12 @@ def main() -> None:
                  ac_mode=a.ac, selective_ac_option="op", optimizer_groups=B.ADAMW_GROUPS, scheduler="linear_warmup_cosine",
                  warmup_steps=100, train_num_steps=10_000, enable_checkpoint=False, synthetic_data=True,
                  synthetic_vocab_size=a.vocab or 128256, fused_collectives=not a.no_fused_collectives,
-                 ep_peer_dispatch=a.ep_peer)
+                 ep_peer_dispatch=a.ep_peer, context_parallel_mode=a.cp_mode, fsdp_reshard_after_forward=a.reshard)
     trainer = Trainer(cfg)
     vocab = trainer.model_args.vocab_size
     mb, seq = cfg.train_batch_size, cfg.seq_len
-    loader = SyntheticLoader(mb, seq, vocab, "geometric:1500", seed=0, rank=trainer.dp_rank, pin=True)
+    docs = a.docs or ("full" if (cp > 1 and a.cp_mode == "ring") else "geometric:1500")
+    loader = SyntheticLoader(mb, seq, vocab, docs, seed=0, rank=trainer.dp_rank, pin=True)
     pool = [next(loader) for _ in range(4)]
     dev_pool = [trainer.to_device(b) for b in pool]
     torch.cuda.synchronize()
@@ -113,7 +119,12 @@ def main() -> None:
             "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
             "config": {"preset": a.preset, "model": f"{cfg.model_name}-{cfg.flavor}", "global_batch": mb * dp, "seq_len": seq,
                        "parallelism": par, "ep_exchange": ("peer-memory kernels" if a.ep_peer else "all_to_all") if ep else None,
-                       "fused_collectives": not a.no_fused_collectives},
+                       "fused_collectives": not a.no_fused_collectives, "documents": docs,
+                       "context_parallel_mode": a.cp_mode if cp > 1 else None,
+                       "resharding": bool(trainer.sharded is not None and trainer.sharded.resharded),
+                       "peak_allocated_gib": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+                       # device-wide (symmetric buffers are not the caching allocator's): used memory at the end
+                       "device_used_gib": round((torch.cuda.mem_get_info()[1] - torch.cuda.mem_get_info()[0]) / 2**30, 2)},
             "clocks": clocks, "gpu_launches": launches,
             "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
                     "h2d_bytes_per_step": sum(v.numel() * v.element_size() for v in pool[0].values()),

@@ -150,6 +150,9 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_embedding_bwd": [_P, _P, _P, _L, _I, _F, _P],
         "mb_ce_fwd_bwd": [_P, _P, _P, _P, _F, _L, _I, _L, _I, _I, _P, _P],
         "mb_adamw": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _I, _P],
+        "mb_peer_copy": [_P, _P, _L, _P],
+        "mb_peer_add_bf16": [_P, _P, _L, _P],
+        "mb_attn_merge": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "mb_multi_sqnorm": [_P, _P, _I, _P, _P, _P],
         "mb_cast_f32_bf16": [_P, _P, _L, _F, _P],
         "mb_attn_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _I, _F, _P],

@@ -416,6 +416,31 @@ def sum_partials(parts: torch.Tensor, res: torch.Tensor | None, out: torch.Tenso
         "sum_partials")
 
 
+def peer_copy(dst: torch.Tensor, src_ptr: int, nbytes: int) -> None:
+    """``dst`` (local, contiguous) <- ``nbytes`` from the device address ``src_ptr``, which may be a peer GPU's
+    memory mapped into this process (plain loads and stores of this library's own kernel)."""
+    assert dst.is_contiguous() and dst.numel() * dst.element_size() >= nbytes
+    _ck(_lib.lib().mb_peer_copy(dst.data_ptr(), int(src_ptr), int(nbytes), _stream()), "peer_copy")
+
+
+def peer_add_bf16(dst: torch.Tensor, src_ptr: int, n: int) -> None:
+    """``dst[:n] += *src_ptr`` (bf16; the source may be peer memory)."""
+    assert dst.is_contiguous() and dst.dtype == torch.bfloat16 and dst.numel() >= n
+    _ck(_lib.lib().mb_peer_add_bf16(dst.data_ptr(), int(src_ptr), int(n), _stream()), "peer_add_bf16")
+
+
+def attn_merge(acc: torch.Tensor, lse: torch.Tensor, part: torch.Tensor, lse_part: torch.Tensor, row_off: int,
+               init: bool) -> None:
+    """Fold a partial attention result ``part`` [B, c, H, hd] (bf16) with log-sum-exp ``lse_part`` [B, H, c] into the
+    fp32 accumulator ``acc`` [B, S, H, hd] / ``lse`` [B, H, S] at rows ``row_off .. row_off + c``."""
+    B, S, H, hd = acc.shape
+    c = part.shape[1]
+    assert acc.is_contiguous() and lse.is_contiguous() and part.is_contiguous() and lse_part.is_contiguous()
+    assert acc.dtype == torch.float32 and part.dtype == torch.bfloat16 and row_off + c <= S
+    _ck(_lib.lib().mb_attn_merge(acc.data_ptr(), lse.data_ptr(), part.data_ptr(), lse_part.data_ptr(), B, c, H, hd, S,
+                                 int(row_off), int(bool(init)), _stream()), "attn_merge")
+
+
 def multi_sqnorm(flat: torch.Tensor, chunks: torch.Tensor, nchunks: int, out: torch.Tensor | None,
                  scale: torch.Tensor | None = None) -> None:
     """``out[t] += sum(x_t ** 2)`` for every tensor t of the flat fp32 buffer (one launch; chunk table as for AdamW);

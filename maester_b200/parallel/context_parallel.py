@@ -10,8 +10,9 @@ ids, and a second all-to-all restores the sequence sharding.  Causal work is bal
 construction, and any mask the kernel supports works unchanged.  Parameters are replicated over
 ``cp`` and sharded over ``dp_shard x cp``; gradients are averaged over that product.
 
-A ring exchange of KV tiles fused into the attention kernel is the alternative for head counts that
-do not divide by ``cp``; it needs query/key offsets in the kernel and is not built yet.
+``mode="ring"`` (``context_parallel_mode``) selects the zig-zag ring form of ``ring_attention.py`` instead: every
+rank keeps its (zig-zag) slice of the sequence for attention too and pulls the peers' K / V chunks over NVLink; it
+works for any head count but supports plain causal attention only.
 """
 from __future__ import annotations
 
@@ -28,6 +29,8 @@ class CPInfo:
     group: object
     size: int
     rank: int
+    mode: str = "alltoall"      # "alltoall" (sequence <-> heads) or "ring" (zig-zag, K / V pulled from the peers)
+    ring_state: object = None
 
 
 def _a2a(x: torch.Tensor, cp: CPInfo) -> torch.Tensor:
@@ -105,15 +108,19 @@ def attention(module, qkv, q_norm_w, k_norm_w, pos, inv_freq, rope_cs, doc, n_he
     if cp is None or cp.size == 1:
         return ops.attention_block(qkv, q_norm_w, k_norm_w, pos, inv_freq, rope_cs, doc, n_heads, n_kv_heads,
                                    head_dim, **kw)
+    if cp.mode == "ring":
+        from maester_b200.parallel.ring_attention import ring_attention_block
+        return ring_attention_block(qkv, q_norm_w, k_norm_w, pos, inv_freq, rope_cs, n_heads, n_kv_heads, head_dim, cp,
+                                    doc_ids=doc, **kw)
     return cp_attention_block(qkv, q_norm_w, k_norm_w, pos, inv_freq, rope_cs, doc, n_heads, n_kv_heads, head_dim,
                               cp, **kw)
 
 
-def apply_cp(model: torch.nn.Module, parallel_dims) -> CPInfo:
+def apply_cp(model: torch.nn.Module, parallel_dims, mode: str = "alltoall") -> CPInfo:
     """Mark every attention module (anything with an ``attn``-like forward that calls
     ``context_parallel.attention``) with the CP group."""
     group = parallel_dims.mesh_group("cp")
-    cp = CPInfo(group, dist.get_world_size(group), dist.get_rank(group))
+    cp = CPInfo(group, dist.get_world_size(group), dist.get_rank(group), mode=mode)
     for m in model.modules():
         if hasattr(m, "cp_capable"):
             m.cp = cp
@@ -127,6 +134,21 @@ def shard_batch_for_cp(batch: dict, cp: CPInfo | None) -> dict:
         return batch
     out = dict(batch)
     S = batch["input_ids"].shape[1]
+    if cp.mode == "ring":
+        # zig-zag: chunk r and chunk 2 cp - 1 - r; positions are those of the local tokens; documents are not
+        # supported (the caller checks that a batch has a single document per row)
+        from maester_b200.parallel.ring_attention import zigzag_index
+        idx = zigzag_index(S, cp.size, cp.rank, device=batch["input_ids"].device)
+        out["input_ids"] = batch["input_ids"].index_select(1, idx)
+        out["labels"] = batch["labels"].index_select(1, idx)
+        pos = batch.get("position_ids")
+        if pos is None:
+            B = batch["input_ids"].shape[0]
+            out["position_ids"] = idx.to(torch.int32)[None].expand(B, idx.numel()).contiguous()
+        else:
+            out["position_ids"] = pos.index_select(1, idx)
+        out.pop("document_ids", None)
+        return out
     assert S % cp.size == 0
     s = S // cp.size
     sl = slice(cp.rank * s, (cp.rank + 1) * s)

@@ -88,7 +88,7 @@ class Trainer:
         self.cp = None
         if pd.cp_enabled:
             from maester_b200.parallel.context_parallel import apply_cp
-            self.cp = apply_cp(self.model, pd)
+            self.cp = apply_cp(self.model, pd, mode=cfg.context_parallel_mode)
         materialize(self.model)
         self.sharded = getattr(self.model, "_sharded", None)
         self.optimizers = model_name_to_optimizers_builder[cfg.model_name](self.model, cfg, pd)
@@ -170,6 +170,11 @@ class Trainer:
         cfg = self.cfg
         if self.sharded is not None and self.grad_accum > 1:
             self.sharded.set_requires_gradient_sync(sync)
+        if self.cp is not None and self.cp.mode == "ring":
+            d = batch.get("document_ids")  # still on the host here: the check costs no device synchronisation
+            if d is not None and not d.is_cuda and bool((d != d[:, :1]).any()):
+                raise NotImplementedError("context_parallel_mode='ring' attends causally over the whole sequence; "
+                                          "packed documents need context_parallel_mode='alltoall'")
         b = self.to_device(batch)
         if self.cp is not None:
             from maester_b200.parallel.context_parallel import shard_batch_for_cp
