@@ -5,7 +5,7 @@
         --master-port P bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...      # the unmodified reference from baseline/_ref
 
-Config (BASELINE.json config 3): 34 layers, d_model 2560, 8 q / 4 kv heads, head_dim 256, GeGLU
+Config: Gemma-3 4B, 34 layers, d_model 2560, 8 q / 4 kv heads, head_dim 256, GeGLU
 10240, vocab 262208 tied, 5:1 local:global attention with window 1024, seq 8192, micro-batch 2 per
 GPU, bf16 compute with fp32 master weights / reduction, selective activation recomputation, AdamW
 without decay on embeddings and norms, sharded data parallel over N GPUs (weak scaling).  Data:
@@ -128,11 +128,14 @@ def timed_region(fn, steps: int, world: int) -> float:
 
 def host_batches(n: int, rank: int, vocab: int, pin: bool = True):
     from maester_b200.datasets.synthetic import SyntheticLoader
-    loader = SyntheticLoader(MICRO_BATCH, SEQ, vocab, "geometric:1500", seed=0, rank=rank, pin=pin)
+    # packed documents with per-document positions: both arms get document_ids AND position_ids, as the reference's
+    # trainer passes both to the model when the batch has them (train.py:324-362 of the reference)
+    loader = SyntheticLoader(MICRO_BATCH, SEQ, vocab, "geometric:1500", seed=0, rank=rank, pin=pin,
+                             with_position_ids=True)
     return [next(loader) for _ in range(n)]
 
 
-def emit(args, world, value, ms_per_step, e2e, clocks, launches, impl):
+def emit(args, world, value, ms_per_step, e2e, clocks, launches, impl, extra=None):
     global_batch = MICRO_BATCH * world
     line = {
         "metric": "tokens_per_sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -145,6 +148,8 @@ def emit(args, world, value, ms_per_step, e2e, clocks, launches, impl):
                    "l2": "per-step working set >> 126 MB L2, no flush needed"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
     }
+    if extra:
+        line["config"].update(extra)
     print(json.dumps(line), flush=True)
 
 
@@ -198,7 +203,14 @@ def run_ours(args):
         extra_mfu = trainer.mfu(value / world)
         sys.stderr.write(f"[bench] {ms / args.steps:.1f} ms/step, {value:,.0f} tok/s, MFU {extra_mfu:.1f}% "
                          f"(of 2.25 PF), e2e {e2e['value']:,.0f} tok/s, loss {losses[-1]:.3f}\n")
-        emit(args, world, value, ms / args.steps, e2e, clocks, launches, "maester_b200")
+        sh = trainer.sharded
+        coll = "none (one GPU)"
+        if world > 1:
+            coll = "nccl" if not (sh and sh.fused) else ("multimem" if sh.symm_grad.multicast_ptr else "peer")
+        free, total = torch.cuda.mem_get_info()
+        emit(args, world, value, ms / args.steps, e2e, clocks, launches, "maester_b200",
+             {"collectives": coll, "resharding": bool(sh is not None and sh.resharded),
+              "device_used_gib": round((total - free) / 2**30, 1)})
     if world > 1:
         dist.destroy_process_group()
 
@@ -260,7 +272,7 @@ def run_reference(args):
         torch.manual_seed(counter[0] + rank)
         if from_host:
             batch = {k: v.cuda(non_blocking=True) for k, v in batch.items()}
-        pred = model(batch["input_ids"], position_ids=None, document_ids=batch["document_ids"])
+        pred = model(batch["input_ids"], position_ids=batch.get("position_ids"), document_ids=batch["document_ids"])
         loss = F.cross_entropy(pred.flatten(0, 1).float(), batch["labels"].flatten(0, 1))
         del pred
         loss.backward()
@@ -281,7 +293,9 @@ def run_reference(args):
     e2e = {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": losses[-1]}
     if rank == 0:
-        emit(args, world, tokens / (ms / 1e3), ms / args.steps, e2e, clocks, None, "reference")
+        emit(args, world, tokens / (ms / 1e3), ms / args.steps, e2e, clocks, None, "reference",
+             {"collectives": "nccl (FSDP2)" if world > 1 else "none (one GPU)",
+              "loss": "full logits + F.cross_entropy (cut_cross_entropy cannot be installed offline)"})
     dist.destroy_process_group()
 
 

@@ -241,9 +241,47 @@ class CheckpointManager:
         return True
 
     def _load(self, states: dict[str, Any], path: str) -> None:
-        # tolerate keys written through a torch.compile wrapper ("._orig_mod")
         from torch.distributed.checkpoint.api import CheckpointException
         try:
-            dcp.load(states, checkpoint_id=path, no_dist=self._no_dist())
+            renamed = _stored_names(path)
+            if renamed:
+                self._load_renamed(states, path, renamed)
+            else:
+                dcp.load(states, checkpoint_id=path, no_dist=self._no_dist())
         except CheckpointException as e:  # derives from BaseException: turn it into an ordinary error
             raise RuntimeError(f"checkpoint {path} is unreadable or does not match the model: {e}") from e
+
+    def _load_renamed(self, states: dict[str, Any], path: str, stored: dict[str, str]) -> None:
+        """Load a checkpoint whose keys carry ``_orig_mod`` components (it was written from modules wrapped by
+        ``torch.compile``): every flat state dict is read under the stored names and handed back under ours."""
+        logger.info(f"{path}: {len(stored)} keys were written through a torch.compile wrapper; mapping them")
+        plain: dict[str, Any] = {}
+        for top, obj in states.items():
+            sd = obj.state_dict() if isinstance(obj, Stateful) else obj
+            if not (isinstance(sd, dict) and all(isinstance(k, str) for k in sd)):
+                plain[top] = obj
+                continue
+            there = {stored.get(f"{top}.{k}", f"{top}.{k}")[len(top) + 1:]: v for k, v in sd.items()}
+            dcp.load({top: there}, checkpoint_id=path, no_dist=self._no_dist())
+            back = {k: there[stored.get(f"{top}.{k}", f"{top}.{k}")[len(top) + 1:]] for k in sd}
+            if isinstance(obj, Stateful):
+                obj.load_state_dict(back)
+            else:
+                obj.update(back)
+        if plain:
+            dcp.load(plain, checkpoint_id=path, no_dist=self._no_dist())
+
+
+def _stored_names(path: str) -> dict[str, str]:
+    """{name without ``_orig_mod`` components: name as stored} for the keys of a checkpoint that have such components
+    (empty for an ordinary checkpoint, or when the metadata cannot be read: the load itself then reports why)."""
+    try:
+        meta = dcp.FileSystemReader(path).read_metadata()
+    except Exception:
+        return {}
+    out = {}
+    for k in meta.state_dict_metadata:
+        clean = ".".join(part for part in k.split(".") if part != "_orig_mod")
+        if clean != k:
+            out[clean] = k
+    return out

@@ -156,8 +156,12 @@ class FusedAdamW(Optimizer):
                 C.fused_rs_adamw_ag(sharded.symm_grad, sharded.symm_full, f["master"], f["m"], f["v"], f["grad"],
                                     fchunks, tensors, fn, lr_t, b1, b2, g0["eps"], st_step, sharded.divide)
             else:
-                C.adamw(f["master"], f["grad"], f["m"], f["v"], f["lowp"], chunks, tensors, nch, lr_t, b1, b2,
+                # the kernel emits the bf16 copy itself; any other compute dtype (fp32 oracle runs) is a plain copy
+                lp = f["lowp"] if (f["lowp"] is not None and f["lowp"].dtype == torch.bfloat16) else None
+                C.adamw(f["master"], f["grad"], f["m"], f["v"], lp, chunks, tensors, nch, lr_t, b1, b2,
                         g0["eps"], st_step)
+                if lp is None and f["lowp"] is not None:
+                    f["lowp"].copy_(f["master"])
             for g in self.param_groups:
                 for p in g["params"]:
                     self.state[p]["step"] = torch.tensor(float(st_step))

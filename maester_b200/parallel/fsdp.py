@@ -246,7 +246,8 @@ class ShardedModel:
         logger.info(
             f"ShardedModel: {sum(len(u.slots) for u in self.units)} params in {len(self.units)} units, "
             f"full={f * self.full.element_size() / 2**30:.2f} GiB {param_dtype}, "
-            f"shard={s * 4 / 2**30:.2f} GiB fp32 x3 (master, grad + optimizer state), world={self.world}"
+            f"shard={s * 4 / 2**30:.2f} GiB fp32 x3 (master, grad + optimizer state), world={self.world}, "
+            f"collectives={'own kernels over ' + ('NVLS multimem' if self.symm_grad.multicast_ptr else 'peer memory') if self.fused else ('nccl/gloo' if self.world * self.rep_world > 1 else 'none')}"
         )
 
     # ------------------------------------------------------------------ construction helpers

@@ -37,7 +37,8 @@ def _worker(rank, world, port, out_dir):
         cfg = Config(model_name="llama3", flavor="debugmodel", seq_len=1024, train_batch_size=2,
                      data_parallel_shard_degree=1, context_parallel_degree=world, context_parallel_mode=mode,
                      ac_mode="none", enable_checkpoint=False, optimizer_groups=ADAMW, scheduler="constant",
-                     synthetic_vocab_size=2048)
+                     synthetic_vocab_size=2048,
+                     fused_collectives=False)  # NCCL reduce-scatter: the reduced gradient shards can be compared
         tr = Trainer(cfg)
         loader = SyntheticLoader(2, 1024, 2048, "full", seed=5, rank=0)   # the CP group shares one batch
         # gradients of the first step (reduced over the group, this rank's rows) before any optimizer arithmetic
