@@ -66,7 +66,10 @@ class FusedWeight:
     def get(self) -> torch.Tensor:
         ps = [getattr(m, self.attr) for m in self.owners]
         grads = [getattr(p, "main_grad", None) for p in ps]
-        flat_ok = all(g is not None for g in grads) and all(
+        # the view's gradient reaches the flat buffer only through the native GEMM's ``main_grad`` epilogue; on the
+        # plain-PyTorch path (CPU, fp32 compute) autograd must see the parameters themselves
+        native = ps[0].is_cuda and ps[0].dtype == torch.bfloat16
+        flat_ok = native and all(g is not None for g in grads) and all(
             _adjacent(ps[i].data, ps[i + 1].data) and _adjacent(grads[i], grads[i + 1]) for i in range(len(ps) - 1)
         )
         if not flat_ok:
