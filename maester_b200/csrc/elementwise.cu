@@ -902,6 +902,102 @@ __global__ void __launch_bounds__(1024) ce_fwd_bwd_kernel(__nv_bfloat16* __restr
   }
 }
 
+// ------------------------------------------------------------------ cross-entropy from GEMM-epilogue statistics
+// The logits GEMM leaves, per row and 256-column tile, (max, sum exp(x - max)) in stats[tile * ld + row] and the
+// target logit in tgt[row].  ce_merge folds a row's tiles into one record {max, sum, target, 0}; ce_grad combines the
+// records of all ranks that hold a slice of the vocabulary (one record per rank, read through peer pointers) into
+// the row's log-sum-exp, adds the row's loss, and turns the stored logits into d(loss)/d(logits) in one pass.
+__global__ void __launch_bounds__(256) ce_merge_kernel(const float2* __restrict__ stats, const float* __restrict__ tgt,
+                                                      float4* __restrict__ rec, int M, int tiles, long long ld) {
+  __shared__ float sm_m[8][32], sm_s[8][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int row = blockIdx.x * 32 + lane;
+  float m = -INFINITY, s = 0.f;
+  if (row < M) {
+    for (int t = w; t < tiles; t += 8) {
+      const float2 v = stats[static_cast<long long>(t) * ld + row];
+      const float nm = fmaxf(m, v.x);
+      s = s * __expf(m - nm) + v.y * __expf(v.x - nm);
+      m = nm;
+    }
+  }
+  sm_m[w][lane] = m;
+  sm_s[w][lane] = s;
+  __syncthreads();
+  if (w == 0 && row < M) {
+    float bm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bm = fmaxf(bm, sm_m[i][lane]);
+    float bs = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bs += sm_m[i][lane] == -INFINITY ? 0.f : sm_s[i][lane] * __expf(sm_m[i][lane] - bm);
+    rec[row] = make_float4(bm, bs, tgt[row], 0.f);
+  }
+}
+
+struct CeRecords {
+  const float4* rank[8];
+};
+
+// logits [R, V] bf16 (pitch ld): this rank's vocabulary slice starts at global column v0.  rec.rank[r][row] is rank
+// r's record of the row.  In place: logits <- (exp(x - lse) - onehot) * (*grad_scale); loss_sum += lse - target.
+__global__ void __launch_bounds__(1024) ce_grad_kernel(__nv_bfloat16* __restrict__ logits,
+                                                      const long long* __restrict__ labels, CeRecords rec, int world,
+                                                      float* __restrict__ loss_sum,
+                                                      const float* __restrict__ grad_scale, int V, long long ld,
+                                                      long long v0, int ignore_index, int write_grad) {
+  const long long row = blockIdx.x;
+  const long long label = labels[row];
+  __nv_bfloat16* lr = logits + row * ld;
+  const int nvec = V >> 3;
+  if (label == ignore_index) {
+    if (!write_grad) return;
+    bf16x8 z;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) reinterpret_cast<bf16x8*>(lr)[v] = z;
+    for (int c = (nvec << 3) + threadIdx.x; c < V; c += blockDim.x) lr[c] = __float2bfloat16(0.f);
+    return;
+  }
+  float m = -INFINITY, tg = 0.f;
+  float4 r[8];
+  for (int i = 0; i < world; ++i) {
+    r[i] = rec.rank[i][row];
+    m = fmaxf(m, r[i].x);
+    tg += r[i].z;
+  }
+  float s = 0.f;
+  for (int i = 0; i < world; ++i) s += r[i].x == -INFINITY ? 0.f : r[i].y * __expf(r[i].x - m);
+  const float lse = m + logf(s);
+  if (threadIdx.x == 0 && loss_sum) atomicAdd(loss_sum, lse - tg);
+  if (!write_grad) return;
+  const float gs = *grad_scale;
+  const long long lab = label - v0;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const bf16x8*>(lr)[v], f);
+    const int c0 = v << 3;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float p = __expf(f[e] - lse);
+      if (c0 + e == lab) p -= 1.f;
+      f[e] = p * gs;
+    }
+    reinterpret_cast<bf16x8*>(lr)[v] = pack8(f);
+  }
+  for (int c = (nvec << 3) + threadIdx.x; c < V; c += blockDim.x) {
+    float p = __expf(__bfloat162float(lr[c]) - lse);
+    if (c == lab) p -= 1.f;
+    lr[c] = __float2bfloat16(p * gs);
+  }
+}
+
+// Records `code` in the status word unless *x equals `want` to within a relative 1e-5 (no trap, no host sync).
+__global__ void expect_scalar_kernel(const float* __restrict__ x, float want, int* __restrict__ status, int code) {
+  const float v = *x;
+  if (!(fabsf(v - want) <= 1e-5f * fmaxf(fabsf(want), 1e-30f))) atomicCAS(status, 0, code);
+}
+
 // ------------------------------------------------------------------ flat multi-tensor AdamW
 // Work is described by chunks {offset, length, tensor}; each tensor has {lr_mult, weight_decay}.
 // p/g/m/v are fp32 flat buffers, lp is the bf16 (or null) copy that the next forward reads.
@@ -1162,6 +1258,36 @@ extern "C" int mb_ce_fwd_bwd(void* logits, const long long* labels, float* loss_
   ce_fwd_bwd_kernel<<<static_cast<unsigned>(R), 1024, 0, st>>>((__nv_bfloat16*)logits, labels, loss_sum, grad_scale,
                                                               logit_scale, V, ld, ignore_index, write_grad, lse_out);
   return mbh::check_launch("ce_fwd_bwd");
+}
+
+extern "C" int mb_ce_merge(const void* stats, const float* tgt, void* rec, int M, int tiles, long long ld,
+                           cudaStream_t st) {
+  if (M <= 0) return 0;
+  if (reinterpret_cast<uintptr_t>(rec) & 15) return -3;
+  ce_merge_kernel<<<(M + 31) / 32, 256, 0, st>>>(static_cast<const float2*>(stats), tgt, static_cast<float4*>(rec), M,
+                                                tiles, ld);
+  return mbh::check_launch("ce_merge");
+}
+
+// recs: host array of `world` device pointers (this rank's own record array included, at its rank's index), each
+// already offset to the first row of this chunk.
+extern "C" int mb_ce_grad(void* logits, const long long* labels, void* const* recs, int world, float* loss_sum,
+                          const float* grad_scale, long long R, int V, long long ld, long long v0, int ignore_index,
+                          int write_grad, cudaStream_t st) {
+  if (R <= 0) return 0;
+  if ((ld & 7) || world < 1 || world > 8) return -3;
+  CeRecords rec;
+  for (int i = 0; i < 8; ++i) rec.rank[i] = i < world ? static_cast<const float4*>(recs[i]) : nullptr;
+  ce_grad_kernel<<<static_cast<unsigned>(R), 1024, 0, st>>>((__nv_bfloat16*)logits, labels, rec, world, loss_sum,
+                                                           grad_scale, V, ld, v0, ignore_index, write_grad);
+  return mbh::check_launch("ce_grad");
+}
+
+extern "C" int mb_expect_scalar(const float* x, float want, cudaStream_t st) {
+  int* status = mbh::status().dev;
+  if (!status) return -4;
+  expect_scalar_kernel<<<1, 1, 0, st>>>(x, want, status, 9 /* ERR_GRAD_SCALE of sm100.cuh */);
+  return mbh::check_launch("expect_scalar");
 }
 
 extern "C" int mb_adamw(float* p, float* g, float* m, float* v, void* lp, const void* chunks, const void* tensors,

@@ -391,6 +391,17 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           tmem_ld_wait();
           store_glu_bwd_chunk(p, r, alpha, row, n0 + c * 32);
         }
+      } else if (p.ce_mode) {
+        float m = -INFINITY, s = 0.f;
+        const long long lab = row < p.M ? p.ce_labels[row] - p.ce_v0 : -1;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          ce_stats_chunk(p, r, alpha, row, n0 + c * 32, lab, m, s);
+        }
+        if (row < p.M) p.ce_stats[static_cast<long long>(nt) * p.ce_ld + row] = make_float2(m, s);
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -730,4 +741,41 @@ extern "C" int mb_syrk_bf16(const void* A, void* C, const void* aux, int M, int 
   p.route_rows = 0;
   p.syrk = 1;
   return launch2<false, false>(A, A, p, lda, lda, stream);
+}
+
+// Logits with cross-entropy statistics (see GemmParams::ce_mode): logits[M, N] = bf16(scale * h w^T) (may be null),
+// stats[tile, row] = (max, sum exp) of every 256-column tile (tile pitch stats_ld >= M rows), tgt[row] = the logit at
+// column labels[row] - v0 when that column is in [0, N), else 0.
+extern "C" int mb_gemm_ce(const void* h, const void* w, void* logits, const long long* labels, void* stats, float* tgt,
+                          int M, int N, int K, long long ldh, long long ldw, long long ldl, long long v0, float scale,
+                          long long stats_ld, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((ldh & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(h) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(stats) & 7) || stats_ld < M)
+    return -3;
+  if (logits && (reinterpret_cast<uintptr_t>(logits) & 15)) return -3;
+  if (cudaMemsetAsync(tgt, 0, sizeof(float) * static_cast<size_t>(M), stream) != cudaSuccess) return -5;
+  GemmParams p;
+  p.C = logits;
+  p.aux = nullptr;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldl;
+  p.ldaux = 0;
+  p.epi = EPI_BF16;
+  p.alpha = scale;
+  p.alpha_dev = nullptr;
+  p.beta = 0.f;
+  p.status = mbh::status().dev;
+  if (!p.status) return -4;
+  p.splits = 1;
+  p.route_rows = 0;
+  p.ce_mode = 1;
+  p.ce_labels = labels;
+  p.ce_v0 = v0;
+  p.ce_stats = static_cast<float2*>(stats);
+  p.ce_ld = stats_ld;
+  p.ce_tgt = tgt;
+  return launch2<false, false>(h, w, p, ldh, ldw, stream);
 }

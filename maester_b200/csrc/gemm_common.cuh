@@ -59,6 +59,17 @@ struct GemmParams {
   // Symmetric rank-k update (C = alpha * A A^T [+ beta * aux], M == N, bf16 out): only the tiles on and below the
   // diagonal are computed; every tile below the diagonal is also stored transposed into its mirror position.
   int syrk = 0;
+  // Cross-entropy statistics (CTA-pair kernel, ce_mode 1): C = bf16(alpha * acc) are the logits [M, N] (C may be
+  // null: nothing is stored).  For every output row and every 256-column tile the epilogue also stores
+  // (max, sum of exp(x - max)) over the tile's valid columns into ce_stats[tile * ce_ld + row], and where
+  // ce_labels[row] - ce_v0 falls inside the tile the logit itself into ce_tgt[row] (cleared by the launcher).  Both
+  // are taken from the rounded bf16 values, so a later pass over the stored logits sees the same numbers.
+  int ce_mode = 0;
+  const long long* ce_labels = nullptr;
+  long long ce_v0 = 0;
+  float2* ce_stats = nullptr;
+  long long ce_ld = 0;
+  float* ce_tgt = nullptr;
   int glu_mode = 0;
   int glu_act = 0;         // 0: tanh-GELU, 1: SiLU
   int glu_F = 0;
@@ -151,6 +162,50 @@ __device__ __forceinline__ void store_glu_bwd_chunk(const GemmParams& p, const u
     vu.x = pack_bf16(du[0], du[1]); vu.y = pack_bf16(du[2], du[3]); vu.z = pack_bf16(du[4], du[5]); vu.w = pack_bf16(du[6], du[7]);
     reinterpret_cast<uint4*>(crow + j0)[j] = vg;
     reinterpret_cast<uint4*>(crow + p.glu_F + j0)[j] = vu;
+  }
+}
+
+// 32 accumulator columns [col0, col0 + 32) of output row `row` as logits: optional bf16 store, and the running
+// (max m, sum s of exp(x - m)) of the row over this tile; `lab` is the row's label relative to column 0 of the matrix.
+__device__ __forceinline__ void ce_stats_chunk(const GemmParams& p, const uint32_t (&r)[32], float alpha, int row,
+                                               int col0, long long lab, float& m, float& s) {
+  using namespace mb;
+  if (row >= p.M || col0 >= p.N) return;
+  const int nvalid = min(32, p.N - col0);
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = bf16_round(__uint_as_float(r[i]) * alpha);
+  if (p.C) {
+    __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+    if (nvalid == 32 && (p.ldc & 7) == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint4 o;
+        o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+        o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+        o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+        o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+        reinterpret_cast<uint4*>(crow)[j] = o;
+      }
+    } else {
+      for (int i = 0; i < nvalid; ++i) crow[i] = __float2bfloat16(v[i]);
+    }
+  }
+  float cm = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) cm = fmaxf(cm, i < nvalid ? v[i] : -INFINITY);
+  const float nm = fmaxf(m, cm);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) acc += i < nvalid ? __expf(v[i] - nm) : 0.f;
+  s = s * __expf(m - nm) + acc;   // m == -inf on the first chunk: exp(-inf) = 0 and s = 0
+  m = nm;
+  const long long rel = lab - col0;
+  if (rel >= 0 && rel < nvalid) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t = (i == static_cast<int>(rel)) ? v[i] : t;
+    p.ce_tgt[row] = t;
   }
 }
 

@@ -24,6 +24,7 @@ enum : int {
   ERR_WAIT_SOFTMAX = 6,
   ERR_WAIT_MISC = 7,
   ERR_BAD_ARG = 8,
+  ERR_GRAD_SCALE = 9,    // a loss whose gradients were produced ahead of backward received another output gradient
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

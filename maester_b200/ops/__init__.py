@@ -7,6 +7,7 @@ from maester_b200.ops.functional import (  # noqa: F401
     kv_block_lower_bounds,
     linear,
     linear_cross_entropy,
+    loss_backward_scale,
     rmsnorm,
     rope_table,
     use_native,

@@ -6,6 +6,7 @@ bounded wait expires.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 import os
 
@@ -24,6 +25,7 @@ _STATUS_NAMES = {
     6: "softmax warps timed out",
     7: "pipeline wait timed out",
     8: "bad argument detected on device",
+    9: "a loss whose gradients were produced during forward received a different output gradient in backward",
 }
 
 launch_count = 0  # number of native kernel launches issued through this module
@@ -231,6 +233,53 @@ def ce_fwd_bwd(logits: torch.Tensor, labels: torch.Tensor, loss_sum: torch.Tenso
     _ck(_lib.lib().mb_ce_fwd_bwd(logits.data_ptr(), labels.data_ptr(), loss_sum.data_ptr(), grad_scale.data_ptr(),
                                  float(logit_scale), R, V, logits.stride(0), -100, int(write_grad), _ptr(lse_out),
                                  _stream()), "ce_fwd_bwd")
+
+
+CE_TILE = 256  # columns per statistics record of gemm_ce (the CTA-pair GEMM's tile width)
+
+
+def gemm_ce(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, v0: int = 0, logit_scale: float = 1.0,
+            logits: torch.Tensor | None = None, store_logits: bool = True):
+    """Logits GEMM with cross-entropy statistics in its epilogue.
+
+    Returns ``(logits, stats, tgt)``: logits ``[M, V]`` bf16 = ``logit_scale * h @ w.T`` (None when
+    ``store_logits`` is false), stats fp32 ``[tiles, M, 2]`` = (max, sum exp(x - max)) per row and 256-column tile,
+    tgt fp32 ``[M]`` = the logit at column ``labels - v0`` where that column exists in ``w``, else 0."""
+    M, K = h.shape
+    V = w.shape[0]
+    tiles = (V + CE_TILE - 1) // CE_TILE
+    if store_logits and logits is None:
+        logits = torch.empty(M, V, device=h.device, dtype=torch.bfloat16)
+    stats = torch.empty(tiles, M, 2, device=h.device, dtype=torch.float32)
+    tgt = torch.empty(M, device=h.device, dtype=torch.float32)
+    _ck(_lib.lib().mb_gemm_ce(h.data_ptr(), w.data_ptr(), logits.data_ptr() if store_logits else None,
+                              labels.data_ptr(), stats.data_ptr(), tgt.data_ptr(), M, V, K, _rows_pitch(h),
+                              _rows_pitch(w), logits.stride(0) if store_logits else 0, int(v0), float(logit_scale), M,
+                              _stream()), "gemm_ce")
+    return (logits if store_logits else None), stats, tgt
+
+
+def ce_merge(stats: torch.Tensor, tgt: torch.Tensor, rec: torch.Tensor) -> None:
+    """Fold the per-tile statistics of every row into ``rec[row] = (max, sum, target, 0)`` (fp32 ``[M, 4]``)."""
+    tiles, M, _ = stats.shape
+    _ck(_lib.lib().mb_ce_merge(stats.data_ptr(), tgt.data_ptr(), rec.data_ptr(), M, tiles, M, _stream()), "ce_merge")
+
+
+def ce_grad(logits: torch.Tensor | None, labels: torch.Tensor, rec_ptrs: list[int], loss_sum: torch.Tensor | None,
+            grad_scale: torch.Tensor, v0: int = 0, write_grad: bool = True, rows: int | None = None) -> None:
+    """Row losses from the records of all vocabulary slices (``rec_ptrs``: one device address per rank, at this
+    chunk's first row) and, in place, ``logits <- (softmax - onehot) * grad_scale``."""
+    R = rows if rows is not None else logits.shape[0]
+    V = logits.shape[1] if logits is not None else 0
+    arr = (ctypes.c_void_p * len(rec_ptrs))(*rec_ptrs)
+    _ck(_lib.lib().mb_ce_grad(_ptr(logits), labels.data_ptr(), arr, len(rec_ptrs), _ptr(loss_sum),
+                              grad_scale.data_ptr(), R, V, logits.stride(0) if logits is not None else 8, int(v0),
+                              -100, int(write_grad and logits is not None), _stream()), "ce_grad")
+
+
+def expect_scalar(x: torch.Tensor, want: float) -> None:
+    """Records a status error (read by ``check_status``) unless the fp32 device scalar ``x`` equals ``want``."""
+    _ck(_lib.lib().mb_expect_scalar(x.data_ptr(), float(want), _stream()), "expect_scalar")
 
 
 def adamw(p, g, m, v, lp, chunks, tensors, nchunks, lr_t, beta1, beta2, eps, step, grad_scale=1.0,

@@ -7,6 +7,8 @@ gradient for that parameter; otherwise the gradient is returned normally.
 """
 from __future__ import annotations
 
+import contextlib
+
 import torch
 from torch.autograd import Function
 
@@ -418,19 +420,44 @@ def attention_block(qkv: torch.Tensor, q_norm_w, k_norm_w, pos: torch.Tensor | N
 # --------------------------------------------------------------------------- linear + cross-entropy
 CE_CHUNK_ROWS = 4096
 CE_STORE_LIMIT_BYTES = 12 << 30
+_BACKWARD_SCALE: float | None = None
+
+
+@contextlib.contextmanager
+def loss_backward_scale(scale: float | None):
+    """Promise that ``backward`` will reach every loss computed inside this block with the output gradient
+    ``scale`` (1 / gradient-accumulation steps in the trainer).  ``linear_cross_entropy`` then produces dH and dW
+    chunk by chunk while the logits chunk is still at hand, so no logits or logit gradients outlive the forward
+    pass; its backward checks the promise on the device and records a status error if it was broken."""
+    global _BACKWARD_SCALE
+    old, _BACKWARD_SCALE = _BACKWARD_SCALE, scale
+    try:
+        yield
+    finally:
+        _BACKWARD_SCALE = old
 
 
 class _LinearCE(Function):
     """mean CE(h·Wᵀ, labels) over labels != -100 without holding all logits at once.
 
-    Forward walks row chunks: logits chunk = GEMM, then one kernel produces the chunk's loss and
-    overwrites the logits with d(loss)/d(logits).  Those gradient chunks are kept (or recomputed if
-    they would exceed ``CE_STORE_LIMIT_BYTES``) and backward turns them into dH and dW with two
-    GEMMs per chunk; dW accumulates in fp32 (directly into ``main_grad`` of a tied embedding).
+    Forward walks row chunks.  The logits GEMM's epilogue leaves per-tile (max, sum-exp) records and the target logit
+    (online log-sum-exp: no separate pass over the logits); one kernel merges them per row, one pass turns the chunk
+    into d(loss)/d(logits) in place.  With a promised output gradient (``loss_backward_scale``) the chunk is consumed
+    at once by the dH and dW GEMMs and its buffer is reused by the next chunk; otherwise the gradient chunks are kept
+    (or recomputed if they would exceed ``CE_STORE_LIMIT_BYTES``) and backward runs the two GEMMs per chunk.  dW
+    accumulates in fp32 (directly into ``main_grad`` of a tied embedding).
     """
 
     @staticmethod
-    def forward(ctx, h, w, labels, logit_scale):
+    def _chunk(C, h, w, labels, r0, r1, logit_scale, rec, loss_sum, gsl, buf, write_grad):
+        logits, stats, tgt = C.gemm_ce(h[r0:r1], w, labels[r0:r1], 0, logit_scale,
+                                       logits=None if buf is None else buf[: r1 - r0], store_logits=write_grad)
+        C.ce_merge(stats, tgt, rec[r0:r1])
+        C.ce_grad(logits, labels[r0:r1], [rec[r0:r1].data_ptr()], loss_sum, gsl, 0, write_grad, rows=r1 - r0)
+        return logits
+
+    @staticmethod
+    def forward(ctx, h, w, labels, logit_scale, ahead):
         C = _C()
         M, D = h.shape
         V = w.shape[0]
@@ -438,40 +465,57 @@ class _LinearCE(Function):
         nvalid = (labels != ref.IGNORE_INDEX).sum().clamp_min(1).to(torch.float32)
         gs = (1.0 / nvalid).reshape(1)
         loss_sum = torch.zeros(1, device=h.device, dtype=torch.float32)
-        store = ctx.needs_input_grad[0] and (M * V * 2 <= CE_STORE_LIMIT_BYTES)
-        chunks = []
+        rec = torch.empty(M, 4, device=h.device, dtype=torch.float32)
+        need = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        ahead = ahead if need else None
+        store = need and ahead is None and (M * V * 2 <= CE_STORE_LIMIT_BYTES)
+        gsl = gs * (logit_scale * (ahead if ahead is not None else 1.0))
+        chunks, dh, dw_buf, buf = [], None, None, None
+        mg = getattr(w, "main_grad", None)
+        if ahead is not None:
+            dh = torch.empty_like(h)
+            dw_buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+            buf = torch.empty(min(M, CE_CHUNK_ROWS), V, device=h.device, dtype=torch.bfloat16)
         for r0 in range(0, M, CE_CHUNK_ROWS):
             r1 = min(M, r0 + CE_CHUNK_ROWS)
-            logits = C.gemm(h[r0:r1], w)
-            C.ce_fwd_bwd(logits, labels[r0:r1], loss_sum, gs, logit_scale, write_grad=store)
-            if store:
-                chunks.append(logits)
-        ctx.save_for_backward(h, w, labels, gs, *chunks)
-        ctx.store = store
-        ctx.logit_scale = logit_scale
+            dl = _LinearCE._chunk(C, h, w, labels, r0, r1, logit_scale, rec, loss_sum, gsl, buf,
+                                  store or ahead is not None)
+            if ahead is not None:
+                C.gemm(dl, w, b_mn=True, out=dh[r0:r1])                                   # [R,V] @ [V,D]
+                C.gemm(dl, h[r0:r1], a_mn=True, b_mn=True, out=dw_buf, epi=C.EPI_F32_ACC)
+            elif store:
+                chunks.append(dl)
+        ctx.ahead, ctx.store, ctx.logit_scale, ctx.has_mg = ahead, store, logit_scale, mg is not None
+        if ahead is not None:
+            ctx.save_for_backward(dh, *(() if mg is not None else (dw_buf,)))
+        else:
+            ctx.save_for_backward(h, w, labels, gsl, rec, *chunks)
         return (loss_sum * gs).reshape(())
 
     @staticmethod
     def backward(ctx, gout):
         C = _C()
-        h, w, labels, gs, *chunks = ctx.saved_tensors
+        if ctx.ahead is not None:
+            dh, *rest = ctx.saved_tensors
+            C.expect_scalar(gout.detach().reshape(1).to(torch.float32).contiguous(), ctx.ahead)
+            return dh, (None if ctx.has_mg else rest[0].to(dh.dtype)), None, None, None
+        h, w, labels, gsl, rec, *chunks = ctx.saved_tensors
         M, D = h.shape
         g = gout.reshape(1).to(torch.float32).contiguous()
         dh = torch.empty_like(h)
         mg = getattr(w, "main_grad", None)
         dw_buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
-        scratch = torch.zeros(1, device=h.device, dtype=torch.float32)
         for i, r0 in enumerate(range(0, M, CE_CHUNK_ROWS)):
             r1 = min(M, r0 + CE_CHUNK_ROWS)
             if ctx.store:
                 dl = chunks[i]
-            else:
-                dl = C.gemm(h[r0:r1], w)
-                C.ce_fwd_bwd(dl, labels[r0:r1], scratch, gs, ctx.logit_scale, write_grad=True)
+            else:  # the row records are kept: only the logits are recomputed
+                dl = C.gemm(h[r0:r1], w, alpha=ctx.logit_scale)
+                C.ce_grad(dl, labels[r0:r1], [rec[r0:r1].data_ptr()], None, gsl, 0, True)
             C.gemm(dl, w, b_mn=True, out=dh[r0:r1], alpha_dev=g)                      # [R,V] @ [V,D]
             C.gemm(dl, h[r0:r1], a_mn=True, b_mn=True, out=dw_buf, epi=C.EPI_F32_ACC, alpha_dev=g)
         dw = None if mg is not None else dw_buf.to(w.dtype)
-        return dh, dw, None, None
+        return dh, dw, None, None, None
 
 
 def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
@@ -479,7 +523,7 @@ def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
     """Mean cross-entropy of ``h @ w.T * logit_scale`` against ``labels`` (ignore_index = -100)."""
     h2 = h.reshape(-1, h.shape[-1])
     if use_native(h2, w) and w.shape[0] % 8 == 0:
-        return _LinearCE.apply(h2.contiguous(), w, labels, logit_scale)
+        return _LinearCE.apply(h2.contiguous(), w, labels, logit_scale, _BACKWARD_SCALE)
     return ref.linear_cross_entropy(h2, w, labels.reshape(-1), logit_scale)
 
 

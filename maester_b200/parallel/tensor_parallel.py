@@ -183,8 +183,114 @@ def _native_logits(h: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.linear(h, w).float()
 
 
+class _RecordExchange:
+    """Symmetric fp32 buffer ``[2, M, 4]`` through which the ranks of a tensor-parallel group read one another's
+    per-row (max, sum-exp, target) records; the two halves alternate between calls, so a rank that runs ahead into
+    its next loss never overwrites records a slower peer is still reading."""
+
+    def __init__(self, tp: TPInfo, M: int, device):
+        from maester_b200.parallel.symm import SymmBuffer
+        self.M = M
+        self.buf = SymmBuffer(2 * M * 4, torch.float32, device, tp.group)
+        self.calls = 0
+
+    def next_half(self):
+        half = self.calls & 1
+        self.calls += 1
+        return self.buf.tensor.view(2, self.M, 4)[half], [p + half * self.M * 16 for p in self.buf.peer_ptrs]
+
+
+_EXCHANGES: dict = {}
+
+
+def _record_exchange(tp: TPInfo, M: int, device) -> _RecordExchange:
+    key = (id(tp.group), M, device.index)
+    if key not in _EXCHANGES:
+        _EXCHANGES[key] = _RecordExchange(tp, M, device)
+    return _EXCHANGES[key]
+
+
+class _VocabParallelCENative(torch.autograd.Function):
+    """The loss-parallel cross-entropy on the native kernels: every rank's logits GEMM leaves per-row records of its
+    vocabulary slice, the ranks read each other's records through symmetric memory (one bounded barrier per chunk,
+    no all-reduce of statistics), and every rank turns its own logits into ``softmax_global - onehot`` in place.
+    Gradients are produced during forward when the output gradient is promised (``ops.loss_backward_scale``)."""
+
+    @staticmethod
+    def forward(ctx, h, w, labels, tp: TPInfo, ahead):
+        from maester_b200.ops import cuda as C
+        import maester_b200.ops.functional as Fm
+        M, D = h.shape
+        Vl = w.shape[0]
+        v0 = tp.rank * Vl
+        labels = labels.reshape(-1).to(torch.int64).contiguous()
+        nvalid = (labels != -100).sum().clamp_min(1).to(torch.float32)
+        gs = (1.0 / nvalid).reshape(1)
+        need = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        ahead = ahead if need else None
+        gsl = gs * (ahead if ahead is not None else 1.0)
+        loss_sum = torch.zeros(1, device=h.device, dtype=torch.float32)
+        ex = _record_exchange(tp, M, h.device)
+        rec, peers = ex.next_half()
+        mg = getattr(w, "main_grad", None)
+        grads, dh, dw = [], None, None
+        if ahead is not None:
+            dh = torch.empty_like(h)
+            dw = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        rows = Fm.CE_CHUNK_ROWS
+        buf = torch.empty(min(M, rows), Vl, device=h.device, dtype=torch.bfloat16) if ahead is not None else None
+        for r0 in range(0, M, rows):
+            r1 = min(M, r0 + rows)
+            logits, stats, tgt = C.gemm_ce(h[r0:r1], w, labels[r0:r1], v0, 1.0,
+                                           logits=None if buf is None else buf[: r1 - r0], store_logits=need)
+            C.ce_merge(stats, tgt, rec[r0:r1])
+            ex.buf.barrier()     # every rank's records of this chunk are written
+            C.ce_grad(logits, labels[r0:r1], [p + r0 * 16 for p in peers], loss_sum, gsl, v0, need, rows=r1 - r0)
+            if ahead is not None:
+                C.gemm(logits, w, b_mn=True, out=dh[r0:r1])
+                C.gemm(logits, h[r0:r1], a_mn=True, b_mn=True, out=dw, epi=C.EPI_F32_ACC)
+            elif need:
+                grads.append(logits)
+        ctx.tp, ctx.ahead, ctx.has_mg = tp, ahead, mg is not None
+        if ahead is not None:
+            dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=tp.group)   # dH is a partial sum over the slices
+            ctx.save_for_backward(dh, *(() if mg is not None else (dw,)))
+        else:
+            ctx.save_for_backward(h, w, *grads)
+        return (loss_sum * gs).reshape(())
+
+    @staticmethod
+    def backward(ctx, gout):
+        from maester_b200.ops import cuda as C
+        import maester_b200.ops.functional as Fm
+        if ctx.ahead is not None:
+            dh, *rest = ctx.saved_tensors
+            C.expect_scalar(gout.detach().reshape(1).to(torch.float32).contiguous(), ctx.ahead)
+            return dh, (None if ctx.has_mg else rest[0].to(dh.dtype)), None, None, None
+        h, w, *grads = ctx.saved_tensors
+        dh = torch.empty_like(h)
+        mg = getattr(w, "main_grad", None)
+        dw = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        scale = gout.detach().to(torch.float32).reshape(1).contiguous()
+        r0 = 0
+        for g in grads:
+            r1 = r0 + g.shape[0]
+            C.gemm(g, w, b_mn=True, out=dh[r0:r1], alpha_dev=scale)
+            C.gemm(g, h[r0:r1], a_mn=True, b_mn=True, out=dw, epi=C.EPI_F32_ACC, alpha_dev=scale)
+            r0 = r1
+        dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=ctx.tp.group)
+        return dh, (None if mg is not None else dw.to(w.dtype)), None, None, None
+
+
 def vocab_parallel_cross_entropy(h: torch.Tensor, w_local: torch.Tensor, labels: torch.Tensor, tp: TPInfo):
-    return _VocabParallelCE.apply(h.reshape(-1, h.shape[-1]), w_local, labels, tp)
+    from maester_b200 import ops
+    from maester_b200.parallel.symm import symmetric_memory_available
+    h2 = h.reshape(-1, h.shape[-1])
+    if (ops.use_native(h2, w_local) and w_local.shape[0] % 8 == 0 and h2.shape[1] % 8 == 0 and tp.size <= 8
+            and symmetric_memory_available(tp.group)):
+        import maester_b200.ops.functional as Fm
+        return _VocabParallelCENative.apply(h2.contiguous(), w_local, labels, tp, Fm._BACKWARD_SCALE)
+    return _VocabParallelCE.apply(h2, w_local, labels, tp)
 
 
 # ------------------------------------------------------------------------------ applying the plan

@@ -26,6 +26,7 @@ from maester_b200.models import (
     model_name_to_parallelize,
     models_config,
 )
+from maester_b200 import ops
 from maester_b200.ops import reference as ref
 from maester_b200.parallel import ParallelDims, materialize
 from maester_b200.utils import clip_grad_norm, device_for_training, get_peak_flops
@@ -180,8 +181,11 @@ class Trainer:
             from maester_b200.parallel.context_parallel import shard_batch_for_cp
             b = shard_batch_for_cp(b, self.cp)
         if cfg.enable_cut_cross_entropy:
-            loss = self.model(b["input_ids"], b["labels"], position_ids=b.get("position_ids"),
-                              document_ids=b.get("document_ids"))
+            # the loss below reaches backward() with exactly this output gradient: the loss layer may produce its
+            # gradients chunk by chunk during forward and keep no logits
+            with ops.loss_backward_scale(1.0 / self.grad_accum):
+                loss = self.model(b["input_ids"], b["labels"], position_ids=b.get("position_ids"),
+                                  document_ids=b.get("document_ids"))
         else:
             pred = self.model(b["input_ids"], position_ids=b.get("position_ids"), document_ids=b.get("document_ids"))
             loss = ref.cross_entropy(pred, b["labels"])

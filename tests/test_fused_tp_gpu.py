@@ -89,3 +89,56 @@ def test_fused_gemm_reduce_scatter_matches_nccl(tmp_path):
         assert a[0] == pytest.approx(b[0], abs=2e-2)
         for k in a[1]:
             assert ((a[1][k] - b[1][k]).norm() / (a[1][k].norm() + 1e-12)).item() < 2e-2, k
+
+
+def _ce_worker(rank, world, port, out_dir):
+    """Loss-parallel cross-entropy on the native kernels (records exchanged through symmetric memory) against the
+    fp32 definition over the whole vocabulary; stored and produced-during-forward gradients; repeated calls."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from maester_b200 import ops
+        from maester_b200.ops import cuda as C
+        from maester_b200.ops import reference as ref
+        import maester_b200.ops.functional as Fm
+        from maester_b200.parallel.tensor_parallel import (TPInfo, _VocabParallelCENative,
+                                                            vocab_parallel_cross_entropy)
+        tp = TPInfo(dist.group.WORLD, world, rank)
+        Fm.CE_CHUNK_ROWS = 256
+        M, D, V = 700, 256, 4000
+        Vl = V // world
+        g = torch.Generator(device="cuda").manual_seed(11)       # same tensors on every rank
+        worst = 0.0
+        for call in range(4):
+            h = torch.randn(M, D, device="cuda", generator=g).to(torch.bfloat16).requires_grad_()
+            wfull = (torch.randn(V, D, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+            labels = torch.randint(0, V, (M,), device="cuda", generator=g)
+            labels[::6] = -100
+            w = wfull[rank * Vl:(rank + 1) * Vl].clone().requires_grad_()
+            ahead = 0.5 if call % 2 else None
+            with ops.loss_backward_scale(ahead):
+                loss = vocab_parallel_cross_entropy(h, w, labels, tp)
+            assert isinstance(loss.grad_fn, _VocabParallelCENative._backward_cls), "the native path did not run"
+            (loss * 0.5).backward()
+            hf, wf = h.detach().float().requires_grad_(), wfull.float().requires_grad_()
+            want = ref.linear_cross_entropy(hf, wf, labels, 1.0)
+            (want * 0.5).backward()
+            rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()
+            errs = (abs(loss.item() - want.item()), rel(h.grad, hf.grad), rel(w.grad, wf.grad[rank * Vl:(rank + 1) * Vl]))
+            assert errs[0] < 2e-2 and errs[1] < 2e-2 and errs[2] < 2e-2, (call, errs)
+            worst = max(worst, *errs)
+        C.check_status()
+        torch.save(worst, os.path.join(out_dir, f"ce{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_loss_parallel_cross_entropy_exchanges_records_through_peer_memory(tmp_path):
+    import torch.multiprocessing as mp
+    from test_parallel_cpu import _free_port
+    mp.spawn(_ce_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    assert all(torch.load(os.path.join(tmp_path, f"ce{r}.pt")) < 2e-2 for r in range(2))

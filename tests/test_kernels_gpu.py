@@ -427,6 +427,114 @@ def test_linear_cross_entropy_fused():
     assert _rel(w.grad, wf.grad) < 2e-2
 
 
+@pytest.mark.parametrize("M,D,V,scale", [(300, 256, 5000, 1.0), (512, 640, 262208, 1.0), (130, 128, 1000, 0.5)])
+def test_logits_gemm_leaves_online_lse_records(M, D, V, scale):
+    """The logits GEMM's epilogue statistics (per 256-column tile) merge to the exact row log-sum-exp and target."""
+    from maester_b200.ops import cuda as C
+    torch.manual_seed(2)
+    h = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(V, D, device="cuda") * 0.2).to(torch.bfloat16)
+    labels = torch.randint(0, V, (M,), device="cuda")
+    labels[::9] = -100
+    logits, stats, tgt = C.gemm_ce(h, w, labels, 0, scale)
+    want = (h.float() @ w.float().T) * scale
+    assert (logits.float() - want).abs().max().item() < 0.02 * want.abs().max().item() + 1e-2
+    rec = torch.empty(M, 4, device="cuda")
+    C.ce_merge(stats, tgt, rec)
+    lf = logits.float()                      # the records describe the stored (rounded) logits exactly
+    lse = torch.logsumexp(lf, dim=1)
+    got = rec[:, 0] + rec[:, 1].log()
+    assert (got - lse).abs().max().item() < 2e-4
+    valid = labels != -100
+    pick = lf.gather(1, labels.clamp_min(0)[:, None]).squeeze(1)
+    assert torch.equal(rec[valid, 2], pick[valid]) and bool((rec[~valid, 2] == 0).all())
+    # without storing logits the records are the same
+    none, stats2, tgt2 = C.gemm_ce(h, w, labels, 0, scale, store_logits=False)
+    assert none is None and torch.equal(stats2, stats) and torch.equal(tgt2, tgt)
+    # loss and gradient from the records
+    loss = torch.zeros(1, device="cuda")
+    gs = (1.0 / valid.sum().float()).reshape(1)
+    C.ce_grad(logits, labels, [rec.data_ptr()], loss, gs)
+    lr = lf.clone().requires_grad_()
+    ref_loss = torch.nn.functional.cross_entropy(lr, labels, ignore_index=-100, reduction="sum")
+    (ref_loss * gs).backward()
+    assert abs(loss.item() - ref_loss.item()) / ref_loss.item() < 1e-4
+    assert _rel(logits, lr.grad) < 1e-2
+    C.check_status()
+
+
+def test_vocabulary_slices_combine_through_their_records():
+    """Two slices of the vocabulary, each with its own records: the combined loss and gradients equal the whole."""
+    from maester_b200.ops import cuda as C
+    torch.manual_seed(3)
+    M, D, V = 200, 256, 3216
+    h = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(V, D, device="cuda") * 0.2).to(torch.bfloat16)
+    labels = torch.randint(0, V, (M,), device="cuda")
+    labels[::4] = -100
+    halves, recs = [], []
+    for r in range(2):
+        v0 = r * (V // 2)
+        lg, st, tg = C.gemm_ce(h, w[v0:v0 + V // 2], labels, v0)
+        rec = torch.empty(M, 4, device="cuda")
+        C.ce_merge(st, tg, rec)
+        halves.append(lg)
+        recs.append(rec)
+    full = torch.cat([x.float() for x in halves], dim=1).requires_grad_()
+    ref_loss = torch.nn.functional.cross_entropy(full, labels, ignore_index=-100, reduction="sum")
+    gs = (1.0 / (labels != -100).sum().float()).reshape(1)
+    (ref_loss * gs).backward()
+    for r in range(2):
+        loss = torch.zeros(1, device="cuda")
+        C.ce_grad(halves[r], labels, [x.data_ptr() for x in recs], loss, gs, v0=r * (V // 2))
+        assert abs(loss.item() - ref_loss.item()) / ref_loss.item() < 1e-4
+        assert _rel(halves[r], full.grad[:, r * (V // 2):(r + 1) * (V // 2)]) < 1e-2
+
+
+@pytest.mark.parametrize("mode", ["stored", "recomputed", "ahead"])
+def test_linear_cross_entropy_modes_agree_with_the_oracle(mode):
+    from maester_b200 import ops
+    from maester_b200.ops import cuda as C
+    import maester_b200.ops.functional as Fm
+    torch.manual_seed(6)
+    M, D, V = 900, 256, 6008
+    h = torch.randn(M, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(V, D, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, V, (M,), device="cuda")
+    labels[::5] = -100
+    old = Fm.CE_CHUNK_ROWS, Fm.CE_STORE_LIMIT_BYTES
+    Fm.CE_CHUNK_ROWS = 256
+    if mode == "recomputed":
+        Fm.CE_STORE_LIMIT_BYTES = 0
+    try:
+        with ops.loss_backward_scale(0.25 if mode == "ahead" else None):
+            loss = ops.linear_cross_entropy(h, w, labels, 0.5)
+        (loss * 0.25).backward()
+    finally:
+        Fm.CE_CHUNK_ROWS, Fm.CE_STORE_LIMIT_BYTES = old
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    want = ref.linear_cross_entropy(hf, wf, labels, 0.5)
+    (want * 0.25).backward()
+    assert abs(loss.item() - want.item()) < 2e-2
+    assert _rel(h.grad, hf.grad) < 2e-2
+    assert _rel(w.grad, wf.grad) < 2e-2
+    C.check_status()
+
+
+def test_a_broken_gradient_promise_is_reported_not_ignored():
+    from maester_b200 import ops
+    from maester_b200.ops import cuda as C
+    h = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(512, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    labels = torch.randint(0, 512, (256,), device="cuda")
+    with ops.loss_backward_scale(1.0):
+        loss = ops.linear_cross_entropy(h, w, labels)
+    (loss * 3.0).backward()
+    with pytest.raises(RuntimeError, match="different output gradient"):
+        C.check_status()
+    C.check_status()   # the status word was cleared: later work is unaffected
+
+
 @pytest.mark.parametrize("M,K", [(256, 64), (1000, 328), (2560, 2560)])
 def test_syrk_triangular_schedule(M, K):
     """A A^T (+ beta C) computed on the tiles below the diagonal and mirrored equals the full product."""

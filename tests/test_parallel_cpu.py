@@ -12,7 +12,9 @@ import torch.multiprocessing as mp
 
 from maester_b200.config import Config
 
-ADAMW = [{"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3, "betas": (0.9, 0.95), "weight_decay": 0.1, "eps": 1e-6},
+# eps well above the rounding noise of fp32 gradients: with a tiny eps Adam turns noise-level gradient entries (the
+# q / k projections of a freshly initialised model) into +-lr steps, and parity between two summation orders is lost
+ADAMW = [{"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3, "betas": (0.9, 0.95), "weight_decay": 0.1, "eps": 1e-4},
           "min_dim": 0}]
 
 
