@@ -176,15 +176,73 @@ def bench_moe(iters: int, small: bool) -> None:
     C.check_status()
 
 
+def bench_ce(iters: int, small: bool) -> None:
+    """LM head + cross-entropy of the Gemma-3 4B step (16384 tokens, hidden 2560, vocabulary 262144): the pieces of
+    a row chunk, and forward + backward of the whole loss in its modes."""
+    from maester_b200 import ops
+    import maester_b200.ops.functional as Fm
+    tf_peak, bw_peak = _peaks()
+    M, D, V = (4096, 2560, 32768) if small else (16384, 2560, 262144)
+    Fm.CE_CHUNK_ROWS = int(os.environ.get("MB_CE_CHUNK_ROWS", Fm.CE_CHUNK_ROWS))
+    R = min(M, Fm.CE_CHUNK_ROWS)
+    warm = 0 if small else 3
+    h = (torch.randn(M, D, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(V, D, device="cuda") * 0.02).to(torch.bfloat16).requires_grad_()
+    w.main_grad = torch.zeros(V, D, device="cuda")
+    labels = torch.randint(0, V, (M,), device="cuda")
+    gs = torch.full((1,), 1.0 / M, device="cuda")
+    fl = 2 * R * V * D
+    buf = torch.empty(R, V, device="cuda", dtype=torch.bfloat16)
+    rec = torch.empty(R, 4, device="cuda")
+    loss = torch.zeros(1, device="cuda")
+    hd, wd = h.detach(), w.detach()
+    t = timeit(lambda: C.gemm(hd[:R], wd, out=buf), iters, warm)
+    print(f"ce logits GEMM plain          [{R} x {V}]: {t:.3f} ms {fl / t / 1e9:6.0f} TF ({fl / t / 1e9 / tf_peak:.2f} of measured)")
+    t = timeit(lambda: C.gemm_ce(hd[:R], wd, labels[:R], logits=buf), iters, warm)
+    print(f"ce logits GEMM + LSE records  [{R} x {V}]: {t:.3f} ms {fl / t / 1e9:6.0f} TF ({fl / t / 1e9 / tf_peak:.2f} of measured)")
+    t = timeit(lambda: C.gemm_ce(hd[:R], wd, labels[:R], store_logits=False), iters, warm)
+    print(f"ce LSE records only (no logits stored)       : {t:.3f} ms {fl / t / 1e9:6.0f} TF")
+    _, stats, tgt = C.gemm_ce(hd[:R], wd, labels[:R], logits=buf)
+    t = timeit(lambda: C.ce_merge(stats, tgt, rec), iters, warm)
+    print(f"ce merge records: {t * 1e3:.1f} us")
+    by = 2 * R * V * 2
+    t = timeit(lambda: C.ce_grad(buf, labels[:R], [rec.data_ptr()], loss, gs), iters, warm)
+    print(f"ce gradient in place (1 read + 1 write): {t * 1e3:.1f} us {by / t / 1e6:.0f} GB/s ({by / t / 1e6 / bw_peak:.2f} of measured)")
+    t = timeit(lambda: C.ce_fwd_bwd(buf, labels[:R], loss, gs), iters, warm)
+    print(f"ce two-pass kernel (row max/sum, then gradient): {t * 1e3:.1f} us {by / t / 1e6:.0f} GB/s")
+    dh32 = torch.zeros(R, D, device="cuda")
+    dhb = torch.empty(R, D, device="cuda", dtype=torch.bfloat16)
+    fl2 = 2 * R * V * D
+    t = timeit(lambda: C.gemm(buf, wd, b_mn=True, out=dhb), iters, warm)
+    print(f"ce dH GEMM, bf16 out (one unit per tile)   : {t:.3f} ms {fl2 / t / 1e9:6.0f} TF")
+    t = timeit(lambda: C.gemm(buf, wd, b_mn=True, out=dh32, epi=C.EPI_F32_ACC), iters, warm)
+    print(f"ce dH GEMM, fp32 accumulate (contraction cut): {t:.3f} ms {fl2 / t / 1e9:6.0f} TF")
+    t = timeit(lambda: C.gemm(buf, hd[:R], a_mn=True, b_mn=True, out=w.main_grad, epi=C.EPI_F32_ACC), iters, warm)
+    print(f"ce dW GEMM, fp32 accumulate                  : {t:.3f} ms {fl2 / t / 1e9:6.0f} TF")
+    for mode in ("stored", "ahead"):
+        def step():
+            with ops.loss_backward_scale(1.0 if mode == "ahead" else None):
+                l = ops.linear_cross_entropy(h, w, labels)
+            l.backward()
+            h.grad = None
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        t = timeit(step, max(1, iters // 2), 1 if small else 2)
+        peak = (torch.cuda.max_memory_allocated() - base) / 2 ** 30
+        print(f"ce loss fwd+bwd, gradients {mode:6s}: {t:.2f} ms ({3 * 2 * M * V * D / t / 1e9:.0f} TF), "
+              f"{peak:.1f} GiB above the inputs")
+    C.check_status()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "grouped", "moe", "all"])
+    ap.add_argument("op", choices=["gemm", "attention", "elementwise", "grouped", "moe", "ce", "all"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--small", action="store_true", help="one cold launch per kernel on a small case")
     a = ap.parse_args()
     iters = 1 if a.small else a.iters
     table = {"gemm": bench_gemm, "attention": bench_attention, "elementwise": bench_elementwise, "grouped": bench_grouped,
-             "moe": bench_moe}
+             "moe": bench_moe, "ce": bench_ce}
     for name, fn in table.items():
         if a.op in (name, "all"):
             fn(iters, a.small)

@@ -98,6 +98,11 @@ __device__ __forceinline__ void glu_act_and_grad(int act, float g, float& a, flo
     da = sg * (1.f + g * (1.f - sg));
   }
 }
+__device__ __forceinline__ float exp2f_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
 
 // 32 accumulator columns of gate and the matching 32 of up for output row `row`, units j0 .. j0+31:
@@ -172,40 +177,63 @@ __device__ __forceinline__ void ce_stats_chunk(const GemmParams& p, const uint32
   using namespace mb;
   if (row >= p.M || col0 >= p.N) return;
   const int nvalid = min(32, p.N - col0);
+  // round once to bf16 pairs (what is stored), then widen again with shifts: the statistics describe the stored values
+  uint32_t pk[16];
   float v[32];
+  // (every instruction here is paid for in clocks: under the board's power limit the extra work of this epilogue
+  // slows the tensor pipe although it runs beside it, so the unit scale skips its multiplies)
+  if (alpha == 1.f) {
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = bf16_round(__uint_as_float(r[i]) * alpha);
+    for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      pk[i] = pack_bf16(__uint_as_float(r[2 * i]) * alpha, __uint_as_float(r[2 * i + 1]) * alpha);
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[2 * i] = __uint_as_float(pk[i] << 16);
+    v[2 * i + 1] = __uint_as_float(pk[i] & 0xffff0000u);
+  }
   if (p.C) {
     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
     if (nvalid == 32 && (p.ldc & 7) == 0) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 o;
-        o.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-        o.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-        o.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-        o.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-        reinterpret_cast<uint4*>(crow)[j] = o;
-      }
+      for (int j = 0; j < 4; ++j)
+        reinterpret_cast<uint4*>(crow)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
     } else {
-      for (int i = 0; i < nvalid; ++i) crow[i] = __float2bfloat16(v[i]);
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (i < nvalid) reinterpret_cast<unsigned short*>(crow)[i] = static_cast<unsigned short>(__float_as_uint(v[i]) >> 16);
     }
   }
   float cm = -INFINITY;
+  if (nvalid == 32) {
 #pragma unroll
-  for (int i = 0; i < 32; ++i) cm = fmaxf(cm, i < nvalid ? v[i] : -INFINITY);
+    for (int i = 0; i < 32; ++i) cm = fmaxf(cm, v[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      v[i] = i < nvalid ? v[i] : -INFINITY;
+      cm = fmaxf(cm, v[i]);
+    }
+  }
   const float nm = fmaxf(m, cm);
+  const float k = 1.4426950408889634f, nmk = nm * k;
   float acc = 0.f;
 #pragma unroll
-  for (int i = 0; i < 32; ++i) acc += i < nvalid ? __expf(v[i] - nm) : 0.f;
-  s = s * __expf(m - nm) + acc;   // m == -inf on the first chunk: exp(-inf) = 0 and s = 0
+  for (int i = 0; i < 32; ++i) acc += exp2f_approx(fmaf(v[i], k, -nmk));   // exp(v - nm); columns past N give 0
+  s = s * exp2f_approx((m - nm) * k) + acc;   // m == -inf on the first chunk: the factor is 0 and s was 0
   m = nm;
   const long long rel = lab - col0;
   if (rel >= 0 && rel < nvalid) {
-    float t = 0.f;
+    // bit masks instead of a select chain: the compiler turns the chain into an indexed read of v[], which moves
+    // the whole array to local memory
+    uint32_t t = 0u;
+    const uint32_t irel = static_cast<uint32_t>(rel);
 #pragma unroll
-    for (int i = 0; i < 32; ++i) t = (i == static_cast<int>(rel)) ? v[i] : t;
-    p.ce_tgt[row] = t;
+    for (uint32_t i = 0; i < 32; ++i) t |= __float_as_uint(v[i]) & (0u - static_cast<uint32_t>(i == irel));
+    p.ce_tgt[row] = __uint_as_float(t);
   }
 }
 

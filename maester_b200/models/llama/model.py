@@ -224,16 +224,20 @@ class Transformer(nn.Module):
 
     def forward(self, tokens, labels=None, position_ids=None, document_ids=None):
         B, S = tokens.shape
-        h = ops.embedding(tokens, self.tok_embeddings.weight)
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            # sequence parallel: this rank embeds its slice of the flattened tokens only; the embedding's gradient
+            # is therefore a partial sum, completed by the all-reduce of replicated parameters' gradients
+            from maester_b200.parallel.tensor_parallel import (gather_seq, local_tokens, sum_over_group,
+                                                                vocab_parallel_cross_entropy)
+            tp.batch = B
+            h = ops.embedding(local_tokens(tokens, tp), self.tok_embeddings.weight)
+        else:
+            h = ops.embedding(tokens, self.tok_embeddings.weight)
         if position_ids is not None and position_ids.dim() == 1:
             position_ids = position_ids.unsqueeze(0)
         if position_ids is None:
             position_ids = torch.arange(S, device=tokens.device, dtype=torch.int32)[None].expand(B, S)
-        tp = getattr(self, "tp", None)
-        if tp is not None:
-            from maester_b200.parallel.tensor_parallel import gather_seq, scatter_seq, vocab_parallel_cross_entropy
-            tp.batch = B
-            h = scatter_seq(h, tp)  # every rank embeds all tokens, keeps its slice of the flattened tokens
         for layer in self.layers.values():
             h = layer(h, position_ids, self.inv_freq, self.rope_cs, document_ids)
         h = self.norm(h)
@@ -241,9 +245,15 @@ class Transformer(nn.Module):
             h = h * (self.model_args.mup_output_alpha / self.model_args.mup_width_mul)
         w = self.tok_embeddings.weight if self.model_args.tied_embeddings else self.output.weight
         if tp is not None:
-            h = gather_seq(h, tp)
-            if self.model_args.tied_embeddings:  # replicated head: ordinary loss on the gathered sequence
-                return ops.linear_cross_entropy(h, w, labels) if labels is not None else ops.linear(h, w)
+            if self.model_args.tied_embeddings:
+                # replicated head: every rank scores its own token slice against the whole vocabulary; the ranks'
+                # partial losses (each divided by the global count of valid labels) add up to the mean
+                if labels is not None:
+                    nvalid = (labels != -100).sum()
+                    part = ops.linear_cross_entropy(h, w, local_tokens(labels, tp), nvalid=nvalid)
+                    return sum_over_group(part, tp)
+                return gather_seq(ops.linear(h, w), tp, same_grad=True)   # [B, S, V], identical on every rank
+            h = gather_seq(h, tp)   # backward sums the ranks' partial dH (one vocabulary slice each)
             if labels is not None:
                 return vocab_parallel_cross_entropy(h, w, labels, tp)
             logits = ops.linear(h, w)  # vocabulary-sharded logits [B, S, V/tp]

@@ -457,12 +457,14 @@ class _LinearCE(Function):
         return logits
 
     @staticmethod
-    def forward(ctx, h, w, labels, logit_scale, ahead):
+    def forward(ctx, h, w, labels, logit_scale, ahead, nvalid):
         C = _C()
         M, D = h.shape
         V = w.shape[0]
         labels = labels.reshape(-1).to(torch.int64).contiguous()
-        nvalid = (labels != ref.IGNORE_INDEX).sum().clamp_min(1).to(torch.float32)
+        if nvalid is None:
+            nvalid = (labels != ref.IGNORE_INDEX).sum()
+        nvalid = nvalid.detach().clamp_min(1).to(torch.float32)
         gs = (1.0 / nvalid).reshape(1)
         loss_sum = torch.zeros(1, device=h.device, dtype=torch.float32)
         rec = torch.empty(M, 4, device=h.device, dtype=torch.float32)
@@ -473,7 +475,9 @@ class _LinearCE(Function):
         chunks, dh, dw_buf, buf = [], None, None, None
         mg = getattr(w, "main_grad", None)
         if ahead is not None:
-            dh = torch.empty_like(h)
+            # dH of a chunk has few output tiles and a very long contraction (the vocabulary): accumulating in fp32
+            # lets the GEMM cut the contraction into several work units per tile and fill its waves
+            dh = torch.zeros(M, D, device=h.device, dtype=torch.float32)
             dw_buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
             buf = torch.empty(min(M, CE_CHUNK_ROWS), V, device=h.device, dtype=torch.bfloat16)
         for r0 in range(0, M, CE_CHUNK_ROWS):
@@ -481,13 +485,13 @@ class _LinearCE(Function):
             dl = _LinearCE._chunk(C, h, w, labels, r0, r1, logit_scale, rec, loss_sum, gsl, buf,
                                   store or ahead is not None)
             if ahead is not None:
-                C.gemm(dl, w, b_mn=True, out=dh[r0:r1])                                   # [R,V] @ [V,D]
+                C.gemm(dl, w, b_mn=True, out=dh[r0:r1], epi=C.EPI_F32_ACC)                # [R,V] @ [V,D]
                 C.gemm(dl, h[r0:r1], a_mn=True, b_mn=True, out=dw_buf, epi=C.EPI_F32_ACC)
             elif store:
                 chunks.append(dl)
         ctx.ahead, ctx.store, ctx.logit_scale, ctx.has_mg = ahead, store, logit_scale, mg is not None
         if ahead is not None:
-            ctx.save_for_backward(dh, *(() if mg is not None else (dw_buf,)))
+            ctx.save_for_backward(dh.to(h.dtype), *(() if mg is not None else (dw_buf,)))
         else:
             ctx.save_for_backward(h, w, labels, gsl, rec, *chunks)
         return (loss_sum * gs).reshape(())
@@ -498,11 +502,11 @@ class _LinearCE(Function):
         if ctx.ahead is not None:
             dh, *rest = ctx.saved_tensors
             C.expect_scalar(gout.detach().reshape(1).to(torch.float32).contiguous(), ctx.ahead)
-            return dh, (None if ctx.has_mg else rest[0].to(dh.dtype)), None, None, None
+            return dh, (None if ctx.has_mg else rest[0].to(dh.dtype)), None, None, None, None
         h, w, labels, gsl, rec, *chunks = ctx.saved_tensors
         M, D = h.shape
         g = gout.reshape(1).to(torch.float32).contiguous()
-        dh = torch.empty_like(h)
+        dh = torch.zeros(M, D, device=h.device, dtype=torch.float32)
         mg = getattr(w, "main_grad", None)
         dw_buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
         for i, r0 in enumerate(range(0, M, CE_CHUNK_ROWS)):
@@ -512,19 +516,25 @@ class _LinearCE(Function):
             else:  # the row records are kept: only the logits are recomputed
                 dl = C.gemm(h[r0:r1], w, alpha=ctx.logit_scale)
                 C.ce_grad(dl, labels[r0:r1], [rec[r0:r1].data_ptr()], None, gsl, 0, True)
-            C.gemm(dl, w, b_mn=True, out=dh[r0:r1], alpha_dev=g)                      # [R,V] @ [V,D]
+            C.gemm(dl, w, b_mn=True, out=dh[r0:r1], epi=C.EPI_F32_ACC, alpha_dev=g)   # [R,V] @ [V,D]
             C.gemm(dl, h[r0:r1], a_mn=True, b_mn=True, out=dw_buf, epi=C.EPI_F32_ACC, alpha_dev=g)
         dw = None if mg is not None else dw_buf.to(w.dtype)
-        return dh, dw, None, None, None
+        return dh.to(h.dtype), dw, None, None, None, None
 
 
 def linear_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor,
-                         logit_scale: float = 1.0) -> torch.Tensor:
-    """Mean cross-entropy of ``h @ w.T * logit_scale`` against ``labels`` (ignore_index = -100)."""
+                         logit_scale: float = 1.0, nvalid: torch.Tensor | None = None) -> torch.Tensor:
+    """Mean cross-entropy of ``h @ w.T * logit_scale`` against ``labels`` (ignore_index = -100).
+
+    ``nvalid`` (0-d tensor) replaces the count of valid labels as the divisor: a rank that holds a slice of the
+    tokens passes the count over all slices, and the sum of the ranks' results is the mean over all tokens."""
     h2 = h.reshape(-1, h.shape[-1])
     if use_native(h2, w) and w.shape[0] % 8 == 0:
-        return _LinearCE.apply(h2.contiguous(), w, labels, logit_scale, _BACKWARD_SCALE)
-    return ref.linear_cross_entropy(h2, w, labels.reshape(-1), logit_scale)
+        return _LinearCE.apply(h2.contiguous(), w, labels, logit_scale, _BACKWARD_SCALE, nvalid)
+    if nvalid is None:
+        return ref.linear_cross_entropy(h2, w, labels.reshape(-1), logit_scale)
+    total = ref.linear_cross_entropy(h2, w, labels.reshape(-1), logit_scale, reduction="sum")
+    return total / nvalid.detach().clamp_min(1).to(total.dtype)
 
 
 # --------------------------------------------------------------------------- grouped (expert) linear

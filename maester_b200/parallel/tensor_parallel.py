@@ -93,8 +93,55 @@ class _ScatterSeq(torch.autograd.Function):
         return _all_gather_seq(g, ctx.tp), None
 
 
-def gather_seq(x: torch.Tensor, tp: TPInfo | None) -> torch.Tensor:
-    return x if tp is None or tp.size == 1 else _GatherSeq.apply(x, tp)
+class _GatherSeqSameGrad(torch.autograd.Function):
+    """All-gather of sequence slices whose consumers compute the same thing on every rank (a replicated loss on the
+    gathered tensor): the incoming gradient is already complete and identical everywhere, so backward keeps this
+    rank's slice instead of summing the ranks' copies."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return _all_gather_seq(x, tp)
+
+    @staticmethod
+    def backward(ctx, g):
+        tp = ctx.tp
+        D = g.shape[-1]
+        t = (g.numel() // D) // tp.size
+        return g.reshape(-1, D)[tp.rank * t:(tp.rank + 1) * t].contiguous().view(1, t, D), None
+
+
+class _SumOverGroup(torch.autograd.Function):
+    """Sum of per-rank partial losses; every rank's partial enters the total with weight one."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        y = x.detach().clone()
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def gather_seq(x: torch.Tensor, tp: TPInfo | None, same_grad: bool = False) -> torch.Tensor:
+    """[1, T/tp, D] -> [B, S, D].  ``same_grad``: what follows is replicated on every rank (see
+    ``_GatherSeqSameGrad``); otherwise the ranks' gradients are partial sums and backward reduce-scatters them."""
+    if tp is None or tp.size == 1:
+        return x
+    return _GatherSeqSameGrad.apply(x, tp) if same_grad else _GatherSeq.apply(x, tp)
+
+
+def local_tokens(tokens: torch.Tensor, tp: TPInfo) -> torch.Tensor:
+    """This rank's slice of the flattened tokens (or labels), shaped [1, T/tp]."""
+    flat = tokens.reshape(-1)
+    t = flat.numel() // tp.size
+    return flat[tp.rank * t:(tp.rank + 1) * t].view(1, t)
+
+
+def sum_over_group(x: torch.Tensor, tp: TPInfo) -> torch.Tensor:
+    return _SumOverGroup.apply(x, tp.group)
 
 
 def reduce_scatter_seq(x: torch.Tensor, tp: TPInfo | None) -> torch.Tensor:
@@ -112,6 +159,9 @@ class _VocabParallelCE(torch.autograd.Function):
     Per chunk of rows: local logits, local log-sum-exp and target logit, two small all-reduces over
     the TP group to form the global log-sum-exp and target logit, then the local gradient
     ``softmax_global − onehot``.  Backward turns the kept gradient chunks into dH and dW_local.
+
+    dH is this rank's PARTIAL sum (its vocabulary slice only): ``h`` comes out of the sequence gather, whose backward
+    reduce-scatters, i.e. sums the ranks' partial gradients.
     """
 
     CHUNK = 4096
@@ -170,8 +220,6 @@ class _VocabParallelCE(torch.autograd.Function):
             else:
                 dh[r0:r1] = ((g.float() @ w.float()) * gout).to(h.dtype)
                 dw.add_((g.float().t() @ h[r0:r1].float()) * gout)
-        # dH is a partial sum over the vocabulary shards
-        dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=ctx.tp.group)
         return dh, (None if mg is not None else dw.to(w.dtype)), None, None
 
 
@@ -214,7 +262,9 @@ class _VocabParallelCENative(torch.autograd.Function):
     """The loss-parallel cross-entropy on the native kernels: every rank's logits GEMM leaves per-row records of its
     vocabulary slice, the ranks read each other's records through symmetric memory (one bounded barrier per chunk,
     no all-reduce of statistics), and every rank turns its own logits into ``softmax_global - onehot`` in place.
-    Gradients are produced during forward when the output gradient is promised (``ops.loss_backward_scale``)."""
+    Gradients are produced during forward when the output gradient is promised (``ops.loss_backward_scale``).
+    dH is this rank's partial sum over its vocabulary slice; the backward of the sequence gather that produced ``h``
+    sums the ranks' parts."""
 
     @staticmethod
     def forward(ctx, h, w, labels, tp: TPInfo, ahead):
@@ -235,7 +285,7 @@ class _VocabParallelCENative(torch.autograd.Function):
         mg = getattr(w, "main_grad", None)
         grads, dh, dw = [], None, None
         if ahead is not None:
-            dh = torch.empty_like(h)
+            dh = torch.zeros(M, D, device=h.device, dtype=torch.float32)   # fp32: the GEMM may cut the long contraction
             dw = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
         rows = Fm.CE_CHUNK_ROWS
         buf = torch.empty(min(M, rows), Vl, device=h.device, dtype=torch.bfloat16) if ahead is not None else None
@@ -247,14 +297,13 @@ class _VocabParallelCENative(torch.autograd.Function):
             ex.buf.barrier()     # every rank's records of this chunk are written
             C.ce_grad(logits, labels[r0:r1], [p + r0 * 16 for p in peers], loss_sum, gsl, v0, need, rows=r1 - r0)
             if ahead is not None:
-                C.gemm(logits, w, b_mn=True, out=dh[r0:r1])
+                C.gemm(logits, w, b_mn=True, out=dh[r0:r1], epi=C.EPI_F32_ACC)
                 C.gemm(logits, h[r0:r1], a_mn=True, b_mn=True, out=dw, epi=C.EPI_F32_ACC)
             elif need:
                 grads.append(logits)
         ctx.tp, ctx.ahead, ctx.has_mg = tp, ahead, mg is not None
         if ahead is not None:
-            dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=tp.group)   # dH is a partial sum over the slices
-            ctx.save_for_backward(dh, *(() if mg is not None else (dw,)))
+            ctx.save_for_backward(dh.to(h.dtype), *(() if mg is not None else (dw,)))
         else:
             ctx.save_for_backward(h, w, *grads)
         return (loss_sum * gs).reshape(())
@@ -268,18 +317,17 @@ class _VocabParallelCENative(torch.autograd.Function):
             C.expect_scalar(gout.detach().reshape(1).to(torch.float32).contiguous(), ctx.ahead)
             return dh, (None if ctx.has_mg else rest[0].to(dh.dtype)), None, None, None
         h, w, *grads = ctx.saved_tensors
-        dh = torch.empty_like(h)
+        dh = torch.zeros(h.shape, device=h.device, dtype=torch.float32)
         mg = getattr(w, "main_grad", None)
         dw = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
         scale = gout.detach().to(torch.float32).reshape(1).contiguous()
         r0 = 0
         for g in grads:
             r1 = r0 + g.shape[0]
-            C.gemm(g, w, b_mn=True, out=dh[r0:r1], alpha_dev=scale)
+            C.gemm(g, w, b_mn=True, out=dh[r0:r1], epi=C.EPI_F32_ACC, alpha_dev=scale)
             C.gemm(g, h[r0:r1], a_mn=True, b_mn=True, out=dw, epi=C.EPI_F32_ACC, alpha_dev=scale)
             r0 = r1
-        dist.all_reduce(dh, op=dist.ReduceOp.SUM, group=ctx.tp.group)
-        return dh, (None if mg is not None else dw.to(w.dtype)), None, None, None
+        return dh.to(h.dtype), (None if mg is not None else dw.to(w.dtype)), None, None, None
 
 
 def vocab_parallel_cross_entropy(h: torch.Tensor, w_local: torch.Tensor, labels: torch.Tensor, tp: TPInfo):

@@ -147,6 +147,23 @@ def test_tensor_parallel_matches_single_process():
             assert _close(params[k], want[k]), k
 
 
+def test_tensor_parallel_with_a_tied_replicated_head_matches_single_process():
+    """Tied embeddings: the head is replicated, every rank scores its own token slice; embedding and head gradients
+    are partial sums completed by the all-reduce of replicated parameters.  (With Adam's eps far below the gradient
+    scale a gradient that is too large by the group size would go unnoticed: eps is 1e-4 here.)"""
+    from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
+    full = _full_weights(_cfg())
+    batches = _batches(2, 2, 64, 512)
+    want_losses, want_params = _single(_cfg(), full, batches)
+    res = run_ranks(2, _tp_rank, full, batches)
+    for r in range(2):
+        losses, params = res[r]
+        assert losses == pytest.approx(want_losses, abs=1e-4)
+        want = tp_slice_state_dict(want_params, 2, r)
+        for k in want:
+            assert _close(params[k], want[k], tol=1e-3), k
+
+
 def _tp_rank_debug(rank, world, full, batches):
     from maester_b200.trainer import Trainer
     tr = Trainer(_cfg(flavor="debugmodel", tensor_parallel_degree=2, data_parallel_shard_degree=1))
