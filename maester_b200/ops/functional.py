@@ -8,6 +8,7 @@ gradient for that parameter; otherwise the gradient is returned normally.
 from __future__ import annotations
 
 import contextlib
+import os
 
 import torch
 from torch.autograd import Function
@@ -430,6 +431,8 @@ def loss_backward_scale(scale: float | None):
     chunk by chunk while the logits chunk is still at hand, so no logits or logit gradients outlive the forward
     pass; its backward checks the promise on the device and records a status error if it was broken."""
     global _BACKWARD_SCALE
+    if os.environ.get("MB_CE_AHEAD", "1") == "0":   # keep the gradient chunks until backward instead (tuning runs)
+        scale = None
     old, _BACKWARD_SCALE = _BACKWARD_SCALE, scale
     try:
         yield

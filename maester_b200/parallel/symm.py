@@ -77,13 +77,76 @@ class SymmBuffer:
                        barrier_timeout_ms() if timeout_ms is None else timeout_ms)
 
 
-def symmetric_memory_available(group) -> bool:
-    """True on CUDA with an initialised NCCL group (the rendezvous itself is the final check)."""
-    if not (torch.cuda.is_available() and dist.is_initialized()):
-        return False
+_PREFLIGHT: dict = {}
+
+
+def preflight(group, device: torch.device | None = None, nbytes: int = 1 << 20) -> dict:
+    """Start-up check of the peer-memory plane of ``group`` (cached per group): rendezvous of a small symmetric
+    buffer, one bounded cross-rank barrier, and a pull of every peer's pattern through its mapped pointer.
+
+    Returns ``{"ok", "reason", "world", "multicast", "pull_gbs"}``; all ranks agree on ``ok`` (it is all-reduced), so
+    either every rank uses the peer-memory kernels or every rank uses NCCL.  Nothing here can hang: the barrier
+    gives up after a few seconds and reports through the status word."""
+    key = id(group)
+    if key in _PREFLIGHT:
+        return _PREFLIGHT[key]
+    out = {"ok": False, "reason": "", "world": 1, "multicast": False, "pull_gbs": 0.0}
     try:
         import importlib
+
         importlib.import_module("torch.distributed._symmetric_memory")
-    except ImportError:
+        if not (torch.cuda.is_available() and dist.is_initialized()):
+            raise RuntimeError("needs CUDA and an initialised process group")
+        if dist.get_backend(group) != "nccl":
+            raise RuntimeError(f"backend is {dist.get_backend(group)}, not nccl")
+        from maester_b200.ops import cuda as C
+
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        world = dist.get_world_size(group)
+        out["world"] = world
+        local_ok, reason = 1, ""
+        try:
+            buf = SymmBuffer(nbytes // 4, torch.int32, device, group)
+            out["multicast"] = bool(buf.multicast_ptr)
+            buf.tensor.fill_(buf.rank + 1)
+            buf.barrier(channel=PAD_CHANNELS - 1, timeout_ms=5000.0)
+            got = torch.empty(nbytes // 4, dtype=torch.int32, device=device)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            for r in range(world):
+                if r == buf.rank:
+                    continue
+                e0.record()
+                C.peer_copy(got, buf.peer_ptrs[r], nbytes)
+                e1.record()
+                torch.cuda.synchronize(device)
+                if not bool((got == r + 1).all()):
+                    local_ok, reason = 0, f"rank {buf.rank} read a wrong pattern from rank {r}"
+                out["pull_gbs"] = max(out["pull_gbs"], nbytes / max(e0.elapsed_time(e1), 1e-3) / 1e6)
+            buf.barrier(channel=PAD_CHANNELS - 1, timeout_ms=5000.0)   # nobody frees the buffer while a peer reads it
+            C.check_status()
+        except Exception as e:  # noqa: BLE001  (no peer access, unsupported driver, an expired barrier, ...)
+            local_ok, reason = 0, f"{type(e).__name__}: {e}"
+        flag = torch.tensor([local_ok], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        out["ok"] = bool(flag.item())
+        out["reason"] = reason if not out["ok"] else ""
+        if not out["ok"] and not reason:
+            out["reason"] = "another rank of the group failed the check"
+    except Exception as e:  # noqa: BLE001
+        out["reason"] = f"{type(e).__name__}: {e}"
+    _PREFLIGHT[key] = out
+    from maester_b200.log_utils import logger
+
+    if out["ok"]:
+        logger.info(f"peer-memory preflight: {out['world']} ranks, multicast={out['multicast']}, "
+                    f"pull {out['pull_gbs']:.0f} GB/s at {nbytes >> 10} KiB")
+    elif out["world"] > 1 or "nccl" not in out["reason"]:
+        logger.info(f"peer-memory preflight failed, NCCL collectives are used instead: {out['reason']}")
+    return out
+
+
+def symmetric_memory_available(group) -> bool:
+    """True when the peer-memory plane of ``group`` passed its start-up check (see ``preflight``)."""
+    if not (torch.cuda.is_available() and dist.is_initialized()):
         return False
-    return dist.get_backend(group) == "nccl"
+    return preflight(group)["ok"]

@@ -243,3 +243,19 @@ def test_an_expired_wait_blocks_the_checkpoint_on_the_gpu(tmp_path):
     assert not (tmp_path / "job" / "checkpoints" / "step-2").exists()
     ck.save(2)  # the failed check cleared the status word
     assert (tmp_path / "job" / "checkpoints" / "step-2" / ".metadata").exists()
+
+
+def _preflight_rank(rank, world):
+    import torch.distributed as dist
+    from maester_b200.parallel.symm import preflight, symmetric_memory_available
+    res = preflight(dist.group.WORLD)
+    return res["ok"], res["reason"], symmetric_memory_available(dist.group.WORLD)
+
+
+def test_peer_memory_preflight_declines_without_a_gpu_plane():
+    """On a gloo group the start-up check of the peer-memory plane answers "no" with a reason on every rank (and the
+    framework then uses the process group's collectives); it neither raises nor waits."""
+    from test_parallel_cpu import run_ranks
+    for ok, reason, avail in run_ranks(2, _preflight_rank):
+        assert ok is False and avail is False
+        assert reason
