@@ -125,6 +125,10 @@ class Muon(Optimizer):
                 u = g.lerp(m, group["momentum"]) if group["nesterov"] else m
                 work.append((p, group, u.to(torch.bfloat16)))
 
+        if work and self._peer_exchange_ok(work):
+            self._step_over_peer_memory(work)
+            return loss
+
         inflight: deque = deque()
 
         def launch(i: int):
@@ -174,6 +178,83 @@ class Muon(Optimizer):
         while inflight:
             finish(inflight.popleft())
         return loss
+
+
+    # ------------------------------------------------------------------ gather / scatter over peer memory
+    peer_exchange = True   # class-wide switch (tests compare against the process-group path)
+
+    def _chunk_rows(self, p, world: int) -> int:
+        full_rows = self.full_shape_of(p)[0]
+        return (full_rows + world - 1) // world
+
+    def _peer_exchange_ok(self, work) -> bool:
+        """All matrices are sharded over one NCCL group whose peer-memory plane passed its start-up check, and every
+        row chunk is a multiple of 16 bytes (the copy kernel moves 16-byte words)."""
+        if not (self.peer_exchange and self.full_shape_of is not None and work[0][2].is_cuda):
+            return False
+        pg, world, _ = self._world(work[0][0])
+        if world == 1:
+            return False
+        for p, _, u in work:
+            g, w, _ = self._world(p)
+            if g is not pg or (self._chunk_rows(p, world) * u.shape[1]) % 8:
+                return False
+        from maester_b200.parallel.symm import symmetric_memory_available
+        return symmetric_memory_available(pg)
+
+    def _step_over_peer_memory(self, work) -> None:
+        """Every rank stages its row chunks of all update matrices in one symmetric buffer; after ONE cross-rank
+        barrier the owner of a matrix (round robin) pulls the other ranks' chunks through their mapped pointers,
+        orthogonalises, and leaves the result in its own symmetric buffer; after a SECOND barrier every rank pulls
+        its rows of every result from the owner.  Two barriers and plain peer loads replace a gather and a scatter
+        collective per matrix (the reference batches point-to-point sends instead:
+        maester/optimizers/muon_/muon.py gather / scatter of shards)."""
+        from maester_b200.ops import cuda as C
+        from maester_b200.parallel.symm import SymmBuffer
+        pg, world, rank = self._world(work[0][0])
+        dev = work[0][2].device
+        chunks = [self._chunk_rows(p, world) for p, _, _ in work]
+        cols = [u.shape[1] for _, _, u in work]
+        sizes = [c * n for c, n in zip(chunks, cols)]                    # elements of one rank's chunk of matrix i
+        in_off = [0]
+        for sz in sizes:
+            in_off.append(in_off[-1] + sz)
+        out_off, fill = [], [0] * world                                   # results live in their owner's buffer
+        for i, sz in enumerate(sizes):
+            out_off.append(fill[i % world])
+            fill[i % world] += sz * world
+        key = (id(pg), in_off[-1], max(fill))
+        if getattr(self, "_peer_key", None) != key:                       # collective allocation, first step only
+            self._peer_in = SymmBuffer(max(in_off[-1], 8), torch.bfloat16, dev, pg)
+            self._peer_out = SymmBuffer(max(max(fill), 8), torch.bfloat16, dev, pg)
+            self._peer_key = key
+        stage, res = self._peer_in, self._peer_out
+        for i, (p, _, u) in enumerate(work):
+            dst = stage.tensor[in_off[i]: in_off[i] + sizes[i]].view(chunks[i], cols[i])
+            dst[: u.shape[0]].copy_(u)
+            if u.shape[0] < chunks[i]:
+                dst[u.shape[0]:].zero_()
+        stage.barrier()                                                   # every rank's chunks are staged
+        for i, (p, group, u) in enumerate(work):
+            if i % world != rank:
+                continue
+            full = torch.empty(world * chunks[i], cols[i], device=dev, dtype=torch.bfloat16)
+            for r in range(world):
+                C.peer_copy(full[r * chunks[i]:(r + 1) * chunks[i]], stage.peer_ptrs[r] + in_off[i] * 2, sizes[i] * 2)
+            rows = self.full_shape_of(p)[0]
+            o = res.tensor[out_off[i]: out_off[i] + sizes[i] * world].view(world * chunks[i], cols[i])
+            o[:rows].copy_(newton_schulz(full[:rows], group["ns_steps"]))
+        res.barrier()                                                     # every owner's results are in place
+        for i, (p, group, u) in enumerate(work):
+            mine = torch.empty(chunks[i], cols[i], device=dev, dtype=torch.bfloat16)
+            C.peer_copy(mine, res.peer_ptrs[i % world] + (out_off[i] + rank * sizes[i]) * 2, sizes[i] * 2)
+            shape = self.full_shape_of(p)
+            scale = max(1.0, shape[0] / math.prod(shape[1:])) ** 0.5
+            p.data.mul_(1 - group["lr"] * group["wd"])
+            p.data.add_(mine[: u.shape[0]].reshape(p.shape).to(p.dtype), alpha=-group["lr"] * scale)
+        # the next step's staging writes come after its own barrier-free copies; a rank may only overwrite its
+        # buffers once every peer has finished pulling from them
+        res.barrier()
 
 
 class MuonDDP(Optimizer):

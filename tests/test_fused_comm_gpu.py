@@ -116,3 +116,54 @@ def test_resharding_mode_trains_like_the_resident_mode():
             resident, resharded, rel = torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False)
             assert resharded == pytest.approx(resident, abs=2e-2)
             assert rel < 2e-3
+
+
+MUON = [{"opt_class": "maester_b200.optimizers.Muon", "opt_cfg": {"lr": 0.02, "momentum": 0.95, "wd": 0.01},
+         "min_dim": 2, "exclude_names": ["tok_embeddings"]},
+        {"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3, "betas": (0.9, 0.95), "weight_decay": 0.0},
+         "min_dim": 0}]
+
+
+def _muon_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from maester_b200.config import Config
+    from maester_b200.datasets.synthetic import SyntheticLoader
+    from maester_b200.ops import cuda as C
+    from maester_b200.optimizers.muon import Muon
+    from maester_b200.trainer import Trainer
+    results = {}
+    for peer in (False, True):
+        Muon.peer_exchange = peer
+        torch.manual_seed(0)
+        cfg = Config(model_name="llama3", flavor="tiny", seq_len=256, train_batch_size=2, synthetic_vocab_size=512,
+                     data_parallel_shard_degree=world, ac_mode="none", enable_checkpoint=False,
+                     optimizer_groups=MUON, scheduler="constant", fused_collectives=False)
+        tr = Trainer(cfg)
+        muons = [o for o in tr.optimizers.optimizers if isinstance(o, Muon)]
+        assert muons, "the Muon group was not built"
+        loader = SyntheticLoader(2, 256, 512, "uniform:16:128", seed=3, rank=rank)
+        losses = [tr.train_step(next(loader)).item() for _ in range(3)]
+        C.check_status()
+        used = any(getattr(o, "_peer_key", None) is not None for o in muons)
+        assert used == peer, f"peer exchange used={used}, wanted {peer}"
+        results[peer] = (losses, tr.sharded.master.clone())
+        del tr
+    torch.save((results[False][0], results[True][0], torch.equal(results[False][1], results[True][1]),
+                ((results[False][1] - results[True][1]).norm() / results[False][1].norm()).item()),
+               os.path.join(out_dir, f"m{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_muon_gathers_and_scatters_over_peer_memory_like_the_collectives():
+    world = 2
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_muon_worker, args=(world, _free_port(), d), nprocs=world, join=True)
+        for r in range(world):
+            nccl_losses, peer_losses, same, rel = torch.load(os.path.join(d, f"m{r}.pt"), weights_only=False)
+            assert peer_losses == pytest.approx(nccl_losses, abs=2e-2)
+            assert rel < 4e-3, rel     # (weight gradients sum in a run-dependent order: not bitwise)

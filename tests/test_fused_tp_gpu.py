@@ -123,6 +123,11 @@ def _ce_worker(rank, world, port, out_dir):
                 loss = vocab_parallel_cross_entropy(h, w, labels, tp)
             assert isinstance(loss.grad_fn, _VocabParallelCENative._backward_cls), "the native path did not run"
             (loss * 0.5).backward()
+            # every rank holds the part of dH that belongs to its vocabulary slice (in the model the backward of
+            # the sequence gather sums the parts)
+            dh = h.grad.float()
+            dist.all_reduce(dh)
+            h.grad = dh.to(h.dtype)
             hf, wf = h.detach().float().requires_grad_(), wfull.float().requires_grad_()
             want = ref.linear_cross_entropy(hf, wf, labels, 1.0)
             (want * 0.5).backward()
