@@ -107,8 +107,9 @@ class RingState:
 
 def _chunk(t: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
     """Rows ``lo:hi`` of ``[B, s, heads, hd]`` with the batch stride the kernels expect (a view when B == 1)."""
-    v = t[:, lo:hi]
-    return v if t.shape[0] == 1 else v.contiguous()
+    if t.shape[0] == 1:
+        return t[0, lo:hi].unsqueeze(0)   # (unsqueeze gives the new batch dimension the stride of the chunk itself)
+    return t[:, lo:hi].contiguous()
 
 
 class _RingAttnBlock(torch.autograd.Function):

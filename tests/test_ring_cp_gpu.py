@@ -22,7 +22,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, batch):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     torch.cuda.set_device(rank)
@@ -34,13 +34,13 @@ def _worker(rank, world, port, out_dir):
     out = {}
     for mode in ("alltoall", "ring"):
         torch.manual_seed(0)
-        cfg = Config(model_name="llama3", flavor="debugmodel", seq_len=1024, train_batch_size=2,
+        cfg = Config(model_name="llama3", flavor="debugmodel", seq_len=1024, train_batch_size=batch,
                      data_parallel_shard_degree=1, context_parallel_degree=world, context_parallel_mode=mode,
                      ac_mode="none", enable_checkpoint=False, optimizer_groups=ADAMW, scheduler="constant",
                      synthetic_vocab_size=2048,
                      fused_collectives=False)  # NCCL reduce-scatter: the reduced gradient shards can be compared
         tr = Trainer(cfg)
-        loader = SyntheticLoader(2, 1024, 2048, "full", seed=5, rank=0)   # the CP group shares one batch
+        loader = SyntheticLoader(batch, 1024, 2048, "full", seed=5, rank=0)   # the CP group shares one batch
         # gradients of the first step (reduced over the group, this rank's rows) before any optimizer arithmetic
         tr.optimizers.zero_grad()
         tr.forward_backward(next(loader))
@@ -57,10 +57,11 @@ def _worker(rank, world, port, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_ring_context_parallel_trains_like_the_all_to_all_form():
+@pytest.mark.parametrize("batch", [2, 1])   # batch 1: the chunks of a rank's sequence are views, not copies
+def test_ring_context_parallel_trains_like_the_all_to_all_form(batch):
     world = 2
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(_worker, args=(world, _free_port(), d), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), d, batch), nprocs=world, join=True)
         a2a = [torch.load(os.path.join(d, f"r{r}.pt"), weights_only=False) for r in range(world)]
         # the two forms shard the sequence differently, so compare the mean loss over the CP group
         mean_a2a = [sum(a2a[r][0][i] for r in range(world)) / world for i in range(4)]
