@@ -149,6 +149,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_embedding_fwd": [_P, _P, _P, _L, _I, _F, _I, _P],
         "mb_embedding_bwd": [_P, _P, _P, _L, _I, _F, _P],
         "mb_ce_fwd_bwd": [_P, _P, _P, _P, _F, _L, _I, _L, _I, _I, _P, _P],
+        "mb_set_norm_pipeline": [_I],
         "mb_gemm_ce": [_P, _P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _L, _L, _F, _L, _P],
         "mb_ce_merge": [_P, _P, _P, _I, _I, _L, _P],
         "mb_ce_grad": [_P, _P, _P, _I, _P, _P, _L, _I, _L, _L, _I, _I, _P],

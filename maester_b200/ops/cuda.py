@@ -117,6 +117,12 @@ def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor | None, eps: float, unit_offset
     return y.view(x.shape), rstd
 
 
+def set_norm_pipeline(on: bool) -> None:
+    """Select the bulk-copy pipelined RMSNorm kernels (csrc/norm_tma.cu) for tall inputs instead of the default
+    row-per-warp kernels (measured slightly slower at the benchmark shape; kept selectable and tested)."""
+    _lib.lib().mb_set_norm_pipeline(int(bool(on)))
+
+
 def rmsnorm_bwd(dy: torch.Tensor, x: torch.Tensor, w: torch.Tensor | None, rstd: torch.Tensor,
                 unit_offset: bool, dw_acc: torch.Tensor | None, dres_add: torch.Tensor | None = None):
     D = x.shape[-1]

@@ -95,6 +95,50 @@ def test_rmsnorm(M, D, unit):
     assert _rel(dw, wf.grad) < 5e-3
 
 
+@pytest.mark.parametrize("M,D", [(1185, 256), (4099, 2560), (2400, 1024), (3000, 2048), (1300, 3072), (16384, 2560)])
+@pytest.mark.parametrize("unit", [False, True])
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_rmsnorm_on_tall_inputs(M, D, unit, pipeline):
+    """Inputs tall enough for the pipelined kernels (a ring of shared-memory stages filled by bulk copies): ragged last
+    tile, every vector width, residual / gradient-accumulate streams, and the same results as the row-per-warp form."""
+    from maester_b200.ops import cuda as C
+    C.set_norm_pipeline(pipeline)
+    try:
+        _check_tall_rmsnorm(C, M, D, unit)
+    finally:
+        C.set_norm_pipeline(False)
+
+
+def _check_tall_rmsnorm(C, M, D, unit):
+    torch.manual_seed(M + D)
+    x = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    w = (torch.randn(D, device="cuda") * 0.1).to(torch.bfloat16)
+    res = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    y, rstd = C.rmsnorm_fwd(x, w, 1e-6, unit)
+    want = ref.rmsnorm(x.float(), w.float(), 1e-6, unit)
+    assert _rel(y, want) < 4e-3
+    assert (y.float() - want).abs().max().item() < 0.05 * want.abs().max().item()
+    assert _rel(rstd, torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)) < 1e-5
+    y2, _ = C.rmsnorm_fwd(x, w, 1e-6, unit, residual=res)
+    assert _rel(y2, ref.rmsnorm(x, w, 1e-6, unit, residual=res)) < 4e-3
+    dy = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    xf = x.float().requires_grad_()
+    wf = w.float().requires_grad_()
+    ref.rmsnorm(xf, wf, 1e-6, unit).backward(dy.float())
+    dw = torch.zeros(D, device="cuda")
+    dx = C.rmsnorm_bwd(dy, x, w, rstd, unit, dw)
+    assert _rel(dx, xf.grad) < 5e-3
+    assert _rel(dw, wf.grad) < 5e-3
+    add = torch.randn(M, D, device="cuda", dtype=torch.bfloat16)
+    dw2 = torch.zeros(D, device="cuda")
+    dx2 = C.rmsnorm_bwd(dy, x, w, rstd, unit, dw2, dres_add=add)
+    assert _rel(dx2, xf.grad + add.float()) < 5e-3
+    assert _rel(dw2, wf.grad) < 5e-3
+    dx3 = C.rmsnorm_bwd(dy, x, w, rstd, unit, None)          # no weight gradient wanted
+    assert torch.equal(dx3, dx)
+    C.check_status()
+
+
 @pytest.mark.parametrize("hd,rot,layout", [(256, 256, "half"), (128, 128, "interleaved"), (128, 64, "half"), (64, 64, "interleaved")])
 @pytest.mark.parametrize("norm", [True, False])
 def test_qknorm_rope(hd, rot, layout, norm):
