@@ -21,7 +21,7 @@ import torch.nn as nn
 
 from maester_b200 import ops
 from maester_b200.models.deepseek.args import DeepSeekModelArgs
-from maester_b200.models.layers import Linear, maybe_checkpoint
+from maester_b200.models.layers import Linear
 from maester_b200.models.moe import FeedForward, MoE
 from maester_b200.models.norms import RMSNorm
 from maester_b200.ops import reference as ref
@@ -154,9 +154,9 @@ class TransformerBlock(nn.Module):
 
     def forward(self, x, position_ids, inv_freq, document_ids):
         rc = self.selective_recompute
-        x = self.attention(maybe_checkpoint(self.attention_norm, rc, x), position_ids, inv_freq, document_ids,
+        x = self.attention(self.attention_norm(x), position_ids, inv_freq, document_ids,
                            residual=x)
-        h = maybe_checkpoint(self.ffn_norm, rc, x)
+        h = self.ffn_norm(x)
         if self.moe_enabled:
             return x + self.moe(h)
         return self.feed_forward(h, residual=x)

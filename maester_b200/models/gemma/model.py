@@ -22,7 +22,7 @@ import torch.nn as nn
 
 from maester_b200 import ops
 from maester_b200.log_utils import logger
-from maester_b200.models.layers import Embedding, FusedWeight, Linear, maybe_checkpoint
+from maester_b200.models.layers import Embedding, FusedWeight, Linear
 from maester_b200.ops import reference as ref
 
 
@@ -55,7 +55,7 @@ class ModelArgs:
     init_std: float = 0.02
     norm_type: str = "rmsnorm"
     # execution options of this framework
-    selective_recompute: bool = False  # recompute norms / GeGLU in backward instead of saving them
+    selective_recompute: bool = False  # per-op recomputation plan is active (parallel/parallelize.py::apply_ac)
 
     def get_nparams_and_flops(self, model: nn.Module, seq_len: int) -> tuple[int, int]:
         """Parameter count and FLOPs/token: ``6·(N − N_emb) + 12·L·H·(dim//H)·T`` (model.py:44-82)."""
@@ -76,6 +76,10 @@ class RMSNorm(nn.Module):
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, self.add_unit_offset, residual)
+
+    def fork(self, x: torch.Tensor):
+        """(norm(x), x): the second value is the skip connection of the branch that the first one enters."""
+        return ops.rmsnorm_fork(x, self.weight, self.eps, self.add_unit_offset)
 
     def reset_parameters(self) -> None:
         nn.init.zeros_(self.weight)
@@ -159,14 +163,14 @@ class Gemma2DecoderLayer(nn.Module):
 
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids):
         rc = self.selective_recompute
-        h = maybe_checkpoint(self.input_layernorm, rc, x)
+        h, skip = self.input_layernorm.fork(x)
         h = self.self_attn(h, position_ids, inv_freq, rope_cs, document_ids)
-        x = self.post_attention_layernorm(h, residual=x)  # x + norm(attn)
-        h = maybe_checkpoint(self.pre_feedforward_layernorm, rc, x) if self.pre_feedforward_layernorm is not None else x
+        x = self.post_attention_layernorm(h, residual=skip)  # x + norm(attn)
+        h, skip = self.pre_feedforward_layernorm.fork(x) if self.pre_feedforward_layernorm is not None else (x, x)
         h = self.mlp(h, recompute_act=rc)
         if self.post_feedforward_layernorm is not None:
-            return self.post_feedforward_layernorm(h, residual=x)
-        return x + h
+            return self.post_feedforward_layernorm(h, residual=skip)
+        return skip + h
 
     def init_weights(self, init_std: float) -> None:
         for n in (self.input_layernorm, self.post_attention_layernorm, self.pre_feedforward_layernorm,

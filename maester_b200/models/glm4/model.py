@@ -18,7 +18,7 @@ import torch.nn as nn
 
 from maester_b200 import ops
 from maester_b200.log_utils import logger
-from maester_b200.models.layers import FusedWeight, Linear, maybe_checkpoint
+from maester_b200.models.layers import FusedWeight, Linear
 from maester_b200.models.moe import MoE, MoEArgs
 from maester_b200.models.norms import RMSNorm
 from maester_b200.ops import reference as ref
@@ -164,9 +164,9 @@ class Glm4MoeDecoderLayer(nn.Module):
 
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids):
         rc = self.selective_recompute
-        x = self.self_attn(maybe_checkpoint(self.input_layernorm, rc, x), position_ids, inv_freq, rope_cs,
+        x = self.self_attn(self.input_layernorm(x), position_ids, inv_freq, rope_cs,
                            document_ids, residual=x)
-        h = maybe_checkpoint(self.post_attention_layernorm, rc, x)
+        h = self.post_attention_layernorm(x)
         if self.moe_enabled:
             return x + self.moe(h)
         return self.mlp(h, residual=x)

@@ -1,12 +1,10 @@
 """Building blocks shared by the model families: bias-free Linear / Embedding modules whose
-parameters keep the reference's fully-qualified names, fused views over adjacent weights, and the
-activation-checkpoint helper used for the selective "op" policy.
+parameters keep the reference's fully-qualified names, and fused views over adjacent weights.
 """
 from __future__ import annotations
 
 import torch
 import torch.nn as nn
-from torch.utils.checkpoint import checkpoint
 
 from maester_b200 import ops
 
@@ -85,10 +83,3 @@ class FusedWeight:
             w.main_grad = g
             self._view, self._key = w, key
         return self._view
-
-
-def maybe_checkpoint(fn, enabled: bool, *args):
-    """Recompute ``fn`` in backward instead of saving its internals (selective "op" policy)."""
-    if enabled and torch.is_grad_enabled():
-        return checkpoint(fn, *args, use_reentrant=False)
-    return fn(*args)

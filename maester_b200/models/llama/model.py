@@ -21,7 +21,7 @@ import torch.nn as nn
 
 from maester_b200 import ops
 from maester_b200.log_utils import logger
-from maester_b200.models.layers import FusedWeight, Linear, maybe_checkpoint
+from maester_b200.models.layers import FusedWeight, Linear
 from maester_b200.models.norms import create_norm
 from maester_b200.ops import reference as ref
 
@@ -129,7 +129,7 @@ class FeedForward(nn.Module):
             gate_up = ag_linear(x, self._fused().get(), self.tp_fused)
         else:
             return ops.glu_mlp(x, self._fused().get(), self.w2.weight, "silu", residual=residual)
-        act = maybe_checkpoint(lambda t: ops.glu(t, "silu"), recompute_act, gate_up)
+        act = ops.glu(gate_up, "silu")
         if self.tp_fused is not None:
             return linear_rs(act, self.w2.weight, residual, self.tp_fused)
         return self.w2(act, residual=residual)
@@ -137,6 +137,12 @@ class FeedForward(nn.Module):
     def init_weights(self, init_std: float) -> None:
         for lin in (self.w1, self.w2, self.w3):
             nn.init.normal_(lin.weight, mean=0.0, std=init_std)
+
+
+def _fork(norm: nn.Module, x: torch.Tensor):
+    """(norm(x), x) with the two gradients merged in the norm's backward kernel where the norm supports it."""
+    fork = getattr(norm, "fork", None)
+    return fork(x) if fork is not None else (norm(x), x)
 
 
 class TransformerBlock(nn.Module):
@@ -157,13 +163,14 @@ class TransformerBlock(nn.Module):
         rc = self.selective_recompute
         if self.tp is not None and self.attention.tp_fused is None:
             from maester_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
-            a_in = gather_seq(maybe_checkpoint(self.attention_norm, rc, x), self.tp)
+            a_in = gather_seq(self.attention_norm(x), self.tp)
             h = x + reduce_scatter_seq(self.attention(a_in, position_ids, inv_freq, rope_cs, document_ids), self.tp)
-            f_in = gather_seq(maybe_checkpoint(self.ffn_norm, rc, h), self.tp)
+            f_in = gather_seq(self.ffn_norm(h), self.tp)
             return h + reduce_scatter_seq(self.feed_forward(f_in, recompute_act=rc), self.tp)
-        h = self.attention(maybe_checkpoint(self.attention_norm, rc, x), position_ids, inv_freq, rope_cs,
-                           document_ids, residual=x)
-        return self.feed_forward(maybe_checkpoint(self.ffn_norm, rc, h), residual=h, recompute_act=rc)
+        a_in, skip = _fork(self.attention_norm, x)
+        h = self.attention(a_in, position_ids, inv_freq, rope_cs, document_ids, residual=skip)
+        f_in, skip = _fork(self.ffn_norm, h)
+        return self.feed_forward(f_in, residual=skip, recompute_act=rc)
 
     def init_weights(self) -> None:
         for norm in (self.attention_norm, self.ffn_norm):

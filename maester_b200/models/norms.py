@@ -21,6 +21,10 @@ class RMSNorm(nn.Module):
     def forward(self, x: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
         return ops.rmsnorm(x, self.weight, self.eps, False, residual)
 
+    def fork(self, x: torch.Tensor):
+        """(norm(x), x): the second value is the skip connection of the branch that the first one enters."""
+        return ops.rmsnorm_fork(x, self.weight, self.eps, False)
+
     def reset_parameters(self) -> None:
         nn.init.ones_(self.weight)
 

@@ -9,6 +9,7 @@ from maester_b200.ops.functional import (  # noqa: F401
     linear_cross_entropy,
     loss_backward_scale,
     rmsnorm,
+    rmsnorm_fork,
     rope_table,
     use_native,
 )

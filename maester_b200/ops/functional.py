@@ -109,6 +109,42 @@ class _RMSNorm(Function):
         return dx, dw, None, None, (dy if ctx.has_res else None)
 
 
+class _RMSNormFork(Function):
+    """``x -> (rmsnorm(x), x)``: the start of a pre-norm residual branch.  Autograd hands both gradients to ONE
+    backward, so the gradient that arrives over the skip connection is added inside the norm's backward kernel
+    (``dres_add``) instead of by a separate pass over the activations."""
+
+    @staticmethod
+    def forward(ctx, x, w, eps, unit_offset):
+        y, rstd = _C().rmsnorm_fwd(x, w, eps, unit_offset, None)
+        ctx.save_for_backward(x, w, rstd)
+        ctx.unit_offset = unit_offset
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dskip):
+        C = _C()
+        x, w, rstd = ctx.saved_tensors
+        if dy is None:
+            return dskip, None, None, None
+        add = None if dskip is None else dskip.contiguous()
+        mg = getattr(w, "main_grad", None) if w is not None else None
+        buf = None
+        if w is not None and ctx.needs_input_grad[1]:
+            buf = mg if mg is not None else torch.zeros(w.shape, device=w.device, dtype=torch.float32)
+        dx = C.rmsnorm_bwd(dy.contiguous(), x, w, rstd, ctx.unit_offset, buf, dres_add=add)
+        dw = None if (buf is None or mg is not None) else buf.to(w.dtype)
+        return dx, dw, None, None
+
+
+def rmsnorm_fork(x: torch.Tensor, w: torch.Tensor | None, eps: float, unit_offset: bool = False):
+    """``(rmsnorm(x) * (w | 1+w), x)``: use the second value as the residual of the branch that the first one
+    enters; the two gradients are then merged inside the norm's backward kernel."""
+    if use_native(x) and x.shape[-1] % 8 == 0 and torch.is_grad_enabled() and x.requires_grad:
+        return _RMSNormFork.apply(x.contiguous(), w, eps, unit_offset)
+    return rmsnorm(x, w, eps, unit_offset), x
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor | None, eps: float, unit_offset: bool = False,
             residual: torch.Tensor | None = None) -> torch.Tensor:
     """``[residual +] rmsnorm(x) * (w | 1+w)``."""
@@ -344,7 +380,8 @@ class _AttnBlock(Function):
     """qkv (packed) -> [QK-norm] -> RoPE -> masked GQA attention, one autograd node."""
 
     @staticmethod
-    def forward(ctx, qkv, qw, kw, pos, cs, doc, H, KV, hd, layout, eps, unit_offset, scale, causal, window):
+    def forward(ctx, qkv, qw, kw, pos, cs, doc, H, KV, hd, layout, eps, unit_offset, scale, causal, window,
+                recompute_qk):
         C = _C()
         B, S, _ = qkv.shape
         qkv2 = qkv.reshape(B * S, -1)
@@ -359,7 +396,9 @@ class _AttnBlock(Function):
         v = qkv2[:, (H + KV) * hd:].view(B, S, KV, hd)
         plan = cached_attention_plan(S, window, doc, qkv.device, B, causal)
         out, lse = C.attn_fwd(q, k, v, scale, causal, window, plan)
-        ctx.save_for_backward(qkv2, qk if need_qk else None, qw, kw, pos32, cs, out, lse)
+        # per-op recomputation: the normalised and rotated q / k are rebuilt from the packed projection in backward
+        # (one pass of the QK-norm + RoPE kernel) instead of being kept
+        ctx.save_for_backward(qkv2, qk if (need_qk and not recompute_qk) else None, qw, kw, pos32, cs, out, lse)
         ctx.plan = plan
         ctx.cfg = (B, S, H, KV, hd, layout, eps, unit_offset, scale, causal, window, need_qk)
         return out.view(B, S, H * hd)
@@ -370,7 +409,7 @@ class _AttnBlock(Function):
         qkv2, qk, qw, kw, pos32, cs, out, lse = ctx.saved_tensors
         B, S, H, KV, hd, layout, eps, unit_offset, scale, causal, window, need_qk = ctx.cfg
         if qk is None:
-            qk = qkv2
+            qk = C.qknorm_rope_fwd(qkv2, qw, kw, pos32, cs, H, KV, hd, layout, eps, unit_offset) if need_qk else qkv2
         q = qk[:, : H * hd].view(B, S, H, hd)
         k = qk[:, H * hd:(H + KV) * hd].view(B, S, KV, hd)
         v = qkv2[:, (H + KV) * hd:].view(B, S, KV, hd)
@@ -385,19 +424,20 @@ class _AttnBlock(Function):
             C.qknorm_rope_bwd(dqkv, qkv2, qw, kw, pos32, cs, bq, bk, H, KV, hd, layout, eps, unit_offset)
             dqw = None if (mq is not None or qw is None) else bq.to(qw.dtype)
             dkw = None if (mk is not None or kw is None) else bk.to(kw.dtype)
-        return (dqkv.view(B, S, -1), dqw, dkw) + (None,) * 12
+        return (dqkv.view(B, S, -1), dqw, dkw) + (None,) * 13
 
 
 def attention_block(qkv: torch.Tensor, q_norm_w, k_norm_w, pos: torch.Tensor | None,
                     inv_freq: torch.Tensor | None, rope_cs: torch.Tensor | None, doc_ids: torch.Tensor | None,
                     n_heads: int, n_kv_heads: int, head_dim: int, *, layout: str = "half", eps: float = 1e-6,
                     unit_offset: bool = False, scale: float | None = None, causal: bool = True,
-                    window: int | None = None) -> torch.Tensor:
+                    window: int | None = None, recompute_qk: bool = False) -> torch.Tensor:
     """Packed ``qkv`` [B,S,(H+2KV)*hd] → attention output [B,S,H*hd].
 
     Optional per-head RMSNorm on q and k, RoPE (``inv_freq`` for the reference path, ``rope_cs``
     table for the native path), then softmax attention with causal / inclusive sliding-window /
-    same-document masking and GQA.
+    same-document masking and GQA.  ``recompute_qk``: rebuild the normalised, rotated q / k in backward instead
+    of keeping them (the per-op activation-recomputation policy).
     """
     B, S, _ = qkv.shape
     H, KV, hd = n_heads, n_kv_heads, head_dim
@@ -406,7 +446,7 @@ def attention_block(qkv: torch.Tensor, q_norm_w, k_norm_w, pos: torch.Tensor | N
         if pos is None and rope_cs is not None:
             pos = torch.arange(S, device=qkv.device, dtype=torch.int32)[None].expand(B, S)
         return _AttnBlock.apply(qkv, q_norm_w, k_norm_w, pos, rope_cs, doc_ids, H, KV, hd,
-                                0 if layout == "half" else 1, eps, unit_offset, scale, causal, window)
+                                0 if layout == "half" else 1, eps, unit_offset, scale, causal, window, recompute_qk)
     q, k, v = qkv.split([H * hd, KV * hd, KV * hd], dim=-1)
     q = q.reshape(B, S, H, hd)
     k = k.reshape(B, S, KV, hd)

@@ -107,7 +107,7 @@ def attention(module, qkv, q_norm_w, k_norm_w, pos, inv_freq, rope_cs, doc, n_he
     cp = getattr(module, "cp", None)
     if cp is None or cp.size == 1:
         return ops.attention_block(qkv, q_norm_w, k_norm_w, pos, inv_freq, rope_cs, doc, n_heads, n_kv_heads,
-                                   head_dim, **kw)
+                                   head_dim, recompute_qk=getattr(module, "recompute_qk", False), **kw)
     if cp.mode == "ring":
         from maester_b200.parallel.ring_attention import ring_attention_block
         return ring_attention_block(qkv, q_norm_w, k_norm_w, pos, inv_freq, rope_cs, n_heads, n_kv_heads, head_dim, cp,

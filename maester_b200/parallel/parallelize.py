@@ -46,8 +46,12 @@ def apply_ac(model: nn.Module, cfg) -> None:
     """ac_mode: none | full | selective; selective_ac_option: "op" or an integer N (every N-th block).
 
     "op" is the per-op policy of the reference (save GEMM and attention outputs, recompute the rest,
-    parallelize_llama.py:183-250): with hand-written kernels it becomes an explicit plan in the
-    blocks — norms and the gated activation are recomputed, GEMM and attention outputs are kept.
+    parallelize_llama.py:183-250).  With hand-written fused kernels it becomes an explicit plan: the attention
+    modules rebuild the normalised, rotated q / k from the packed projection in backward (one QK-norm + RoPE pass,
+    (H + KV) * head_dim values per token and block not kept); GEMM, attention and norm outputs are kept, because a
+    norm's output is the GEMM operand that the weight gradient needs anyway.  The blocks' ``selective_recompute``
+    flag additionally lets a gated MLP rebuild its activation (``glu_mlp(save_act=False)``), which costs a full
+    pass over [tokens, ffn] per block and is left off.
     """
     mode = cfg.ac_mode
     if mode == "none":
@@ -56,6 +60,9 @@ def apply_ac(model: nn.Module, cfg) -> None:
     if mode == "selective" and str(cfg.selective_ac_option) == "op":
         for _, b in blocks:
             b.selective_recompute = True
+            for m in b.modules():
+                if hasattr(m, "cp_capable"):
+                    m.recompute_qk = True
         logger.info("Applied selective (per-op) activation recomputation to %d blocks", len(blocks))
         return
     every = 1

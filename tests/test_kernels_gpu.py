@@ -579,6 +579,29 @@ def test_a_broken_gradient_promise_is_reported_not_ignored():
     C.check_status()   # the status word was cleared: later work is unaffected
 
 
+def test_attention_block_with_recomputed_qk_matches_the_kept_form():
+    """The per-op recomputation plan (rotated q / k rebuilt in backward) changes no number."""
+    from maester_b200 import ops
+    torch.manual_seed(4)
+    B, S, H, KV, hd = 2, 512, 4, 2, 128
+    qkv0 = torch.randn(B, S, (H + 2 * KV) * hd, device="cuda", dtype=torch.bfloat16)
+    qw = (torch.randn(hd, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_()
+    kw = (torch.randn(hd, device="cuda") * 0.1).to(torch.bfloat16).requires_grad_()
+    pos = torch.arange(S, device="cuda", dtype=torch.int32)[None].expand(B, S)
+    cs = ops.rope_table(ref.rope_inv_freq(hd, 10000.0, device="cuda"), 1024)
+    do = torch.randn(B, S, H * hd, device="cuda", dtype=torch.bfloat16)
+    res = []
+    for rc in (False, True):
+        qkv = qkv0.clone().requires_grad_()
+        qw.grad = kw.grad = None
+        out = ops.attention_block(qkv, qw, kw, pos, None, cs, None, H, KV, hd, eps=1e-6, unit_offset=True,
+                                  recompute_qk=rc)
+        out.backward(do)
+        res.append((out.detach(), qkv.grad, qw.grad.clone(), kw.grad.clone()))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("M,K", [(256, 64), (1000, 328), (2560, 2560)])
 def test_syrk_triangular_schedule(M, K):
     """A A^T (+ beta C) computed on the tiles below the diagonal and mirrored equals the full product."""
