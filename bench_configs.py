@@ -34,13 +34,16 @@ PRESETS = {
     "llama3-8b-cp2": dict(model_name="llama3", flavor="8B", seq_len=32768, train_batch_size=1, context_parallel_degree=2),
     "deepseek-moe-ep8": dict(model_name="deepseek", flavor="bench16L", seq_len=4096, train_batch_size=4,
                              expert_parallel="world"),
+    # the same model over 4 ranks (16 experts per rank): the A/B against the reference where 8-GPU boxes are scarce
+    "deepseek-moe-ep4": dict(model_name="deepseek", flavor="bench16L", seq_len=4096, train_batch_size=4,
+                             expert_parallel="world"),
     # fp32 master + Adam state + gradient shard: 16 B/parameter, 54 GB per GPU at 8 GPUs; the bf16 parameters exist
     # per block only while the block runs (resharding mode of the sharding runtime)
     "gemma3-27b": dict(model_name="gemma3", flavor="27B", seq_len=8192, train_batch_size=1),
     "deepseek-moe-1gpu": dict(model_name="deepseek", flavor="bench6L", seq_len=4096, train_batch_size=4),
 }
 # smallest world size whose GPUs hold the configuration (sharded fp32 state + activations within 180 GB each)
-MIN_GPUS = {"llama3-8b-cp2": 4, "deepseek-moe-ep8": 8, "gemma3-27b": 8}
+MIN_GPUS = {"llama3-8b-cp2": 4, "deepseek-moe-ep8": 8, "deepseek-moe-ep4": 4, "gemma3-27b": 8}
 
 
 def main() -> None:
