@@ -46,6 +46,7 @@ class FusedAdamW(Optimizer):
         defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self._flat = None  # set by attach_flat()
+        self.cleared_grad = False  # the last step() cleared the gradients it consumed
         self._eager = None  # set by eager_begin() for the duration of one step
         self._unit_tables: dict = {}
 
@@ -158,8 +159,13 @@ class FusedAdamW(Optimizer):
             else:
                 # the kernel emits the bf16 copy itself; any other compute dtype (fp32 oracle runs) is a plain copy
                 lp = f["lowp"] if (f["lowp"] is not None and f["lowp"].dtype == torch.bfloat16) else None
+                # one rank: the kernel reads the accumulation buffer itself, so it clears what it has read and the
+                # next step needs no separate pass over the 4 B/parameter buffer
+                clear = bool(sharded is not None and getattr(sharded, "grad_cleared_by_optimizer", None) is not None
+                             and sharded.full_grad is sharded.shard_grad and f["grad"] is sharded.shard_grad)
                 C.adamw(f["master"], f["grad"], f["m"], f["v"], lp, chunks, tensors, nch, lr_t, b1, b2,
-                        g0["eps"], st_step)
+                        g0["eps"], st_step, zero_grad=clear)
+                self.cleared_grad = clear
                 if lp is None and f["lowp"] is not None:
                     f["lowp"].copy_(f["master"])
             for g in self.param_groups:

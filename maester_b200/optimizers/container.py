@@ -85,6 +85,12 @@ class OptimizersContainer(Optimizer, Stateful):
                     u.eager_done = False
             sharded.lowp_fresh = sharded.device.type == "cuda" and all(
                 isinstance(o, FusedAdamW) and o._flat is not None for o in self.optimizers)
+            # every parameter's gradient was consumed and cleared by a kernel that owns it: zero_grad() may skip
+            if sharded.grad_cleared_by_optimizer is not None:
+                sharded.grad_cleared_by_optimizer = all(getattr(o, "cleared_grad", False) for o in self.optimizers)
+            for o in self.optimizers:
+                if hasattr(o, "cleared_grad"):
+                    o.cleared_grad = False
             sharded.gather_params()
         return loss
 

@@ -150,6 +150,7 @@ class ShardedModel:
         self.divide = gradient_divide_factor or float(self.world * self.rep_world)
         self.require_sync = True
         self.lowp_fresh = False
+        self.grad_cleared_by_optimizer = False   # set by the optimizer container after a step that cleared the gradients
         self._use_cuda = device.type == "cuda"
         self.comm_stream = torch.cuda.Stream(device) if (self._use_cuda and self.world * self.rep_world > 1) else None
 
@@ -809,6 +810,10 @@ class ShardedModel:
 
     @torch.no_grad()
     def zero_grad(self) -> None:
+        if self.grad_cleared_by_optimizer:   # the optimizer kernel cleared what it read; nothing has been written since
+            self.grad_cleared_by_optimizer = False
+            return
+        # (None switches the optimizer's clearing off for good: tests compare the two ways)
         self.shard_grad.zero_()
         if self.resharded:
             return  # the staging buffers are cleared by the reduce-scatter that empties them
