@@ -515,6 +515,8 @@ class ShardedModel:
             u.gather_event = None
 
     def _pre_forward(self, u: Unit, i: int) -> None:
+        if i == len(self.units) - 2:
+            self._wait_zeroed()   # gradient buffer cleared (side stream) before anything can write into it
         if not self.resharded:
             self._wait_gather(u)
             return
@@ -818,7 +820,27 @@ class ShardedModel:
         if self.resharded:
             return  # the staging buffers are cleared by the reduce-scatter that empties them
         if self.full_grad is not self.shard_grad:
-            self.full_grad.zero_()
+            if self._use_cuda and self.world * self.rep_world > 1:
+                # 4 B/parameter of zeros take milliseconds: written on a side stream under the forward pass, which
+                # never touches the gradient buffer; the last block's forward pre-hook waits for the event, before
+                # the loss layer or the backward pass can write a gradient
+                if self._zero_stream is None:
+                    self._zero_stream = torch.cuda.Stream(self.device)
+                self._zero_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self._zero_stream):
+                    self.full_grad.zero_()
+                self._zero_event = torch.cuda.Event()
+                self._zero_event.record(self._zero_stream)
+            else:
+                self.full_grad.zero_()
+
+    _zero_stream = None
+    _zero_event = None
+
+    def _wait_zeroed(self) -> None:
+        if self._zero_event is not None:
+            torch.cuda.current_stream().wait_event(self._zero_event)
+            self._zero_event = None
 
     # ------------------------------------------------------------------ state for checkpoints
     def master_state_dict(self) -> dict[str, torch.Tensor]:
