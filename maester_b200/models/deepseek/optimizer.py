@@ -7,8 +7,10 @@ counter.  Balance statistics — max violation, coefficient of variation, fracti
 (load below 5 % of the ideal) for the batch and as running totals — are published in
 ``optimizers._hook_stats`` for the metric logger.
 
-All layers are processed with one stacked all-reduce and one device-to-host transfer per step (the
-reference issues one of each per layer).
+All layers are processed with one stacked all-reduce per step (the reference issues one per layer).  The
+statistics stay on the device: ``optimizers._hook_stats`` is a mapping that computes its values, with ONE
+device-to-host transfer, the first time it is read after a step (the metric logger reads it on log steps only), so
+the optimizer step itself never waits for the GPU.
 """
 from __future__ import annotations
 
@@ -22,16 +24,82 @@ _DEAD_THRESHOLD_FRACTION = 0.05
 
 
 class _MoEBalanceTracker:
-    """Running per-layer totals of tokens per expert."""
+    """Running per-layer totals of tokens per expert (kept where the counters live)."""
 
     def __init__(self):
-        self.totals: torch.Tensor | None = None  # [layers, experts] on CPU
+        self.totals: torch.Tensor | None = None  # [layers, experts]
         self.batches = 0
 
-    def update(self, tokens: torch.Tensor) -> dict[str, torch.Tensor]:
+    def update(self, tokens: torch.Tensor) -> None:
         self.totals = tokens.clone() if self.totals is None else self.totals + tokens
         self.batches += 1
-        return _balance_stats(self.totals)
+
+
+class _LazyStats(dict):
+    """Mapping of balance statistics that is filled in on first read (one host transfer of two small tensors)."""
+
+    def __init__(self):
+        super().__init__()
+        self._pending = None   # (batch tokens, running totals, batches, extra) still on the device
+
+    def defer(self, batch: torch.Tensor, totals: torch.Tensor, batches: int, extra) -> None:
+        super().clear()
+        self._pending = (batch, totals, batches, extra)
+
+    def clear(self) -> None:
+        super().clear()
+        self._pending = None
+
+    def _fill(self) -> None:
+        if self._pending is None:
+            return
+        batch, totals, batches, extra = self._pending
+        self._pending = None
+        both = torch.stack([batch.float(), totals.float()]).cpu()   # the only host transfer
+        for key, vals in (("batch", _balance_stats(both[0])), ("global", _balance_stats(both[1]))):
+            super().__setitem__(f"expert_balance/{key}_maxvio_mean", vals["maxvio"].mean().item())
+            super().__setitem__(f"expert_balance/{key}_maxvio_max", vals["maxvio"].max().item())
+            super().__setitem__(f"expert_balance/{key}_cv_mean", vals["cv"].mean().item())
+            super().__setitem__(f"expert_balance/{key}_dead_frac_mean", vals["dead_frac"].mean().item())
+        super().__setitem__("expert_balance/batches", batches)
+        if extra is not None:
+            for k, v in extra().items():
+                super().__setitem__(k, v)
+
+    def __getitem__(self, k):
+        self._fill()
+        return super().__getitem__(k)
+
+    def __contains__(self, k):
+        self._fill()
+        return super().__contains__(k)
+
+    def __iter__(self):
+        self._fill()
+        return super().__iter__()
+
+    def __len__(self):
+        self._fill()
+        return super().__len__()
+
+    def __bool__(self):
+        return self._pending is not None or super().__len__() > 0
+
+    def keys(self):
+        self._fill()
+        return super().keys()
+
+    def items(self):
+        self._fill()
+        return super().items()
+
+    def values(self):
+        self._fill()
+        return super().values()
+
+    def get(self, k, default=None):
+        self._fill()
+        return super().get(k, default)
 
 
 def _balance_stats(tokens: torch.Tensor) -> dict[str, torch.Tensor]:
@@ -57,7 +125,7 @@ def _moe_modules(model: nn.Module) -> list[nn.Module]:
 
 def build_deepseek_optimizers(model: nn.Module, cfg, parallel_dims) -> OptimizersContainer:
     optimizers = build_optimizers(model, cfg, parallel_dims)
-    optimizers._hook_stats = {}
+    optimizers._hook_stats = _LazyStats()
     tracker = _MoEBalanceTracker()
     optimizers._moe_balance_tracker = tracker
 
@@ -77,24 +145,21 @@ def build_deepseek_optimizers(model: nn.Module, cfg, parallel_dims) -> Optimizer
                     delta = m.load_balance_coeff * torch.sign(t.mean() - t)
                     m.expert_bias.add_(delta - delta.mean())
                 m.tokens_per_expert.zero_()
-            tokens_cpu = tokens.float().cpu()  # the only host transfer of the hook
-        batch = _balance_stats(tokens_cpu)
-        running = tracker.update(tokens_cpu)
-        st = optimizers._hook_stats
-        for key, vals in (("batch", batch), ("global", running)):
-            st[f"expert_balance/{key}_maxvio_mean"] = vals["maxvio"].mean().item()
-            st[f"expert_balance/{key}_maxvio_max"] = vals["maxvio"].max().item()
-            st[f"expert_balance/{key}_cv_mean"] = vals["cv"].mean().item()
-            st[f"expert_balance/{key}_dead_frac_mean"] = vals["dead_frac"].mean().item()
-        st["expert_balance/batches"] = tracker.batches
-        if cfg.enable_wandb:
-            try:
-                import wandb
-                for i, m in enumerate(moes):
-                    if m.expert_bias is not None:
-                        st[f"expert_balance/bias_hist_layer{i}"] = wandb.Histogram(m.expert_bias.float().cpu().numpy())
-            except ImportError:
-                pass
+            tracker.update(tokens)
+
+        def histograms() -> dict:
+            out = {}
+            if cfg.enable_wandb:
+                try:
+                    import wandb
+                    for i, m in enumerate(moes):
+                        if m.expert_bias is not None:
+                            out[f"expert_balance/bias_hist_layer{i}"] = wandb.Histogram(m.expert_bias.float().cpu().numpy())
+                except ImportError:
+                    pass
+            return out
+
+        optimizers._hook_stats.defer(tokens, tracker.totals.clone(), tracker.batches, histograms)
 
     optimizers.register_step_pre_hook(update_expert_bias)
     return optimizers

@@ -116,3 +116,40 @@ def test_newton_schulz_native_matches_reference():
         assert ((got - want).norm() / want.norm()) < 5e-2
     from maester_b200.ops import cuda as C
     C.check_status()
+
+
+def test_moe_load_balance_hook_updates_biases_and_defers_its_statistics():
+    """The optimizer pre-hook of the MoE families (reference: maester/models/deepseek/optimizer.py:14-222) moves the
+    expert biases against the load and clears the counters; the balance statistics are only computed when read."""
+    from maester_b200.config import Config
+    from maester_b200.trainer import Trainer
+    cfg = Config(model_name="deepseek", flavor="debug_flex", seq_len=64, train_batch_size=2, enable_checkpoint=False,
+                 synthetic_vocab_size=512, scheduler="constant", ac_mode="none", data_parallel_shard_degree=1,
+                 optimizer_groups=[{"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3}, "min_dim": 0}])
+    from maester_b200.models import models_config
+    flavor = models_config["deepseek"]["debug_flex"]
+    old = flavor.moe_args.load_balance_coeff
+    flavor.moe_args.load_balance_coeff = 1e-3          # the debug flavors switch the bias update off
+    try:
+        tr = Trainer(cfg)
+    finally:
+        flavor.moe_args.load_balance_coeff = old
+    moes = [l.moe for l in tr.model.layers.values() if getattr(l, "moe_enabled", False)]
+    assert moes and all(m.expert_bias is not None for m in moes)
+    before = [m.expert_bias.clone() for m in moes]
+    g = torch.Generator().manual_seed(0)
+    batch = {"input_ids": torch.randint(0, 512, (2, 64), generator=g), "labels": torch.randint(0, 512, (2, 64), generator=g)}
+    tr.train_step(batch)
+    stats = tr.optimizers._hook_stats
+    assert stats._pending is not None and dict.__len__(stats) == 0        # nothing computed yet
+    assert all(float(m.tokens_per_expert.abs().sum()) == 0 for m in moes)  # counters cleared by the hook
+    assert any(not torch.equal(b, m.expert_bias) for b, m in zip(before, moes))
+    assert all(abs(float(m.expert_bias.mean())) < 1e-6 for m in moes)      # re-centred
+    assert bool(stats)
+    out = dict(stats)                                                      # first read computes
+    assert stats._pending is None
+    assert out["expert_balance/batches"] == 1
+    for key in ("batch_maxvio_mean", "batch_cv_mean", "global_maxvio_max", "global_dead_frac_mean"):
+        assert f"expert_balance/{key}" in out
+    tr.train_step(batch)
+    assert dict(tr.optimizers._hook_stats)["expert_balance/batches"] == 2
