@@ -576,20 +576,15 @@ extern "C" int mb_gemm_bf16_rs(const void* A, const void* B, void* const* peer_o
 // consumed as soon as its counter in `flags` ([M / 256] ints, zeroed here) shows that every share has landed.
 // The caller makes sure (cross-rank barrier) that the peers' blocks are complete before the launch and are
 // not overwritten before all ranks have finished.
-extern "C" int mb_gemm_bf16_ag(void* a_full, void* const* peer_src, int world, int my_rank, const void* B, void* C,
-                               int M, int N, int K, long long ldb, long long ldc, int b_mn, int copiers, int* flags,
-                               cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
+namespace {
+// Fills the all-gather fields of `p` (whose output / epilogue fields are set by the caller) and launches.
+int ag_launch(GemmParams& p, void* a_full, void* const* peer_src, int world, int my_rank, const void* B, long long ldb,
+              int b_mn, int copiers, int* flags, cudaStream_t stream) {
+  const int M = p.M, K = p.K;
   if (world < 2 || world > 8 || M % (world * 2 * BM) || (K & 7)) return -3;
   if (copiers != 1 && copiers != 2 && copiers != 4 && copiers != 8) return -3;
   if ((ldb & 7) || (reinterpret_cast<uintptr_t>(a_full) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
-  GemmParams p;
-  p.C = C;
   p.aux = nullptr;
-  p.M = M;
-  p.N = N;
-  p.K = K;
-  p.ldc = ldc;
   p.ldaux = 0;
   p.epi = EPI_BF16;
   p.alpha = 1.f;
@@ -612,6 +607,53 @@ extern "C" int mb_gemm_bf16_ag(void* a_full, void* const* peer_src, int world, i
   if (cudaMemsetAsync(flags, 0, sizeof(int) * (M / (2 * BM)), stream) != cudaSuccess) return -5;
   if (b_mn) return launch2<false, true>(a_full, B, p, K, ldb, stream);
   return launch2<false, false>(a_full, B, p, K, ldb, stream);
+}
+}  // namespace
+
+extern "C" int mb_gemm_bf16_ag(void* a_full, void* const* peer_src, int world, int my_rank, const void* B, void* C,
+                               int M, int N, int K, long long ldb, long long ldc, int b_mn, int copiers, int* flags,
+                               cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  GemmParams p;
+  p.C = C;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  return ag_launch(p, a_full, peer_src, world, my_rank, B, ldb, b_mn, copiers, flags, stream);
+}
+
+// The all-gather GEMM with a gated-linear-unit epilogue (GemmParams::glu_mode), for tensor-parallel MLPs:
+//  glu_mode 1: B = fused weight [gate rows | up rows] ([2F, K], K-major); C = [gate | up] ([M, 2F], pitch ldc, may be
+//              null) and io = act(gate) * up ([M, F], pitch ld_io).
+//  glu_mode 2: the gathered A is dy [M, K], B = down-projection weight [K, F] (b_mn layout); io = the saved [gate | up]
+//              ([M, 2F], pitch ld_io) and C = d[gate | up] ([M, 2F], pitch ldc).
+extern "C" int mb_gemm_bf16_ag_glu(void* a_full, void* const* peer_src, int world, int my_rank, const void* B,
+                                   void* C, int M, int F, int K, long long ldb, long long ldc, int copiers, int* flags,
+                                   int glu_mode, int act, void* io, long long ld_io, cudaStream_t stream) {
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if ((glu_mode != 1 && glu_mode != 2) || (ldc & 7) || (ld_io & 7) || (reinterpret_cast<uintptr_t>(io) & 15) ||
+      (C && (reinterpret_cast<uintptr_t>(C) & 15)))
+    return -3;
+  if (glu_mode == 1 ? (F % BNH) != 0 : (F % 32) != 0) return -3;
+  if (glu_mode == 2 && !C) return -3;
+  GemmParams p;
+  p.C = C;
+  p.M = M;
+  p.N = glu_mode == 1 ? 2 * F : F;
+  p.K = K;
+  p.ldc = ldc;
+  p.glu_mode = glu_mode;
+  p.glu_act = act;
+  p.glu_F = F;
+  if (glu_mode == 1) {
+    p.glu_out = io;
+    p.glu_ldo = ld_io;
+  } else {
+    p.glu_in = io;
+    p.glu_ldi = ld_io;
+  }
+  return ag_launch(p, a_full, peer_src, world, my_rank, B, ldb, glu_mode == 2, copiers, flags, stream);
 }
 
 // Grouped GEMM over the contraction range on CTA pairs (weight gradients of stacked expert weights):

@@ -125,14 +125,13 @@ class FeedForward(nn.Module):
 
     def forward(self, x, residual=None, recompute_act: bool = False):
         if self.tp_fused is not None:
-            from maester_b200.parallel.fused_tp import ag_linear, linear_rs
-            gate_up = ag_linear(x, self._fused().get(), self.tp_fused)
-        else:
-            return ops.glu_mlp(x, self._fused().get(), self.w2.weight, "silu", residual=residual)
-        act = ops.glu(gate_up, "silu")
-        if self.tp_fused is not None:
-            return linear_rs(act, self.w2.weight, residual, self.tp_fused)
-        return self.w2(act, residual=residual)
+            from maester_b200.parallel.fused_tp import ag_linear, glu_mlp_tp, linear_rs
+            w_gu = self._fused().get()
+            if (w_gu.shape[0] // 2) % 128 == 0 and w_gu.is_contiguous() and ops.use_native(x, w_gu):
+                return glu_mlp_tp(x, w_gu, self.w2.weight, "silu", residual, self.tp_fused)
+            gate_up = ag_linear(x, w_gu, self.tp_fused)
+            return linear_rs(ops.glu(gate_up, "silu"), self.w2.weight, residual, self.tp_fused)
+        return ops.glu_mlp(x, self._fused().get(), self.w2.weight, "silu", residual=residual)
 
     def init_weights(self, init_std: float) -> None:
         for lin in (self.w1, self.w2, self.w3):

@@ -132,6 +132,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_peer_slot_dot": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _L, _P],
         "mb_gemm_bf16_rs": [_P, _P, _P, _I, _I, _I, _I, _I, _L, _L, _L, _I, _I, _F, _P],
         "mb_gemm_bf16_ag": [_P, _P, _I, _I, _P, _P, _I, _I, _I, _L, _L, _I, _I, _P, _P],
+        "mb_gemm_bf16_ag_glu": [_P, _P, _I, _I, _P, _P, _I, _I, _I, _L, _L, _I, _P, _I, _I, _P, _L, _P],
         "mb_sum_partials": [_P, _P, _P, _L, _I, _P],
         "mb_pull_sum": [_P, _I, _I, _P, _P, _L, _L, _P],
         "mb_wait_flag_probe": [_P, _I, _F, _P, _P],

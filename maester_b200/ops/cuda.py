@@ -443,6 +443,32 @@ def gemm_ag(a_full: torch.Tensor, symm_blocks, my_rank: int, b: torch.Tensor, fl
     return out
 
 
+def gemm_ag_glu(a_full: torch.Tensor, symm_blocks, my_rank: int, b: torch.Tensor, flags: torch.Tensor, *, mode: int,
+                act: int, gate_up: torch.Tensor | None = None, copiers: int = 4):
+    """The all-gather GEMM with a gated-linear-unit epilogue.
+
+    mode 1 (forward): ``b`` = fused weight ``[2F, K]``; returns ``(gate_up [M, 2F], act(gate) * up [M, F])``.
+    mode 2 (backward): ``a_full`` gathers dy ``[M, K]``, ``b`` = down-projection weight ``[K, F]``, ``gate_up`` the
+    tensor saved by the forward pass; returns ``d[gate | up]`` ``[M, 2F]``."""
+    M, K = a_full.shape
+    assert a_full.is_contiguous() and a_full.dtype == torch.bfloat16 and flags.numel() >= M // 256
+    if mode == 1:
+        F = b.shape[0] // 2
+        assert b.shape[1] == K
+        c = torch.empty(M, 2 * F, device=a_full.device, dtype=torch.bfloat16)
+        io = torch.empty(M, F, device=a_full.device, dtype=torch.bfloat16)
+    else:
+        F = b.shape[1]
+        assert b.shape[0] == K and gate_up is not None and gate_up.shape == (M, 2 * F) and gate_up.is_contiguous()
+        c = torch.empty(M, 2 * F, device=a_full.device, dtype=torch.bfloat16)
+        io = gate_up
+    _ck(_lib.lib().mb_gemm_bf16_ag_glu(a_full.data_ptr(), symm_blocks.ptr_array, symm_blocks.world, my_rank,
+                                       b.data_ptr(), c.data_ptr(), M, F, K, _rows_pitch(b), 2 * F, copiers,
+                                       flags.data_ptr(), int(mode), int(act), io.data_ptr(), _rows_pitch(io), _stream()),
+        "gemm_ag_glu")
+    return (c, io) if mode == 1 else c
+
+
 def wait_flag(flag: torch.Tensor, expect: int, timeout_ms: float, observed: torch.Tensor | None = None) -> None:
     """Stream-ordered bounded wait until ``flag[0] >= expect`` (int32 device tensor, may be peer memory).
     On expiry the library status word is set (``check_status`` raises) and the stream simply continues."""

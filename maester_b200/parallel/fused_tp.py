@@ -77,19 +77,25 @@ class FusedTP:
         return out
 
 
-    def ag_gemm(self, x2: torch.Tensor, b: torch.Tensor, *, b_mn: bool) -> tuple[torch.Tensor, torch.Tensor]:
+    def ag_gemm(self, x2: torch.Tensor, b: torch.Tensor, *, b_mn: bool, glu=None):
         """``(all_gather(x2), all_gather(x2) @ op(b).T)`` with the gather inside the GEMM kernel
         (``mb_gemm_bf16_ag``): every rank publishes its row block in a symmetric buffer; a few CTA pairs of the
         GEMM pull the other blocks over NVLink with bulk copies while the rest multiply the local rows, and a
         remote row tile is consumed as soon as its counter shows that it has landed.  Two buffers alternate,
-        so one cross-rank barrier per call.  Falls back to NCCL + GEMM for shapes the kernel does not take."""
+        so one cross-rank barrier per call.  Falls back to NCCL + GEMM for shapes the kernel does not take.
+
+        ``glu = (mode, act, gate_up)`` adds the gated-linear-unit epilogue (``ops.cuda.gemm_ag_glu``): the second
+        value is then ``(gate_up, act(gate) * up)`` (mode 1) or ``d[gate | up]`` (mode 2)."""
         from maester_b200.ops import cuda as C
         tp = self.tp
         Ml, K = x2.shape
         M = Ml * tp.size
         if self.ag_mode != "fused" or Ml % 256 or K % 8 or not x2.is_contiguous():
             full = _all_gather_rows(x2, tp)
-            return full, C.gemm(full, b, b_mn=b_mn)
+            if glu is None:
+                return full, C.gemm(full, b, b_mn=b_mn)
+            mode, act, gate_up = glu
+            return full, (C.gemm_glu_fwd(full, b, act) if mode == 1 else C.gemm_glu_bwd(full, b, gate_up, act))
         if not self.ag_pair:
             self.ag_pair = [SymmBuffer(Ml * K, torch.bfloat16, x2.device, tp.group) for _ in range(2)]
             self.ag_flags = torch.zeros(max(M // 256, 1), dtype=torch.int32, device=x2.device)
@@ -111,6 +117,10 @@ class FusedTP:
             copiers = 1
             while copiers < 8 and copiers * N < 27000:
                 copiers *= 2
+        if glu is not None:
+            mode, act, gate_up = glu
+            return full, C.gemm_ag_glu(full, buf, tp.rank, b, self.ag_flags, mode=mode, act=act, gate_up=gate_up,
+                                       copiers=copiers)
         return full, C.gemm_ag(full, buf, tp.rank, b, self.ag_flags, b_mn=b_mn, copiers=copiers)
 
 
@@ -177,6 +187,43 @@ class _LinearRS(Function):
             dy_full, dx = _all_gather_rows(dy2, ctx.fused.tp), None
         dw = _wgrad(w, dy_full, x2) if ctx.needs_input_grad[1] else None
         return dx, dw, (dy if ctx.has_res else None), None
+
+
+class _AGGluRS(Function):
+    """Tensor-parallel gated MLP on a token-sharded input as ONE autograd node:
+    ``reduce_scatter(act(all_gather(x) w_gate^T) * (all_gather(x) w_up^T)) w_down^T) (+ residual)``.
+    The gather runs inside the gate|up GEMM whose epilogue also forms the activation; backward gathers dy inside the
+    down-projection's input-gradient GEMM whose epilogue applies the activation's derivative; the two remaining
+    collectives are GEMM + reduce-scatter kernels.  No stand-alone element-wise pass, no NCCL call."""
+
+    @staticmethod
+    def forward(ctx, x, w_gu, w_down, residual, fused: FusedTP, act: int):
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        x_full, (gate_up, a) = fused.ag_gemm(x2, w_gu, b_mn=False, glu=(1, act, None))
+        res2 = residual.reshape(-1, w_down.shape[0]).contiguous() if residual is not None else None
+        out = fused.gemm_rs(a, w_down, b_mn=False, residual=res2)
+        ctx.save_for_backward(x_full, w_gu, w_down, gate_up, a)
+        ctx.fused, ctx.act, ctx.x_shape, ctx.has_res = fused, act, x.shape, residual is not None
+        return out.view(1, out.shape[0], w_down.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, w_gu, w_down, gate_up, a = ctx.saved_tensors
+        fused = ctx.fused
+        dy2 = dy.reshape(-1, w_down.shape[0]).contiguous()
+        dy_full, d_gu = fused.ag_gemm(dy2, w_down, b_mn=True, glu=(2, ctx.act, gate_up))
+        dw_down = _wgrad(w_down, dy_full, a) if ctx.needs_input_grad[2] else None
+        dx = fused.gemm_rs(d_gu, w_gu, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw_gu = _wgrad(w_gu, d_gu, x_full) if ctx.needs_input_grad[1] else None
+        return dx, dw_gu, dw_down, (dy if ctx.has_res else None), None, None
+
+
+def glu_mlp_tp(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, activation: str,
+               residual: torch.Tensor | None, fused: FusedTP) -> torch.Tensor:
+    """Gated MLP of a tensor-parallel block (``w_gate_up``: this rank's ``[gate rows | up rows]``, ``w_down``: this
+    rank's columns) on the token-sharded residual stream; returns this rank's token rows of the summed result."""
+    from maester_b200.ops.functional import _ACT
+    return _AGGluRS.apply(x, w_gate_up, w_down, residual, fused, _ACT[activation])
 
 
 def ag_linear(x: torch.Tensor, w: torch.Tensor, fused: FusedTP) -> torch.Tensor:

@@ -50,3 +50,42 @@ def test_pull_sum_with_local_peer_table(world, M, N, with_res):
         want = total[rank * rows:(rank + 1) * rows] + (res.float() if with_res else 0)
         assert ((out.float() - want).norm() / want.norm()).item() < 6e-3
     C.check_status()
+
+
+@pytest.mark.parametrize("world,Ml,K,F,act", [(2, 256, 512, 384, 1), (2, 512, 1024, 1024, 0), (4, 256, 256, 128, 1)])
+def test_all_gather_gemm_with_gated_unit_epilogues(world, Ml, K, F, act):
+    """Forward (gate|up GEMM + activation) and backward (down-projection dgrad + activation derivative) of the
+    tensor-parallel gated MLP, with the gather of the row blocks inside the same kernel (local peer table)."""
+    from maester_b200.ops import cuda as C
+    from maester_b200.ops import reference as ref
+    torch.manual_seed(7)
+    blocks = [torch.randn(Ml, K, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    peers = _Blocks(blocks)
+    w_gu = (torch.randn(2 * F, K, device="cuda") * K ** -0.5).to(torch.bfloat16)
+    full = torch.cat(blocks)
+    glu = ref.swiglu if act == 1 else ref.geglu
+    want_gu = (full.float() @ w_gu.float().t())
+    flags = torch.zeros(world * Ml // 256, dtype=torch.int32, device="cuda")
+    for rank in range(world):
+        a = torch.full((world * Ml, K), float("nan"), device="cuda", dtype=torch.bfloat16)
+        a[rank * Ml:(rank + 1) * Ml].copy_(blocks[rank])
+        gu, out = C.gemm_ag_glu(a, peers, rank, w_gu, flags, mode=1, act=act, copiers=2)
+        assert torch.equal(a, full)
+        assert ((gu.float() - want_gu).norm() / want_gu.norm()).item() < 1e-2
+        want_out = glu(gu.float())                    # the activation sees the rounded [gate | up] that is stored
+        assert ((out.float() - want_out).norm() / want_out.norm()).item() < 1e-2
+    # backward: the gathered operand is dy [M, D]; weight [D, F]; epilogue applies act'
+    D = K
+    dys = [torch.randn(Ml, D, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    dpeers = _Blocks(dys)
+    w_down = (torch.randn(D, F, device="cuda") * D ** -0.5).to(torch.bfloat16)
+    dy_full = torch.cat(dys)
+    guf = gu.float().requires_grad_()
+    glu(guf).backward(dy_full.float() @ w_down.float())
+    for rank in range(world):
+        a = torch.full((world * Ml, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+        a[rank * Ml:(rank + 1) * Ml].copy_(dys[rank])
+        d_gu = C.gemm_ag_glu(a, dpeers, rank, w_down, flags, mode=2, act=act, gate_up=gu, copiers=2)
+        assert torch.equal(a, dy_full)
+        assert ((d_gu.float() - guf.grad).norm() / guf.grad.norm()).item() < 1.5e-2
+    C.check_status()
