@@ -37,13 +37,14 @@ PRESETS = {
     # the same model over 4 ranks (16 experts per rank): the A/B against the reference where 8-GPU boxes are scarce
     "deepseek-moe-ep4": dict(model_name="deepseek", flavor="bench16L", seq_len=4096, train_batch_size=4,
                              expert_parallel="world"),
-    # fp32 master + Adam state + gradient shard: 16 B/parameter, 54 GB per GPU at 8 GPUs; the bf16 parameters exist
-    # per block only while the block runs (resharding mode of the sharding runtime)
+    # fp32 master + Adam state + gradient shard: 16 B/parameter, 108 GB per GPU at 4 GPUs (54 GB at 8); the bf16
+    # parameters exist per block only while the block runs (resharding mode of the sharding runtime); run it with
+    # --ac full on 4 GPUs (the activations of 62 blocks at 8192 tokens would not fit beside the state otherwise)
     "gemma3-27b": dict(model_name="gemma3", flavor="27B", seq_len=8192, train_batch_size=1),
     "deepseek-moe-1gpu": dict(model_name="deepseek", flavor="bench6L", seq_len=4096, train_batch_size=4),
 }
 # smallest world size whose GPUs hold the configuration (sharded fp32 state + activations within 180 GB each)
-MIN_GPUS = {"llama3-8b-cp2": 4, "deepseek-moe-ep8": 8, "deepseek-moe-ep4": 4, "gemma3-27b": 8}
+MIN_GPUS = {"llama3-8b-cp2": 4, "deepseek-moe-ep8": 8, "deepseek-moe-ep4": 4, "gemma3-27b": 4}
 
 
 def main() -> None:
