@@ -91,6 +91,37 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(float* __restrict__ acc
   if (lane == 0) lse[li] = ln;
 }
 
+// One entry per (parameter, source rank) of a sharded block: `len` elements of 2 bytes from offset `src_off` of rank
+// `rank`'s shard buffer to offset `dst_off` of the local staging buffer.  All three are multiples of 8 elements.
+struct GatherDesc {
+  long long dst_off;
+  long long src_off;
+  long long len;
+  long long rank;
+};
+struct GatherPeers {
+  const uint4* base[8];
+};
+
+// grid (entries, slices): slice y of an entry's 16-byte words, eight independent loads in flight per thread.
+__global__ void __launch_bounds__(256) peer_gather_kernel(uint4* __restrict__ dst, GatherPeers peers,
+                                                         const GatherDesc* __restrict__ descs) {
+  const GatherDesc d = descs[blockIdx.x];
+  const uint4* __restrict__ src = peers.base[d.rank] + (d.src_off >> 3);
+  uint4* __restrict__ out = dst + (d.dst_off >> 3);
+  const long long n16 = d.len >> 3;
+  const long long stride = static_cast<long long>(gridDim.y) * blockDim.x;
+  long long i = static_cast<long long>(blockIdx.y) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], e = src[i + 3 * stride];
+    out[i] = a;
+    out[i + stride] = b;
+    out[i + 2 * stride] = c;
+    out[i + 3 * stride] = e;
+  }
+  for (; i < n16; i += stride) out[i] = src[i];
+}
+
 int copy_grid(long long n16) {
   long long blocks = (n16 + 256 * 4 - 1) / (256 * 4);
   const long long cap = static_cast<long long>(mbh::sm_count());  // one light block per SM beside the attention CTAs
@@ -127,4 +158,21 @@ extern "C" int mb_attn_merge(float* acc, float* lse, const void* part, const flo
   attn_merge_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(acc, lse, static_cast<const __nv_bfloat16*>(part),
                                                                   lse_part, B, c, H, hd, S_acc, row_off, init);
   return mbh::check_launch("attn_merge");
+}
+
+// All-gather of one sharded block into its staging buffer by plain peer loads: `peer_base[r]` is rank r's shard
+// buffer (bf16, this rank's own included), `descs` a device array of `ndesc` GatherDesc entries, `slices` the number
+// of blocks that share one entry.  Callers make sure with a cross-rank barrier that the shard buffers are final.
+extern "C" int mb_peer_gather(void* dst, void* const* peer_base, int world, const void* descs, int ndesc, int slices,
+                              cudaStream_t st) {
+  if (ndesc <= 0) return 0;
+  if (world < 1 || world > 8 || slices < 1 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -3;
+  GatherPeers peers;
+  for (int r = 0; r < 8; ++r) {
+    peers.base[r] = r < world ? static_cast<const uint4*>(peer_base[r]) : nullptr;
+    if (r < world && (!peer_base[r] || (reinterpret_cast<uintptr_t>(peer_base[r]) & 15))) return -3;
+  }
+  peer_gather_kernel<<<dim3(ndesc, slices), 256, 0, st>>>(static_cast<uint4*>(dst), peers,
+                                                         static_cast<const GatherDesc*>(descs));
+  return mbh::check_launch("peer_gather");
 }

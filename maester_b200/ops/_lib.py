@@ -157,6 +157,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_expect_scalar": [_P, _F, _P],
         "mb_adamw": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _I, _P],
         "mb_peer_copy": [_P, _P, _L, _P],
+        "mb_peer_gather": [_P, _P, _I, _P, _I, _I, _P],
         "mb_peer_add_bf16": [_P, _P, _L, _P],
         "mb_attn_merge": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "mb_multi_sqnorm": [_P, _P, _I, _P, _P, _P],

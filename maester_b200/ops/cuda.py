@@ -504,6 +504,15 @@ def peer_copy(dst: torch.Tensor, src_ptr: int, nbytes: int) -> None:
     _ck(_lib.lib().mb_peer_copy(dst.data_ptr(), int(src_ptr), int(nbytes), _stream()), "peer_copy")
 
 
+def peer_gather(dst: torch.Tensor, symm_shards, descs: torch.Tensor, slices: int = 8) -> None:
+    """Fill ``dst`` (local bf16 staging buffer) from the ranks' shard buffers (``symm_shards``: SymmBuffer) as listed
+    by ``descs`` (int64 ``[n, 4]``: destination offset, source offset, length in elements; source rank), with the
+    library's own copy kernel over peer-mapped memory."""
+    assert dst.is_contiguous() and descs.dtype == torch.int64 and descs.is_contiguous() and descs.shape[1] == 4
+    _ck(_lib.lib().mb_peer_gather(dst.data_ptr(), symm_shards.ptr_array, symm_shards.world, descs.data_ptr(),
+                                  descs.shape[0], int(slices), _stream()), "peer_gather")
+
+
 def peer_add_bf16(dst: torch.Tensor, src_ptr: int, n: int) -> None:
     """``dst[:n] += *src_ptr`` (bf16; the source may be peer memory)."""
     assert dst.is_contiguous() and dst.dtype == torch.bfloat16 and dst.numel() >= n

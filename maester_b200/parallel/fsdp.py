@@ -41,6 +41,7 @@ in pinned host memory with the optimizer step running there.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 
 import torch
@@ -234,7 +235,7 @@ class ShardedModel:
             # until the weights are initialised the parameters are views of a temporary full buffer; gradients only
             # exist in the staging buffers created by _enter_reshard()
             self.full_grad = None
-            self.shard_lp = torch.zeros(s, dtype=param_dtype, device=device)
+            self.shard_lp = self._symmetric_rows(s, param_dtype, device, shard_group)
         elif self.world > 1:
             self.full_grad = self.symm_grad.tensor.zero_() if self.fused else \
                 torch.zeros(f, dtype=torch.float32, device=device)
@@ -313,6 +314,7 @@ class ShardedModel:
         self.root_grad = torch.zeros(r.full_hi - r.full_lo, dtype=torch.float32, device=dev)
         self.full = None
         self.resharded = True
+        self._setup_peer_gather()
         self.slot_owner = [-1] * self.STAGES
         self.gslot_event = [None] * self.STAGES
         self._rebind_parameters()
@@ -325,6 +327,42 @@ class ShardedModel:
             f"root unit resident ({(r.full_hi - r.full_lo) * 2 / 2**30:.2f} GiB), "
             f"optimizer state on {'the host' if self.cpu_offload else 'the device'}"
         )
+
+    peer_gather = False   # blocks are gathered by the library's copy kernel over peer memory instead of NCCL
+    symm_lp = None
+
+    def _symmetric_rows(self, s: int, dtype, device, group) -> torch.Tensor:
+        """Buffer of this rank's compute-dtype rows (resharding mode).  Where the peer-memory plane is usable it is a
+        symmetric allocation, so that the other ranks can read the rows they need for a block directly."""
+        usable = (device.type == "cuda" and 1 < self.world <= 8 and not self.has_experts and dtype == torch.bfloat16
+                  and os.environ.get("MB_RESHARD_PEER_GATHER", "1") != "0")
+        if usable:
+            from maester_b200.parallel.symm import SymmBuffer, symmetric_memory_available
+            if symmetric_memory_available(group):
+                try:
+                    self.symm_lp = SymmBuffer(s, dtype, device, group)
+                    return self.symm_lp.tensor.zero_()
+                except Exception as e:  # noqa: BLE001
+                    logger.warning(f"symmetric memory unavailable for the block gathers, using NCCL: {e}")
+                    self.symm_lp = None
+        return torch.zeros(s, dtype=dtype, device=device)
+
+    def _setup_peer_gather(self) -> None:
+        """One copy table per block: entry = (offset in the block's staging buffer, offset in the owner's rows,
+        length, owner).  Needs the symmetric row buffer and 16-byte aligned pieces."""
+        if self.symm_lp is None:
+            return
+        blocks = self.units[:-1]
+        if any((sl.padded_numel | sl.shard_off | (sl.full_off - u.full_lo)) % 8 for u in blocks for sl in u.slots):
+            return
+        world = self.domains[0].world
+        self._gather_tables = {}
+        for i, u in enumerate(blocks):
+            rows = [(sl.full_off - u.full_lo + r * sl.padded_numel, sl.shard_off, sl.padded_numel, r)
+                    for sl in u.slots for r in range(world)]
+            self._gather_tables[i] = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        self.peer_gather = True
+        self.symm_lp.barrier()   # every rank's rows are in place before the first gather
 
     def _replace_param(self, old: nn.Parameter, new: nn.Parameter) -> None:
         """Swap a Parameter object everywhere it is registered (tied weights appear more than once)."""
@@ -478,6 +516,8 @@ class ShardedModel:
     def _shards_to_lowp(self) -> None:
         """bf16 copy of this rank's master rows (what the per-block all-gathers send)."""
         self.shard_lp.copy_(self.master, non_blocking=True)
+        if self.peer_gather:
+            self.symm_lp.barrier()   # every rank's new rows are visible before anyone gathers a block from them
 
     @torch.no_grad()
     def load_full_weights(self, weights: dict[str, torch.Tensor]) -> None:
@@ -557,14 +597,19 @@ class ShardedModel:
             # (tensors saved for the backward pass are views of this buffer: block i always returns to the same
             # addresses, so refilling it must not look like an in-place modification to autograd)
             dom = self.domains[0]
-            n_shard = u.shard_hi - u.shard_lo
-            recv = torch.empty(dom.world * n_shard, dtype=self.param_dtype, device=self.device)
-            dist.all_gather_into_tensor(recv, self.shard_lp[u.shard_lo:u.shard_hi], group=dom.group)
-            rv = recv.view(dom.world, n_shard)
-            for sl in u.slots:
-                o = sl.full_off - u.full_lo
-                buf[o: o + sl.padded_numel * dom.world].view(dom.world, sl.padded_numel).copy_(
-                    rv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel])
+            if self.peer_gather:
+                # one launch: every (parameter, owner) piece goes straight from the owner's rows to its place
+                from maester_b200.ops import cuda as C
+                C.peer_gather(buf, self.symm_lp, self._gather_tables[i])
+            else:
+                n_shard = u.shard_hi - u.shard_lo
+                recv = torch.empty(dom.world * n_shard, dtype=self.param_dtype, device=self.device)
+                dist.all_gather_into_tensor(recv, self.shard_lp[u.shard_lo:u.shard_hi], group=dom.group)
+                rv = recv.view(dom.world, n_shard)
+                for sl in u.slots:
+                    o = sl.full_off - u.full_lo
+                    buf[o: o + sl.padded_numel * dom.world].view(dom.world, sl.padded_numel).copy_(
+                        rv[:, sl.shard_off - u.shard_lo: sl.shard_off - u.shard_lo + sl.padded_numel])
             if stream is not None:
                 u.gather_event = torch.cuda.Event()
                 u.gather_event.record(stream)
@@ -712,6 +757,8 @@ class ShardedModel:
             # every rank refreshes the bf16 copy of its rows; blocks are gathered when they run, the root unit now
             if not self.lowp_fresh or self.cpu_offload:
                 self._shards_to_lowp()
+            elif self.peer_gather:
+                self.symm_lp.barrier()   # (the optimizer kernel wrote the rows) visible before anyone gathers a block
             self.lowp_fresh = False
             self.slot_owner = [-1] * self.STAGES
             stream = self.comm_stream

@@ -94,6 +94,8 @@ def _reshard_worker(rank, world, port, out_dir):
                      fsdp_reshard_after_forward=mode)
         tr = Trainer(cfg)
         assert tr.sharded.resharded == (mode == "always")
+        if mode == "always":   # blocks are gathered by the library's own copy kernel from the peers' symmetric rows
+            assert tr.sharded.peer_gather, "the peer-memory block gather is not active"
         loader = SyntheticLoader(2, 512, tr.model_args.vocab_size, "uniform:16:256", seed=3, rank=rank)
         losses = [tr.train_step(next(loader)).item() for _ in range(4)]
         C.check_status()
