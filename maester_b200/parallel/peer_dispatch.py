@@ -20,7 +20,10 @@ peer-visible buffer itself: no ``[T*k, dim]`` tensor in sorted order, no full-bu
 Backward is the mirror image (gradients of the results are scattered, gradients of the inputs are
 gathered).  Cross-rank ordering is by stream-ordered barriers on the symmetric buffers' signal pads.
 Buffers hold ``capacity_factor x`` the balanced load; rows beyond that are dropped and counted in
-``overflow`` (read it with ``dropped()``; it costs a synchronisation, so only do so when logging).
+``overflow`` (read it with ``dropped()``; it costs a synchronisation, so only do so when logging).  The largest
+row count any call wanted is tracked on the device; ``adapt_capacity()`` (called by the trainer where it reads the
+drop counter) grows the buffers to 1.5 x that peak once a rank comes within 80 % of its capacity, so a drifting
+router load is answered before it overflows; only a jump past the capacity within one logging interval drops rows.
 """
 from __future__ import annotations
 
@@ -167,6 +170,7 @@ class PeerDispatcher:
         self.ep = ep
         self.capacity_factor = capacity_factor
         self.cap = 0
+        self.peak_need: torch.Tensor | None = None   # largest row count any call wanted on this rank (device scalar)
         self._ws: dict[int, SymmBuffer] = {}
         self._inputs: dict[int, SymmBuffer] = {}   # per MoE block: its input buffer is saved for backward
         self._outputs: dict[int, SymmBuffer] = {}  # per MoE block with gates after the experts: outputs kept likewise
@@ -179,7 +183,9 @@ class PeerDispatcher:
         if cap > self.cap:
             assert self.cap == 0, "the number of routing slots per rank must not grow between steps"
             self.cap = cap
+            self._shape = (n_slots, n_local, dim)
             self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
+            self.peak_need = torch.zeros((), dtype=torch.int64, device=device)
             # symmetric allocations are collective: make them here, where all ranks are in step
             for which in (0, 1):
                 self._ws[which] = SymmBuffer(self.cap * dim, torch.bfloat16, device, self.ep.group)
@@ -202,6 +208,43 @@ class PeerDispatcher:
     def barrier(self) -> None:
         self.workspace(0, 0).barrier()
 
+    def _note_need(self, allc: torch.Tensor, n_local: int) -> None:
+        """Track (on the device) how many buffer rows this rank's experts wanted: the groups' 128-padded sizes."""
+        lo = self.ep.rank * n_local
+        tot = allc[:, lo: lo + n_local].sum(0, dtype=torch.int64)
+        need = ((tot + GROUP_ALIGN - 1) // GROUP_ALIGN * GROUP_ALIGN).sum()
+        torch.maximum(self.peak_need, need, out=self.peak_need)
+
+    def adapt_capacity(self, headroom: float = 0.8) -> bool:
+        """Grow the buffers when the fullest rank came within ``headroom`` of its capacity (or overflowed) since the
+        last call.  Collective over the expert-parallel group and synchronising: call it between steps, where the
+        trainer reads the drop counter anyway.  Returns True if the buffers were reallocated (1.5 x the peak)."""
+        if self.peak_need is None:
+            return False
+        peak = self.peak_need.clone()
+        dist.all_reduce(peak, op=dist.ReduceOp.MAX, group=self.ep.group)
+        peak_rows = int(peak.item())
+        self.peak_need.zero_()
+        if peak_rows <= headroom * self.cap:
+            return False
+        n_slots, n_local, dim = self._shape
+        new_cap = (int(1.5 * peak_rows) + GROUP_ALIGN - 1) // GROUP_ALIGN * GROUP_ALIGN
+        if new_cap <= self.cap:
+            return False
+        from maester_b200.log_utils import logger
+        logger.warning(f"expert-parallel peer dispatch: a rank wanted {peak_rows} of {self.cap} buffer rows; "
+                       f"growing the symmetric buffers to {new_cap} rows")
+        device = self.overflow.device
+        self.cap = new_cap
+        self.capacity_factor = new_cap / max(n_slots, 1)
+        self._inputs.clear()
+        self._outputs.clear()
+        self._ws.clear()
+        torch.cuda.synchronize(device)
+        for which in (0, 1):
+            self._ws[which] = SymmBuffer(self.cap * dim, torch.bfloat16, device, self.ep.group)
+        return True
+
     def dropped(self) -> int:
         """Rows dropped over capacity since the last reset (synchronises with the device: call when logging)."""
         return int(self.overflow.item()) if self.overflow is not None else 0
@@ -216,6 +259,7 @@ class PeerDispatcher:
         E = counts.numel()
         allc = torch.empty(ep.size, E, dtype=counts.dtype, device=counts.device)
         dist.all_gather_into_tensor(allc.view(-1), counts.contiguous(), group=ep.group)
+        self._note_need(allc, n_local)
         tot = allc.sum(0)                                              # rows per expert over all ranks
         padded = (tot + GROUP_ALIGN - 1) // GROUP_ALIGN * GROUP_ALIGN
         pv = padded.view(ep.size, n_local)
@@ -246,6 +290,7 @@ class PeerDispatcher:
         self._ensure(route.T * route.k, n_local, dim, x.device)
         allc = torch.empty(ep.size, route.E, dtype=torch.int32, device=x.device)
         dist.all_gather_into_tensor(allc.view(-1), route.counts, group=ep.group)
+        self._note_need(allc, n_local)
         p = _Plan()
         p.slot_rank, p.slot_row, p.offs = C.ep_plan(allc, ep.rank, n_local, route.idx.view(-1), route.inv, GROUP_ALIGN,
                                                     self.cap)

@@ -153,6 +153,7 @@ class Trainer:
             return None
         n = int(disp.dropped())
         disp.reset_dropped()
+        disp.adapt_capacity()   # collective over the expert-parallel group: every rank reaches this on log steps
         if n:
             logger.warning(f"expert-parallel peer dispatch dropped {n} rows over capacity "
                            f"(ep_capacity_factor={self.cfg.ep_capacity_factor}); the all-to-all dispatcher never drops")
