@@ -178,10 +178,12 @@ class PeerDispatcher:
 
     # ------------------------------------------------------------------ buffers
     def _ensure(self, n_slots: int, n_local: int, dim: int, device: torch.device) -> None:
+        if self.cap:   # sized at the first call (and possibly grown by adapt_capacity since)
+            assert n_slots <= self._shape[0], "the number of routing slots per rank must not grow between steps"
+            return
         cap = int(self.capacity_factor * n_slots) + n_local * GROUP_ALIGN
         cap = (cap + GROUP_ALIGN - 1) // GROUP_ALIGN * GROUP_ALIGN
         if cap > self.cap:
-            assert self.cap == 0, "the number of routing slots per rank must not grow between steps"
             self.cap = cap
             self._shape = (n_slots, n_local, dim)
             self.overflow = torch.zeros(1, dtype=torch.int32, device=device)
@@ -236,7 +238,6 @@ class PeerDispatcher:
                        f"growing the symmetric buffers to {new_cap} rows")
         device = self.overflow.device
         self.cap = new_cap
-        self.capacity_factor = new_cap / max(n_slots, 1)
         self._inputs.clear()
         self._outputs.clear()
         self._ws.clear()
