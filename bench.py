@@ -143,7 +143,10 @@ def emit(args, world, value, ms_per_step, e2e, clocks, launches, impl, extra=Non
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": impl,
         "config": {"model": "gemma3-4B", "global_batch": global_batch, "seq_len": SEQ,
                    "parallelism": f"dp{world}" if world > 1 else "single",
-                   "micro_batch_per_gpu": MICRO_BATCH, "activation_checkpointing": "selective(op): q/k normalisation + rotation recomputed in backward",
+                   "micro_batch_per_gpu": MICRO_BATCH,
+                   "activation_checkpointing": ("selective(op): the reference's per-op policy under torch.compile"
+                                                if impl == "reference" else
+                                                "selective(op): q/k normalisation + rotation recomputed in backward"),
                    "optimizer": "AdamW (no decay on embeddings/norms), fp32 master",
                    "l2": "per-step working set >> 126 MB L2, no flush needed"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
