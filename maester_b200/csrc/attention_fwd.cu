@@ -447,6 +447,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           for (int i = 0; i < 32; ++i) o32[i] = 0;
         }
         if (q < p.S) {
+          MB_CHECK_OR(p.status, q >= 0 && b >= 0 && b < p.B && h >= 0 && h < p.H && set * OC + c * 32 + 32 <= HD, continue);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             uint4 o;

@@ -6,6 +6,7 @@
 //   * attn_merge: combine two partial attention results over the same query rows by their log-sum-exp.
 // No waits: callers bracket these with cross-rank barriers on the stream.  No TMA, no multicast.
 #include "host_common.cuh"
+#include "sm100.cuh"
 #include <cuda_bf16.h>
 #include <math.h>
 
@@ -105,8 +106,12 @@ struct GatherPeers {
 
 // grid (entries, slices): slice y of an entry's 16-byte words, eight independent loads in flight per thread.
 __global__ void __launch_bounds__(256) peer_gather_kernel(uint4* __restrict__ dst, GatherPeers peers,
-                                                         const GatherDesc* __restrict__ descs) {
+                                                         const GatherDesc* __restrict__ descs, long long dst_elems,
+                                                         int* status) {
   const GatherDesc d = descs[blockIdx.x];
+  MB_CHECK_OR(status, d.rank >= 0 && d.rank < 8 && peers.base[d.rank] && d.dst_off >= 0 && d.src_off >= 0 &&
+                          d.len >= 0 && !((d.dst_off | d.src_off | d.len) & 7) && d.dst_off + d.len <= dst_elems,
+              return);
   const uint4* __restrict__ src = peers.base[d.rank] + (d.src_off >> 3);
   uint4* __restrict__ out = dst + (d.dst_off >> 3);
   const long long n16 = d.len >> 3;
@@ -163,8 +168,8 @@ extern "C" int mb_attn_merge(float* acc, float* lse, const void* part, const flo
 // All-gather of one sharded block into its staging buffer by plain peer loads: `peer_base[r]` is rank r's shard
 // buffer (bf16, this rank's own included), `descs` a device array of `ndesc` GatherDesc entries, `slices` the number
 // of blocks that share one entry.  Callers make sure with a cross-rank barrier that the shard buffers are final.
-extern "C" int mb_peer_gather(void* dst, void* const* peer_base, int world, const void* descs, int ndesc, int slices,
-                              cudaStream_t st) {
+extern "C" int mb_peer_gather(void* dst, long long dst_elems, void* const* peer_base, int world, const void* descs,
+                              int ndesc, int slices, cudaStream_t st) {
   if (ndesc <= 0) return 0;
   if (world < 1 || world > 8 || slices < 1 || (reinterpret_cast<uintptr_t>(dst) & 15)) return -3;
   GatherPeers peers;
@@ -173,6 +178,7 @@ extern "C" int mb_peer_gather(void* dst, void* const* peer_base, int world, cons
     if (r < world && (!peer_base[r] || (reinterpret_cast<uintptr_t>(peer_base[r]) & 15))) return -3;
   }
   peer_gather_kernel<<<dim3(ndesc, slices), 256, 0, st>>>(static_cast<uint4*>(dst), peers,
-                                                         static_cast<const GatherDesc*>(descs));
+                                                         static_cast<const GatherDesc*>(descs), dst_elems,
+                                                         mbh::status().dev);
   return mbh::check_launch("peer_gather");
 }

@@ -111,6 +111,8 @@ __device__ __forceinline__ void store_glu_fwd_chunk(const GemmParams& p, const u
                                                     const uint32_t (&ru)[32], float alpha, int row, int j0) {
   using namespace mb;
   if (row >= p.M) return;
+  MB_CHECK_OR(p.status, row >= 0 && j0 >= 0 && j0 + 32 <= p.glu_F && p.glu_F <= p.glu_ldo &&
+                            (!p.C || 2LL * p.glu_F <= p.ldc), return);
   __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
   __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.glu_out) + static_cast<long long>(row) * p.glu_ldo + j0;
 #pragma unroll
@@ -141,6 +143,8 @@ __device__ __forceinline__ void store_glu_bwd_chunk(const GemmParams& p, const u
                                                     int j0) {
   using namespace mb;
   if (row >= p.M || j0 >= p.N) return;
+  MB_CHECK_OR(p.status, row >= 0 && j0 >= 0 && j0 + 32 <= p.glu_F && 2LL * p.glu_F <= p.ldc && 2LL * p.glu_F <= p.glu_ldi,
+              return);
   const __nv_bfloat16* irow = reinterpret_cast<const __nv_bfloat16*>(p.glu_in) + static_cast<long long>(row) * p.glu_ldi;
   __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc;
 #pragma unroll
@@ -176,6 +180,7 @@ __device__ __forceinline__ void ce_stats_chunk(const GemmParams& p, const uint32
                                                int col0, long long lab, float& m, float& s) {
   using namespace mb;
   if (row >= p.M || col0 >= p.N) return;
+  MB_CHECK_OR(p.status, row >= 0 && col0 >= 0 && (!p.C || static_cast<long long>(min(col0 + 32, p.N)) <= p.ldc), return);
   const int nvalid = min(32, p.N - col0);
   // round once to bf16 pairs (what is stored), then widen again with shifts: the statistics describe the stored values
   uint32_t pk[16];
@@ -281,6 +286,7 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint3
                                                 int col0, long long c_off = 0) {
   using namespace mb;
   if (row >= p.M || col0 >= p.N) return;
+  MB_CHECK_OR(p.status, row >= 0 && col0 >= 0 && static_cast<long long>(min(col0 + 32, p.N)) <= p.ldc, return);
   const bool full_chunk = (col0 + 32 <= p.N);
   float v[32];
 #pragma unroll

@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(32 * (R + 1), 1)
       const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
       if (lane == 0 && rstd_out) rstd_out[row] = rstd;
       bf16x8* yr = reinterpret_cast<bf16x8*>(y + static_cast<size_t>(row) * D);
+      MB_CHECK_OR(status, row >= 0 && row < M && NV * 256 >= D, continue);
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
         const int v = lane + 32 * i;

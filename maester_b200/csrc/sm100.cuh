@@ -24,8 +24,26 @@ enum : int {
   ERR_WAIT_SOFTMAX = 6,
   ERR_WAIT_MISC = 7,
   ERR_BAD_ARG = 8,
-  ERR_GRAD_SCALE = 9,    // a loss whose gradients were produced ahead of backward received another output gradient
+  ERR_GRAD_SCALE = 9,
+  ERR_BAD_INDEX = 10,    // checked build only: a store would have left its tensor (it was skipped)    // a loss whose gradients were produced ahead of backward received another output gradient
 };
+
+// Checked build (-DMB_CHECKED, `ops._lib.build(checked=True)`): index checks in front of the kernels' global stores.  A
+// failing check records ERR_BAD_INDEX in the status word and SKIPS the store; nothing traps.  In the normal build the
+// macro is empty.  Use: MB_CHECK_OR(status_ptr, condition, statement_when_bad);
+#ifdef MB_CHECKED
+#define MB_CHECK_OR(status, ok, bad)               \
+  do {                                             \
+    if (!(ok)) {                                   \
+      if (status) atomicCAS((status), 0, mb::ERR_BAD_INDEX); \
+      bad;                                         \
+    }                                              \
+  } while (0)
+#else
+#define MB_CHECK_OR(status, ok, bad) \
+  do {                               \
+  } while (0)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

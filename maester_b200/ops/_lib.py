@@ -16,7 +16,10 @@ from pathlib import Path
 _PKG = Path(__file__).resolve().parent.parent
 CSRC = _PKG / "csrc"
 OUT_DIR = _PKG / "_C"
-LIB_PATH = OUT_DIR / "libmaester_b200.so"
+# MB_CHECKED_KERNELS=1 selects the checked build (index checks in front of the kernels' global stores: a failing check
+# skips the store and records a status code; see csrc/sm100.cuh::MB_CHECK_OR).  It is a separate shared object.
+CHECKED = os.environ.get("MB_CHECKED_KERNELS", "0") == "1"
+LIB_PATH = OUT_DIR / ("libmaester_b200_checked.so" if CHECKED else "libmaester_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -52,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if nvcc is None:
         raise RuntimeError("nvcc not found; cannot build maester_b200 kernels")
     OUT_DIR.mkdir(exist_ok=True)
-    obj_dir = OUT_DIR / "obj"
+    obj_dir = OUT_DIR / ("obj_checked" if CHECKED else "obj")
     obj_dir.mkdir(exist_ok=True)
     procs = []
     objs = []
@@ -62,7 +65,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         objs.append(obj)
         if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_t):
             continue
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *(["-DMB_CHECKED"] if CHECKED else []), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -157,7 +160,7 @@ def _declare(l: ctypes.CDLL) -> None:
         "mb_expect_scalar": [_P, _F, _P],
         "mb_adamw": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _F, _F, _F, _F, _F, _F, _I, _P],
         "mb_peer_copy": [_P, _P, _L, _P],
-        "mb_peer_gather": [_P, _P, _I, _P, _I, _I, _P],
+        "mb_peer_gather": [_P, _L, _P, _I, _P, _I, _I, _P],
         "mb_peer_add_bf16": [_P, _P, _L, _P],
         "mb_attn_merge": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "mb_multi_sqnorm": [_P, _P, _I, _P, _P, _P],

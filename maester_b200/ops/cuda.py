@@ -26,6 +26,7 @@ _STATUS_NAMES = {
     7: "pipeline wait timed out",
     8: "bad argument detected on device",
     9: "a loss whose gradients were produced during forward received a different output gradient in backward",
+    10: "checked build: a store outside its tensor was skipped",
 }
 
 launch_count = 0  # number of native kernel launches issued through this module
@@ -509,8 +510,8 @@ def peer_gather(dst: torch.Tensor, symm_shards, descs: torch.Tensor, slices: int
     by ``descs`` (int64 ``[n, 4]``: destination offset, source offset, length in elements; source rank), with the
     library's own copy kernel over peer-mapped memory."""
     assert dst.is_contiguous() and descs.dtype == torch.int64 and descs.is_contiguous() and descs.shape[1] == 4
-    _ck(_lib.lib().mb_peer_gather(dst.data_ptr(), symm_shards.ptr_array, symm_shards.world, descs.data_ptr(),
-                                  descs.shape[0], int(slices), _stream()), "peer_gather")
+    _ck(_lib.lib().mb_peer_gather(dst.data_ptr(), dst.numel(), symm_shards.ptr_array, symm_shards.world,
+                                  descs.data_ptr(), descs.shape[0], int(slices), _stream()), "peer_gather")
 
 
 def peer_add_bf16(dst: torch.Tensor, src_ptr: int, n: int) -> None:

@@ -106,3 +106,45 @@ def test_norms_rope_and_optimizer_repeat_bitwise():
         return C.rmsnorm_bwd(dy, x, w, rstd, True, dw)   # dw is summed with atomics across blocks: not checked
     _twice(nb)
     C.check_status()
+
+
+def test_checked_build_runs_the_kernels_without_a_report():
+    """The checked build (index checks in front of the kernels' global stores, a failing check skips the store and
+    records a status code) runs in a process of its own, selected by MB_CHECKED_KERNELS=1: same results within
+    tolerance, status word clean."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from maester_b200.ops import _lib, cuda as C
+assert _lib.CHECKED and _lib.LIB_PATH.name.endswith("_checked.so")
+torch.manual_seed(0)
+x = torch.randn(1000, 328, device="cuda", dtype=torch.bfloat16)
+w = torch.randn(520, 328, device="cuda", dtype=torch.bfloat16) * 0.05
+y = C.gemm(x, w)
+want = x.float() @ w.float().T
+assert ((y.float() - want).norm() / want.norm()).item() < 1e-2
+wgu = torch.randn(512, 328, device="cuda", dtype=torch.bfloat16) * 0.05
+gu, a = C.gemm_glu_fwd(x, wgu, 1)
+labels = torch.randint(0, 520, (1000,), device="cuda")
+logits, stats, tgt = C.gemm_ce(x, w, labels)
+rec = torch.empty(1000, 4, device="cuda")
+C.ce_merge(stats, tgt, rec)
+lse = torch.logsumexp(logits.float(), dim=1)
+assert ((rec[:, 0] + rec[:, 1].log()) - lse).abs().max().item() < 2e-4
+q = torch.randn(1, 512, 4, 128, device="cuda", dtype=torch.bfloat16)
+k = torch.randn(1, 512, 2, 128, device="cuda", dtype=torch.bfloat16)
+out, l = C.attn_fwd(q, k, k, 128 ** -0.5, True, None, None)
+assert torch.isfinite(out.float()).all()
+C.set_norm_pipeline(True)
+xn = torch.randn(4099, 2560, device="cuda", dtype=torch.bfloat16)
+yn, rstd = C.rmsnorm_fwd(xn, torch.zeros(2560, device="cuda", dtype=torch.bfloat16), 1e-6, True)
+assert torch.isfinite(yn.float()).all()
+C.check_status()
+print("checked build ok")
+'''
+    env = dict(os.environ, MB_CHECKED_KERNELS="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "checked build ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
