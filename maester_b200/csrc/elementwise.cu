@@ -150,16 +150,17 @@ __global__ void __launch_bounds__(128, 3) rmsnorm_fwd_stream_kernel(const __nv_b
       for (int i = 0; i < NV; ++i)
         if (lane + 32 * i < nvec) nxt[i] = xn[lane + 32 * i];
     }
-    float ss = 0.f;
+    float s8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // eight independent chains instead of one of 8 NV adds
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       if (lane + 32 * i < nvec) {
         float f[8];
         unpack8(cur[i], f);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+        for (int e = 0; e < 8; ++e) s8[e] = fmaf(f[e], f[e], s8[e]);
       }
     }
+    float ss = ((s8[0] + s8[1]) + (s8[2] + s8[3])) + ((s8[4] + s8[5]) + (s8[6] + s8[7]));
     ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / static_cast<float>(D) + eps);
     if (lane == 0 && rstd_out) rstd_out[row] = rstd;
@@ -412,7 +413,7 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_smemacc_kernel(
         cx[i] = xr[v];
       }
     }
-    float dot = 0.f;
+    float d8[2] = {0.f, 0.f};  // two independent chains (more would spill at 128 registers)
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
@@ -426,9 +427,9 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_smemacc_kernel(
         float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          const float xh = xf[e] * rstd;
-          dot += g[e] * (w ? wf[e] + off : 1.f) * xh;
-          a[e] += g[e] * xh;
+          const float gx = g[e] * (xf[e] * rstd);
+          d8[e & 1] = fmaf(gx, (w ? wf[e] + off : 1.f), d8[e & 1]);
+          a[e] += gx;
         }
         if (dw) {
           acc4[0] = make_float4(a[0], a[1], a[2], a[3]);
@@ -436,7 +437,9 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_smemacc_kernel(
         }
       }
     }
+    float dot = d8[0] + d8[1];
     dot = warp_sum(dot) / static_cast<float>(D);
+    const float rd = rstd * rstd * dot;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int v = lane + 32 * i;
@@ -446,7 +449,7 @@ __global__ void __launch_bounds__(256, 2) rmsnorm_bwd_smemacc_kernel(
         unpack8(cx[i], xf);
         if (w) unpack8(wr[v], wf);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[e] * (w ? wf[e] + off : 1.f) - xf[e] * rstd * dot);
+        for (int e = 0; e < 8; ++e) o[e] = fmaf(rstd * (w ? wf[e] + off : 1.f), g[e], -xf[e] * rd);
         if (ar) {
           float a[8];
           unpack8(ar[v], a);
@@ -1162,6 +1165,7 @@ extern "C" int mb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
   } while (0)
       if (nv <= 4) MB_NORM_BWD2(4);
       else if (nv <= 8) MB_NORM_BWD2(8);
+      else if (nv <= 10) MB_NORM_BWD2(10);   // hidden size 2560: two vectors fewer to cache, no register spills
       else MB_NORM_BWD2(12);
 #undef MB_NORM_BWD2
       return mbh::check_launch("rmsnorm_bwd_smemacc");
