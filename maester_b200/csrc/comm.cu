@@ -16,6 +16,7 @@
 // brackets it with cross-rank barriers on the stream (all ranks' gradients complete before, all
 // stores visible after).  The gradient buffers are read-only here; they are cleared by zero_grad.
 #include "host_common.cuh"
+#include <stdlib.h>
 #include <cuda_bf16.h>
 
 namespace {
@@ -140,7 +141,16 @@ extern "C" int mb_fused_rs_adamw_ag(const float* grad_mc, void* full_mc, const v
     pp.grad[r] = peer_grad ? static_cast<const float*>(peer_grad[r]) : nullptr;
     pp.full[r] = peer_full ? static_cast<__nv_bfloat16*>(peer_full[r]) : nullptr;
   }
-  const int blocks = nchunks < mbh::sm_count() * 8 ? nchunks : mbh::sm_count() * 8;
+  // Blocks per SM of this kernel.  It usually runs on a side stream beside the backward pass's GEMMs, whose persistent
+  // CTAs share the SMs with it: fewer resident warps here leave them more issue slots and cache, at the price of
+  // fewer peer loads in flight (MB_FUSED_OPT_BLOCKS_PER_SM, default 8).
+  static const int per_sm = []() {
+    const char* e = getenv("MB_FUSED_OPT_BLOCKS_PER_SM");
+    const int v = e ? atoi(e) : 8;
+    return v < 1 ? 1 : (v > 8 ? 8 : v);
+  }();
+  const int cap = mbh::sm_count() * per_sm;
+  const int blocks = nchunks < cap ? nchunks : cap;
   if (grad_mc && full_mc)
     fused_rs_adamw_ag_kernel<true><<<blocks, 256, 0, st>>>(
         grad_mc, static_cast<__nv_bfloat16*>(full_mc), pp, world, master, m, v, shard_grad_out,
