@@ -118,6 +118,29 @@ __device__ __forceinline__ bool wait_counter(const int* p, int target) {
   return true;
 }
 
+// Work unit u -> (tile in rasterisation order, slice sp of nsp of the contraction).  Plain split: all tiles' first
+// slices run before any second slice.  Hybrid split: the tiles of the whole waves first, one unit each, then the
+// slices of the tail tiles.  Grouped weight gradients: sp is the group.
+__device__ __forceinline__ void unit_decode(const GemmParams& p, int u, int num_tiles, int splits, int& tile, int& sp,
+                                            int& nsp) {
+  if (!p.grp_offs && p.tail_splits > 0) {
+    if (u < p.full_tiles) {
+      tile = u;
+      sp = 0;
+      nsp = 1;
+    } else {
+      const int v = u - p.full_tiles, tail = num_tiles - p.full_tiles;
+      tile = p.full_tiles + v % tail;
+      sp = v / tail;
+      nsp = p.tail_splits;
+    }
+    return;
+  }
+  tile = u % num_tiles;
+  sp = u / num_tiles;
+  nsp = splits;
+}
+
 // k-block range of a work unit: slice `sp` of a split contraction, or (grouped weight gradients) the rows of group
 // `sp`, whose offsets are multiples of 128 rows
 __device__ __forceinline__ void unit_krange(const GemmParams& p, int sp, int kblocks, int splits, int& kb0, int& kb1) {
@@ -222,7 +245,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   // second range, so partial sums of one tile rarely meet in the reduction atomics
   const int splits = p.splits > 1 ? p.splits : 1;
   // grouped weight gradients: unit u = (tile u % num_tiles, group u / num_tiles), contraction over the group's rows
-  const int num_units = num_tiles * (p.grp_offs ? p.grp_count : splits);
+  const int num_units = (!p.grp_offs && p.tail_splits > 0)
+                            ? p.full_tiles + (num_tiles - p.full_tiles) * p.tail_splits
+                            : num_tiles * (p.grp_offs ? p.grp_count : splits);
   // fused all-gather: the last `copiers` pairs copy; the tile order is rotated so that this rank's rows come first
   const int copiers = p.ag_world > 1 ? p.ag_copiers : 0;
   const int gpairs = npairs - copiers;
@@ -259,9 +284,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t it = 0;
       bool ok = true;
       for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
-        int mt, nt;
-        if (p.syrk) tri_coords(u % num_tiles, mt, nt);
-        else tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
+        int mt, nt, tile, sp, nsp;
+        unit_decode(p, u, num_tiles, splits, tile, sp, nsp);
+        if (p.syrk) tri_coords(tile, mt, nt);
+        else tile_coords(tile, tm, tn, p.group_m, mt, nt);
         mt = (mt + mt_rot) % tm;
         if (copiers > 0 && mt / (tm / p.ag_world) != p.ag_rank) {
           // rows of another rank: every copying CTA has to have delivered its share of this tile
@@ -273,7 +299,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           asm volatile("fence.proxy.async;" ::: "memory");
         }
         int kb0, kb1;
-        unit_krange(p, u / num_tiles, kblocks, splits, kb0, kb1);
+        unit_krange(p, sp, kblocks, nsp, kb0, kb1);
         const int m0 = mt * 2 * BM + static_cast<int>(cta) * BM;
         // gated forward: the even CTA stages 128 gate rows of the fused weight, the odd CTA the matching up rows
         const int n0 = p.glu_mode == 1 ? nt * BNH + static_cast<int>(cta) * p.glu_F : nt * BN + static_cast<int>(cta) * BNH;
@@ -310,8 +336,9 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t it = 0, tcount = 0;
       bool ok = true;
       for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
-        int kb0, kb1;
-        unit_krange(p, u / num_tiles, kblocks, splits, kb0, kb1);
+        int kb0, kb1, tile, sp, nsp;
+        unit_decode(p, u, num_tiles, splits, tile, sp, nsp);
+        unit_krange(p, sp, kblocks, nsp, kb0, kb1);
         if (kb0 == kb1) continue;  // a group without rows: no accumulator is produced (the epilogue skips it too)
         const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
         ++tcount;
@@ -353,16 +380,19 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     bool ok = true;
     long long c_off = 0;  // per-unit output base for grouped weight gradients
     for (int u = pair - copiers; u < num_units && ok; u += gpairs) {
-      int mt, nt;
-      if (p.syrk) tri_coords(u % num_tiles, mt, nt);
-      else tile_coords(u % num_tiles, tm, tn, p.group_m, mt, nt);
+      int mt, nt, tile, sp, nsp;
+      unit_decode(p, u, num_tiles, splits, tile, sp, nsp);
+      if (p.syrk) tri_coords(tile, mt, nt);
+      else tile_coords(tile, tm, tn, p.group_m, mt, nt);
       mt = (mt + mt_rot) % tm;
       if (p.grp_offs) {
         int kb0, kb1;
-        unit_krange(p, u / num_tiles, kblocks, splits, kb0, kb1);
+        unit_krange(p, sp, kblocks, nsp, kb0, kb1);
         if (kb0 == kb1) continue;
-        c_off = static_cast<long long>(u / num_tiles) * p.grp_c_elems;
+        c_off = static_cast<long long>(sp) * p.grp_c_elems;
       }
+      // hybrid split: whole tiles add to C with a plain read-modify-write, slices of the tail tiles with atomics
+      const int epi_unit = (p.tail_splits > 0 && !p.grp_offs) ? (nsp == 1 ? EPI_F32_ACC : EPI_F32_RED) : -1;
       const uint32_t acc = tcount & 1, acc_ph = (tcount >> 1) & 1;
       ++tcount;
       if (!mbar_wait(&acc_full[acc], acc_ph)) {
@@ -408,7 +438,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           uint32_t r[32];
           tmem_ld_32x32(taddr + c * 32, r);
           tmem_ld_wait();
-          store_acc_chunk(p, r, alpha, row, n0 + c * 32, c_off);
+          store_acc_chunk(p, r, alpha, row, n0 + c * 32, c_off, epi_unit);
           if (p.syrk && nt < mt) store_acc_chunk_mirrored(p, r, alpha, row, n0 + c * 32);
         }
       }
@@ -455,8 +485,10 @@ int launch2(const void* A, const void* B, const GemmParams& p, long long lda, lo
   pp.group_m = choose_group_m(p.M, p.N, p.K);
   MB_SET_MAX_SMEM_ONCE((gemm_bf16_2cta_kernel<A_MN, B_MN>), SMEM_BYTES);
   const int tm_h = (p.M + 2 * BM - 1) / (2 * BM);
-  const int tiles = (p.syrk ? tm_h * (tm_h + 1) / 2 : tm_h * ((p.N + BN - 1) / BN)) *
-                    (p.grp_offs ? p.grp_count : (p.splits > 1 ? p.splits : 1));
+  const int out_tiles = p.syrk ? tm_h * (tm_h + 1) / 2 : tm_h * ((p.N + BN - 1) / BN);
+  const int tiles = (!p.grp_offs && p.tail_splits > 0)
+                        ? p.full_tiles + (out_tiles - p.full_tiles) * p.tail_splits
+                        : out_tiles * (p.grp_offs ? p.grp_count : (p.splits > 1 ? p.splits : 1));
   const int cop = p.ag_world > 1 ? p.ag_copiers : 0;  // pairs that copy instead of computing (fused all-gather)
   const int max_pairs = mbh::sm_count() / 2 - cop;    // every CTA of the grid is resident: waiting on one another is safe
   if (max_pairs < 1) return -3;
@@ -522,7 +554,24 @@ extern "C" int mb_gemm_bf16_2cta(const void* A, const void* B, void* C, const vo
         p.splits = s;
       }
     }
-    if (p.splits > 1) p.epi = EPI_F32_RED;
+    // Hybrid: whole waves un-cut, only the tiles of the last partial wave cut (fewer atomics, fewer pipeline ramps).
+    const int full = (tiles / pairs) * pairs, tail = tiles - full;
+    if (full > 0 && tail > 0) {
+      int st = pairs / tail;
+      if (st > 16) st = 16;
+      if (st * 8 > kblocks) st = kblocks / 8;
+      if (st >= 2) {
+        const long long cost = static_cast<long long>(tiles / pairs) * (kblocks + overhead) +
+                               static_cast<long long>((tail * st + pairs - 1) / pairs) * ((kblocks + st - 1) / st + overhead);
+        static const bool allow = !(getenv("MB_GEMM_HYBRID_SPLIT") && atoi(getenv("MB_GEMM_HYBRID_SPLIT")) == 0);
+        if (allow && cost * 100 < best * 99) {
+          p.splits = 1;
+          p.full_tiles = full;
+          p.tail_splits = st;
+        }
+      }
+    }
+    if (p.splits > 1 || p.tail_splits > 0) p.epi = EPI_F32_RED;
   }
   if (!a_mn && !b_mn) return launch2<false, false>(A, B, p, lda, ldb, stream);
   if (!a_mn && b_mn) return launch2<false, true>(A, B, p, lda, ldb, stream);

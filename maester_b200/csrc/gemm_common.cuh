@@ -24,6 +24,11 @@ struct GemmParams {
   const float* alpha_dev;  // optional device scalar multiplied into alpha
   int* status;
   int splits;              // >1: the contraction is cut into this many ranges, each a separate work unit
+  // Hybrid form of the same (CTA-pair kernel, accumulating fp32 output, tail_splits > 0): the first full_tiles tiles
+  // (whole waves of the grid) are single work units with a plain read-modify-write epilogue; only the tiles of the
+  // last, partial wave are cut into tail_splits ranges each and merged with reduction atomics.
+  int full_tiles = 0;
+  int tail_splits = 0;
   // Row routing of bf16 outputs (GEMM fused with a reduce-scatter over peer memory): output row r belongs to
   // rank r / route_rows and is stored into that rank's buffer route_base[owner], in the slot of THIS
   // rank: row  route_slot * route_rows + r % route_rows.  route_rows == 0 turns routing off.
@@ -283,22 +288,23 @@ __device__ __forceinline__ void store_acc_chunk_mirrored(const GemmParams& p, co
 // Store 32 consecutive accumulator columns [col0, col0+32) of output row `row`.
 // `c_off` (elements) shifts the base of fp32 outputs (grouped weight gradients on the CTA-pair kernel).
 __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint32_t (&r)[32], float alpha, int row,
-                                                int col0, long long c_off = 0) {
+                                                int col0, long long c_off = 0, int epi_unit = -1) {
   using namespace mb;
   if (row >= p.M || col0 >= p.N) return;
+  const int epi = epi_unit >= 0 ? epi_unit : p.epi;   // (the hybrid split chooses the epilogue per work unit)
   MB_CHECK_OR(p.status, row >= 0 && col0 >= 0 && static_cast<long long>(min(col0 + 32, p.N)) <= p.ldc, return);
   const bool full_chunk = (col0 + 32 <= p.N);
   float v[32];
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-  if (p.epi == EPI_BF16 || p.epi == EPI_BF16_ADD) {
+  if (epi == EPI_BF16 || epi == EPI_BF16_ADD) {
     __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
     if (p.route_rows > 0) {
       const int owner = row / p.route_rows;
       const long long slot_row = static_cast<long long>(p.route_slot) * p.route_rows + (row - owner * p.route_rows);
       crow = reinterpret_cast<__nv_bfloat16*>(p.route_base[owner]) + slot_row * p.ldc + col0;
     }
-    if (p.epi == EPI_BF16_ADD) {
+    if (epi == EPI_BF16_ADD) {
       const __nv_bfloat16* arow =
           reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ldaux + col0;
       if (full_chunk && (p.ldaux & 7) == 0) {
@@ -332,7 +338,7 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint3
     }
   } else {
     float* crow = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + col0;
-    if (p.epi == EPI_F32_RED) {
+    if (epi == EPI_F32_RED) {
       if (full_chunk && (p.ldc & 3) == 0) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -348,14 +354,14 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, const uint3
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float4 o = make_float4(v[j * 4], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
-        if (p.epi == EPI_F32_ACC) {
+        if (epi == EPI_F32_ACC) {
           float4 old = reinterpret_cast<float4*>(crow)[j];
           o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
         }
         reinterpret_cast<float4*>(crow)[j] = o;
       }
     } else {
-      for (int i = 0; i < 32 && col0 + i < p.N; ++i) crow[i] = (p.epi == EPI_F32_ACC ? crow[i] : 0.f) + v[i];
+      for (int i = 0; i < 32 && col0 + i < p.N; ++i) crow[i] = (epi == EPI_F32_ACC ? crow[i] : 0.f) + v[i];
     }
   }
 }

@@ -579,6 +579,26 @@ def test_a_broken_gradient_promise_is_reported_not_ignored():
     C.check_status()   # the status word was cleared: later work is unaffected
 
 
+@pytest.mark.parametrize("Mo,No,K", [(4096, 2560, 4096), (2560, 2048, 8192), (5120, 2560, 1024), (1024, 512, 4096),
+                                      (4104, 2568, 2048), (4104, 2312, 4096)])
+def test_accumulating_gemm_splits_only_the_tail_wave(Mo, No, K):
+    """C += A^T B (the weight-gradient form, fp32 accumulate) over shapes whose tiles fill whole waves plus a tail
+    (whole tiles read-modify-write, tail tiles cut and merged with atomics), exactly whole waves, fewer tiles than
+    CTA pairs (every tile cut), and ragged edges; repeated calls keep accumulating."""
+    from maester_b200.ops import cuda as C
+    torch.manual_seed(Mo + No)
+    dy = (torch.randn(K, Mo, device="cuda") * 0.1).to(torch.bfloat16)
+    x = (torch.randn(K, No, device="cuda") * 0.1).to(torch.bfloat16)
+    buf = torch.randn(Mo, No, device="cuda")
+    want = buf.clone()
+    for _ in range(2):
+        C.gemm(dy, x, a_mn=True, b_mn=True, out=buf, epi=C.EPI_F32_ACC)
+        want += dy.float().T @ x.float()
+    assert _rel(buf, want) < 2e-3
+    assert (buf - want).abs().max().item() < 2e-2 * want.abs().max().item()
+    C.check_status()
+
+
 def test_attention_block_with_recomputed_qk_matches_the_kept_form():
     """The per-op recomputation plan (rotated q / k rebuilt in backward) changes no number."""
     from maester_b200 import ops
