@@ -459,7 +459,7 @@ def attention_block(qkv: torch.Tensor, q_norm_w, k_norm_w, pos: torch.Tensor | N
 
 
 # --------------------------------------------------------------------------- linear + cross-entropy
-CE_CHUNK_ROWS = 4096
+CE_CHUNK_ROWS = int(os.environ.get("MB_CE_CHUNK_ROWS", "4096"))   # rows of logits held at a time
 CE_STORE_LIMIT_BYTES = 12 << 30
 _BACKWARD_SCALE: float | None = None
 
