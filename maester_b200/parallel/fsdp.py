@@ -36,7 +36,16 @@ soon as the backward pass has left the block.  Only the root unit (embedding, fi
 the whole step.  Per GPU this needs ``2 bytes x (root + STAGES blocks)`` and ``4 bytes x (root + STAGES blocks)``
 instead of ``6 bytes x all parameters``.  Gradient accumulation reduces after every micro-batch in this mode (the
 staging buffers are reused), and ``cpu_offload`` keeps the fp32 master weights, gradient shards and optimizer state
-in pinned host memory with the optimizer step running there.
+in pinned host memory with the optimizer step running there.  Where the peer-memory plane is usable the ranks' rows
+live in a symmetric buffer and a block is gathered by ONE launch of the library's table-driven copy kernel
+(``csrc/cp_ring.cu::mb_peer_gather``: every (parameter, owner) piece goes from the owner's rows straight to its place
+in the staging buffer over NVLink), ordered by one cross-rank barrier per step; otherwise by an all-gather of the
+process group plus per-parameter copies.
+
+Gradient clearing.  With one rank the AdamW kernel clears the accumulation buffer as it reads it, so ``zero_grad``
+has nothing left to do; with several ranks the buffer is cleared on a side stream while the forward pass (which never
+touches it) runs, and the last block's forward pre-hook waits for that before the loss layer or the backward pass can
+write a gradient.
 """
 from __future__ import annotations
 
