@@ -9,7 +9,10 @@ normalisation, on the wide orientation of the matrix (:22-49); update
 
 Distribution: parameters are dim-0 shards of the flat-buffer sharding runtime.  Matrix ``i`` is owned
 by rank ``i % world``: the shards of ``u`` are gathered there, orthogonalised once and scattered
-back, with up to ``prefetch_factor`` matrices in flight (reference :210-264).  ``MuonDDP`` is the
+back, with up to ``prefetch_factor`` matrices in flight (reference :210-264).  On CUDA with a usable peer-memory
+plane the exchange does not go through the process group at all: every rank stages its row chunks of all matrices in
+one symmetric buffer, the owners pull them with the library's copy kernel, and the results are pulled back the same
+way, two cross-rank barriers per step (``_step_over_peer_memory``).  ``MuonDDP`` is the
 replicated-parameter variant: every rank holds full matrices, work is split round-robin and the
 results are exchanged with one all-gather per bucket (reference :297-460).
 

@@ -10,8 +10,12 @@ is the mirrored collective, and ``apply_tp`` re-shapes the parameters of a model
 the meta device.
 
 Embedding and norm weights are replicated across the TP group and see only this rank's sequence
-slice, so their gradients are summed over the group after backward (``tp_replicated`` flag, handled
-by the sharding runtime).
+slice (the embedding looks up only this rank's tokens), so their gradients are partial sums that are
+summed over the group after backward (``tp_replicated`` flag, handled by the sharding runtime).  A tied,
+replicated head scores this rank's token slice against the whole vocabulary; an untied head is
+vocabulary-parallel and its dH is a partial sum that the backward of the sequence gather reduces.  On
+CUDA the loss-parallel cross-entropy runs on the native kernels: the ranks read each other's per-row
+(max, sum-exp, target) records through symmetric memory instead of all-reducing them.
 """
 from __future__ import annotations
 
