@@ -367,9 +367,7 @@ class ShardedModel:
         world = self.domains[0].world
         self._gather_tables = {}
         for i, u in enumerate(blocks):
-            rows = [(sl.full_off - u.full_lo + r * sl.padded_numel, sl.shard_off, sl.padded_numel, r)
-                    for sl in u.slots for r in range(world)]
-            self._gather_tables[i] = torch.tensor(rows, dtype=torch.int64, device=self.device)
+            self._gather_tables[i] = torch.tensor(gather_table(u, world), dtype=torch.int64, device=self.device)
         self.peer_gather = True
         self.symm_lp.barrier()   # every rank's rows are in place before the first gather
 
@@ -901,6 +899,14 @@ class ShardedModel:
     # ------------------------------------------------------------------ state for checkpoints
     def master_state_dict(self) -> dict[str, torch.Tensor]:
         return {fqn: p.data for fqn, p in self.named_master_parameters()}
+
+
+def gather_table(u: "Unit", world: int) -> list[tuple[int, int, int, int]]:
+    """Copy plan of one block's parameter gather: ``(offset in the block's staging buffer, offset in the owner's row
+    buffer, length, owner rank)`` per parameter and rank, in elements.  The staging buffer holds each parameter as
+    ``world`` consecutive pieces of ``padded_numel`` elements (rank-major), which is the parameter's full dim-0 layout."""
+    return [(sl.full_off - u.full_lo + r * sl.padded_numel, sl.shard_off, sl.padded_numel, r)
+            for sl in u.slots for r in range(world)]
 
 
 class _null:

@@ -255,3 +255,38 @@ def test_resharding_mode_matches_single_process(ac, accum, offload):
                   for r in range(2)]
         got = torch.cat(pieces, dim=0)[: max(1, w.shape[0] if w.dim() > 0 else 1)].reshape(w.shape)
         assert _close(got, w), fqn
+
+
+def _gather_tables_rank(rank, world):
+    from maester_b200.parallel.fsdp import gather_table
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_cfg(data_parallel_shard_degree=world, fsdp_reshard_after_forward="always"))
+    sh = tr.sharded
+    out = []
+    for u in sh.units[:-1]:
+        table = gather_table(u, world)
+        size = u.full_hi - u.full_lo
+        covered = sorted((d, d + n) for d, s, n, r in table)
+        # the pieces tile the parameters' ranges of the staging buffer without overlap ...
+        assert all(a[1] <= b[0] for a, b in zip(covered, covered[1:])) and covered[-1][1] <= size
+        assert sum(n for _, _, n, _ in table) == sum(sl.padded_numel * world for sl in u.slots)
+        # ... every source range lies inside the owner's rows of this unit, and each (parameter, rank) appears once
+        assert all(u.shard_lo <= s and s + n <= u.shard_hi and 0 <= r < world for _, s, n, r in table)
+        assert len({(s, r) for _, s, _, r in table}) == len(table)
+        # what the table describes is what the collective path produces: compare against the staged block
+        sh._ensure_block(sh.units.index(u))
+        buf = sh.stage[sh.units.index(u) % sh.STAGES]
+        rows = [torch.empty_like(sh.shard_lp) for _ in range(world)]
+        import torch.distributed as dist
+        dist.all_gather(rows, sh.shard_lp)
+        for d, s, n, r in table:
+            assert torch.equal(buf[d:d + n], rows[r][s:s + n])
+        out.append(len(table))
+    return out
+
+
+def test_block_gather_tables_describe_the_all_gathered_blocks():
+    """The copy plan that the peer-memory gather of the resharding mode executes on a GPU, checked on CPU against the
+    block that the process-group all-gather stages: same bytes at the same places."""
+    res = run_ranks(2, _gather_tables_rank)
+    assert res[0] == res[1] and all(n > 0 for n in res[0])
