@@ -218,14 +218,7 @@ class Muon(Optimizer):
         dev = work[0][2].device
         chunks = [self._chunk_rows(p, world) for p, _, _ in work]
         cols = [u.shape[1] for _, _, u in work]
-        sizes = [c * n for c, n in zip(chunks, cols)]                    # elements of one rank's chunk of matrix i
-        in_off = [0]
-        for sz in sizes:
-            in_off.append(in_off[-1] + sz)
-        out_off, fill = [], [0] * world                                   # results live in their owner's buffer
-        for i, sz in enumerate(sizes):
-            out_off.append(fill[i % world])
-            fill[i % world] += sz * world
+        sizes, in_off, out_off, fill = peer_exchange_layout(chunks, cols, world)
         key = (id(pg), in_off[-1], max(fill))
         if getattr(self, "_peer_key", None) != key:                       # collective allocation, first step only
             self._peer_in = SymmBuffer(max(in_off[-1], 8), torch.bfloat16, dev, pg)
@@ -258,6 +251,24 @@ class Muon(Optimizer):
         # the next step's staging writes come after its own barrier-free copies; a rank may only overwrite its
         # buffers once every peer has finished pulling from them
         res.barrier()
+
+
+def peer_exchange_layout(chunks: list[int], cols: list[int], world: int):
+    """Buffer layout of the peer-memory exchange, identical on every rank.
+
+    ``sizes[i]``: elements of one rank's row chunk of matrix i.  ``in_off``: where a rank stages its chunk of matrix i
+    in its own staging buffer (``in_off[-1]`` = buffer size).  ``out_off[i]``: where the owner of matrix i
+    (rank ``i % world``) leaves the orthogonalised matrix, ``world`` chunks back to back, in ITS result buffer;
+    ``fill[r]`` = elements rank r's result buffer needs."""
+    sizes = [c * n for c, n in zip(chunks, cols)]
+    in_off = [0]
+    for sz in sizes:
+        in_off.append(in_off[-1] + sz)
+    out_off, fill = [], [0] * world
+    for i, sz in enumerate(sizes):
+        out_off.append(fill[i % world])
+        fill[i % world] += sz * world
+    return sizes, in_off, out_off, fill
 
 
 class MuonDDP(Optimizer):

@@ -153,3 +153,29 @@ def test_moe_load_balance_hook_updates_biases_and_defers_its_statistics():
         assert f"expert_balance/{key}" in out
     tr.train_step(batch)
     assert dict(tr.optimizers._hook_stats)["expert_balance/batches"] == 2
+
+
+def test_muon_peer_exchange_layout_never_overlaps():
+    """Offsets of the symmetric staging / result buffers of Muon's peer-memory exchange: every matrix has its own range
+    in every rank's staging buffer, every owner's result ranges are disjoint, and all offsets keep 16-byte alignment
+    when the chunks do."""
+    from maester_b200.optimizers.muon import peer_exchange_layout
+    import random
+    rng = random.Random(0)
+    for world in (2, 3, 4, 8):
+        for _ in range(20):
+            n = rng.randint(1, 40)
+            chunks = [rng.choice([8, 64, 320, 1280, 2560]) for _ in range(n)]
+            cols = [rng.choice([8, 256, 2560, 10240]) for _ in range(n)]
+            sizes, in_off, out_off, fill = peer_exchange_layout(chunks, cols, world)
+            assert in_off[0] == 0 and all(in_off[i + 1] - in_off[i] == sizes[i] for i in range(n))
+            for owner in range(world):
+                spans = sorted((out_off[i], out_off[i] + sizes[i] * world) for i in range(n) if i % world == owner)
+                assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))
+                assert (spans[-1][1] if spans else 0) == fill[owner]
+            assert all(o % 8 == 0 for o in in_off + out_off)
+            # the piece rank r pulls back from the owner lies inside the owner's range of that matrix
+            for i in range(n):
+                for r in range(world):
+                    lo = out_off[i] + r * sizes[i]
+                    assert out_off[i] <= lo and lo + sizes[i] <= out_off[i] + sizes[i] * world
