@@ -30,6 +30,7 @@ import bench as B
 PRESETS = {
     "gemma3-4b": dict(model_name="gemma3", flavor="4B", seq_len=8192, train_batch_size=2),
     "gemma3-1b": dict(model_name="gemma3", flavor="1B", seq_len=8192, train_batch_size=4),
+    "gemma3-4b-tp2": dict(model_name="gemma3", flavor="4B", seq_len=8192, train_batch_size=2, tensor_parallel_degree=2),
     "llama3-8b-tp2": dict(model_name="llama3", flavor="8B", seq_len=8192, train_batch_size=2, tensor_parallel_degree=2),
     "llama3-8b-cp2": dict(model_name="llama3", flavor="8B", seq_len=32768, train_batch_size=1, context_parallel_degree=2),
     "deepseek-moe-ep8": dict(model_name="deepseek", flavor="bench16L", seq_len=4096, train_batch_size=4,
@@ -44,7 +45,7 @@ PRESETS = {
     "deepseek-moe-1gpu": dict(model_name="deepseek", flavor="bench6L", seq_len=4096, train_batch_size=4),
 }
 # smallest world size whose GPUs hold the configuration (sharded fp32 state + activations within 180 GB each)
-MIN_GPUS = {"llama3-8b-cp2": 4, "deepseek-moe-ep8": 8, "deepseek-moe-ep4": 4, "gemma3-27b": 4}
+MIN_GPUS = {"gemma3-4b-tp2": 2, "llama3-8b-cp2": 4, "deepseek-moe-ep8": 8, "deepseek-moe-ep4": 4, "gemma3-27b": 4}
 
 
 def main() -> None:
@@ -72,8 +73,8 @@ def main() -> None:
     need = MIN_GPUS.get(a.preset, 1)
     if int(os.environ.get("WORLD_SIZE", a.gpus)) < need:  # refuse before anything is allocated
         if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"preset": a.preset, "unavailable": f"needs at least {need} GPUs: the fp32 state of the "
-                              "whole model does not fit the memory of fewer"}))
+            print(json.dumps({"preset": a.preset, "unavailable": f"needs at least {need} GPUs (the preset's parallel degrees, "
+                              "or the fp32 state of the whole model, which does not fit the memory of fewer)"}))
         return
     if a.impl == "reference":
         try:

@@ -56,6 +56,8 @@ def _as_dtensor(local: torch.Tensor, slot, sharded) -> torch.Tensor:
 
     if sharded is None:
         return local
+    if getattr(slot, "tp_segments", None) is not None:
+        return _as_row_pieces(local, slot, sharded)
     meshes = getattr(sharded, "ckpt_meshes", None) or {}
     tp = slot.tp_dim >= 0
     if slot.dom == 1:
@@ -84,6 +86,54 @@ def _as_dtensor(local: torch.Tensor, slot, sharded) -> torch.Tensor:
     shape = slot.global_shape
     stride = torch.empty(shape, device="meta").stride()
     return DTensor.from_local(local, mesh, placements, run_check=False, shape=shape, stride=stride)
+
+
+def row_pieces(slot, own_lo: int, own_hi: int) -> list[tuple[int, int, int]]:
+    """For a parameter whose tensor-parallel slice consists of several row ranges of the whole tensor
+    (``slot.tp_segments``): the pieces of this rank's rows ``[own_lo, own_hi)`` of the LOCAL slice as
+    ``(first local row relative to own_lo, first global row, rows)``."""
+    out, start = [], 0
+    for g0, n in slot.tp_segments:
+        lo, hi = max(own_lo, start), min(own_hi, start + n)
+        if hi > lo:
+            out.append((lo - own_lo, g0 + (lo - start), hi - lo))
+        start += n
+    return out
+
+
+def _as_row_pieces(local: torch.Tensor, slot, sharded) -> torch.Tensor:
+    """This rank's rows of a head-group-split projection as a checkpointable object with SEVERAL chunks, each at its
+    place in the whole tensor (the reference's row order), so that the checkpoint holds the tensor exactly as an
+    unsharded model has it and any other layout can load it.  DTensor cannot describe this (one contiguous range per
+    rank), so the tensor carries DCP's checkpointable hooks itself: one write / read item per piece."""
+    from torch.distributed.checkpoint.metadata import ChunkStorageMetadata, MetadataIndex, TensorProperties
+    from torch.distributed.checkpoint.planner import TensorWriteData, WriteItem, WriteItemType
+
+    lo, hi = sharded._own_rows(slot)
+    cols = tuple(slot.shape[1:])
+    rows2d = local.reshape(-1, *cols)[: hi - lo] if hi > lo else local.reshape(-1, *cols)[:0]
+    pieces = row_pieces(slot, lo, hi)
+    size = slot.global_shape
+    zeros = (0,) * len(cols)
+    t = rows2d.view(rows2d.shape)          # a fresh tensor object over the same memory to carry the hooks
+    chunks = [ChunkStorageMetadata(offsets=torch.Size((g0, *zeros)), sizes=torch.Size((n, *cols))) for _, g0, n in pieces]
+    views = {c.offsets: rows2d[l0: l0 + n] for c, (l0, _, n) in zip(chunks, pieces)}
+
+    def create_write_items(fqn, obj):
+        return [WriteItem(index=MetadataIndex(fqn, c.offsets), type=WriteItemType.SHARD,
+                          tensor_data=TensorWriteData(chunk=c, properties=TensorProperties.create_from_tensor(rows2d),
+                                                      size=size)) for c in chunks]
+
+    def get_tensor_shard(index):
+        return views[torch.Size(index.offset)]
+
+    t.__create_write_items__ = create_write_items
+    t.__create_chunk_list__ = lambda: list(chunks)
+    t.__get_tensor_shard__ = get_tensor_shard
+    # the load planner compares ``obj.size()`` with the stored (whole) size before it asks for the chunk list
+    t.size = lambda *dim: size if not dim else size[dim[0]]
+    t._mb_rewrap = lambda new_local: _as_row_pieces(new_local, slot, sharded)   # after a dtype conversion
+    return t
 
 
 class ModelWrapper(Stateful):
@@ -189,7 +239,8 @@ class CheckpointManager:
         if force and self.model_weights_only:
             sd = self.states["model"].state_dict()
             if self.export_dtype != torch.float32:
-                sd = {k: v.to(self.export_dtype) for k, v in sd.items()}
+                sd = {k: (v._mb_rewrap(v.to(self.export_dtype)) if hasattr(v, "_mb_rewrap") else v.to(self.export_dtype))
+                      for k, v in sd.items()}
             states = {"model": sd}
             logger.info(f"Saving a model weights only checkpoint in {self.export_dtype} at step {curr_step}")
         else:

@@ -26,4 +26,5 @@ gemma3_configs = {
     "27B": _g3(262_208, 5376, 62, 32, 16, 128, 21504, 1024, True, qscalar=168),
     # small shapes for tests and CPU runs
     "debug": _g3(32_000, 256, 2, 4, 1, 64, 1024, 128, False),
+    "debug_gqa": _g3(32_000, 256, 2, 4, 2, 64, 1024, 128, False),  # two key / value heads: splits over 2 TP ranks
 }

@@ -161,8 +161,23 @@ class Gemma2DecoderLayer(nn.Module):
         self.post_feedforward_layernorm = RMSNorm(config.dim, eps=eps) if config.use_post_ffw_norm else None
         self.selective_recompute = config.selective_recompute
 
+    tp = None  # set by apply_tp: the residual stream is then sharded along the flattened token dimension
+
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids):
         rc = self.selective_recompute
+        if self.tp is not None:
+            # sequence parallel: the four norms and the residual stream work on this rank's token rows; the
+            # attention and MLP blocks see all tokens (all-gather in front) with this rank's heads / hidden slice and
+            # return partial sums (reduce-scatter behind)
+            from maester_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
+            a = self.self_attn(gather_seq(self.input_layernorm(x), self.tp), position_ids, inv_freq, rope_cs,
+                               document_ids)
+            x = self.post_attention_layernorm(reduce_scatter_seq(a, self.tp), residual=x)
+            h = self.pre_feedforward_layernorm(x) if self.pre_feedforward_layernorm is not None else x
+            m = reduce_scatter_seq(self.mlp(gather_seq(h, self.tp), recompute_act=rc), self.tp)
+            if self.post_feedforward_layernorm is not None:
+                return self.post_feedforward_layernorm(m, residual=x)
+            return x + m
         h, skip = self.input_layernorm.fork(x)
         h = self.self_attn(h, position_ids, inv_freq, rope_cs, document_ids)
         x = self.post_attention_layernorm(h, residual=skip)  # x + norm(attn)
@@ -239,7 +254,13 @@ class GemmaTextModel(nn.Module):
     # -- forward ----------------------------------------------------------------------------
     def forward(self, tokens, labels=None, position_ids=None, document_ids=None):
         B, S = tokens.shape
-        x = self.tok_embeddings(tokens, scale=self.config.dim ** 0.5)
+        tp = getattr(self, "tp", None)
+        if tp is not None:   # this rank embeds its slice of the flattened tokens only (partial embedding gradient)
+            from maester_b200.parallel.tensor_parallel import gather_seq, local_tokens, sum_over_group
+            tp.batch = B
+            x = self.tok_embeddings(local_tokens(tokens, tp), scale=self.config.dim ** 0.5)
+        else:
+            x = self.tok_embeddings(tokens, scale=self.config.dim ** 0.5)
         if position_ids is None:
             position_ids = torch.arange(S, device=tokens.device, dtype=torch.int32)[None].expand(B, S)
         tables = {
@@ -250,6 +271,13 @@ class GemmaTextModel(nn.Module):
             x = layer(x, position_ids, inv, cs, document_ids)
         h = self.model.norm(x)
         w = self.tok_embeddings.weight
+        if tp is not None:
+            # tied, replicated head: every rank scores its own token slice against the whole vocabulary; the ranks'
+            # partial losses (each divided by the global count of valid labels) add up to the mean
+            if labels is not None:
+                nvalid = (labels != -100).sum()
+                return sum_over_group(ops.linear_cross_entropy(h, w, local_tokens(labels, tp), nvalid=nvalid), tp)
+            return gather_seq(ops.linear(h, w), tp, same_grad=True)
         if labels is not None:
             return ops.linear_cross_entropy(h, w, labels)
         return ops.linear(h, w)

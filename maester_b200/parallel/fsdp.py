@@ -77,6 +77,10 @@ class ParamSlot:
     row_base: int = 0            # first global row of this rank's local slice (expert-parallel offset)
     tp_dim: int = -1             # tensor-parallel slice dimension of this parameter (-1: not tensor-parallel)
     tp_size: int = 1
+    # A tensor-parallel slice on dim 0 that is NOT one contiguous row range of the whole tensor (the fused q|k|v
+    # projection split by head groups): the local rows are these ranges of the whole tensor, in order:
+    # ((first global row, rows), ...).  None: the slice is the contiguous range given by the rank.
+    tp_segments: tuple | None = None
 
     @property
     def padded_numel(self) -> int:
@@ -271,8 +275,10 @@ class ShardedModel:
         ep, er = (self.ep_size, self.ep_rank) if dom == 1 else (1, 0)
         tp_dim = int(getattr(p, "tp_dim", -1))
         tp_size = dist.get_world_size(self.tp_group) if (tp_dim >= 0 and self.tp_group is not None) else 1
+        seg = getattr(p, "tp_segments", None)
         return ParamSlot(fqn, p, shape, rows, row_numel, chunk, dom=dom, global_rows=rows * ep, row_base=rows * er,
-                         tp_dim=tp_dim if tp_size > 1 else -1, tp_size=tp_size)
+                         tp_dim=tp_dim if tp_size > 1 else -1, tp_size=tp_size,
+                         tp_segments=tuple(seg) if (seg is not None and tp_size > 1) else None)
 
     def _rebind_parameters(self) -> None:
         """Point every model parameter at its view of ``full`` and create the fp32 master shards."""

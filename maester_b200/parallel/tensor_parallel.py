@@ -16,6 +16,10 @@ replicated head scores this rank's token slice against the whole vocabulary; an 
 vocabulary-parallel and its dH is a partial sum that the backward of the sequence gather reduces.  On
 CUDA the loss-parallel cross-entropy runs on the native kernels: the ranks read each other's per-row
 (max, sum-exp, target) records through symmetric memory instead of all-reducing them.
+
+Gemma (maester/parallelisms/parallelize_gemma.py:77-178) follows the same scheme with its own block layout
+(``_apply_tp_gemma``): the fused ``qkv_proj`` is split by head groups (``qkv_segments``), the four block norms and the
+QK-norms are replicated, and the tied head is the replicated form above.
 """
 from __future__ import annotations
 
@@ -356,14 +360,19 @@ def _reshape_linear(lin: nn.Module, out_features: int, in_features: int, tp_dim:
 
 
 def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
-    """Shard a Llama-family ``Transformer`` over the ``tp`` mesh dimension (model still on meta)."""
+    """Shard a Llama-family ``Transformer`` or a Gemma text model over the ``tp`` mesh dimension (model still on
+    meta)."""
     from maester_b200.models.llama.model import Transformer
 
-    if not isinstance(model, Transformer):
-        raise NotImplementedError(
-            f"tensor parallelism is implemented for the Llama family; got {type(model).__name__}")
     group = parallel_dims.mesh_group("tp")
     tp = TPInfo(group, dist.get_world_size(group), dist.get_rank(group), parallel_dims.loss_parallel_enabled)
+    from maester_b200.models.gemma.model import GemmaTextModel
+    inner = getattr(model, "language_model", model)
+    if isinstance(inner, GemmaTextModel):
+        return _apply_tp_gemma(inner, tp)
+    if not isinstance(model, Transformer):
+        raise NotImplementedError(
+            f"tensor parallelism is implemented for the Llama and Gemma families; got {type(model).__name__}")
     a = model.model_args
     n_kv = a.n_kv_heads or a.n_heads
     assert a.n_heads % tp.size == 0 and n_kv % tp.size == 0, "heads must divide by the TP degree"
@@ -403,17 +412,68 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
                 f"loss parallel={tp.loss_parallel}, fused GEMM+reduce-scatter={fused is not None})")
 
 
+def qkv_segments(n_heads: int, n_kv_heads: int, head_dim: int, tp_size: int, tp_rank: int):
+    """Row ranges ``((first row, rows), ...)`` of the fused ``[q heads | k heads | v heads]`` projection that belong
+    to one tensor-parallel rank: its query heads, its key heads and its value heads (a head-group-aware split: a rank
+    holds the query heads that attend to its own key / value heads)."""
+    q, kv = n_heads // tp_size * head_dim, n_kv_heads // tp_size * head_dim
+    q_all, kv_all = n_heads * head_dim, n_kv_heads * head_dim
+    return ((tp_rank * q, q), (q_all + tp_rank * kv, kv), (q_all + kv_all + tp_rank * kv, kv))
+
+
+def _apply_tp_gemma(model, tp: TPInfo) -> None:
+    """Shard a Gemma text model over the ``tp`` group (model still on meta).  The reference's plan for this family
+    (maester/parallelisms/parallelize_gemma.py:77-178) column-shards the fused ``qkv_proj`` as one matrix, which mixes
+    query, key and value heads across ranks; here every rank takes its query heads and the key / value heads they
+    attend to (``qkv_segments``), ``o_proj`` and ``down_proj`` are row-parallel, ``gate_proj`` / ``up_proj``
+    column-parallel, the four block norms, the QK-norms, the final norm and the tied embedding / head are replicated
+    and work on this rank's token rows (sequence parallel).  Collectives are the process group's (no fused kernels for
+    this family)."""
+    cfg = model.config
+    H, KV, hd = cfg.n_heads, cfg.num_key_value_heads, cfg.head_dim
+    assert H % tp.size == 0 and KV % tp.size == 0, "query and key / value heads must divide by the TP degree"
+    assert cfg.intermediate_size % tp.size == 0
+    for layer in model.model.layers:
+        att, mlp = layer.self_attn, layer.mlp
+        att.num_heads, att.num_kv_heads = H // tp.size, KV // tp.size
+        att.q_size, att.kv_size = att.num_heads * hd, att.num_kv_heads * hd
+        _reshape_linear(att.qkv_proj, att.q_size + 2 * att.kv_size, cfg.dim, 0)
+        att.qkv_proj.weight.tp_segments = qkv_segments(H, KV, hd, tp.size, tp.rank)
+        _reshape_linear(att.o_proj, cfg.dim, att.q_size, 1)
+        _reshape_linear(mlp.gate_proj, cfg.intermediate_size // tp.size, cfg.dim, 0)
+        _reshape_linear(mlp.up_proj, cfg.intermediate_size // tp.size, cfg.dim, 0)
+        _reshape_linear(mlp.down_proj, cfg.dim, cfg.intermediate_size // tp.size, 1)
+        layer.tp = tp
+        for norm in (layer.input_layernorm, layer.post_attention_layernorm, layer.pre_feedforward_layernorm,
+                     layer.post_feedforward_layernorm, att.query_norm, att.key_norm):
+            if norm is not None:
+                for p in norm.parameters():
+                    p.tp_replicated = True
+    model.tok_embeddings.weight.tp_replicated = True
+    for p in model.model.norm.parameters():
+        p.tp_replicated = True
+    model.tp = tp
+    logger.info(f"Applied tensor parallelism to the Gemma model (degree {tp.size}, sequence parallel, head-group split "
+                f"of qkv_proj, replicated tied head)")
+
+
 # ------------------------------------------------------------------------------ checkpoints / tests
-_COLWISE = ("attention.wq.", "attention.wk.", "attention.wv.", "feed_forward.w1.", "feed_forward.w3.", "output.")
-_ROWWISE = ("attention.wo.", "feed_forward.w2.")
+_COLWISE = ("attention.wq.", "attention.wk.", "attention.wv.", "feed_forward.w1.", "feed_forward.w3.", "output.",
+            "mlp.gate_proj.", "mlp.up_proj.")
+_ROWWISE = ("attention.wo.", "feed_forward.w2.", "self_attn.o_proj.", "mlp.down_proj.")
 
 
-def tp_slice_state_dict(full_state: dict[str, torch.Tensor], tp_size: int, tp_rank: int) -> dict[str, torch.Tensor]:
-    """This rank's tensor-parallel slices of an unsharded Llama state dict (column-parallel weights
-    split on dim 0, row-parallel on dim 1, everything else replicated)."""
+def tp_slice_state_dict(full_state: dict[str, torch.Tensor], tp_size: int, tp_rank: int,
+                        heads: tuple[int, int, int] | None = None) -> dict[str, torch.Tensor]:
+    """This rank's tensor-parallel slices of an unsharded state dict (column-parallel weights split on dim 0,
+    row-parallel on dim 1, everything else replicated).  ``heads = (query heads, key / value heads, head size)`` is
+    needed for a fused ``qkv_proj`` (Gemma), which is split by head groups."""
     out = {}
     for k, v in full_state.items():
-        if any(t in k for t in _COLWISE) and v.dim() == 2:
+        if "qkv_proj." in k and v.dim() == 2:
+            assert heads is not None, "qkv_proj needs the head counts"
+            out[k] = torch.cat([v[a:a + n] for a, n in qkv_segments(*heads, tp_size, tp_rank)]).contiguous()
+        elif any(t in k for t in _COLWISE) and v.dim() == 2:
             out[k] = v.chunk(tp_size, dim=0)[tp_rank].contiguous()
         elif any(t in k for t in _ROWWISE) and v.dim() == 2:
             out[k] = v.chunk(tp_size, dim=1)[tp_rank].contiguous()

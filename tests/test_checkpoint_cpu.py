@@ -215,6 +215,58 @@ def test_tensor_parallel_checkpoint_reassembles_full_weights(tmp_path, world, dp
     assert {"layers.0.attention.wq.weight", "layers.0.attention.wo.weight", "layers.0.feed_forward.w2.weight"} <= set(flat)
 
 
+def _gemma_tp_save(rank, world, tmp, full, batches, dp):
+    """Gemma under TP 2: one step, save, and a second trainer with the same layout loads the checkpoint back."""
+    import torch.distributed as dist
+    from test_parallel_cpu import GEMMA_HEADS
+    cfg = _mk(tmp, model_name="gemma3", flavor="debug_gqa", tensor_parallel_degree=2, data_parallel_shard_degree=dp)
+    tr, state, ck = _trainer_with_ckpt(cfg)
+    g = tr.parallel_dims.mesh_group("tp")
+    _load_full(tr, full, tp=(2, dist.get_rank(g), GEMMA_HEADS))
+    mine = {k: v[tr.dp_rank * 2:(tr.dp_rank + 1) * 2] for k, v in batches[0].items()}
+    tr.train_step(mine)
+    state.step = 2
+    ck.save(2)
+    tr2, state2, ck2 = _trainer_with_ckpt(cfg)
+    assert ck2.load() and state2.step == 2
+    want, got = _params(tr), _params(tr2)
+    for k in want:
+        assert torch.equal(got[k], want[k]), k
+    o1, o2 = tr.optimizers.optimizers[0], tr2.optimizers.optimizers[0]
+    for key in ("m", "v"):
+        assert o1._flat[key].abs().sum() > 0 and torch.equal(o1._flat[key], o2._flat[key]), key
+    # the last checkpoint of a run: weights only, in the export dtype (the row pieces survive the conversion)
+    ck.model_weights_only, ck.export_dtype = True, torch.bfloat16
+    ck.save(4, force=True)
+    return {k: v for k, v in want.items()} if tr.dp_rank == 0 or dp == 1 else None
+
+
+@pytest.mark.parametrize("world,dp", [(2, 1), (4, 2)])
+def test_gemma_tensor_parallel_checkpoint_holds_whole_tensors_in_the_reference_row_order(tmp_path, world, dp):
+    """The fused qkv projection is split by head groups, so a rank's rows are three separate row ranges of the whole
+    [q; k; v] matrix (more when a data-parallel shard boundary cuts one): the checkpoint must hold the whole matrix in
+    that order, readable without knowing the parallel layout."""
+    from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
+    from test_parallel_cpu import GEMMA_HEADS, _gemma_cfg
+    full = _full_weights(_gemma_cfg())
+    res = run_ranks(world, _gemma_tp_save, str(tmp_path), full, _batches(1, 2 * dp, 64, 512), dp)
+    from maester_b200.convert.io import read_dcp_model
+    flat = read_dcp_model(tmp_path / "job" / "checkpoints" / "step-2")
+    assert set(full) <= set(flat)
+    for k in full:
+        assert flat[k].shape == full[k].shape, k
+    export = read_dcp_model(tmp_path / "job" / "checkpoints" / "step-4")
+    for k in full:
+        assert export[k].dtype == torch.bfloat16 and torch.equal(export[k], flat[k].to(torch.bfloat16)), k
+    # the trained slices of each TP rank are the head-group slices of the stored whole tensors
+    for r in range(world):
+        if res[r] is None:
+            continue
+        want = tp_slice_state_dict({k: flat[k] for k in full}, 2, r % 2, GEMMA_HEADS)
+        for k, v in res[r].items():
+            assert torch.equal(v.float(), want[k].float()), (r, k)
+
+
 def _expert_tp_save(rank, world, tmp, full, cfg_kw):
     from test_expert_parallel_cpu import _cfg as ep_cfg, _load
     from train import TrainState

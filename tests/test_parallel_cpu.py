@@ -69,7 +69,7 @@ def _full_weights(cfg):
 
 def _load_full(trainer, full, tp=None):
     from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
-    sd = tp_slice_state_dict(full, tp[0], tp[1]) if tp else full
+    sd = tp_slice_state_dict(full, *tp) if tp else full
     sh = trainer.sharded
     with torch.no_grad():
         for u in sh.units:
@@ -161,6 +161,44 @@ def test_tensor_parallel_with_a_tied_replicated_head_matches_single_process():
         assert losses == pytest.approx(want_losses, abs=1e-4)
         want = tp_slice_state_dict(want_params, 2, r)
         for k in want:
+            assert _close(params[k], want[k], tol=1e-3), k
+
+
+GEMMA_HEADS = (4, 2, 64)  # query heads, key / value heads, head size of the gemma3 "debug_gqa" flavor
+
+
+def _gemma_cfg(**kw):
+    return _cfg(model_name="gemma3", flavor="debug_gqa", **kw)
+
+
+def _tp_rank_gemma(rank, world, full, batches):
+    from maester_b200.trainer import Trainer
+    tr = Trainer(_gemma_cfg(tensor_parallel_degree=2, data_parallel_shard_degree=1))
+    _load_full(tr, full, tp=(2, rank, GEMMA_HEADS))
+    losses = [tr.train_step(b).item() for b in batches]
+    return losses, {sl.fqn: sl.param.data.clone() for u in tr.sharded.units for sl in u.slots}
+
+
+def test_gemma_tensor_parallel_matches_single_process():
+    """Gemma: head-group split of the fused qkv projection, sequence-parallel norms (block norms, QK-norms, final
+    norm: replicated weights with partial gradients), tied replicated head."""
+    from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
+    full = _full_weights(_gemma_cfg())
+    # norm weights start at zero, where several gradient paths vanish: move them off zero
+    g = torch.Generator().manual_seed(7)
+    for k, v in full.items():
+        if "norm" in k:
+            v.copy_(0.2 * torch.randn(v.shape, generator=g))
+    batches = _batches(2, 2, 64, 512)
+    want_losses, want_params = _single(_gemma_cfg(), full, batches)
+    res = run_ranks(2, _tp_rank_gemma, full, batches)
+    for r in range(2):
+        losses, params = res[r]
+        assert losses == pytest.approx(want_losses, abs=1e-4)
+        want = tp_slice_state_dict(want_params, 2, r, GEMMA_HEADS)
+        assert set(want) == set(params)
+        for k in want:
+            assert params[k].shape == want[k].shape, k
             assert _close(params[k], want[k], tol=1e-3), k
 
 
