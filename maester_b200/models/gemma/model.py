@@ -93,9 +93,18 @@ class GemmaMLP(nn.Module):
         self.down_proj = Linear(intermediate_size, hidden_size)
         self._gate_up = FusedWeight([self.gate_proj, self.up_proj])
 
+    tp_fused = None    # set by apply_tp when the fused tensor-parallel kernels are usable
+
     def forward(self, x: torch.Tensor, recompute_act: bool = False) -> torch.Tensor:
+        w_gu = self._gate_up.get()
+        if self.tp_fused is not None:  # x: this rank's token rows; returns this rank's token rows of the summed result
+            from maester_b200.parallel.fused_tp import ag_linear, glu_mlp_tp, linear_rs
+            if (w_gu.shape[0] // 2) % 128 == 0 and w_gu.is_contiguous() and ops.use_native(x, w_gu):
+                return glu_mlp_tp(x, w_gu, self.down_proj.weight, "gelu_tanh", None, self.tp_fused)
+            return linear_rs(ops.glu(ag_linear(x, w_gu, self.tp_fused), "gelu_tanh"), self.down_proj.weight, None,
+                             self.tp_fused)
         # one autograd node: the gated activation lives in the GEMM epilogues (forward and backward)
-        return ops.glu_mlp(x, self._gate_up.get(), self.down_proj.weight, "gelu_tanh")
+        return ops.glu_mlp(x, w_gu, self.down_proj.weight, "gelu_tanh")
 
     def init_weights(self, init_std: float) -> None:
         for lin in (self.gate_proj, self.up_proj, self.down_proj):
@@ -124,8 +133,14 @@ class GemmaAttention(nn.Module):
         self.sliding_window_size = config.sliding_window_size
         self.eps = config.rms_norm_eps
 
+    tp_fused = None    # set by apply_tp when the fused tensor-parallel kernels are usable
+
     def forward(self, x, position_ids, inv_freq, rope_cs, document_ids):
-        qkv = self.qkv_proj(x)
+        if self.tp_fused is not None:  # x is this rank's token shard: the all-gather lives in the projection
+            from maester_b200.parallel.fused_tp import ag_linear, linear_rs
+            qkv = ag_linear(x, self.qkv_proj.weight, self.tp_fused)
+        else:
+            qkv = self.qkv_proj(x)
         window = self.sliding_window_size if (self.attn_type == "local_sliding" and self.sliding_window_size) else None
         from maester_b200.parallel.context_parallel import attention as cp_aware_attention
         out = cp_aware_attention(
@@ -136,6 +151,8 @@ class GemmaAttention(nn.Module):
             self.num_heads, self.num_kv_heads, self.head_dim,
             layout="half", eps=self.eps, unit_offset=True, scale=self.scaling, causal=True, window=window,
         )
+        if self.tp_fused is not None:  # GEMM + reduce-scatter over peer memory: this rank's token rows of the sum
+            return linear_rs(out, self.o_proj.weight, None, self.tp_fused)
         return self.o_proj(out)
 
     def init_weights(self, init_std: float) -> None:
@@ -168,16 +185,20 @@ class Gemma2DecoderLayer(nn.Module):
         if self.tp is not None:
             # sequence parallel: the four norms and the residual stream work on this rank's token rows; the
             # attention and MLP blocks see all tokens (all-gather in front) with this rank's heads / hidden slice and
-            # return partial sums (reduce-scatter behind)
+            # return partial sums (reduce-scatter behind).  With the fused kernels the two collectives live inside
+            # the blocks' first and last GEMM.
             from maester_b200.parallel.tensor_parallel import gather_seq, reduce_scatter_seq
-            a = self.self_attn(gather_seq(self.input_layernorm(x), self.tp), position_ids, inv_freq, rope_cs,
-                               document_ids)
-            x = self.post_attention_layernorm(reduce_scatter_seq(a, self.tp), residual=x)
-            h = self.pre_feedforward_layernorm(x) if self.pre_feedforward_layernorm is not None else x
-            m = reduce_scatter_seq(self.mlp(gather_seq(h, self.tp), recompute_act=rc), self.tp)
+            fused = self.self_attn.tp_fused is not None
+            gather = (lambda t: t) if fused else (lambda t: gather_seq(t, self.tp))
+            scatter = (lambda t: t) if fused else (lambda t: reduce_scatter_seq(t, self.tp))
+            h, skip = self.input_layernorm.fork(x)
+            a = scatter(self.self_attn(gather(h), position_ids, inv_freq, rope_cs, document_ids))
+            x = self.post_attention_layernorm(a, residual=skip)
+            h, skip = self.pre_feedforward_layernorm.fork(x) if self.pre_feedforward_layernorm is not None else (x, x)
+            m = scatter(self.mlp(gather(h), recompute_act=rc))
             if self.post_feedforward_layernorm is not None:
-                return self.post_feedforward_layernorm(m, residual=x)
-            return x + m
+                return self.post_feedforward_layernorm(m, residual=skip)
+            return skip + m
         h, skip = self.input_layernorm.fork(x)
         h = self.self_attn(h, position_ids, inv_freq, rope_cs, document_ids)
         x = self.post_attention_layernorm(h, residual=skip)  # x + norm(attn)

@@ -369,7 +369,7 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
     from maester_b200.models.gemma.model import GemmaTextModel
     inner = getattr(model, "language_model", model)
     if isinstance(inner, GemmaTextModel):
-        return _apply_tp_gemma(inner, tp)
+        return _apply_tp_gemma(inner, tp, cfg)
     if not isinstance(model, Transformer):
         raise NotImplementedError(
             f"tensor parallelism is implemented for the Llama and Gemma families; got {type(model).__name__}")
@@ -421,14 +421,20 @@ def qkv_segments(n_heads: int, n_kv_heads: int, head_dim: int, tp_size: int, tp_
     return ((tp_rank * q, q), (q_all + tp_rank * kv, kv), (q_all + kv_all + tp_rank * kv, kv))
 
 
-def _apply_tp_gemma(model, tp: TPInfo) -> None:
+def _apply_tp_gemma(model, tp: TPInfo, cfg=None) -> None:
     """Shard a Gemma text model over the ``tp`` group (model still on meta).  The reference's plan for this family
     (maester/parallelisms/parallelize_gemma.py:77-178) column-shards the fused ``qkv_proj`` as one matrix, which mixes
     query, key and value heads across ranks; here every rank takes its query heads and the key / value heads they
     attend to (``qkv_segments``), ``o_proj`` and ``down_proj`` are row-parallel, ``gate_proj`` / ``up_proj``
     column-parallel, the four block norms, the QK-norms, the final norm and the tied embedding / head are replicated
-    and work on this rank's token rows (sequence parallel).  Collectives are the process group's (no fused kernels for
-    this family)."""
+    and work on this rank's token rows (sequence parallel).  With ``fused_collectives`` on a CUDA device the
+    all-gathers and reduce-scatters live inside the blocks' GEMM kernels (``fused_tp``), else they are the process
+    group's."""
+    fused = None
+    from maester_b200.parallel.fused_tp import FusedTP, fused_tp_available
+    from maester_b200.utils import device_for_training
+    if getattr(cfg, "fused_collectives", False) and fused_tp_available(tp, device_for_training()):
+        fused = FusedTP(tp)
     cfg = model.config
     H, KV, hd = cfg.n_heads, cfg.num_key_value_heads, cfg.head_dim
     assert H % tp.size == 0 and KV % tp.size == 0, "query and key / value heads must divide by the TP degree"
@@ -444,6 +450,8 @@ def _apply_tp_gemma(model, tp: TPInfo) -> None:
         _reshape_linear(mlp.up_proj, cfg.intermediate_size // tp.size, cfg.dim, 0)
         _reshape_linear(mlp.down_proj, cfg.dim, cfg.intermediate_size // tp.size, 1)
         layer.tp = tp
+        if fused is not None:
+            att.tp_fused = mlp.tp_fused = fused
         for norm in (layer.input_layernorm, layer.post_attention_layernorm, layer.pre_feedforward_layernorm,
                      layer.post_feedforward_layernorm, att.query_norm, att.key_norm):
             if norm is not None:
@@ -454,7 +462,7 @@ def _apply_tp_gemma(model, tp: TPInfo) -> None:
         p.tp_replicated = True
     model.tp = tp
     logger.info(f"Applied tensor parallelism to the Gemma model (degree {tp.size}, sequence parallel, head-group split "
-                f"of qkv_proj, replicated tied head)")
+                f"of qkv_proj, replicated tied head, fused collective GEMMs={fused is not None})")
 
 
 # ------------------------------------------------------------------------------ checkpoints / tests

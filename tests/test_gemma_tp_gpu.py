@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, full, batches, out_dir):
+def _worker(rank, world, port, full, batches, fused, out_dir):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
@@ -19,7 +19,9 @@ def _worker(rank, world, port, full, batches, out_dir):
         from test_parallel_cpu import GEMMA_HEADS, _gemma_cfg, _load_full
         from maester_b200.ops import cuda as C
         from maester_b200.trainer import Trainer
-        tr = Trainer(_gemma_cfg(tensor_parallel_degree=2, data_parallel_shard_degree=1, seq_len=256, ac_mode="selective"))
+        tr = Trainer(_gemma_cfg(tensor_parallel_degree=2, data_parallel_shard_degree=1, seq_len=256, ac_mode="selective",
+                                fused_collectives=fused))
+        assert (tr.model.model.layers[0].self_attn.tp_fused is not None) == fused
         _load_full(tr, full, tp=(2, rank, GEMMA_HEADS))
         before = C.launch_count
         losses = [tr.train_step(b).item() for b in batches]
@@ -32,7 +34,8 @@ def _worker(rank, world, port, full, batches, out_dir):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_gemma_tensor_parallel_follows_the_single_gpu_run(tmp_path):
+@pytest.mark.parametrize("fused", [False, True], ids=["nccl", "fused_gemms"])
+def test_gemma_tensor_parallel_follows_the_single_gpu_run(tmp_path, fused):
     import torch.multiprocessing as mp
     from test_parallel_cpu import GEMMA_HEADS, _batches, _free_port, _full_weights, _gemma_cfg, _load_full
     from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
@@ -43,7 +46,7 @@ def test_gemma_tensor_parallel_follows_the_single_gpu_run(tmp_path):
         if "norm" in k:
             v.copy_(0.2 * torch.randn(v.shape, generator=g))
     batches = _batches(3, 2, 256, 512)
-    mp.spawn(_worker, args=(2, _free_port(), full, batches, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), full, batches, fused, str(tmp_path)), nprocs=2, join=True)
     os.environ.pop("WORLD_SIZE", None)
     os.environ.pop("RANK", None)
     tr = Trainer(_gemma_cfg(seq_len=256, ac_mode="selective"))
