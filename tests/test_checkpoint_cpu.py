@@ -267,6 +267,34 @@ def test_gemma_tensor_parallel_checkpoint_holds_whole_tensors_in_the_reference_r
             assert torch.equal(v.float(), want[k].float()), (r, k)
 
 
+def _gemma_tp_load(rank, world, tmp, dp):
+    import torch.distributed as dist
+    cfg = _mk(tmp, model_name="gemma3", flavor="debug_gqa", tensor_parallel_degree=2, data_parallel_shard_degree=dp)
+    tr, state, ck = _trainer_with_ckpt(cfg)
+    assert ck.load() and state.step == 2
+    return dist.get_rank(tr.parallel_dims.mesh_group("tp")), _params(tr)
+
+
+@pytest.mark.parametrize("world,dp", [(2, 1), (4, 2)])
+def test_unsharded_gemma_checkpoint_loads_into_tensor_parallel_ranks(tmp_path, world, dp):
+    """A checkpoint written by one process (the layout of the reference and of converted HF weights) is read by
+    tensor-parallel ranks: each takes its head groups out of the whole [q; k; v] matrix."""
+    os.environ.pop("WORLD_SIZE", None)
+    from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
+    from test_parallel_cpu import GEMMA_HEADS, _gemma_cfg
+    full = _full_weights(_gemma_cfg())
+    tr, state, ck = _trainer_with_ckpt(_mk(tmp_path, model_name="gemma3", flavor="debug_gqa"))
+    _load_full(tr, full)
+    tr.train_step(_batches(1, 2, 64, 512)[0])
+    state.step = 2
+    ck.save(2)
+    want_full = _params(tr)
+    for tp_rank, got in run_ranks(world, _gemma_tp_load, str(tmp_path), dp):
+        want = tp_slice_state_dict(want_full, 2, tp_rank, GEMMA_HEADS)
+        for k, v in got.items():
+            assert torch.equal(v, want[k]), k
+
+
 def _expert_tp_save(rank, world, tmp, full, cfg_kw):
     from test_expert_parallel_cpu import _cfg as ep_cfg, _load
     from train import TrainState
