@@ -76,6 +76,21 @@ def test_submit_dry_run_creates_job_dir(tmp_path):
     assert "--job-name=j1" in (job / "slurm.sh").read_text()
 
 
+def test_every_shipped_config_is_a_valid_job_whose_degrees_fill_its_gpus():
+    import tomllib
+    from maester_b200.models import models_config
+    for path in sorted((ROOT / "configs").rglob("*.toml")):
+        cfg = Config(**tomllib.loads(path.read_text()))
+        assert cfg.flavor in models_config[cfg.model_name], path
+        shard = cfg.data_parallel_shard_degree
+        fixed = cfg.data_parallel_replicate_degree * cfg.tensor_parallel_degree * cfg.context_parallel_degree
+        gpus = cfg.num_nodes * 8
+        assert gpus % fixed == 0 and (shard == -1 or shard * fixed == gpus), (path, shard, fixed, gpus)
+        if cfg.tensor_parallel_degree > 1 and cfg.model_name == "gemma3":
+            a = models_config["gemma3"][cfg.flavor]
+            assert a.n_heads % cfg.tensor_parallel_degree == 0 and a.num_key_value_heads % cfg.tensor_parallel_degree == 0
+
+
 def test_sweep_generation(tmp_path, monkeypatch):
     monkeypatch.chdir(tmp_path)
     import sweep
