@@ -43,9 +43,12 @@ def build_experimental_data_loader(cfg, rank: int, world_size: int, tokenizer=No
     dirs, weights = parse_data_args(cfg.dataset.data_dirs, cfg.dataset.dataset_weights)
     drop = {int(x) for x in str(cfg.dataset.drop_tokens).split(",") if str(x).strip()}
     sources = [
+        # the reference's arguments (maester/datasets/experimental_otf.py:1565-1578): documents shorter than 3 tokens
+        # are skipped, chunks of at most 1024 tokens, no BOS when the config says -1; with them the token stream and
+        # the saved loader state are the reference's
         ParquetDataset(d, rank, world_size, tokenizer, delimiter_token=cfg.dataset.eos_token,
-                       bos_token=cfg.dataset.bos_token, strip_tokens=drop, max_chunksize=cfg.seq_len,
-                       cache_row_groups=cfg.dataset.cache_row_groups)
+                       bos_token=None if cfg.dataset.bos_token == -1 else cfg.dataset.bos_token, strip_tokens=drop,
+                       min_length=3, seed=42, max_chunksize=1024, cache_row_groups=cfg.dataset.cache_row_groups)
         for d in dirs
     ]
     ds = Sampling_Dataset(sources, weights, delimiter_token=cfg.dataset.eos_token, rank=rank, worldsize=world_size)

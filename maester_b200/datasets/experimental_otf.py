@@ -223,7 +223,10 @@ class Checkpoint_Dataset(_Wrapper_Dataset):
 
 
 class Preload_Buffer_Dataset(_Wrapper_Dataset):
-    """Shuffle buffer: fill ``window_size`` items, then swap a random slot out for every new item."""
+    """Shuffle buffer with one in/out slot array (reference: maester/datasets/experimental_otf.py:383-452).  Every step
+    yields a random slot and refills it; while the buffer is below ``window_size`` a step also appends one item first,
+    so the buffer grows by one per yielded item (two reads per step) and output starts with the very first step instead
+    of after ``window_size`` reads.  The random draws are the same as the reference's, so is the stream."""
 
     def __init__(self, dataset: _Stateful_Dataset, window_size: int):
         super().__init__(dataset)
@@ -243,7 +246,6 @@ class Preload_Buffer_Dataset(_Wrapper_Dataset):
             if self.buffer_size < self.window_size:
                 self.buffer[self.buffer_size] = next(it)
                 self.buffer_size += 1
-                continue
             i = torch.randint(self.buffer_size, (1,), generator=self.generator).item()
             out = self.buffer[i]
             self.buffer[i] = next(it)

@@ -277,23 +277,23 @@ class Sampling_Dataset(_Stateful_Dataset):
             else:
                 total = sum(self.tokens_seen) + 1e-9
                 deficit = [self.weights[i] - self.tokens_seen[i] / total for i in range(len(self.data))]
-                self.current_iterator = max(range(len(deficit)), key=deficit.__getitem__)
+                # among equally starved sources the LAST one wins, as in the reference (a max over (deficit, index)
+                # pairs, maester/datasets/experimental_otf.py:1352-1358): same stream from the first document on
+                self.current_iterator = max((x, i) for i, x in enumerate(deficit))[1]
 
     def state_dict(self) -> dict:
-        out = {}
-        for d in self.data:
-            for k, v in d.state_dict().items():
-                out[f"{d.data if hasattr(d, 'data') else id(d)}::{k}"] = v
+        """The sources' states as a list under ``sample_iterator_states``, in the order of the sources: the layout of
+        the reference's loader checkpoints (maester/datasets/experimental_otf.py:1360-1369)."""
+        out = {self.statename("sample_iterator_states"): [d.state_dict() for d in self.data]}
         out.update(super().state_dict())
         return out
 
     def load_state_dict(self, state_dicts, sharded_input: bool = False):
         sharded = super().load_state_dict(state_dicts, sharded_input)
-        for d in self.data:
-            prefix = f"{d.data if hasattr(d, 'data') else id(d)}::"
-            sub = [{k[len(prefix):]: v for k, v in sd.items() if k.startswith(prefix)} for sd in sharded]
+        key = self.statename("sample_iterator_states")
+        for i, d in enumerate(self.data):
             d.load_worldsize = self.load_worldsize
-            d.load_state_dict(sub, True)
+            d.load_state_dict([sd[key][i] for sd in sharded], True)
         return sharded
 
 
