@@ -177,7 +177,7 @@ def newton_schulz(g: torch.Tensor, steps: int = 5, eps: float = 1e-7) -> torch.T
     x = x / (x.norm(dim=(-2, -1), keepdim=True) + eps)
     for _ in range(steps):
         A = x @ x.mT
-        Bm = b * A + c * (A @ A)
+        Bm = b * A + (c * A) @ A   # the scaled matrix is the left factor, as in the reference: same bf16 roundings
         x = a * x + Bm @ x
     if transposed:
         x = x.mT

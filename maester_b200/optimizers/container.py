@@ -35,6 +35,11 @@ def _named_trainable(model: torch.nn.Module) -> list[tuple[str, torch.nn.Paramet
 
 
 def _import(path: str):
+    """Class by dotted path.  Paths into the reference's package (``maester.optimizers.Muon``, the default of its
+    ``optimizer_groups``, maester/config.py:132-157) name this package's class of the same name, so a job directory
+    written by the reference's tooling runs unchanged."""
+    if path.startswith("maester."):
+        path = "maester_b200." + path[len("maester."):]
     mod, _, name = path.rpartition(".")
     return getattr(importlib.import_module(mod), name)
 

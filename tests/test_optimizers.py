@@ -36,6 +36,13 @@ def test_default_groups_split_muon_and_adamw():
     assert any(k.startswith("opt0_") for k in keys) and any(k.startswith("opt1_") for k in keys)
 
 
+def test_class_paths_of_the_reference_package_name_this_package():
+    from maester_b200.optimizers import Muon, MuonDDP
+    from maester_b200.optimizers.container import _import
+    assert _import("maester.optimizers.Muon") is Muon and _import("maester.optimizers.MuonDDP") is MuonDDP
+    assert _import("torch.optim.AdamW") is torch.optim.AdamW
+
+
 def test_unassigned_parameter_is_an_error():
     model = _tiny_llama()
     cfg = Config(optimizer_groups=[{"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3}, "min_dim": 2}])

@@ -1,0 +1,108 @@
+"""Optimizer-side parity with the reference's own code (installed copy of the reference package), on CPU as one gloo
+rank: Muon with its built-in Adam groups step for step (bitwise: the Newton–Schulz iteration runs in bf16, so even the
+grouping of a scalar factor matters), the learning-rate schedules, and the job configuration both ways.
+
+Two process-wide adjustments, neither of which changes the reference's arithmetic: ``TORCHDYNAMO_DISABLE=1`` (no host
+compiler set-up for Inductor here; ``torch.compile`` becomes the eager function) and the reference's asynchronous
+``gather`` / ``scatter`` made blocking: on NCCL they are ordered by the stream, on gloo nothing orders them before the
+next line reads their output."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "maester")), reason="the reference is not installed")
+
+
+def _setup():
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "shims"))
+    sys.path.insert(0, REF)
+    sys.path.insert(0, ROOT)
+    import maester.models  # noqa: F401  (the reference's packages import each other in a circle unless this one goes first)
+
+
+def _muon():
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29617")
+    dist.init_process_group("gloo", rank=0, world_size=1)
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import Shard, distribute_tensor
+    import maester.optimizers.muon as ref_muon
+    from maester_b200.optimizers import Muon
+    gather, scatter = ref_muon.gather, ref_muon.scatter
+    ref_muon.gather = lambda *a, **k: gather(*a, **{**k, "async_op": False})
+    ref_muon.scatter = lambda *a, **k: scatter(*a, **{**k, "async_op": False})
+    mesh = init_device_mesh("cpu", (1,))
+    g = torch.Generator().manual_seed(0)
+    shapes = [(64, 32), (32, 64), (48, 48), (40, 24)]
+    adam_shapes = [(96, 16), (16,)]
+    make = lambda ss: [torch.randn(s, generator=g) * 0.05 for s in ss]
+    w, wa = make(shapes), make(adam_shapes)
+    steps = [(make(shapes), make(adam_shapes)) for _ in range(4)]
+    dt = lambda t: distribute_tensor(t.clone(), mesh, [Shard(0)])
+    rp, ra = [torch.nn.Parameter(dt(t)) for t in w], [torch.nn.Parameter(dt(t)) for t in wa]
+    op, oa = [torch.nn.Parameter(t.clone()) for t in w], [torch.nn.Parameter(t.clone()) for t in wa]
+    adam = dict(use_muon=False, lr=3e-3, betas=(0.9, 0.95), eps=1e-8, wd=0.1)
+    ref = ref_muon.Muon([dict(params=rp, use_muon=True, lr=0.02, wd=0.01, momentum=0.95, ns_steps=5), dict(params=ra, **adam)])
+    ours = Muon([dict(params=op, use_muon=True, lr=0.02, wd=0.01, momentum=0.95, ns_steps=5), dict(params=oa, **adam)])
+    for gm, ga in steps:
+        for p, q, t in zip(rp + ra, op + oa, gm + ga):
+            p.grad, q.grad = dt(t), t.clone()
+        ref.step()
+        ours.step()
+        for p, q in zip(rp, op):
+            assert torch.equal(p.data.to_local(), q.data), tuple(q.shape)       # Muon matrices: bitwise
+        for p, q in zip(ra, oa):
+            assert torch.allclose(p.data.to_local(), q.data, rtol=1e-6, atol=1e-8), tuple(q.shape)
+    moved = ((op[0].data - w[0]).norm() / w[0].norm()).item()
+    assert moved > 0.05, moved
+    dist.destroy_process_group()
+    print(f"muon: 4 steps bitwise equal on {shapes}; first matrix moved by {moved:.3f} of its norm")
+
+
+def _schedules_and_config():
+    import torch
+    from maester.config import Config as RefConfig
+    from maester.lr_scheduling import get_lr_scheduler as ref_sched
+    from maester_b200.config import Config
+    from maester_b200.lr_scheduling import get_lr_scheduler
+    for kw in (dict(scheduler="linear_warmup_cosine", warmup_steps=7, train_num_steps=60),
+               dict(scheduler="linear_warmup_constant_sqrt_decay", warmup_steps=5, train_num_steps=50, cooldown_steps=12)):
+        lrs = []
+        for cfg, build in ((RefConfig(**kw), ref_sched), (Config(**kw), get_lr_scheduler)):
+            opt = torch.optim.SGD([torch.nn.Parameter(torch.zeros(1))], lr=0.5)
+            sched, seq = build(opt, cfg), []
+            for _ in range(kw["train_num_steps"]):
+                seq.append(opt.param_groups[0]["lr"])
+                opt.step()
+                sched.step()
+            lrs.append(seq)
+        assert lrs[0] == pytest.approx(lrs[1], rel=1e-12), kw
+    # a job configuration written by the reference's tooling is a valid configuration here, field for field
+    ref = RefConfig(model_name="gemma3", flavor="4B", job_name="from-reference")
+    dumped = json.loads(ref.model_dump_json())
+    cfg = Config(**dumped)
+    for k, v in dumped.items():
+        assert json.loads(cfg.model_dump_json())[k] == v, k
+    from maester_b200.optimizers.container import _import
+    for group in cfg.optimizer_groups:   # "maester.optimizers.Muon" and "torch.optim.AdamW" both resolve
+        assert _import(group["opt_class"]).__name__ == group["opt_class"].rpartition(".")[2]
+    print("schedules equal; the reference's config.json loads field for field")
+
+
+@pytest.mark.parametrize("what", ["muon", "schedules_and_config"])
+def test_optimizer_side_parity_with_the_reference(what):
+    r = subprocess.run([sys.executable, os.path.abspath(__file__), what], capture_output=True, text=True,
+                       env=dict(os.environ, TORCHDYNAMO_DISABLE="1"), timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    print(r.stdout.strip().splitlines()[-1])
+
+
+if __name__ == "__main__":
+    _setup()
+    {"muon": _muon, "schedules_and_config": _schedules_and_config}[sys.argv[1]]()
