@@ -76,7 +76,7 @@ def _pair(name, family, ref_cfgs, our_cfgs):
     ours.init_weights()
     missing, unexpected = ours.load_state_dict(dict(ref.state_dict()), strict=False)
     assert not missing and not [k for k in unexpected if not k.endswith("freqs_cis")], (missing, unexpected)
-    return ref, ours
+    return ref, ours, ra, oa
 
 
 def _child(family: str) -> None:
@@ -89,7 +89,7 @@ def _child(family: str) -> None:
     from maester.models import models_config as ref_cfgs
     from maester_b200.models import models_config as our_cfgs
     name = family.split("_")[0]
-    ref, ours = _pair(name, family, ref_cfgs, our_cfgs)
+    ref, ours, ref_args, our_args = _pair(name, family, ref_cfgs, our_cfgs)
     bf16_experts = name in ("glm4", "deepseek")   # the reference runs its experts in bf16 whatever the model's dtype
     tol = 2e-2 if bf16_experts else 2e-5
     gen = torch.Generator().manual_seed(1)
@@ -110,6 +110,9 @@ def _child(family: str) -> None:
         print(f"{family}: packed-document logits max abs diff {err:.2e}")
         return
 
+    # parameter count and FLOPs per token (they set the reported MFU)
+    counts = ref_args.get_nparams_and_flops(ref, 96)
+    assert counts == our_args.get_nparams_and_flops(ours, 96), (counts, our_args.get_nparams_and_flops(ours, 96))
     a = ref(tok).float()
     b = ours(tok).float()
     scale = a.abs().max().item()
@@ -131,7 +134,7 @@ def _child(family: str) -> None:
         rel = ((p.grad - q.grad).norm() / (p.grad.norm() + 1e-12)).item()
         worst = max(worst, (n, rel), key=lambda t: t[1])
         assert rel < (5e-2 if bf16_experts else 1e-4), (n, rel)
-    print(f"{family}: logits max abs diff {err:.2e} (scale {scale:.2f}), loss {want_loss.item():.6f} vs "
+    print(f"{family}: {counts[0]:,} parameters, {counts[1]:,} FLOPs/token; logits max abs diff {err:.2e} (scale {scale:.2f}), loss {want_loss.item():.6f} vs "
           f"{got_loss.item():.6f}, worst gradient {worst[0]} rel {worst[1]:.2e}")
 
 
