@@ -56,11 +56,14 @@ class _LazyStats(dict):
         batch, totals, batches, extra = self._pending
         self._pending = None
         both = torch.stack([batch.float(), totals.float()]).cpu()   # the only host transfer
-        for key, vals in (("batch", _balance_stats(both[0])), ("global", _balance_stats(both[1]))):
-            super().__setitem__(f"expert_balance/{key}_maxvio_mean", vals["maxvio"].mean().item())
-            super().__setitem__(f"expert_balance/{key}_maxvio_max", vals["maxvio"].max().item())
-            super().__setitem__(f"expert_balance/{key}_cv_mean", vals["cv"].mean().item())
-            super().__setitem__(f"expert_balance/{key}_dead_frac_mean", vals["dead_frac"].mean().item())
+        # the reference's metric names (maester/models/deepseek/optimizer.py:181-203): average, maximum and minimum
+        # over the MoE layers of each statistic, for this step's batch and for the running totals
+        for kind, vals in (("batch", _balance_stats(both[0])), ("global", _balance_stats(both[1]))):
+            for stat in ("maxvio", "dead_frac", "cv"):
+                v = vals[stat]
+                super().__setitem__(f"expert_balance/{stat}_{kind}_avg", v.mean().item())
+                super().__setitem__(f"expert_balance/{stat}_{kind}_max", v.max().item())
+                super().__setitem__(f"expert_balance/{stat}_{kind}_min", v.min().item())
         super().__setitem__("expert_balance/batches", batches)
         if extra is not None:
             for k, v in extra().items():
@@ -115,12 +118,13 @@ def _balance_stats(tokens: torch.Tensor) -> dict[str, torch.Tensor]:
             "dead_frac": torch.where(zero, torch.zeros_like(dead), dead).squeeze(1)}
 
 
-def _moe_modules(model: nn.Module) -> list[nn.Module]:
+def _moe_modules(model: nn.Module, with_names: bool = False) -> list:
     layers = getattr(model, "layers", None)
     if layers is None:
         return []
-    vals = layers.values() if isinstance(layers, nn.ModuleDict) else layers
-    return [l.moe for l in vals if getattr(l, "moe_enabled", False) and hasattr(l.moe, "tokens_per_expert")]
+    named = layers.items() if isinstance(layers, nn.ModuleDict) else ((str(i), l) for i, l in enumerate(layers))
+    found = [(n, l.moe) for n, l in named if getattr(l, "moe_enabled", False) and hasattr(l.moe, "tokens_per_expert")]
+    return found if with_names else [m for _, m in found]
 
 
 def build_deepseek_optimizers(model: nn.Module, cfg, parallel_dims) -> OptimizersContainer:
@@ -152,9 +156,9 @@ def build_deepseek_optimizers(model: nn.Module, cfg, parallel_dims) -> Optimizer
             if cfg.enable_wandb:
                 try:
                     import wandb
-                    for i, m in enumerate(moes):
+                    for name, m in _moe_modules(model, with_names=True):   # keyed by the layer's name in the model
                         if m.expert_bias is not None:
-                            out[f"expert_balance/bias_hist_layer{i}"] = wandb.Histogram(m.expert_bias.float().cpu().numpy())
+                            out[f"expert_balance_bias/layer{name}"] = wandb.Histogram(m.expert_bias.float().cpu().tolist())
                 except ImportError:
                     pass
             return out

@@ -156,7 +156,7 @@ def test_moe_load_balance_hook_updates_biases_and_defers_its_statistics():
     out = dict(stats)                                                      # first read computes
     assert stats._pending is None
     assert out["expert_balance/batches"] == 1
-    for key in ("batch_maxvio_mean", "batch_cv_mean", "global_maxvio_max", "global_dead_frac_mean"):
+    for key in ("maxvio_batch_avg", "cv_batch_min", "maxvio_global_max", "dead_frac_global_avg"):
         assert f"expert_balance/{key}" in out
     tr.train_step(batch)
     assert dict(tr.optimizers._hook_stats)["expert_balance/batches"] == 2

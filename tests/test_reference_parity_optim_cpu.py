@@ -95,7 +95,54 @@ def _schedules_and_config():
     print("schedules equal; the reference's config.json loads field for field")
 
 
-@pytest.mark.parametrize("what", ["muon", "schedules_and_config"])
+def _load_balance():
+    """The auxiliary-loss-free balancing hook: same counters in, same biases and the same 18 statistics out, under the
+    same metric names, step after step (running totals included)."""
+    import copy
+    import types
+    import torch
+    from maester.config import Config as RefConfig
+    from maester.models import model_name_to_cls as ref_cls, models_config as ref_cfgs
+    from maester.models.deepseek.optimizer import build_deepseek_optimizers as ref_build
+    from maester_b200.config import Config
+    from maester_b200.models import model_name_to_cls as our_cls, models_config as our_cfgs
+    from maester_b200.models.deepseek.optimizer import build_deepseek_optimizers
+    ra, oa = copy.deepcopy(ref_cfgs["deepseek"]["debug"]), copy.deepcopy(our_cfgs["deepseek"]["debug"])
+    for a in (ra, oa):
+        a.vocab_size, a.max_seq_len, a.n_layers, a.moe_args.load_balance_coeff = 512, 96, 4, 1e-2
+    ref, ours = ref_cls["deepseek"].from_model_args(ra), our_cls["deepseek"].from_model_args(oa)
+    ref.init_weights()
+    ours.init_weights()
+    groups = [{"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3}, "min_dim": 0}]
+    dims = types.SimpleNamespace(dp_enabled=False, world_mesh=None)
+    ref_opt = ref_build(ref, RefConfig(optimizer_groups=groups, enable_wandb=False), dims)
+    our_opt = build_deepseek_optimizers(ours, Config(optimizer_groups=groups, enable_wandb=False), dims)
+    ref_moes = [l.moe for l in ref.layers.values() if l.moe_enabled]
+    our_moes = ours.moe_layers()
+    assert len(ref_moes) == len(our_moes) == 3
+    g = torch.Generator().manual_seed(0)
+    for step in range(4):
+        for a, b in zip(ref_moes, our_moes):
+            counts = torch.randint(0, 200, a.tokens_per_expert.shape, generator=g)
+            if step == 2:
+                counts[:3] = 0   # dead experts
+            a.tokens_per_expert.copy_(counts)
+            b.tokens_per_expert.copy_(counts)
+        for p in list(ref.parameters()) + list(ours.parameters()):
+            p.grad = torch.zeros_like(p)
+        ref_opt.step()
+        our_opt.step()
+        for a, b in zip(ref_moes, our_moes):
+            assert torch.equal(a.expert_bias, b.expert_bias) and a.expert_bias.abs().max() > 0
+            assert not a.tokens_per_expert.any() and not b.tokens_per_expert.any()
+        want, got = dict(ref_opt._hook_stats), dict(our_opt._hook_stats)
+        assert len(want) == 18 and set(want) <= set(got), sorted(set(want) - set(got))
+        for k, v in want.items():
+            assert got[k] == pytest.approx(v, rel=1e-5, abs=1e-7), (step, k, v, got[k])
+    print("load balance: biases equal and 18 statistics equal over 4 steps")
+
+
+@pytest.mark.parametrize("what", ["muon", "schedules_and_config", "load_balance"])
 def test_optimizer_side_parity_with_the_reference(what):
     r = subprocess.run([sys.executable, os.path.abspath(__file__), what], capture_output=True, text=True,
                        env=dict(os.environ, TORCHDYNAMO_DISABLE="1"), timeout=900)
@@ -105,4 +152,4 @@ def test_optimizer_side_parity_with_the_reference(what):
 
 if __name__ == "__main__":
     _setup()
-    {"muon": _muon, "schedules_and_config": _schedules_and_config}[sys.argv[1]]()
+    {"muon": _muon, "schedules_and_config": _schedules_and_config, "load_balance": _load_balance}[sys.argv[1]]()
