@@ -196,6 +196,19 @@ class OptimizerWrapper(Stateful):
         self.optimizer.load_state_dict(plain)
 
 
+def resume_step(cfg) -> int:
+    """The optimizer step of the checkpoint that ``CheckpointManager.load()`` will resume from with this configuration
+    (0: none, or a model-only load from ``forced_load_path``).  The data pipeline is built before the manager exists and
+    needs the step to load the loader state that belongs to it."""
+    if not cfg.enable_checkpoint or cfg.forced_load_path:
+        return 0
+    folder = os.path.join(cfg.dump_dir, cfg.job_name, cfg.checkpoint_folder)
+    if not os.path.isdir(folder):
+        return 0
+    steps = [int(m.group(1)) for f in os.listdir(folder) if (m := re.fullmatch(r"step-(\d+)", f))]
+    return max(steps) if steps else 0
+
+
 class CheckpointManager:
     def __init__(self, model: nn.Module, optimizer, lr_scheduler, dataloader, states: dict[str, Any], cfg) -> None:
         self.enable_checkpoint: bool = cfg.enable_checkpoint

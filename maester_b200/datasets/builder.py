@@ -28,7 +28,7 @@ def parse_data_args(datas, weights):
     return d, w
 
 
-def build_experimental_data_loader(cfg, rank: int, world_size: int, tokenizer=None):
+def build_experimental_data_loader(cfg, rank: int, world_size: int, tokenizer=None, resume_step: int | None = None):
     """Sampling → Buffer(seq_len+1, hard) → Preload(10000) → Preprocess(causal_lm) → Checkpoint → DataLoader.
 
     The DataLoader uses exactly one worker process: the pipeline keeps its position in Python objects
@@ -58,7 +58,7 @@ def build_experimental_data_loader(cfg, rank: int, world_size: int, tokenizer=No
     ckpt_dir = os.path.join(cfg.dump_dir, cfg.job_name, cfg.checkpoint_folder, "dataloader")
     ds = Checkpoint_Dataset(ds, ckpt_dir, cfg.checkpoint_interval,
                             steps_per_batch=cfg.train_batch_size * max(1, cfg.gradient_accumulation_steps),
-                            save_path=ckpt_dir)
+                            save_path=ckpt_dir, load_step=resume_step)
     workers = 1  # more than one worker would duplicate the stateful pipeline
     return torch.utils.data.DataLoader(ds, batch_size=cfg.train_batch_size, num_workers=workers,
                                        prefetch_factor=8, pin_memory=torch.cuda.is_available(),

@@ -165,14 +165,32 @@ class Checkpoint_Dataset(_Wrapper_Dataset):
     prefetches, the saved state runs ahead of consumption by the prefetch depth."""
 
     def __init__(self, dataset: _Stateful_Dataset, load_path: str, interval: int, steps_per_batch: int = 1,
-                 save_path: str = ""):
+                 save_path: str = "", load_step: int | None = None):
+        """``load_step``: the optimizer step of the model checkpoint that the job resumes from.  ``None`` loads the
+        NEWEST loader state, as the reference does (maester/datasets/experimental_otf.py:354-381).  That one can be
+        ahead of the newest model checkpoint: the worker process saves on its own count of yielded batches, and the
+        DataLoader lets it run ahead of the training loop by the prefetch depth, so a job that stopped after the
+        loader wrote ``step-12`` but before the model reached it would skip the batches in between.  With a step
+        given, exactly ``step-<load_step>`` is loaded (an error if it is missing), and 0 starts from scratch whatever
+        states lie around."""
         super().__init__(dataset)
         self.interval, self.spb = interval, steps_per_batch
         self.save_path = save_path or load_path
         self.path = self.save_path
         self.step = 0
         self.ministep = 0
-        self.load_from_path(load_path)
+        if load_step is None:
+            self.load_from_path(load_path)
+        elif load_step > 0:
+            exact = os.path.join(self.path, f"step-{load_step}")
+            if not (os.path.isdir(exact) and any("loader" in x for x in os.listdir(exact))):
+                raise RuntimeError(f"the model resumes from step {load_step} but {exact} holds no loader state: "
+                                   "the job would train on the wrong part of the stream")
+            self.dataset.load_from_path(exact)
+            self.step = load_step
+            self._report(f"Dataset checkpoint loaded from {exact}, the step of the model checkpoint")
+        else:
+            self._report("Data pipeline starts from scratch (the model does)")
 
     def setup(self) -> None:
         pass

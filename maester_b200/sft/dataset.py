@@ -100,7 +100,7 @@ def packed_collate_fn(batch: list[dict[str, Any]]) -> dict[str, Any]:
     return out
 
 
-def build_sft_data_loader(cfg, rank: int, world_size: int, tokenizer=None):
+def build_sft_data_loader(cfg, rank: int, world_size: int, tokenizer=None, resume_step: int | None = None):
     assert cfg.sft is not None, "cfg.sft must be set for SFT data"
     if cfg.sft.use_packed:
         from maester_b200.sft.packed_dataset import PackedSFTDataset
@@ -124,6 +124,6 @@ def build_sft_data_loader(cfg, rank: int, world_size: int, tokenizer=None):
     ckpt_dir = os.path.join(cfg.dump_dir, cfg.job_name, cfg.checkpoint_folder, "dataloader")
     ds = Checkpoint_Dataset(ds, ckpt_dir, cfg.checkpoint_interval,
                             steps_per_batch=cfg.train_batch_size * max(1, cfg.gradient_accumulation_steps),
-                            save_path=ckpt_dir)
+                            save_path=ckpt_dir, load_step=resume_step)
     return torch.utils.data.DataLoader(ds, batch_size=cfg.train_batch_size, num_workers=1, prefetch_factor=4,
                                        pin_memory=torch.cuda.is_available(), persistent_workers=True)

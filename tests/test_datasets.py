@@ -183,3 +183,25 @@ def test_checkpoint_dataset_saves_and_autoloads(tmp_path):
     resumed = take(iter(b), 5)
     for x, y in zip(resumed, items[20:]):
         assert torch.equal(x["input_ids"], y["input_ids"])
+
+
+def test_loader_state_of_a_given_step_is_loaded_not_the_newest(tmp_path):
+    """The worker saves ahead of the training loop (prefetch); a job resumes from the state of the MODEL's step."""
+    make_corpus(tmp_path / "d")
+
+    def pipeline(load_step):
+        src = ParquetDataset(str(tmp_path / "d"), 0, 1, ToyTokenizer(), delimiter_token=1, max_chunksize=32)
+        ds = Preload_Buffer_Dataset(Buffer_Dataset(Sampling_Dataset([src], None, delimiter_token=1), 17, pack_hard=True), 20)
+        return Checkpoint_Dataset(ds, str(tmp_path / "ck"), 3, steps_per_batch=2, save_path=str(tmp_path / "ck"),
+                                  load_step=load_step)
+
+    first = pipeline(0)
+    lines = take(iter(first), 2 * 9 + 1)                 # 9 steps of 2 lines each: states step-3, step-6, step-9 exist
+    assert sorted(os.listdir(tmp_path / "ck")) == ["step-3", "step-6", "step-9"]
+    assert take(iter(pipeline(None)), 1)[0] == lines[18]  # the newest state (the reference's choice): line after step 9
+    resumed = pipeline(3)                                 # the model checkpoint is at step 3
+    assert resumed.step == 3
+    assert take(iter(resumed), 6) == lines[6:12]
+    assert take(iter(pipeline(0)), 4) == lines[:4]        # no model checkpoint: from scratch despite stale states
+    with pytest.raises(RuntimeError, match="holds no loader state"):
+        pipeline(4)

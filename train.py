@@ -27,7 +27,7 @@ from torch.distributed.elastic.multiprocessing.errors import record
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
-from maester_b200.checkpoint import CheckpointManager  # noqa: E402
+from maester_b200.checkpoint import CheckpointManager, resume_step  # noqa: E402
 from maester_b200.config import Config  # noqa: E402
 from maester_b200.log_utils import init_logger, logger  # noqa: E402
 from maester_b200.memory import cleanup_before_training  # noqa: E402
@@ -64,11 +64,13 @@ def build_data_loader(cfg: Config, trainer: Trainer):
     if cfg.synthetic_data:
         from maester_b200.datasets.synthetic import build_synthetic_data_loader
         return build_synthetic_data_loader(cfg, trainer.dp_rank, trainer.dp_degree, trainer.model_args.vocab_size)
+    # the loader state that belongs to the model checkpoint this job resumes from (the newest loader state can be ahead)
+    step = resume_step(cfg) if cfg.enable_checkpoint else None
     if cfg.sft is not None:
         from maester_b200.sft import build_sft_data_loader
-        return build_sft_data_loader(cfg, rank=trainer.dp_rank, world_size=trainer.dp_degree)
+        return build_sft_data_loader(cfg, rank=trainer.dp_rank, world_size=trainer.dp_degree, resume_step=step)
     from maester_b200.datasets.experimental_otf import build_experimental_data_loader
-    return build_experimental_data_loader(cfg, rank=trainer.dp_rank, world_size=trainer.dp_degree)
+    return build_experimental_data_loader(cfg, rank=trainer.dp_rank, world_size=trainer.dp_degree, resume_step=step)
 
 
 def tokenizer_vocab_size(cfg: Config) -> int | None:
@@ -170,12 +172,16 @@ def main() -> None:
                     tps = ntokens_since_last_log / (time_delta * pd.model_parallel_size)
                     mfu = trainer.mfu(tps)
                     time_e2e = time_delta / cfg.log_freq
+                    # per rank: mean time per batch and share of the logging interval; reported as the mean and the
+                    # maximum over all ranks (tensor-parallel ranks load the same data redundantly)
                     t_data = float(np.mean(data_loading_times))
+                    t_data_pct = 100 * float(np.sum(data_loading_times)) / max(time_delta, 1e-9)
                     if distributed:
-                        t_data_avg = dist_mean(t_data).item()
-                        t_data_max = dist_max(float(np.max(data_loading_times))).item()
+                        t_data_avg, t_data_max = dist_mean(t_data).item(), dist_max(t_data).item()
+                        t_data_pct_avg, t_data_pct_max = dist_mean(t_data_pct).item(), dist_max(t_data_pct).item()
                     else:
-                        t_data_avg, t_data_max = t_data, float(np.max(data_loading_times))
+                        t_data_avg = t_data_max = t_data
+                        t_data_pct_avg = t_data_pct_max = t_data_pct
                     mem = gpu_memory_monitor.get_peak_stats()
                     metrics = {
                         "loss/global_avg": global_avg_loss,
@@ -186,7 +192,8 @@ def main() -> None:
                         "time/end_to_end(s)": time_e2e,
                         "time/data_loading_avg(s)": t_data_avg,
                         "time/data_loading_max(s)": t_data_max,
-                        "time/data_loading(%)": 100 * t_data_avg * trainer.grad_accum / max(time_e2e, 1e-9),
+                        "time/data_loading_avg(%)": t_data_pct_avg,
+                        "time/data_loading_max(%)": t_data_pct_max,
                         "memory/max_active(GiB)": mem.max_active_gib,
                         "memory/max_active(%)": mem.max_active_pct,
                         "memory/max_reserved(GiB)": mem.max_reserved_gib,
@@ -214,7 +221,7 @@ def main() -> None:
                         f"Step {train_state.step:2}: lr={metrics['lr']:.2E}, loss={global_avg_loss:7.4f} "
                         f"(max={global_max_loss:7.4f}), tps={round(tps):,}, mfu={mfu:.2f}%, "
                         f"mem={mem.max_reserved_gib:.2f}GiB({mem.max_reserved_pct:.2f}%), "
-                        f"data={t_data_avg:.4f}s"
+                        f"time/data_loading={t_data_avg:.2f}s (max={t_data_max:.2f}s, {t_data_pct_max:.2f}%)"
                     )
                     losses_since_last_log.clear()
                     padding_lengths.clear()
