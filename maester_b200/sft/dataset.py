@@ -112,6 +112,10 @@ def build_sft_data_loader(cfg, rank: int, world_size: int, tokenizer=None, resum
         from transformers import AutoTokenizer, PreTrainedTokenizerFast
         tokenizer = (PreTrainedTokenizerFast(tokenizer_file=cfg.tokenizer_name) if os.path.isfile(cfg.tokenizer_name)
                      else AutoTokenizer.from_pretrained(cfg.tokenizer_name))
+    if getattr(tokenizer, "eos_token_id", None) is None:
+        raise ValueError(f"the tokenizer {cfg.tokenizer_name!r} defines no EOS token: every conversation ends with one "
+                         "(a bare tokenizer.json carries no special-token roles; point tokenizer_name at a folder "
+                         "saved with save_pretrained)")
     vocab = tokenizer.get_vocab() if hasattr(tokenizer, "get_vocab") else {}
     for tok in (cfg.sft.im_start_token, cfg.sft.im_end_token):
         if vocab and tok not in vocab:

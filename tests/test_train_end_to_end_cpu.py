@@ -115,3 +115,79 @@ lr = 3e-3
     w1, w2 = read_dcp_model(whole / "checkpoints" / "step-8"), read_dcp_model(cut / "checkpoints" / "step-8")
     for k in w1:
         assert ((w1[k].float() - w2[k].float()).norm() / (w1[k].float().norm() + 1e-12)).item() < 2e-2, k
+
+
+def _chat_tokenizer_file(path) -> str:
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    words = ["<unk>", "<eos>", "<bos>", "<|im_start|>", "<|im_end|>", "system", "user", "assistant"] + [f"w{i}" for i in range(200)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tok.add_special_tokens(["<|im_start|>", "<|im_end|>", "<eos>", "<bos>"])
+    # a folder as save_pretrained writes it: the special-token roles live in a config beside tokenizer.json
+    from transformers import PreTrainedTokenizerFast
+    folder = str(path) + ".d"
+    PreTrainedTokenizerFast(tokenizer_object=tok, bos_token="<bos>", eos_token="<eos>").save_pretrained(folder)
+    return folder
+
+
+def _conversations(path, column) -> None:
+    os.makedirs(path)
+    g = torch.Generator().manual_seed(0)
+    rnd = lambda lo, hi: int(torch.randint(lo, hi, (1,), generator=g))
+    rows = []
+    for _ in range(200):
+        turns = []
+        for t in range(rnd(2, 5)):
+            turns.append({"role": "user" if t % 2 == 0 else "assistant",
+                          "content": " " + " ".join(f"w{rnd(0, 200)}" for _ in range(rnd(2, 12))) + " "})
+        rows.append(json.dumps(turns))
+    pq.write_table(pa.table({column: rows}), os.path.join(path, "c.parquet"), row_group_size=40)
+
+
+@pytest.mark.parametrize("mode", ["sft", "sft_packed", "deepseek_default_optimizers", "gemma3_mup_off_selective_ac"])
+def test_train_py_other_modes_run_to_the_end(tmp_path, mode):
+    """The remaining branches of the entry point, a few steps each on CPU: SFT on conversations tokenised on the fly
+    (assistant-only masking, padding statistics), SFT on a file written by the packer, a MoE model under the default
+    optimizer groups (Muon + AdamW) with the load-balancing hook, Gemma 3 with selective recomputation."""
+    head = ""
+    if mode.startswith("sft"):
+        tok = _chat_tokenizer_file(tmp_path / "tokenizer.json")
+        _conversations(tmp_path / "conv", "conversations")
+        packed = tmp_path / "packed.parquet"
+        if mode == "sft_packed":
+            _run([sys.executable, os.path.join(ROOT, "scripts", "pack_sft_data.py"), "--input", str(tmp_path / "conv"),
+                  "--output", str(packed), "--tokenizer", tok, "--max-seq-len", "64", "--im-start", "<|im_start|>",
+                  "--im-end", "<|im_end|>"], cwd=tmp_path)
+            assert packed.exists()
+        head = f'''
+model_name = "llama3"
+flavor = "tiny"
+tokenizer_name = "{tok}"
+[dataset]
+data_dirs = ["{tmp_path / 'conv'}"]
+dataset_weights = "1"
+[sft]
+use_packed = {"true" if mode == "sft_packed" else "false"}
+packed_path = "{packed}"
+im_start_token = "<|im_start|>"
+im_end_token = "<|im_end|>"
+'''
+        groups = '[[optimizer_groups]]\nopt_class = "torch.optim.AdamW"\nmin_dim = 0\n[optimizer_groups.opt_cfg]\nlr = 1e-3\n'
+    elif mode.startswith("deepseek"):
+        head = 'model_name = "deepseek"\nflavor = "debug_flex"\nsynthetic_data = true\nsynthetic_vocab_size = 512\nenable_cut_cross_entropy = false\n'
+        groups = ""   # the default: Muon for the matrices, AdamW for the rest
+    else:
+        head = 'model_name = "gemma3"\nflavor = "debug"\nsynthetic_data = true\nsynthetic_vocab_size = 512\nac_mode = "selective"\nselective_ac_option = "op"\n'
+        groups = ""
+    top, _, tables = head.partition("[dataset]") if "[dataset]" in head else (head, "", "")
+    (tmp_path / "job.toml").write_text(
+        top + 'seq_len = 64\ntrain_batch_size = 2\nlog_freq = 1\ntrain_num_steps = 3\nenable_checkpoint = true\n'
+        'checkpoint_interval = 2\ncompile = false\nfused_collectives = false\ndata_parallel_shard_degree = 1\n'
+        + (("[dataset]" + tables) if tables else "") + groups)
+    _run([sys.executable, os.path.join(ROOT, "submit.py"), "--config-file", str(tmp_path / "job.toml"), "--dump-dir",
+          str(tmp_path / "jobs"), "--job-name", "j", "--dry-run", "--yes"], cwd=tmp_path)
+    log = _run([sys.executable, os.path.join(ROOT, "train.py"), str(tmp_path / "jobs" / "j")], cwd=tmp_path)
+    losses = _steps(log)
+    assert sorted(losses) == [1, 2, 3] and all(0 < v < 12 for v in losses.values()), (losses, log[-2000:])
+    assert (tmp_path / "jobs" / "j" / "checkpoints" / "step-2" / ".metadata").exists()
+    assert (tmp_path / "jobs" / "j" / "checkpoints" / "step-3" / ".metadata").exists()
