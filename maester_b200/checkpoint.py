@@ -172,9 +172,26 @@ class OptimizerWrapper(Stateful):
     def __init__(self, model: nn.Module, optimizer):
         self.model, self.optimizer = model, optimizer
 
+    def _merged(self) -> dict[str, Any]:
+        """One ``state.<fqn>.<key>`` namespace and one ``param_groups`` list over ALL optimizers of the container, in
+        their order: what ``get_optimizer_state_dict(model, [opt0, opt1, ...])`` gives the reference's wrapper
+        (maester/checkpoint.py:54-70), so the default Muon + AdamW job has the same keys on disk on both sides.  (The
+        container's own ``state_dict`` prefixes ``opt{i}_``; like the reference's, it is not what checkpoints use.)"""
+        opts = getattr(self.optimizer, "optimizers", None)
+        if opts is None or len(opts) == 1:
+            return self.optimizer.state_dict()
+        out: dict[str, Any] = {}
+        groups: list = []
+        for opt in opts:
+            sd = self.optimizer._opt_state(opt)
+            groups += sd.pop("param_groups")
+            out.update(sd)
+        out["param_groups"] = groups
+        return out
+
     def state_dict(self) -> dict[str, Any]:
         sharded = getattr(self.model, "_sharded", None)
-        flat = self.optimizer.state_dict()
+        flat = self._merged()
         if sharded is None:
             return flat
         slots = {sl.fqn: sl for u in sharded.units for sl in u.slots}
@@ -193,7 +210,18 @@ class OptimizerWrapper(Stateful):
             if hasattr(v, "to_local"):
                 v = v.to_local()
             plain[k] = v
-        self.optimizer.load_state_dict(plain)
+        opts = getattr(self.optimizer, "optimizers", None)
+        if opts is None or len(opts) == 1:
+            self.optimizer.load_state_dict(plain)
+            return
+        first = 0
+        for opt in opts:   # every optimizer takes the entries of its own parameters and its run of the group list
+            names = {self.optimizer._names.get(id(p), str(id(p))) for g in opt.param_groups for p in g["params"]}
+            sub = {k: v for k, v in plain.items()
+                   if k.startswith("state.") and k[len("state."):].rpartition(".")[0] in names}
+            sub["param_groups"] = plain.get("param_groups", [])[first:first + len(opt.param_groups)]
+            first += len(opt.param_groups)
+            self.optimizer._load_opt_state(opt, sub)
 
 
 def resume_step(cfg) -> int:

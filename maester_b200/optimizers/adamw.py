@@ -43,7 +43,10 @@ def build_chunk_table(segments, device):
 
 class FusedAdamW(Optimizer):
     def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=1e-2, fused=None, **_):
-        defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay)
+        # the remaining entries are the ones ``torch.optim.AdamW`` keeps in its groups: a checkpoint written here then
+        # has every key that the reference's optimizer asks for when it loads one (and they state what this class does)
+        defaults = dict(lr=lr, betas=tuple(betas), eps=eps, weight_decay=weight_decay, amsgrad=False, maximize=False,
+                        foreach=None, capturable=False, differentiable=False, fused=True, decoupled_weight_decay=True)
         super().__init__(params, defaults)
         self._flat = None  # set by attach_flat()
         self.cleared_grad = False  # the last step() cleared the gradients it consumed

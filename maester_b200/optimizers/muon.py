@@ -86,12 +86,31 @@ class Muon(Optimizer):
     def __init__(self, params, lr: float = 0.02, momentum: float = 0.95, ns_steps: int = 5, wd: float = 0.01,
                  nesterov: bool = True, use_muon: bool = True, prefetch_factor: int = 8, shard_group=None,
                  full_shape_of=None, **adam_kw):
-        defaults = dict(lr=lr, momentum=momentum, ns_steps=ns_steps, wd=wd, nesterov=nesterov, use_muon=use_muon,
-                        **adam_kw)
+        # group keys as in the reference's optimizer (lr, momentum, ns_steps, wd, use_muon): they are what a checkpoint
+        # stores per group, so both sides can load each other's; ``nesterov`` is a property of the optimizer
+        defaults = dict(lr=lr, momentum=momentum, ns_steps=ns_steps, wd=wd, use_muon=use_muon, **adam_kw)
         super().__init__(params, defaults)
+        self.nesterov = nesterov
         self.prefetch_factor = prefetch_factor
         self.shard_group = shard_group
         self.full_shape_of = full_shape_of
+        self._init_state()
+
+    def _init_state(self) -> None:
+        """Every buffer exists from the start, as in the reference ("init buffers ahead of time",
+        maester/optimizers/muon.py:129-150): a checkpoint is loaded into the state dict of a freshly built optimizer, and
+        what is not there yet would silently not be restored."""
+        for group in self.param_groups:
+            for p in group["params"]:
+                st = self.state[p]
+                if group["use_muon"] and p.dim() >= 2:
+                    if "m" not in st:
+                        st["m"] = torch.zeros(p.shape[0], math.prod(p.shape[1:]), dtype=torch.float32, device=p.device)
+                    st["param_shape"] = tuple(self.full_shape_of(p)) if self.full_shape_of else tuple(p.shape)
+                elif "exp_avg" not in st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
 
     def attach_sharding(self, sharded) -> None:
         """Use the sharding runtime's group and shapes (called by the optimizer builder)."""
@@ -99,6 +118,7 @@ class Muon(Optimizer):
         self.full_shape_of = lambda p: sharded.slot_of(p).shape
         # expert-parallel parameters are sharded over their own (smaller) group
         self.group_of = lambda p: (lambda d: d.group if d.world > 1 else None)(sharded.domains[sharded.slot_of(p).dom])
+        self._init_state()   # the unsharded shapes are known now
 
     group_of = None
 
@@ -123,9 +143,11 @@ class Muon(Optimizer):
                 g = p.grad.reshape(p.shape[0], -1).float()
                 if "m" not in st:
                     st["m"] = torch.zeros_like(g)
+                if "param_shape" not in st:   # the unsharded shape, kept beside the momentum as the reference does
+                    st["param_shape"] = tuple(self.full_shape_of(p)) if self.full_shape_of else tuple(p.shape)
                 m = st["m"]
                 m.lerp_(g, 1 - group["momentum"])
-                u = g.lerp(m, group["momentum"]) if group["nesterov"] else m
+                u = g.lerp(m, group["momentum"]) if self.nesterov else m
                 work.append((p, group, u.to(torch.bfloat16)))
 
         if work and self._peer_exchange_ok(work):

@@ -142,7 +142,53 @@ def _load_balance():
     print("load balance: biases equal and 18 statistics equal over 4 steps")
 
 
-@pytest.mark.parametrize("what", ["muon", "schedules_and_config", "load_balance"])
+def _groups():
+    """Which optimizer, learning rate and weight decay every parameter gets: the muP three-group rule and the
+    first-match-wins ``optimizer_groups`` (``min_dim``, ``exclude_names``); and the container's state-dict keys."""
+    import copy
+    import types
+    import torch
+    from maester.config import Config as RefConfig
+    from maester.models import model_name_to_cls as ref_cls, models_config as ref_cfgs
+    from maester.optimizers import build_optimizers as ref_build
+    from maester_b200.config import Config
+    from maester_b200.models import model_name_to_cls as our_cls, models_config as our_cfgs
+    from maester_b200.optimizers import build_optimizers
+
+    def assignment(model, opt):
+        names = {id(p): n for n, p in model.named_parameters()}
+        return {names[id(p)]: (type(o).__name__, g.get("lr"), g.get("weight_decay"), g.get("momentum"))
+                for o in opt.optimizers for g in o.param_groups for p in g["params"]}
+
+    dims = types.SimpleNamespace(dp_enabled=False, world_mesh=None)
+    adamw = {"opt_class": "torch.optim.AdamW", "opt_cfg": {"lr": 1e-3, "weight_decay": 0.1}, "min_dim": 0}
+    cases = {
+        "mup": dict(enable_mup=True, base_model_width=256, model_width=1024, optimizer_groups=[adamw]),
+        "first match wins": dict(optimizer_groups=[
+            {"opt_class": "torch.optim.SGD", "opt_cfg": {"lr": 0.02, "momentum": 0.9}, "min_dim": 2,
+             "exclude_names": ["tok_embeddings", "output"]}, adamw]),
+    }
+    for name, kw in cases.items():
+        ra, oa = copy.deepcopy(ref_cfgs["llama3"]["debugmodel"]), copy.deepcopy(our_cfgs["llama3"]["debugmodel"])
+        for a in (ra, oa):
+            a.vocab_size = 512
+            if name == "mup":
+                a.enable_mup, a.mup_width_mul = True, 4.0
+        ref, ours = ref_cls["llama3"].from_model_args(ra), our_cls["llama3"].from_model_args(oa)
+        ref_opt, our_opt = ref_build(ref, RefConfig(**kw), dims), build_optimizers(ours, Config(**kw), dims)
+        want, got = assignment(ref, ref_opt), assignment(ours, our_opt)
+        assert want == got, {k: (want[k], got.get(k)) for k in want if want[k] != got.get(k)}
+        assert len({v for v in want.values()}) >= 2, name          # the rule did split the parameters
+        for m, o in ((ref, ref_opt), (ours, our_opt)):             # one step, so that there is state to name
+            for p in m.parameters():
+                p.grad = torch.ones_like(p)
+            o.step()
+        ref_keys, our_keys = set(ref_opt.state_dict()), set(our_opt.state_dict())
+        assert ref_keys == our_keys, sorted(ref_keys ^ our_keys)[:10]
+    print("optimizer groups: same assignment under muP and under first-match-wins; same state-dict keys")
+
+
+@pytest.mark.parametrize("what", ["muon", "schedules_and_config", "load_balance", "groups"])
 def test_optimizer_side_parity_with_the_reference(what):
     r = subprocess.run([sys.executable, os.path.abspath(__file__), what], capture_output=True, text=True,
                        env=dict(os.environ, TORCHDYNAMO_DISABLE="1"), timeout=900)
@@ -152,4 +198,5 @@ def test_optimizer_side_parity_with_the_reference(what):
 
 if __name__ == "__main__":
     _setup()
-    {"muon": _muon, "schedules_and_config": _schedules_and_config, "load_balance": _load_balance}[sys.argv[1]]()
+    {"muon": _muon, "schedules_and_config": _schedules_and_config, "load_balance": _load_balance,
+     "groups": _groups}[sys.argv[1]]()
