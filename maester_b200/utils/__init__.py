@@ -169,14 +169,16 @@ def clip_grad_norm(
 
 
 def clean_param_name(name: str) -> str:
-    """Map a parameter FQN to a grouped metric name such as ``layer3/ffn/w1/weight``."""
+    """Map a parameter FQN to a grouped metric name such as ``layer3/ffn/proj/weight``.  The grouping words are the
+    reference's (maester/utils.py:290-311: "attention", then "mlp" / "ffn", else "other"), so that the metric names of
+    an existing dashboard stay the same: Llama's ``feed_forward`` and Gemma's ``self_attn`` land in "other" there too."""
     parts = re.split(r"[._]", name)
     tail = "/".join(parts[-2:])
     if "layers" in parts:
         idx = parts[parts.index("layers") + 1]
-        if "attention" in name or "attn" in name:
+        if "attention" in name:
             kind = "attention"
-        elif any(k in name for k in ("mlp", "ffn", "feed_forward", "moe")):
+        elif any(k in name for k in ("mlp", "ffn")):
             kind = "ffn"
         else:
             kind = "other"

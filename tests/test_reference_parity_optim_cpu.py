@@ -188,7 +188,44 @@ def _groups():
     print("optimizer groups: same assignment under muP and under first-match-wins; same state-dict keys")
 
 
-@pytest.mark.parametrize("what", ["muon", "schedules_and_config", "load_balance", "groups"])
+def _utilities():
+    """Peak-FLOPs table (the MFU denominator), metric names derived from parameter names, gradient clipping, the weight
+    scale monitor."""
+    import copy
+    import torch
+    import maester.metrics as ref_metrics
+    import maester.utils as ref_utils
+    import maester_b200.metrics as metrics
+    import maester_b200.utils as utils
+    from maester_b200.models import model_name_to_cls, models_config
+    for device in ("NVIDIA A100-SXM4-80GB", "NVIDIA H100 80GB HBM3", "NVIDIA H100 NVL", "NVIDIA H100 PCIe", "NVIDIA H200",
+                   "NVIDIA B200", "AMD Instinct MI250X", "AMD Instinct MI300X", "something else"):
+        assert ref_utils.get_peak_flops(device) == utils.get_peak_flops(device), device
+    for name, flavor in (("llama3", "debugmodel"), ("gemma3", "debug"), ("glm4", "debug"), ("deepseek", "debug")):
+        args = copy.deepcopy(models_config[name][flavor])
+        args.vocab_size = 512
+        with torch.device("meta"):
+            model = model_name_to_cls[name].from_model_args(args)
+        for n, _ in model.named_parameters():
+            for wrapped in (n, n.replace("layers.", "layers._checkpoint_wrapped_module.", 1), "_orig_mod." + n):
+                assert ref_utils.clean_param_name(wrapped) == utils.clean_param_name(wrapped), wrapped
+    g = torch.Generator().manual_seed(0)
+    for kw in (dict(max_norm=1.0), dict(max_norm=0.5, norm_type=float("inf")), dict(max_norm=2.0, norm_type=1.0)):
+        ps = [torch.nn.Parameter(torch.randn(5, 7, generator=g)) for _ in range(3)]
+        qs = [torch.nn.Parameter(p.detach().clone()) for p in ps]
+        for p, q in zip(ps, qs):
+            p.grad = 3 * torch.randn(5, 7, generator=g)
+            q.grad = p.grad.clone()
+        ref_utils.clip_grad_norm(ps, **kw)
+        utils.clip_grad_norm(qs, **kw)
+        assert all(torch.allclose(p.grad, q.grad, rtol=1e-6) for p, q in zip(ps, qs)), kw
+    net = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Linear(3, 2))
+    want, got = ref_metrics.WeightScaleMonitor(net, log_freq=1).step_monitor(), metrics.WeightScaleMonitor(net, log_freq=1).step_monitor()
+    assert sorted(want) == sorted(got) and all(got[k] == pytest.approx(v, rel=1e-6) for k, v in want.items())
+    print("utilities: peak FLOPs, metric names, clipping and the weight scale monitor agree")
+
+
+@pytest.mark.parametrize("what", ["muon", "schedules_and_config", "load_balance", "groups", "utilities"])
 def test_optimizer_side_parity_with_the_reference(what):
     r = subprocess.run([sys.executable, os.path.abspath(__file__), what], capture_output=True, text=True,
                        env=dict(os.environ, TORCHDYNAMO_DISABLE="1"), timeout=900)
@@ -199,4 +236,4 @@ def test_optimizer_side_parity_with_the_reference(what):
 if __name__ == "__main__":
     _setup()
     {"muon": _muon, "schedules_and_config": _schedules_and_config, "load_balance": _load_balance,
-     "groups": _groups}[sys.argv[1]]()
+     "groups": _groups, "utilities": _utilities}[sys.argv[1]]()
