@@ -21,7 +21,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "baseline", "_ref")
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "maester")), reason="the reference is not installed")
 
-FAMILIES = ["gemma3", "gemma3_packed", "llama3", "llama3_tied", "mistral", "glm4", "deepseek"]
+FAMILIES = ["gemma3", "gemma3_packed", "gemma3_scaled", "llama3", "llama3_tied", "llama3_mup", "mistral", "glm4",
+            "glm4_qknorm_bias", "deepseek", "deepseek_qlora_yarn"]
 
 
 def _adjust_reference_for_cpu():
@@ -55,13 +56,23 @@ def _pair(name, family, ref_cfgs, our_cfgs):
     from maester_b200.models import model_name_to_cls as our_cls
     if name == "gemma3":
         ra, oa = _small_gemma(ref_cfgs), _small_gemma(our_cfgs)
+        if family == "gemma3_scaled":   # what the 4B+ / 27B flavors add: scaled global RoPE, an explicit softmax scale
+            for a in (ra, oa):
+                a.rope_scaling, a.query_pre_attn_scalar = {"factor": 8.0}, 24
     else:
-        flavor = {"llama3": "debugmodel", "llama3_tied": "tiny", "mistral": "debugmodel", "glm4": "debug",
-                  "deepseek": "debug"}[family]
+        flavor = {"llama3": "debugmodel", "llama3_tied": "tiny", "llama3_mup": "debugmodel", "mistral": "debugmodel",
+                  "glm4": "debug", "glm4_qknorm_bias": "debug", "deepseek": "debug", "deepseek_qlora_yarn": "debug"}[family]
         ra, oa = copy.deepcopy(ref_cfgs[name][flavor]), copy.deepcopy(our_cfgs[name][flavor])
         ra.vocab_size = oa.vocab_size = 512
         if name == "deepseek":
             ra.max_seq_len = oa.max_seq_len = 96   # the reference applies its whole RoPE table: length == sequence
+        for a in (ra, oa):
+            if family == "llama3_mup":          # 1/d attention scale, output multiplier
+                a.enable_mup, a.mup_width_mul, a.mup_output_alpha = True, 4.0, 2.0
+            if family == "glm4_qknorm_bias":
+                a.use_qk_norm, a.attention_bias = True, True
+            if family == "deepseek_qlora_yarn":  # low-rank queries; sequence beyond the original length: YaRN + mscale
+                a.q_lora_rank, a.original_seq_len, a.n_layers = 64, 32, 3
     torch.manual_seed(0)
     ref = ref_cls[name].from_model_args(ra)
     ref.init_weights()
