@@ -183,7 +183,15 @@ def _groups():
             for p in m.parameters():
                 p.grad = torch.ones_like(p)
             o.step()
-        ref_keys, our_keys = set(ref_opt.state_dict()), set(our_opt.state_dict())
+        # the reference's container returns nested dictionaries, this one flat dotted keys; a checkpoint stores the
+        # dotted paths, which is where the two have to agree
+        def dotted(d, prefix=""):
+            out = set()
+            for k, v in (d.items() if isinstance(d, dict) else enumerate(d)):
+                key = f"{prefix}{k}"
+                out |= dotted(v, key + ".") if isinstance(v, (dict, list)) and k != "params" and len(v) else {key}
+            return out
+        ref_keys, our_keys = dotted(ref_opt.state_dict()), dotted(our_opt.state_dict())
         assert ref_keys == our_keys, sorted(ref_keys ^ our_keys)[:10]
     print("optimizer groups: same assignment under muP and under first-match-wins; same state-dict keys")
 
