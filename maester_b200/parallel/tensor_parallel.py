@@ -376,7 +376,8 @@ def apply_tp(model: nn.Module, parallel_dims, cfg) -> None:
     a = model.model_args
     n_kv = a.n_kv_heads or a.n_heads
     assert a.n_heads % tp.size == 0 and n_kv % tp.size == 0, "heads must divide by the TP degree"
-    assert a.vocab_size % tp.size == 0, "vocabulary must divide by the TP degree"
+    # only an untied head is split over the vocabulary; a tied one is replicated and scores token slices
+    assert a.tied_embeddings or a.vocab_size % tp.size == 0, "vocabulary must divide by the TP degree"
     fused = None
     from maester_b200.parallel.fused_tp import FusedTP, fused_tp_available
     from maester_b200.utils import device_for_training

@@ -46,8 +46,11 @@ def _steps(log: str) -> dict[int, float]:
     return {int(m.group(1)): float(m.group(2)) for m in re.finditer(r"Step\s+(\d+): lr=\S+ loss=\s*([0-9.]+)", log)}
 
 
-@pytest.mark.parametrize("ranks", [1, 2])
-def test_train_py_runs_saves_resumes_and_exports(tmp_path, ranks):
+@pytest.mark.parametrize("layout", ["dp1", "dp2", "dp1_then_tp2"])
+def test_train_py_runs_saves_resumes_and_exports(tmp_path, layout):
+    """``dp1_then_tp2``: the second job resumes the single-process checkpoint as two tensor-parallel ranks (the
+    checkpoint is resharded on load; both ranks read the same data) and must still reproduce the losses."""
+    ranks = 2 if layout == "dp2" else 1
     tok = _tokenizer_file(tmp_path / "tokenizer.json")
     _corpus(tmp_path / "data")
     (tmp_path / "job.toml").write_text(f"""
@@ -80,9 +83,9 @@ min_dim = 0
 lr = 3e-3
 """)
     common = ["--config-file", str(tmp_path / "job.toml"), "--dump-dir", str(tmp_path / "jobs"), "--dry-run", "--yes"]
-    launch = [sys.executable] if ranks == 1 else \
-        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}", "--master-addr",
-         "127.0.0.1", "--master-port", str(29650 + ranks)]
+    torchrun = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                "127.0.0.1", "--master-port", str(29650 + len(layout))]
+    launch = [sys.executable] if ranks == 1 else torchrun
 
     def job(name, steps):
         _run([sys.executable, os.path.join(ROOT, "submit.py"), *common, "--job-name", name, "--train-num-steps", str(steps)],
@@ -97,6 +100,10 @@ lr = 3e-3
     cut = job("cut", 8)
     shutil.copytree(whole / "checkpoints", cut / "checkpoints", dirs_exist_ok=True,
                     ignore=lambda d, names: [n for n in names if n == "step-8"])
+    if layout == "dp1_then_tp2":
+        cfg = json.loads((cut / "config.json").read_text())
+        (cut / "config.json").write_text(json.dumps({**cfg, "tensor_parallel_degree": 2}))
+        launch = torchrun
     log_second = _run([*launch, os.path.join(ROOT, "train.py"), str(cut)], cwd=tmp_path)
 
     a, b = _steps(log_whole), _steps(log_second)
@@ -104,7 +111,7 @@ lr = 3e-3
     assert all(0 < v < 8 for v in a.values()), a              # near ln(vocabulary) on random tokens, never diverging
     for s in (6, 8):                                           # resumed: same data, same weights, same schedule
         assert b[s] == pytest.approx(a[s], abs=2e-4), (s, a, b)
-    lr = lambda log: re.findall(r"Step\s+8: lr=(\S+),", log)
+    lr = lambda log: set(re.findall(r"Step\s+8: lr=(\S+),", log))   # every rank writes the line
     assert lr(log_whole) == lr(log_second) and lr(log_whole)
 
     # the last step of each job wrote a weights-only export in bf16
