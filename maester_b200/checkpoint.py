@@ -263,6 +263,21 @@ class CheckpointManager:
     def reset(self) -> None:
         self.begin = time.monotonic()
 
+    def _stateful_loader(self):
+        """What carries the position of the data stream in THIS process: a loader with its own ``state_dict``, or the
+        dataset of a loader without worker processes (the packed SFT reader: its epoch and index advance as batches
+        are taken, nothing is prefetched).  Pipelines that run inside a worker process save themselves from there
+        (``Checkpoint_Dataset``); the copy of the dataset in this process never moves and is not saved."""
+        dl = self.dataloader
+        if dl is None:
+            return None
+        if hasattr(dl, "state_dict") and hasattr(dl, "load_state_dict"):
+            return dl
+        ds = getattr(dl, "dataset", None)
+        if getattr(dl, "num_workers", 1) == 0 and hasattr(ds, "state_dict") and hasattr(ds, "load_state_dict"):
+            return ds
+        return None
+
     def _checkpoint_id(self, step: int) -> str:
         return os.path.join(self.folder, f"step-{step}")
 
@@ -288,11 +303,12 @@ class CheckpointManager:
             logger.info(f"Saving a full checkpoint at step {curr_step}")
         begin = time.monotonic()
         dcp.save(states, checkpoint_id=self._checkpoint_id(curr_step), no_dist=self._no_dist())
-        if self.dataloader is not None and hasattr(self.dataloader, "state_dict"):
+        stateful = self._stateful_loader()
+        if stateful is not None:
             rank = dist.get_rank() if dist.is_initialized() else 0
             d = os.path.join(self.folder, "dataloader", f"step-{curr_step}")
             os.makedirs(d, exist_ok=True)
-            torch.save(self.dataloader.state_dict(), os.path.join(d, f"loader_state_{rank}.pth"))
+            torch.save(stateful.state_dict(), os.path.join(d, f"loader_state_{rank}.pth"))
         self.reset()
         logger.info(f"Finished saving the checkpoint in {time.monotonic() - begin:.2f} seconds")
 
@@ -324,11 +340,12 @@ class CheckpointManager:
         logger.info(f"Loading the checkpoint at step {step}, containing keys {list(states.keys())}")
         begin = time.monotonic()
         self._load(states, self._checkpoint_id(step))
-        if states is self.states and self.dataloader is not None and hasattr(self.dataloader, "load_state_dict"):
+        stateful = self._stateful_loader()
+        if states is self.states and stateful is not None:
             rank = dist.get_rank() if dist.is_initialized() else 0
             f = os.path.join(self.folder, "dataloader", f"step-{step}", f"loader_state_{rank}.pth")
             if os.path.exists(f):
-                self.dataloader.load_state_dict(torch.load(f, weights_only=False))
+                stateful.load_state_dict(torch.load(f, weights_only=False))
         logger.info(f"Finished loading the checkpoint in {time.monotonic() - begin:.2f} seconds")
         return True
 

@@ -196,5 +196,12 @@ im_end_token = "<|im_end|>"
     log = _run([sys.executable, os.path.join(ROOT, "train.py"), str(tmp_path / "jobs" / "j")], cwd=tmp_path)
     losses = _steps(log)
     assert sorted(losses) == [1, 2, 3] and all(0 < v < 12 for v in losses.values()), (losses, log[-2000:])
-    assert (tmp_path / "jobs" / "j" / "checkpoints" / "step-2" / ".metadata").exists()
-    assert (tmp_path / "jobs" / "j" / "checkpoints" / "step-3" / ".metadata").exists()
+    ck = tmp_path / "jobs" / "j" / "checkpoints"
+    assert (ck / "step-2" / ".metadata").exists() and (ck / "step-3" / ".metadata").exists()
+    if mode == "sft_packed":
+        # the packed reader runs in the training process; its position is saved beside the model checkpoint, so a job
+        # restarted from step 2 sees the same third batch
+        assert (ck / "dataloader" / "step-2" / "loader_state_0.pth").exists()
+        shutil.rmtree(ck / "step-3")
+        again = _steps(_run([sys.executable, os.path.join(ROOT, "train.py"), str(tmp_path / "jobs" / "j")], cwd=tmp_path))
+        assert sorted(again) == [3] and again[3] == pytest.approx(losses[3], abs=2e-4), (again, losses)
