@@ -205,3 +205,35 @@ im_end_token = "<|im_end|>"
         shutil.rmtree(ck / "step-3")
         again = _steps(_run([sys.executable, os.path.join(ROOT, "train.py"), str(tmp_path / "jobs" / "j")], cwd=tmp_path))
         assert sorted(again) == [3] and again[3] == pytest.approx(losses[3], abs=2e-4), (again, losses)
+
+
+def test_metrics_written_by_train_py_have_the_reference_names(tmp_path):
+    """Gradient accumulation, TensorBoard logging and the profiler hooks switched on: the scalar tags are the
+    reference trainer's (train.py:448-465 there), so existing dashboards keep working."""
+    (tmp_path / "job.toml").write_text(
+        'model_name = "llama3"\nflavor = "tiny"\nsynthetic_data = true\nsynthetic_vocab_size = 512\nseq_len = 64\n'
+        'train_batch_size = 2\ngradient_accumulation_steps = 2\nlog_freq = 1\ntrain_num_steps = 3\ncompile = false\n'
+        'data_parallel_shard_degree = 1\nenable_tensorboard = true\nenable_profiling = true\nprofile_freq = 2\n'
+        'enable_checkpoint = false\n[[optimizer_groups]]\nopt_class = "torch.optim.AdamW"\nmin_dim = 0\n'
+        '[optimizer_groups.opt_cfg]\nlr = 1e-3\n')
+    _run([sys.executable, os.path.join(ROOT, "submit.py"), "--config-file", str(tmp_path / "job.toml"), "--dump-dir",
+          str(tmp_path / "jobs"), "--job-name", "j", "--dry-run", "--yes"], cwd=tmp_path)
+    log = _run([sys.executable, os.path.join(ROOT, "train.py"), str(tmp_path / "jobs" / "j")], cwd=tmp_path)
+    assert sorted(_steps(log)) == [1, 2, 3]
+    from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
+    events = [os.path.join(r, f) for r, _, fs in os.walk(tmp_path / "jobs" / "j") for f in fs if "tfevents" in f]
+    assert events, "no TensorBoard event file"
+    acc = EventAccumulator(os.path.dirname(events[0]))
+    acc.Reload()
+    tags = set(acc.Tags()["scalars"])
+    reference_tags = {
+        "loss/global_avg", "loss/global_max", "tps", "mfu(%)", "data/total_tokens", "time/end_to_end(s)",
+        "time/data_loading_avg(s)", "time/data_loading_max(s)", "time/data_loading_avg(%)", "time/data_loading_max(%)",
+        "memory/max_active(GiB)", "memory/max_active(%)", "memory/max_reserved(GiB)", "memory/max_reserved(%)",
+        "memory/num_alloc_retries", "memory/num_ooms"}
+    assert reference_tags <= tags, sorted(reference_tags - tags)
+    assert [e.step for e in acc.Scalars("loss/global_avg")] == [1, 2, 3]
+    # 3 steps x 2 micro-batches x 2 sequences x 64 tokens
+    assert acc.Scalars("data/total_tokens")[-1].value == 3 * 2 * 2 * 64
+    traces = [f for r, _, fs in os.walk(tmp_path / "jobs" / "j") for f in fs if f.endswith(".json") and "config" not in f]
+    assert traces, "the profiler wrote no trace"
