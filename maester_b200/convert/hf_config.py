@@ -54,16 +54,19 @@ def _deepseek(a) -> dict:
     return {
         "architectures": ["DeepseekV3ForCausalLM" if v3 else "DeepseekV2ForCausalLM"],
         "model_type": "deepseek_v3" if v3 else "deepseek_v2",
-        "hidden_size": a.dim, "intermediate_size": a.inter_dim, "moe_intermediate_size": a.moe_inter_dim,
+        "hidden_size": a.dim, "intermediate_size": a.inter_dim, "moe_intermediate_size": a.moe_intermediate_size,
         "num_hidden_layers": a.n_layers, "first_k_dense_replace": a.n_dense_layers,
         "num_attention_heads": a.n_heads, "num_key_value_heads": a.n_heads, "vocab_size": a.vocab_size,
         "n_routed_experts": m.num_experts, "n_shared_experts": m.num_shared_experts,
         "num_experts_per_tok": m.top_k, "routed_scaling_factor": m.route_scale, "norm_topk_prob": m.route_norm,
+        # one routing group holding every expert: this model family has no group-limited routing
+        "n_group": 1, "topk_group": 1, "topk_method": "noaux_tc" if v3 else "greedy",
         "scoring_func": m.score_func, "q_lora_rank": a.q_lora_rank or None, "kv_lora_rank": a.kv_lora_rank,
         "qk_nope_head_dim": a.qk_nope_head_dim, "qk_rope_head_dim": a.qk_rope_head_dim, "v_head_dim": a.v_head_dim,
         "rms_norm_eps": a.norm_eps, "rope_theta": float(a.rope_theta), "max_position_embeddings": a.max_seq_len,
-        "rope_scaling": ({"type": "yarn", "factor": a.rope_factor, "original_max_position_embeddings": a.original_seq_len,
-                          "beta_fast": a.beta_fast, "beta_slow": a.beta_slow, "mscale": a.mscale, "mscale_all_dim": a.mscale}
+        "rope_scaling": ({"type": "yarn", "factor": float(a.rope_factor),
+                          "original_max_position_embeddings": a.original_seq_len, "beta_fast": float(a.beta_fast),
+                          "beta_slow": float(a.beta_slow), "mscale": a.mscale, "mscale_all_dim": a.mscale}
                          if a.max_seq_len > a.original_seq_len else None),
         "tie_word_embeddings": bool(a.tied_embeddings), "hidden_act": "silu", "torch_dtype": "bfloat16",
     }

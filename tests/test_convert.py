@@ -127,3 +127,72 @@ def test_mup_llama_export_matches_native_model(tmp_path):
     tok = torch.randint(0, 96, (1, 20))
     with torch.no_grad():
         assert (mine(tok).float() - hf(tok).logits).abs().max().item() < 2e-4
+
+
+def _hub_layout(state):
+    """transformers keeps the routed experts of a layer as two stacked tensors in memory (``gate_up_proj`` [E, 2I, H],
+    ``down_proj`` [E, H, I]); checkpoints on disk, which the converters read, hold one matrix per expert."""
+    out = {}
+    for k, v in state.items():
+        if k.endswith("mlp.experts.gate_up_proj"):
+            for e in range(v.shape[0]):
+                gate, up = v[e].chunk(2, dim=0)
+                out[k.replace("gate_up_proj", f"{e}.gate_proj.weight")] = gate
+                out[k.replace("gate_up_proj", f"{e}.up_proj.weight")] = up
+        elif k.endswith("mlp.experts.down_proj"):
+            for e in range(v.shape[0]):
+                out[k.replace("down_proj", f"{e}.down_proj.weight")] = v[e]
+        else:
+            out[k] = v
+    return out
+
+
+def _against_transformers(name, family, args, hf_cls, cfg_cls, tol=1e-4):
+    cfg_d = hf_config_from_args(family, args)
+    cfg = cfg_cls(**{k: v for k, v in cfg_d.items() if k not in ("architectures", "model_type", "torch_dtype")})
+    torch.manual_seed(1)
+    hf = hf_cls(cfg).eval()
+    with torch.no_grad():   # the selection bias is zero after construction: give it values so that it matters
+        for n, p in list(hf.named_parameters()) + list(hf.named_buffers()):
+            if "e_score_correction_bias" in n:
+                p.copy_(0.1 * torch.randn_like(p))
+    mine = model_name_to_cls[name].from_model_args(args).eval()
+    mine.init_weights()
+    native = to_native(FAMILIES[family], _hub_layout(hf.state_dict()), arch_from_hf_config(family, cfg.to_dict()))
+    missing, unexpected = mine.load_state_dict(native, strict=False)
+    assert not unexpected and not [k for k in missing if "expert_bias" not in k], (missing, unexpected)
+    tok = torch.randint(0, args.vocab_size, (2, 40))
+    with torch.no_grad():
+        want, got = hf(tok).logits, mine(tok).float()
+    assert (got - want).abs().max().item() < tol * max(1.0, want.abs().max().item())
+    assert torch.equal(got.argmax(-1), want.argmax(-1))
+
+
+def test_glm4_moe_logits_match_transformers():
+    """Partial rotary embedding, sigmoid router with the selection bias, renormalised top-k, shared expert."""
+    from transformers import Glm4MoeConfig, Glm4MoeForCausalLM
+    for qk_norm in (False, True):
+        a = copy.deepcopy(models_config["glm4"]["debug"])
+        a.vocab_size, a.use_qk_norm, a.attention_bias = 512, qk_norm, qk_norm
+        _against_transformers("glm4", "glm4", a, Glm4MoeForCausalLM, Glm4MoeConfig)
+
+
+@pytest.mark.parametrize("variant", ["v3_sigmoid_yarn", "v3_low_rank_queries", "v2_softmax"])
+def test_deepseek_logits_match_transformers(variant):
+    """Latent attention (with and without low-rank queries), YaRN with its softmax-scale correction, both routers.
+    The experts' outputs are weighted AFTER the experts, as DeepSeek does (``score_before_experts=False``; the
+    reference's own DeepSeek flavors weight the inputs instead, which is a different function).  The softmax (V2)
+    variant runs without YaRN: transformers' V2 port leaves the softmax-scale correction out."""
+    import transformers
+    a = copy.deepcopy(models_config["deepseek"]["debug_flex"])
+    a.vocab_size, a.moe_args.score_before_experts, a.moe_args.load_balance_coeff = 512, False, 1e-3
+    if variant == "v2_softmax":
+        a.max_seq_len = a.original_seq_len
+        cls, cfg = transformers.DeepseekV2ForCausalLM, transformers.DeepseekV2Config
+    else:
+        a.moe_args.score_func, a.moe_args.route_norm = "sigmoid", True
+        assert a.max_seq_len > a.original_seq_len
+        if variant == "v3_low_rank_queries":
+            a.q_lora_rank = 64
+        cls, cfg = transformers.DeepseekV3ForCausalLM, transformers.DeepseekV3Config
+    _against_transformers("deepseek", "deepseek", a, cls, cfg)
