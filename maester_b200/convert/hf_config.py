@@ -35,7 +35,10 @@ def _gemma(a) -> dict:
         "architectures": ["Gemma3ForCausalLM"], "model_type": "gemma3_text",
         "hidden_size": a.dim, "intermediate_size": a.intermediate_size, "num_hidden_layers": a.n_layers,
         "num_attention_heads": a.n_heads, "num_key_value_heads": a.num_key_value_heads, "head_dim": a.head_dim,
-        "vocab_size": a.vocab_size, "rms_norm_eps": a.rms_norm_eps, "sliding_window": a.sliding_window_size,
+        # the model was trained with the window INCLUSIVE of both ends (a query sees keys q-W .. q, W + 1 of them, as
+        # the reference's mask does: maester/models/gemma/model.py:206-214); transformers counts the keys, so the
+        # exported window is one larger and the exported model computes what was trained
+        "vocab_size": a.vocab_size, "rms_norm_eps": a.rms_norm_eps, "sliding_window": a.sliding_window_size + 1,
         "layer_types": layer_types, "sliding_window_pattern": len(types),
         "query_pre_attn_scalar": a.query_pre_attn_scalar or a.head_dim,
         "rope_theta": float(wl.get("global", 1_000_000)), "rope_local_base_freq": float(wl.get("local_sliding", 10_000)),
