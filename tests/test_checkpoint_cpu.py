@@ -340,3 +340,36 @@ def test_tensor_parallel_expert_checkpoint_holds_whole_tensors(tmp_path, world, 
             assert torch.equal(flat[k], v.float()), k
             checked += 1
     assert checked > 10 and any(k.endswith("moe.experts.w2") for k in flat)
+
+
+def test_row_pieces_tile_the_owned_rows_and_point_at_the_right_global_rows():
+    """Pure function behind the head-group-split checkpoints: for every split of a rank's local rows over data-parallel
+    shards, the pieces cover exactly the owned rows, in order, without overlap, and each local row maps to the global
+    row that the segment table says."""
+    import itertools
+    import types
+    from maester_b200.checkpoint import row_pieces
+    from maester_b200.parallel.tensor_parallel import qkv_segments
+    for heads, kv, hd, tp in [(4, 2, 8, 2), (8, 4, 16, 4), (32, 16, 4, 2), (6, 3, 5, 3)]:
+        for rank in range(tp):
+            segs = qkv_segments(heads, kv, hd, tp, rank)
+            local_rows = sum(n for _, n in segs)
+            to_global = [g0 + i for g0, n in segs for i in range(n)]       # local row -> global row
+            slot = types.SimpleNamespace(tp_segments=segs)
+            for shards in (1, 2, 3, 5):
+                per = -(-local_rows // shards)
+                covered = []
+                for s in range(shards):
+                    lo, hi = min(s * per, local_rows), min((s + 1) * per, local_rows)
+                    at = 0
+                    for rel, g0, n in row_pieces(slot, lo, hi):
+                        assert rel == at and n > 0                            # pieces follow one another
+                        assert [g0 + i for i in range(n)] == to_global[lo + rel: lo + rel + n]
+                        at += n
+                    assert at == hi - lo
+                    covered += list(range(lo, hi))
+                assert covered == list(range(local_rows))
+        # the ranks' segments partition the whole [q; k; v] matrix
+        rows = sorted(itertools.chain.from_iterable(range(g0, g0 + n) for r in range(tp)
+                                                    for g0, n in qkv_segments(heads, kv, hd, tp, r)))
+        assert rows == list(range((heads + 2 * kv) * hd))
