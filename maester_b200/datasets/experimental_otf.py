@@ -17,15 +17,10 @@ end of the epoch so that an epoch always contains every chunk exactly once.
 """
 from __future__ import annotations
 
-import bisect
-import hashlib
-import json
 import math
 import os
-import random
 import time
-from collections import OrderedDict
-from typing import Any, Callable, List, Optional, Set
+from typing import Any, Callable, List
 
 import torch
 import torch.distributed as dist

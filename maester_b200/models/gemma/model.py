@@ -15,7 +15,7 @@ kernel from ``document_ids`` and per-block index ranges instead of materialised 
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 import torch
 import torch.nn as nn

@@ -9,8 +9,6 @@ Reference behaviour: torch.optim.AdamW(fused=True) as configured in maester/conf
 """
 from __future__ import annotations
 
-import math
-
 import torch
 from torch.optim import Optimizer
 
