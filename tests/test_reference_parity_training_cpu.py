@@ -26,6 +26,9 @@ def _rank(rank, world, batches, family="llama3"):
     from torch.distributed.fsdp import fully_shard
     from maester_b200.trainer import Trainer
 
+    tp = family == "llama3_tp"
+    if tp:
+        family = "llama3"
     if family == "gemma3":   # tied embedding / head, sandwich norms, local and global layers
         import test_reference_parity_cpu as parity
         parity._adjust_reference_for_cpu()
@@ -43,10 +46,16 @@ def _rank(rank, world, batches, family="llama3"):
     else:
         layers = ref.layers.values()
     full = {k: v.detach().clone() for k, v in ref.state_dict().items() if not k.endswith("freqs_cis")}
-    mesh = init_device_mesh("cpu", (world,))
-    for layer in layers:
-        fully_shard(layer, mesh=mesh)
-    fully_shard(ref, mesh=mesh)
+    if tp:
+        # the reference's tensor-parallel plan (DTensor styles: column / row parallel linears, sequence-parallel norms,
+        # all-gather / reduce-scatter along the sequence) on a mesh of two gloo ranks
+        from maester.parallelisms.parallelize_llama import apply_tp
+        apply_tp(ref, init_device_mesh("cpu", (world,), mesh_dim_names=("tp",)), loss_parallel=False, enable_async_tp=False)
+    else:
+        mesh = init_device_mesh("cpu", (world,))
+        for layer in layers:
+            fully_shard(layer, mesh=mesh)
+        fully_shard(ref, mesh=mesh)
     kw = dict(ADAMW[0]["opt_cfg"])
     opt = torch.optim.AdamW(ref.parameters(), lr=kw["lr"], betas=kw["betas"], weight_decay=kw["weight_decay"], eps=kw["eps"])
 
@@ -55,14 +64,16 @@ def _rank(rank, world, batches, family="llama3"):
         ours.models_config["gemma3"]["parity"] = parity._small_gemma(ours.models_config)
         ours.models_config["gemma3"]["parity"].n_layers = 3
         tr = Trainer(_cfg(model_name="gemma3", flavor="parity", data_parallel_shard_degree=world))
+    elif tp:
+        tr = Trainer(_cfg(flavor="debugmodel", data_parallel_shard_degree=1, tensor_parallel_degree=world))
     else:
         tr = Trainer(_cfg(flavor="debugmodel", data_parallel_shard_degree=world))
-    _load_full(tr, full)
+    _load_full(tr, full, tp=(world, rank) if tp else None)
 
-    per = batches[0]["input_ids"].shape[0] // world
+    per = batches[0]["input_ids"].shape[0] // (1 if tp else world)
     ref_losses, our_losses = [], []
     for b in batches:
-        mine = {k: v[rank * per:(rank + 1) * per] for k, v in b.items()}
+        mine = b if tp else {k: v[rank * per:(rank + 1) * per] for k, v in b.items()}   # TP ranks share the batch
         loss = F.cross_entropy(ref(mine["input_ids"]).float().flatten(0, 1), mine["labels"].flatten())
         loss.backward()
         opt.step()
@@ -72,13 +83,16 @@ def _rank(rank, world, batches, family="llama3"):
     assert our_losses == pytest.approx(ref_losses, abs=2e-5), (ref_losses, our_losses)
     want = {n: p.full_tensor().detach() for n, p in ref.named_parameters()}
     got = {sl.fqn: sl.param.data for u in tr.sharded.units for sl in u.slots}
+    if tp:
+        from maester_b200.parallel.tensor_parallel import tp_slice_state_dict
+        want = tp_slice_state_dict(want, world, rank)
     assert sorted(want) == sorted(got)
     for k in want:
         assert _close(got[k], want[k], tol=2e-4), (k, ((got[k] - want[k]).norm() / want[k].norm()).item())
     return ref_losses
 
 
-@pytest.mark.parametrize("world,family", [(1, "llama3"), (2, "llama3"), (2, "gemma3")])
+@pytest.mark.parametrize("world,family", [(1, "llama3"), (2, "llama3"), (2, "gemma3"), (2, "llama3_tp")])
 def test_training_steps_follow_the_reference_under_fsdp2(world, family):
     os.environ["TORCHDYNAMO_DISABLE"] = "1"   # inherited by the spawned ranks: no host compiler set-up for Inductor here
     try:
@@ -87,4 +101,4 @@ def test_training_steps_follow_the_reference_under_fsdp2(world, family):
         os.environ.pop("TORCHDYNAMO_DISABLE", None)
     assert all(len(r) == 4 for r in res)
     if world == 2:
-        assert res[0] != res[1]   # the ranks did see different data
+        assert (res[0] == res[1]) == (family == "llama3_tp")   # data-parallel ranks see different data
