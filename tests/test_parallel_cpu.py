@@ -34,7 +34,8 @@ def _worker(rank, world, port, fn, args, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank))
     # the ranks share the machine's cores: without a limit every rank starts one intra-op thread per core
-    torch.set_num_threads(max(1, (os.cpu_count() or 8) // world))
+    if world > 1:
+        torch.set_num_threads(max(1, torch.get_num_threads() // world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         res = fn(rank, world, *args)
