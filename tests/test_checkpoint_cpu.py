@@ -69,6 +69,15 @@ def test_two_rank_fsdp_save_and_resume(tmp_path):
     assert res == [True, True]
 
 
+def test_two_rank_save_and_resume_with_the_default_muon_and_adamw_groups(tmp_path):
+    """Muon's momentum (and the Adam moments of the other group) must come back from the checkpoint: the resumed run
+    reproduces the continued one only if they do."""
+    from maester_b200.config import Config
+    full = _full_weights(_cfg(flavor="debugmodel"))
+    kw = dict(data_parallel_shard_degree=2, flavor="debugmodel", optimizer_groups=Config().optimizer_groups)
+    assert run_ranks(2, _run_save_resume, kw, str(tmp_path), full, _batches(4, 4, 64, 512)) == [True, True]
+
+
 def _save_only(rank, world, cfg_kw, tmp, full, batches):
     cfg = _mk(tmp, **cfg_kw)
     tr, state, ck = _trainer_with_ckpt(cfg)
