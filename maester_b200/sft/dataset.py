@@ -129,5 +129,7 @@ def build_sft_data_loader(cfg, rank: int, world_size: int, tokenizer=None, resum
     ds = Checkpoint_Dataset(ds, ckpt_dir, cfg.checkpoint_interval,
                             steps_per_batch=cfg.train_batch_size * max(1, cfg.gradient_accumulation_steps),
                             save_path=ckpt_dir, load_step=resume_step)
+    # the collate function adds the count of real tokens per sample, which the trainer turns into padding metrics
     return torch.utils.data.DataLoader(ds, batch_size=cfg.train_batch_size, num_workers=1, prefetch_factor=4,
-                                       pin_memory=torch.cuda.is_available(), persistent_workers=True)
+                                       collate_fn=packed_collate_fn, pin_memory=torch.cuda.is_available(),
+                                       persistent_workers=True)

@@ -191,6 +191,7 @@ im_end_token = "<|im_end|>"
     (tmp_path / "job.toml").write_text(
         top + 'seq_len = 64\ntrain_batch_size = 2\nlog_freq = 1\ntrain_num_steps = 3\nenable_checkpoint = true\n'
         'checkpoint_interval = 2\ncompile = false\nfused_collectives = false\ndata_parallel_shard_degree = 1\n'
+        'enable_tensorboard = true\n'
         + (("[dataset]" + tables) if tables else "") + groups)
     _run([sys.executable, os.path.join(ROOT, "submit.py"), "--config-file", str(tmp_path / "job.toml"), "--dump-dir",
           str(tmp_path / "jobs"), "--job-name", "j", "--dry-run", "--yes"], cwd=tmp_path)
@@ -199,6 +200,14 @@ im_end_token = "<|im_end|>"
     assert sorted(losses) == [1, 2, 3] and all(0 < v < 12 for v in losses.values()), (losses, log[-2000:])
     ck = tmp_path / "jobs" / "j" / "checkpoints"
     assert (ck / "step-2" / ".metadata").exists() and (ck / "step-3" / ".metadata").exists()
+    if mode.startswith("sft"):   # both SFT loaders report how much of each sample is real tokens
+        from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
+        events = [r for r, _, fs in os.walk(tmp_path / "jobs" / "j") for f in fs if "tfevents" in f]
+        acc = EventAccumulator(events[0])
+        acc.Reload()
+        tags = set(acc.Tags()["scalars"])
+        assert {"padding/efficiency", "padding/avg_length", "padding/std_length"} <= tags, sorted(tags)
+        assert 0 < acc.Scalars("padding/efficiency")[-1].value <= 1
     if mode == "sft_packed":
         # the packed reader runs in the training process; its position is saved beside the model checkpoint, so a job
         # restarted from step 2 sees the same third batch
