@@ -99,3 +99,46 @@ def _streams(rank, world, tmp):
 
 def test_data_pipeline_is_the_reference_stream_state_and_files(tmp_path):
     assert run_ranks(1, _streams, str(tmp_path)) == [True]
+
+
+def _builders(rank, world, tmp):
+    """Both ``build_experimental_data_loader`` functions on the same configuration: tokenizer file, Parquet folder,
+    1-worker DataLoader; the batches are the same tensors under the same keys."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "shims"))
+    sys.path.insert(0, REF)
+    import pathlib
+    import maester.models  # noqa: F401
+    import test_train_end_to_end_cpu as e2e
+    from maester.config import Config as RefConfig
+    from maester.datasets.experimental_otf import build_experimental_data_loader as ref_build
+    from maester_b200.config import Config
+    from maester_b200.datasets.experimental_otf import build_experimental_data_loader
+    tmp = pathlib.Path(tmp)
+    tok = e2e._tokenizer_file(tmp / "tokenizer.json")
+    e2e._corpus(tmp / "data")
+    kw = dict(seq_len=64, train_batch_size=2, tokenizer_name=tok, enable_checkpoint=False,
+              dataset=dict(data_dirs=[str(tmp / "data")], dataset_weights="1", bos_token=2, eos_token=1))
+    ref_it, our_it = iter(ref_build(RefConfig(**kw), 0, 1)), iter(build_experimental_data_loader(Config(**kw), 0, 1))
+    for i in range(6):
+        a, b = next(ref_it), next(our_it)
+        assert sorted(a) == sorted(b) == ["input_ids", "labels"], (sorted(a), sorted(b))
+        for k in a:
+            assert a[k].dtype == b[k].dtype and torch.equal(a[k], b[k]), (i, k)
+    os._exit(0)   # the loaders' worker processes are persistent: leave without waiting for them
+
+
+def test_loader_builders_give_the_same_batches(tmp_path):
+    # a child process of its own, started with the interpreter's default method: the reference's pipeline holds live
+    # iterators and only reaches its DataLoader worker by fork
+    import subprocess
+    r = subprocess.run([sys.executable, os.path.abspath(__file__), str(tmp_path)], capture_output=True, text=True,
+                       timeout=600, env={**os.environ, "CUDA_VISIBLE_DEVICES": "", "PYTHONPATH": ROOT})
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+if __name__ == "__main__":
+    import torch.distributed as dist
+    from test_parallel_cpu import _free_port
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()))
+    dist.init_process_group("gloo", rank=0, world_size=1)   # the reference's dataset constructor asks for the rank
+    _builders(0, 1, sys.argv[1])
