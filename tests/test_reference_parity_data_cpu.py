@@ -124,6 +124,23 @@ def _builders(rank, world, tmp):
         assert sorted(a) == sorted(b) == ["input_ids", "labels"], (sorted(a), sorted(b))
         for k in a:
             assert a[k].dtype == b[k].dtype and torch.equal(a[k], b[k]), (i, k)
+    # the SFT builders (conversations tokenised on the fly): same padded samples, label masks and real-token counts
+    from maester.sft.dataset import build_sft_data_loader as ref_sft
+    from maester_b200.sft import build_sft_data_loader
+    chat_tok = e2e._chat_tokenizer_file(tmp / "chat_tokenizer.json")
+    e2e._conversations(tmp / "conv", "messages")
+    kw = dict(seq_len=64, train_batch_size=2, tokenizer_name=chat_tok, enable_checkpoint=False,
+              dataset=dict(data_dirs=[str(tmp / "conv")], dataset_weights="1"),
+              sft=dict(use_packed=False, conversation_column="messages", im_start_token="<|im_start|>",
+                       im_end_token="<|im_end|>"))
+    ref_it, our_it = iter(ref_sft(RefConfig(**kw), 0, 1)), iter(build_sft_data_loader(Config(**kw), 0, 1))
+    for i in range(6):
+        a, b = next(ref_it), next(our_it)
+        assert sorted(a) == sorted(b) == ["attention_mask", "input_ids", "labels", "stats"], (sorted(a), sorted(b))
+        for k in ("input_ids", "labels", "attention_mask"):
+            assert torch.equal(a[k].long(), b[k].long()), (i, k)
+        assert torch.equal(a["stats"]["actual_lengths"], b["stats"]["actual_lengths"])
+        assert (b["labels"] != -100).any()   # assistant turns are trained on
     os._exit(0)   # the loaders' worker processes are persistent: leave without waiting for them
 
 
